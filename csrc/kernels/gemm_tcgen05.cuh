@@ -1,0 +1,392 @@
+// Persistent warp-specialised GEMM for sm_100a: TMA -> shared-memory ring ->
+// tcgen05.mma (cta_group::1, 128 x BN x 16B-K tiles) -> fp32 accumulators in
+// TMEM (double buffered) -> epilogue warps (tcgen05.ld) -> global memory.
+//
+//   C[M,N] = dact(aux_in) * ( act(alpha * A[M,K] . B[K,N] + bias[N]) ) + residual[M,N]
+//
+// Operand storage ("major") is a template parameter so that the forward
+// (x @ W with W stored [in,out]), dgrad (dY @ W^T) and wgrad (X^T @ dY) GEMMs of
+// a Linear layer all run without any transposition pass:
+//   A_MN = false : A stored [M,K] row-major (K contiguous)     true : stored [K,M] (M contiguous)
+//   B_MN = false : B stored [N,K] row-major (K contiguous)     true : stored [K,N] (N contiguous)
+//
+// The reference framework's counterpart is a one-thread-per-output naive matmul
+// (rumus/src/backend/gpu/shaders/matmul.wgsl:22) plus separate bias / activation
+// dispatches (shaders/bias.wgsl:20, shaders/unary.wgsl:20); here those are one kernel.
+//
+// Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+// warps 2..5 = epilogue (TMEM lane quarter = warp_idx % 4).
+//
+// `Hooks` lets the fused collective kernels (all-gather -> GEMM, GEMM ->
+// reduce-scatter) reuse this body: the producer asks the hook before loading a
+// tile (e.g. wait for a peer's slab to land in local staging), the epilogue
+// tells the hook when an output tile is complete.
+#pragma once
+#include "sm100_common.cuh"
+
+namespace rb {
+
+enum : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2, ACT_SILU = 3 };
+
+struct GemmParams {
+  int M, N, K;
+  void* out;             // [M,N], leading dim ldc, dtype = out_f32 ? float : T
+  const void* bias;      // [N] of T (float when T = float) or null
+  const void* residual;  // [M,N] of out dtype, leading dim ldr, or null
+  void* aux_out;         // [M,N] of out dtype: receives (alpha*acc + bias) before act, or null
+  const void* aux_in;    // [M,N] of out dtype: result is multiplied by dact'(aux_in), or null
+  long long ldc, ldr, ldaux_out, ldaux_in;
+  int act;               // activation on (alpha*acc + bias)
+  int dact;              // derivative kind used with aux_in
+  int out_f32;
+  int vec_ok;            // 16-byte vector access is legal for out/residual/aux
+  float alpha;
+  int* status;           // device status word
+  int group_m;           // raster group (m-tiles walked before advancing n)
+};
+
+struct NoHooks {
+  // Called by the producer thread before the first load of an output tile.
+  // Returning false aborts the kernel (bounded wait ran out).
+  __device__ __forceinline__ bool before_tile_load(int m_idx, int n_idx, volatile int* abort_flag,
+                                                   int* status) const {
+    return true;
+  }
+  // Called by the producer thread before each k-block load.
+  __device__ __forceinline__ bool before_k_load(int m_idx, int n_idx, int kb,
+                                                volatile int* abort_flag, int* status) const {
+    return true;
+  }
+  // Called by one lane of each epilogue warp after its 32 rows of a tile are stored.
+  __device__ __forceinline__ void after_tile_store(int m_idx, int n_idx, int quarter) const {}
+  // Maps a linear tile id of this CTA to (m_idx, n_idx); default = grouped raster.
+  static constexpr bool kCustomRaster = false;
+  __device__ __forceinline__ void raster(int tile, int num_m, int num_n, int& m_idx,
+                                         int& n_idx) const {}
+};
+
+template <typename T, int BN>
+struct GemmCfg {
+  static constexpr int BM = 128;
+  static constexpr int ESZ = sizeof(T);
+  static constexpr int BK = 128 / ESZ;      // one 128-byte swizzle row of K
+  static constexpr int UMMA_K = 32 / ESZ;   // K per tcgen05.mma
+  static constexpr int CH = 128 / ESZ;      // MN elements per 128-byte chunk (MN-major operands)
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int NUM_THREADS = 192;
+  static constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <typename T>
+__device__ __forceinline__ void issue_umma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc,
+                                           uint32_t acc) {
+  if constexpr (sizeof(T) == 4)
+    umma_tf32(d, a, b, idesc, acc);
+  else
+    umma_f16(d, a, b, idesc, acc);
+}
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  switch (act) {
+    case ACT_RELU: return fmaxf(v, 0.0f);
+    case ACT_GELU: return gelu_tanh(v);
+    case ACT_SILU: return silu_f(v);
+    default: return v;
+  }
+}
+__device__ __forceinline__ float apply_dact(float x, int dact) {
+  switch (dact) {
+    case ACT_RELU: return x > 0.0f ? 1.0f : 0.0f;
+    case ACT_GELU: return gelu_tanh_grad(x);
+    case ACT_SILU: return silu_grad(x);
+    default: return 1.0f;
+  }
+}
+
+// Loads 32 consecutive elements of row-major `base[row*ld + col ...]` as floats.
+template <typename OT>
+__device__ __forceinline__ void load_row32(const OT* base, long long ld, long long row, int col,
+                                           int ncols_valid, bool vec, float* dst) {
+  const OT* p = base + row * ld + col;
+  if (vec && ncols_valid == 32) {
+    constexpr int PER = 16 / sizeof(OT);
+#pragma unroll
+    for (int i = 0; i < 32 / PER; ++i) {
+      uint4 v = *reinterpret_cast<const uint4*>(p + i * PER);
+      const OT* e = reinterpret_cast<const OT*>(&v);
+#pragma unroll
+      for (int j = 0; j < PER; ++j) dst[i * PER + j] = to_f32<OT>(e[j]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) dst[i] = (i < ncols_valid) ? to_f32<OT>(p[i]) : 0.0f;
+  }
+}
+template <typename OT>
+__device__ __forceinline__ void store_row32(OT* base, long long ld, long long row, int col,
+                                            int ncols_valid, bool vec, const float* src) {
+  OT* p = base + row * ld + col;
+  if (vec && ncols_valid == 32) {
+    constexpr int PER = 16 / sizeof(OT);
+#pragma unroll
+    for (int i = 0; i < 32 / PER; ++i) {
+      uint4 v;
+      OT* e = reinterpret_cast<OT*>(&v);
+#pragma unroll
+      for (int j = 0; j < PER; ++j) e[j] = from_f32<OT>(src[i * PER + j]);
+      *reinterpret_cast<uint4*>(p + i * PER) = v;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < ncols_valid) p[i] = from_f32<OT>(src[i]);
+  }
+}
+
+template <typename T, typename OT>
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t* acc_bits,
+                                               long long row, int col, int ncols_valid) {
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc_bits[i]) * p.alpha;
+  if (p.bias) {
+    const T* b = reinterpret_cast<const T*>(p.bias) + col;
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < ncols_valid) v[i] += to_f32<T>(b[i]);
+  }
+  const bool vec = p.vec_ok != 0;
+  if (p.aux_out) store_row32<OT>(reinterpret_cast<OT*>(p.aux_out), p.ldaux_out, row, col, ncols_valid, vec, v);
+  if (p.act != ACT_NONE) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = apply_act(v[i], p.act);
+  }
+  if (p.aux_in) {
+    float a[32];
+    load_row32<OT>(reinterpret_cast<const OT*>(p.aux_in), p.ldaux_in, row, col, ncols_valid, vec, a);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] *= apply_dact(a[i], p.dact);
+  }
+  if (p.residual) {
+    float r[32];
+    load_row32<OT>(reinterpret_cast<const OT*>(p.residual), p.ldr, row, col, ncols_valid, vec, r);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] += r[i];
+  }
+  store_row32<OT>(reinterpret_cast<OT*>(p.out), p.ldc, row, col, ncols_valid, vec, v);
+}
+
+template <typename T, int BN, bool A_MN, bool B_MN, typename Hooks>
+__device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
+                                              const GemmParams& p, const Hooks& hooks,
+                                              uint8_t* smem_raw, int cta_rank, int num_ctas) {
+  using C = GemmCfg<T, BN>;
+  constexpr int BM = C::BM, BK = C::BK, UMMA_K = C::UMMA_K, CH = C::CH;
+  constexpr int STAGES = C::STAGES;
+
+  // carve shared memory (tiles need 1024-byte alignment for the 128B swizzle)
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * C::A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * C::B_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tmem_full_bar = bars + 2 * STAGES;
+  uint64_t* tmem_empty_bar = bars + 2 * STAGES + 2;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp_idx = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(tma_a);
+    prefetch_tensormap(tma_b);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&tmem_full_bar[s]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[s]), 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp_idx == 1) {
+    tmem_alloc(smem_u32(tmem_ptr_smem), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int total_tiles = num_m * num_n;
+  const int group_m = p.group_m > 0 ? p.group_m : 8;
+
+  auto tile_coords = [&](int tile, int& m_idx, int& n_idx) {
+    if constexpr (Hooks::kCustomRaster) {
+      hooks.raster(tile, num_m, num_n, m_idx, n_idx);
+    } else {
+      const int group_size = group_m * num_n;
+      const int g = tile / group_size;
+      const int first_m = g * group_m;
+      const int gm = min(num_m - first_m, group_m);
+      const int r = tile - g * group_size;
+      m_idx = first_m + r % gm;
+      n_idx = r / gm;
+    }
+  };
+
+  if (warp_idx == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cta_rank; tile < total_tiles && ok; tile += num_ctas) {
+        int m_idx, n_idx;
+        tile_coords(tile, m_idx, n_idx);
+        ok = hooks.before_tile_load(m_idx, n_idx, abort_flag, p.status);
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          ok = hooks.before_k_load(m_idx, n_idx, kb, abort_flag, p.status);
+          if (!ok) break;
+          ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status,
+                         RB_ERR_TIMEOUT_EMPTY);
+          if (!ok) break;
+          const uint32_t bar = smem_u32(&full_bar[stage]);
+          mbar_arrive_expect_tx(bar, C::A_BYTES + C::B_BYTES);
+          const uint32_t a_dst = smem_u32(sA + stage * C::A_BYTES);
+          const uint32_t b_dst = smem_u32(sB + stage * C::B_BYTES);
+          if constexpr (!A_MN) {
+            tma_load_2d(a_dst, tma_a, bar, kb * BK, m_idx * BM);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / CH; ++j)
+              tma_load_2d(a_dst + j * BK * 128, tma_a, bar, m_idx * BM + j * CH, kb * BK);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(b_dst, tma_b, bar, kb * BK, n_idx * BN);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / CH; ++j)
+              tma_load_2d(b_dst + j * BK * 128, tma_b, bar, n_idx * BN + j * CH, kb * BK);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // give copies that are still in flight time to land before the CTA retires
+        for (int i = 0; i < 64; ++i) __nanosleep(10000);
+      }
+    }
+  } else if (warp_idx == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(UmmaFormat<T>::value, A_MN ? 1 : 0, B_MN ? 1 : 0, BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = cta_rank; tile < total_tiles && ok; tile += num_ctas) {
+        ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status,
+                       RB_ERR_TIMEOUT_TMEM_EMPTY);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status,
+                         RB_ERR_TIMEOUT_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(sA + stage * C::A_BYTES);
+          const uint32_t b_base = smem_u32(sB + stage * C::B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc =
+                A_MN ? make_smem_desc_sw128(a_base + k * UMMA_K * 128, BK * 128, 1024)
+                     : make_smem_desc_sw128(a_base + k * 32, 16, 1024);
+            const uint64_t bdesc =
+                B_MN ? make_smem_desc_sw128(b_base + k * UMMA_K * 128, BK * 128, 1024)
+                     : make_smem_desc_sw128(b_base + k * 32, 16, 1024);
+            issue_umma<T>(tmem_d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&empty_bar[stage]));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(smem_u32(&tmem_full_bar[acc]));
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int quarter = warp_idx & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = cta_rank; tile < total_tiles && ok; tile += num_ctas) {
+      int m_idx, n_idx;
+      tile_coords(tile, m_idx, n_idx);
+      ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status,
+                     RB_ERR_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const long long row = static_cast<long long>(m_idx) * BM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int col = n_idx * BN + c * 32;
+        const int ncols_valid = min(32, p.N - col);
+        if (row < p.M && ncols_valid > 0) {
+          if (p.out_f32)
+            epilogue_chunk<T, float>(p, r, row, col, ncols_valid);
+          else
+            epilogue_chunk<T, T>(p, r, row, col, ncols_valid);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+        hooks.after_tile_store(m_idx, n_idx, quarter);
+      }
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp_idx == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+}  // namespace rb
