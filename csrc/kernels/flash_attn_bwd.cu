@@ -1,0 +1,487 @@
+// FlashAttention backward for sm_100a (tcgen05 + TMEM + TMA), head_dim 128.
+//
+// One CTA owns a 128-row K/V tile of one (batch, kv-head) and sweeps the query
+// tiles (64 rows each) that attend to it.  All five GEMMs of a tile pair run on
+// tcgen05 with M = 128 by working on transposed score tiles:
+//
+//   S^T  [kv x q] = K . Q^T                 (recomputed)
+//   dP^T [kv x q] = V . dO^T
+//   P^T = exp2(S^T * c - LSE),  dS^T = P^T * (dP^T - D) * scale      (registers -> smem)
+//   dV  [kv x d] += P^T  . dO                (accumulates in TMEM across q tiles)
+//   dK  [kv x d] += dS^T . Q                 (accumulates in TMEM across q tiles)
+//   dQ^T [d x q]  = K^T . dS^T               (read back, red.add into an fp32 dQ buffer)
+//
+// Every shared tile is a stack of [rows x 64] 128B-swizzled sub-tiles, which the
+// tensor core can read either K-major (row = M/N index) or MN-major (row = K
+// index), so Q, dO and K each serve two GEMMs from one copy.
+//
+// The reference has no fused attention backward: it re-runs the materialised
+// softmax(QK^T)V composition when gradients are needed
+// (rumus/src/tensor/ops.rs:2693-2709, rumus/src/nn/attention.rs:17-58).
+#include "sm100_common.cuh"
+
+namespace rb {
+
+struct FaBwdParams {
+  int B, H, Hkv, Sq, Sk;
+  int causal;
+  float scale, scale_log2;
+  const float* lse;    // [B,H,Sq]
+  const float* delta;  // [B,H,Sq]  rowsum(dO * O)
+  float* dq_accum;     // [B,Sq,H,128] fp32, zero-initialised
+  void* dk;            // [B,Sk,Hkv,128]
+  void* dv;            // [B,Sk,Hkv,128]
+  int* status;
+};
+
+struct FaBwdCfg {
+  static constexpr int HD = 128, BKV = 128, BQ = 64, SUB = 2;
+  static constexpr int KV_TILE = 128 * 128 * 2;   // [128 x 128] 16-bit = 32 KB (2 sub-tiles of 16 KB)
+  static constexpr int KV_SUB = 128 * 128;        // 16 KB
+  static constexpr int Q_TILE = 64 * 128 * 2;     // [64 x 128] = 16 KB (2 sub-tiles of 8 KB)
+  static constexpr int Q_SUB = 64 * 128;          // 8 KB
+  static constexpr int PT_BYTES = 128 * 128;      // [128 kv x 64 q] = 16 KB
+  static constexpr int STAGES = 2;
+  static constexpr int SMEM_BYTES = 2 * KV_TILE + STAGES * 2 * Q_TILE + 2 * PT_BYTES +
+                                    2 * 2 * 64 * 4 /*lse,delta x2 stages*/ + 1024 + 256;
+  static constexpr int COL_ST = 0, COL_DPT = 64, COL_DQT = 128, COL_DV = 256, COL_DK = 384;
+};
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(192, 1)
+    fa_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                  const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
+                  const FaBwdParams p) {
+  using C = FaBwdCfg;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + C::KV_TILE;
+  uint8_t* sQ = sV + C::KV_TILE;               // [STAGES][Q_TILE]
+  uint8_t* sdO = sQ + C::STAGES * C::Q_TILE;   // [STAGES][Q_TILE]
+  uint8_t* sPT = sdO + C::STAGES * C::Q_TILE;
+  uint8_t* sdST = sPT + C::PT_BYTES;
+  float* sLse = reinterpret_cast<float*>(sdST + C::PT_BYTES);  // [2][64]
+  float* sDelta = sLse + 2 * 64;                                // [2][64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDelta + 2 * 64);
+  uint64_t* kv_full = bars;        // 1
+  uint64_t* q_full = bars + 1;     // [2]
+  uint64_t* q_empty = bars + 3;    // [2]
+  uint64_t* st_full = bars + 5;
+  uint64_t* dpt_full = bars + 6;
+  uint64_t* pds_ready = bars + 7;
+  uint64_t* dq_full = bars + 8;
+  uint64_t* dq_free = bars + 9;
+  uint64_t* all_done = bars + 10;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp_idx = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int kv_tile = blockIdx.x;
+  const int hkv = blockIdx.y, b = blockIdx.z;
+  const int group = p.H / p.Hkv;
+  const int kv0 = kv_tile * C::BKV;
+  const int off = p.Sk - p.Sq;
+  const int n_q_tiles = (p.Sq + C::BQ - 1) / C::BQ;
+  int q_tile_start = 0;
+  if (p.causal) {
+    const int first_q = kv0 - off;  // first query row that can see kv0
+    q_tile_start = first_q > 0 ? first_q / C::BQ : 0;
+  }
+  const int tiles_per_head = n_q_tiles > q_tile_start ? n_q_tiles - q_tile_start : 0;
+  const int n_iters = tiles_per_head * group;
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&tq);
+    prefetch_tensormap(&tk);
+    prefetch_tensormap(&tv);
+    prefetch_tensormap(&tdo);
+    mbar_init(smem_u32(kv_full), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&q_full[s]), 1);
+      mbar_init(smem_u32(&q_empty[s]), 1);
+    }
+    mbar_init(smem_u32(st_full), 1);
+    mbar_init(smem_u32(dpt_full), 1);
+    mbar_init(smem_u32(pds_ready), 128);
+    mbar_init(smem_u32(dq_full), 1);
+    mbar_init(smem_u32(dq_free), 128);
+    mbar_init(smem_u32(all_done), 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp_idx == 5) {
+    tmem_alloc(smem_u32(tmem_ptr_smem), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  auto iter_coords = [&](int it, int& qh, int& q0) {
+    const int g = it / tiles_per_head;
+    const int ti = it - g * tiles_per_head;
+    qh = hkv * group + g;
+    q0 = (q_tile_start + ti) * C::BQ;
+  };
+
+  if (warp_idx == 4) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0 && n_iters > 0) {
+      mbar_arrive_expect_tx(smem_u32(kv_full), 2 * C::KV_TILE);
+#pragma unroll
+      for (int s = 0; s < C::SUB; ++s) {
+        tma_load_4d(smem_u32(sK + s * C::KV_SUB), &tk, smem_u32(kv_full), s * 64, kv0, hkv, b);
+        tma_load_4d(smem_u32(sV + s * C::KV_SUB), &tv, smem_u32(kv_full), s * 64, kv0, hkv, b);
+      }
+      bool ok = true;
+      for (int it = 0; it < n_iters && ok; ++it) {
+        const int st = it & 1;
+        ok = mbar_wait(smem_u32(&q_empty[st]), ((it >> 1) & 1) ^ 1, abort_flag, p.status,
+                       RB_ERR_TIMEOUT_EMPTY);
+        if (!ok) break;
+        int qh, q0;
+        iter_coords(it, qh, q0);
+        const uint32_t bar = smem_u32(&q_full[st]);
+        mbar_arrive_expect_tx(bar, 2 * C::Q_TILE);
+#pragma unroll
+        for (int s = 0; s < C::SUB; ++s) {
+          tma_load_4d(smem_u32(sQ + st * C::Q_TILE + s * C::Q_SUB), &tq, bar, s * 64, q0, qh, b);
+          tma_load_4d(smem_u32(sdO + st * C::Q_TILE + s * C::Q_SUB), &tdo, bar, s * 64, q0, qh, b);
+        }
+      }
+      if (!ok)
+        for (int i = 0; i < 64; ++i) __nanosleep(10000);
+    }
+  } else if (warp_idx == 5) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0 && n_iters > 0) {
+      constexpr int F = UmmaFormat<T>::value;
+      constexpr uint32_t idesc_st = make_idesc(F, 0, 0, 128, 64);    // K(A,Kmaj) x Q(B,Kmaj)
+      constexpr uint32_t idesc_acc = make_idesc(F, 0, 1, 128, 128);  // P^T(A,Kmaj) x dO(B,N-maj)
+      constexpr uint32_t idesc_dq = make_idesc(F, 1, 1, 128, 64);    // K^T(A,M-maj) x dS^T(B,N-maj)
+      const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV);
+      const uint32_t pt_base = smem_u32(sPT), dst_base = smem_u32(sdST);
+      bool ok = mbar_wait(smem_u32(kv_full), 0, abort_flag, p.status, RB_ERR_TIMEOUT_FULL);
+      auto issue_scores = [&](int it) {
+        const int st = it & 1;
+        const uint32_t q_base = smem_u32(sQ + st * C::Q_TILE);
+        const uint32_t do_base = smem_u32(sdO + st * C::Q_TILE);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {  // K dim = head_dim 128
+          const uint32_t oa = (k >> 2) * C::KV_SUB + (k & 3) * 32;
+          const uint32_t ob = (k >> 2) * C::Q_SUB + (k & 3) * 32;
+          umma_f16(tmem_base + C::COL_ST, make_smem_desc_sw128(k_base + oa, 16, 1024),
+                   make_smem_desc_sw128(q_base + ob, 16, 1024), idesc_st, k != 0);
+        }
+        umma_commit(smem_u32(st_full));
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t oa = (k >> 2) * C::KV_SUB + (k & 3) * 32;
+          const uint32_t ob = (k >> 2) * C::Q_SUB + (k & 3) * 32;
+          umma_f16(tmem_base + C::COL_DPT, make_smem_desc_sw128(v_base + oa, 16, 1024),
+                   make_smem_desc_sw128(do_base + ob, 16, 1024), idesc_st, k != 0);
+        }
+        umma_commit(smem_u32(dpt_full));
+      };
+      if (ok) {
+        ok = mbar_wait(smem_u32(&q_full[0]), 0, abort_flag, p.status, RB_ERR_TIMEOUT_FULL);
+        if (ok) {
+          tc_fence_after();
+          issue_scores(0);
+        }
+      }
+      for (int it = 0; it < n_iters && ok; ++it) {
+        const int st = it & 1;
+        ok = mbar_wait(smem_u32(pds_ready), it & 1, abort_flag, p.status, RB_ERR_TIMEOUT_FLAG);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t q_base = smem_u32(sQ + st * C::Q_TILE);
+        const uint32_t do_base = smem_u32(sdO + st * C::Q_TILE);
+        // dV += P^T . dO ; dK += dS^T . Q      (K dim = 64 query rows -> 4 steps)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          umma_f16(tmem_base + C::COL_DV, make_smem_desc_sw128(pt_base + k * 32, 16, 1024),
+                   make_smem_desc_sw128(do_base + k * 2048, C::Q_SUB, 1024), idesc_acc,
+                   (it | k) != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          umma_f16(tmem_base + C::COL_DK, make_smem_desc_sw128(dst_base + k * 32, 16, 1024),
+                   make_smem_desc_sw128(q_base + k * 2048, C::Q_SUB, 1024), idesc_acc,
+                   (it | k) != 0);
+        }
+        // dQ^T = K^T . dS^T  (K dim = 128 kv rows -> 8 steps); needs the previous dQ^T drained
+        if (it > 0) {
+          ok = mbar_wait(smem_u32(dq_free), (it - 1) & 1, abort_flag, p.status,
+                         RB_ERR_TIMEOUT_TMEM_EMPTY);
+          if (!ok) break;
+          tc_fence_after();
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          umma_f16(tmem_base + C::COL_DQT,
+                   make_smem_desc_sw128(k_base + k * 2048, C::KV_SUB, 1024),
+                   make_smem_desc_sw128(dst_base + k * 2048, C::PT_BYTES, 1024), idesc_dq, k != 0);
+        }
+        umma_commit(smem_u32(dq_full));
+        umma_commit(smem_u32(&q_empty[st]));
+        if (it + 1 < n_iters) {
+          ok = mbar_wait(smem_u32(&q_full[(it + 1) & 1]), ((it + 1) >> 1) & 1, abort_flag, p.status,
+                         RB_ERR_TIMEOUT_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          issue_scores(it + 1);
+        }
+      }
+      if (ok) umma_commit(smem_u32(all_done));
+    }
+  } else if (n_iters > 0) {
+    // ------------------------------ compute warps ------------------------------
+    const int t = threadIdx.x;  // kv row within tile == TMEM lane (also d index for dQ^T)
+    const int kv = kv0 + t;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp_idx * 32) << 16);
+    bool ok = true;
+    for (int it = 0; it < n_iters; ++it) {
+      int qh, q0;
+      iter_coords(it, qh, q0);
+      const int buf = it & 1;
+      if (t < 64) {
+        const int q = q0 + t;
+        const long long idx = (static_cast<long long>(b) * p.H + qh) * p.Sq + q;
+        sLse[buf * 64 + t] = q < p.Sq ? p.lse[idx] * 1.4426950408889634f : 0.f;
+        sDelta[buf * 64 + t] = q < p.Sq ? p.delta[idx] : 0.f;
+      }
+      named_bar_sync(1, 128);
+      ok = mbar_wait(smem_u32(st_full), it & 1, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      float pr[64];
+      const bool kv_ok = kv < p.Sk;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(lane_addr + C::COL_ST + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int qi = c * 32 + i;
+          const int q = q0 + qi;
+          const bool valid = kv_ok && q < p.Sq && (!p.causal || kv <= q + off);
+          const float v = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, -sLse[buf * 64 + qi]));
+          pr[qi] = valid ? v : 0.f;
+        }
+      }
+      // P^T row -> smem (8 chunks of 16 bytes, swizzled)
+      {
+        uint8_t* rowp = sPT + t * 128;
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+          uint4 v;
+          T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(pr[cc * 8 + i]);
+          *reinterpret_cast<uint4*>(rowp + ((cc ^ (t & 7)) << 4)) = v;
+        }
+      }
+      ok = mbar_wait(smem_u32(dpt_full), it & 1, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(lane_addr + C::COL_DPT + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int qi = c * 32 + i;
+          pr[qi] = pr[qi] * (__uint_as_float(r[i]) - sDelta[buf * 64 + qi]) * p.scale;
+        }
+      }
+      {
+        uint8_t* rowp = sdST + t * 128;
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+          uint4 v;
+          T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(pr[cc * 8 + i]);
+          *reinterpret_cast<uint4*>(rowp + ((cc ^ (t & 7)) << 4)) = v;
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(smem_u32(pds_ready));
+      // drain dQ^T: lane t holds d = t, 64 query columns
+      ok = mbar_wait(smem_u32(dq_full), it & 1, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      float* dq_base = p.dq_accum + ((static_cast<long long>(b) * p.Sq + q0) * p.H + qh) * C::HD + t;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(lane_addr + C::COL_DQT + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int qi = c * 32 + i;
+          if (q0 + qi < p.Sq)
+            atomicAdd(dq_base + static_cast<long long>(qi) * p.H * C::HD, __uint_as_float(r[i]));
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(dq_free));
+    }
+    if (ok) {
+      ok = mbar_wait(smem_u32(all_done), 0, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const long long orow = ((static_cast<long long>(b) * p.Sk + kv) * p.Hkv + hkv) * C::HD;
+      T* dkp = reinterpret_cast<T*>(p.dk) + orow;
+      T* dvp = reinterpret_cast<T*>(p.dv) + orow;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(lane_addr + C::COL_DV + c * 32, r);
+        tmem_ld_wait();
+        if (kv < p.Sk) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 v;
+            T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(__uint_as_float(r[q * 8 + i]));
+            *reinterpret_cast<uint4*>(dvp + c * 32 + q * 8) = v;
+          }
+        }
+        tmem_ld_32x32b_x32(lane_addr + C::COL_DK + c * 32, r);
+        tmem_ld_wait();
+        if (kv < p.Sk) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 v;
+            T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(__uint_as_float(r[q * 8 + i]));
+            *reinterpret_cast<uint4*>(dkp + c * 32 + q * 8) = v;
+          }
+        }
+      }
+    }
+  } else {
+    // no query tile attends to this K/V tile: gradients are zero
+    const int t = threadIdx.x;
+    const int kv = kv0 + t;
+    if (t < 128 && kv < p.Sk) {
+      const long long orow = ((static_cast<long long>(b) * p.Sk + kv) * p.Hkv + hkv) * C::HD;
+      uint4 z = make_uint4(0, 0, 0, 0);
+      for (int c = 0; c < C::HD / 8; ++c) {
+        *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.dk) + orow + c * 8) = z;
+        *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.dv) + orow + c * 8) = z;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp_idx == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[b,h,q] = sum_d dO[b,q,h,d] * O[b,q,h,d]   (one warp per row)
+template <typename T>
+__global__ void fa_bwd_delta_kernel(const T* __restrict__ o, const T* __restrict__ dout,
+                                    long long do_sb, long long do_ss, long long do_sh,
+                                    float* __restrict__ delta, int B, int H, int Sq, int HD) {
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(B) * Sq * H;
+  if (warp >= total) return;
+  const int h = warp % H;
+  const long long bq = warp / H;
+  const int q = bq % Sq;
+  const int b = bq / Sq;
+  const T* op = o + warp * HD;
+  const T* dp = dout + b * do_sb + q * do_ss + h * do_sh;
+  float acc = 0.f;
+  for (int d = lane; d < HD; d += 32) acc += to_f32<T>(op[d]) * to_f32<T>(dp[d]);
+  acc = warp_sum(acc);
+  if (lane == 0) delta[(static_cast<long long>(b) * H + h) * Sq + q] = acc;
+}
+
+template <typename T>
+int launch_fa_bwd(int dtype, const void* q, const void* k, const void* v, const void* o,
+                  const void* dout, const long long* qs, const long long* ks, const long long* vs,
+                  const long long* dos, float* delta, const FaBwdParams& p, cudaStream_t st) {
+  using C = FaBwdCfg;
+  {
+    const long long rows = static_cast<long long>(p.B) * p.Sq * p.H;
+    const int threads = 256;
+    const long long blocks = (rows * 32 + threads - 1) / threads;
+    fa_bwd_delta_kernel<T><<<(unsigned)blocks, threads, 0, st>>>(
+        (const T*)o, (const T*)dout, dos[0], dos[1], dos[2], delta, p.B, p.H, p.Sq, C::HD);
+  }
+  CUtensorMap tq, tk, tv, tdo;
+  auto mk = [&](CUtensorMap* m, const void* base, const long long* s, int S, int heads, int rows) {
+    uint64_t dims[4] = {(uint64_t)C::HD, (uint64_t)S, (uint64_t)heads, (uint64_t)p.B};
+    uint64_t strides[4] = {2, (uint64_t)s[1] * 2, (uint64_t)s[2] * 2, (uint64_t)s[0] * 2};
+    uint32_t box[4] = {64, (uint32_t)rows, 1, 1};
+    return rbh::encode_tensor_map(m, dtype, 4, const_cast<void*>(base), dims, strides, box, 1);
+  };
+  int rc = mk(&tq, q, qs, p.Sq, p.H, C::BQ);
+  if (!rc) rc = mk(&tk, k, ks, p.Sk, p.Hkv, C::BKV);
+  if (!rc) rc = mk(&tv, v, vs, p.Sk, p.Hkv, C::BKV);
+  if (!rc) rc = mk(&tdo, dout, dos, p.Sq, p.H, C::BQ);
+  if (rc) return 1000 + rc;
+  auto kern = fa_bwd_kernel<T>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  if (e != cudaSuccess) return 2000 + (int)e;
+  dim3 grid((p.Sk + C::BKV - 1) / C::BKV, p.Hkv, p.B);
+  kern<<<grid, 192, C::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
+}
+
+}  // namespace rb
+
+extern "C" {
+// head_dim must be 128.  Strides are {batch, seq, head} in elements.
+// o is [B,Sq,H,128] contiguous; dq_accum is fp32 [B,Sq,H,128] and must be zero on entry;
+// delta is fp32 scratch [B,H,Sq]; dk/dv are [B,Sk,Hkv,128] contiguous.
+int rb_flash_attn_bwd(int dtype, int head_dim, const void* q, const void* k, const void* v,
+                      const void* o, const void* dout, const float* lse, const long long* q_strides,
+                      const long long* k_strides, const long long* v_strides,
+                      const long long* do_strides, float* delta, float* dq_accum, void* dk,
+                      void* dv, int B, int H, int Hkv, int Sq, int Sk, int causal, float scale,
+                      void* stream) {
+  using namespace rb;
+  if (head_dim != 128) return 20;
+  if (B <= 0 || H <= 0 || Sq <= 0 || Sk <= 0) return 0;
+  FaBwdParams p;
+  p.B = B; p.H = H; p.Hkv = Hkv; p.Sq = Sq; p.Sk = Sk; p.causal = causal;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse = lse; p.delta = delta; p.dq_accum = dq_accum; p.dk = dk; p.dv = dv;
+  p.status = rbh::device_status_word();
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == rbh::DT_BF16)
+    return launch_fa_bwd<__nv_bfloat16>(dtype, q, k, v, o, dout, q_strides, k_strides, v_strides, do_strides, delta, p, st);
+  if (dtype == rbh::DT_F16)
+    return launch_fa_bwd<__half>(dtype, q, k, v, o, dout, q_strides, k_strides, v_strides, do_strides, delta, p, st);
+  return 20;
+}
+}

@@ -1,0 +1,367 @@
+// FlashAttention forward for sm_100a (tcgen05 + TMEM + TMA).
+//
+// One CTA owns a 128-row query tile of one (batch, head).  K/V tiles of 128 rows
+// stream through a 2-stage TMA ring.  S = Q K^T and O += P V run on tcgen05 with
+// S (double buffered) and O living in TMEM; four softmax warps own one query row
+// per thread (TMEM lane == row), keep the running max / sum in registers, write
+// P as bf16/fp16 into a 128B-swizzled shared tile that the second MMA consumes,
+// and rescale O in TMEM only when the running max moved by more than 2^8 (lazy
+// rescale).  exp is exp2 with the softmax scale folded in.  LSE is saved for the
+// backward pass.
+//
+// Layout: q/k/v/o are [B, S, H, D] views with arbitrary batch/seq/head strides
+// (so the fused qkv projection output is consumed in place); D in {64, 128}.
+//
+// The reference kernel (rumus/src/backend/gpu/shaders/flash_attn.wgsl:35) is a
+// forward-only scalar loop: one thread per query row, K/V tiles of <= 16 rows in
+// 16 KB of workgroup memory (rumus/src/backend/gpu/compute.rs:2079-2138).
+#include "sm100_common.cuh"
+
+namespace rb {
+
+struct FaFwdParams {
+  int B, H, Hkv, Sq, Sk;
+  int causal;
+  float scale_log2;  // softmax scale * log2(e)
+  void* o;           // [B, Sq, H, D] contiguous
+  float* lse;        // [B, H, Sq]
+  int* status;
+};
+
+template <int HD>
+struct FaFwdCfg {
+  static constexpr int BM = 128, BN = 128;
+  static constexpr int SUB = HD / 64;             // 64-column sub-tiles per row
+  static constexpr int TILE_BYTES = 128 * 128;    // one [128 x 64] 16-bit sub-tile
+  static constexpr int Q_BYTES = SUB * TILE_BYTES;
+  static constexpr int KV_BYTES = SUB * TILE_BYTES;  // per K or V tile
+  static constexpr int P_BYTES = 2 * TILE_BYTES;     // [128 x 128]
+  static constexpr int STAGES = 2;
+  static constexpr int SMEM_BYTES = Q_BYTES + STAGES * 2 * KV_BYTES + P_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int S_COL0 = 0;       // S buffers at columns [0,128) and [128,256)
+  static constexpr int O_COL = 256;      // O at [256, 256+HD)
+};
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(192, 1)
+    fa_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                  const __grid_constant__ CUtensorMap tv, const FaFwdParams p) {
+  using C = FaFwdCfg<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + C::Q_BYTES;                       // [STAGES][KV_BYTES]
+  uint8_t* sV = sK + C::STAGES * C::KV_BYTES;          // [STAGES][KV_BYTES]
+  uint8_t* sP = sV + C::STAGES * C::KV_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::P_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;    // [2]
+  uint64_t* kv_empty = bars + 3;   // [2]
+  uint64_t* s_full = bars + 5;     // [2]
+  uint64_t* p_ready = bars + 7;
+  uint64_t* pv_done = bars + 8;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp_idx = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int q_tile = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hkv = h / (p.H / p.Hkv);
+  const int q0 = q_tile * C::BM;
+  const int off = p.Sk - p.Sq;
+  int n_tiles = (p.Sk + C::BN - 1) / C::BN;
+  if (p.causal) {
+    const int last_kv = min(p.Sk - 1, q0 + C::BM - 1 + off);
+    n_tiles = last_kv < 0 ? 0 : last_kv / C::BN + 1;
+  }
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&tq);
+    prefetch_tensormap(&tk);
+    prefetch_tensormap(&tv);
+    mbar_init(smem_u32(q_full), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&kv_full[s]), 1);
+      mbar_init(smem_u32(&kv_empty[s]), 1);
+      mbar_init(smem_u32(&s_full[s]), 1);
+    }
+    mbar_init(smem_u32(p_ready), 128);
+    mbar_init(smem_u32(pv_done), 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp_idx == 5) {
+    tmem_alloc(smem_u32(tmem_ptr_smem), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp_idx == 4) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0 && n_tiles > 0) {
+      mbar_arrive_expect_tx(smem_u32(q_full), C::Q_BYTES);
+#pragma unroll
+      for (int s = 0; s < C::SUB; ++s)
+        tma_load_4d(smem_u32(sQ + s * C::TILE_BYTES), &tq, smem_u32(q_full), s * 64, q0, h, b);
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        ok = mbar_wait(smem_u32(&kv_empty[st]), ph ^ 1, abort_flag, p.status, RB_ERR_TIMEOUT_EMPTY);
+        if (!ok) break;
+        const uint32_t bar = smem_u32(&kv_full[st]);
+        mbar_arrive_expect_tx(bar, 2 * C::KV_BYTES);
+#pragma unroll
+        for (int s = 0; s < C::SUB; ++s) {
+          tma_load_4d(smem_u32(sK + st * C::KV_BYTES + s * C::TILE_BYTES), &tk, bar, s * 64,
+                      j * C::BN, hkv, b);
+          tma_load_4d(smem_u32(sV + st * C::KV_BYTES + s * C::TILE_BYTES), &tv, bar, s * 64,
+                      j * C::BN, hkv, b);
+        }
+      }
+      if (!ok)
+        for (int i = 0; i < 64; ++i) __nanosleep(10000);
+    }
+  } else if (warp_idx == 5) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_s = make_idesc(UmmaFormat<T>::value, 0, 0, 128, 128);
+      constexpr uint32_t idesc_o = make_idesc(UmmaFormat<T>::value, 0, 1, 128, HD);
+      bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, p.status, RB_ERR_TIMEOUT_FULL);
+      auto issue_s = [&](int j) {
+        const int st = j & 1;
+        const uint32_t q_base = smem_u32(sQ);
+        const uint32_t k_base = smem_u32(sK + st * C::KV_BYTES);
+        const uint32_t d = tmem_base + C::S_COL0 + (j & 1) * 128;
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t o = (k >> 2) * C::TILE_BYTES + (k & 3) * 32;
+          umma_f16(d, make_smem_desc_sw128(q_base + o, 16, 1024),
+                   make_smem_desc_sw128(k_base + o, 16, 1024), idesc_s, k != 0);
+        }
+        umma_commit(smem_u32(&s_full[j & 1]));
+      };
+      if (ok) {
+        ok = mbar_wait(smem_u32(&kv_full[0]), 0, abort_flag, p.status, RB_ERR_TIMEOUT_FULL);
+        if (ok) {
+          tc_fence_after();
+          issue_s(0);
+        }
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) {
+          ok = mbar_wait(smem_u32(&kv_full[(j + 1) & 1]), ((j + 1) >> 1) & 1, abort_flag, p.status,
+                         RB_ERR_TIMEOUT_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(j + 1);
+        }
+        ok = mbar_wait(smem_u32(p_ready), j & 1, abort_flag, p.status, RB_ERR_TIMEOUT_FLAG);
+        if (!ok) break;
+        tc_fence_after();
+        const int st = j & 1;
+        const uint32_t p_base = smem_u32(sP);
+        const uint32_t v_base = smem_u32(sV + st * C::KV_BYTES);
+        const uint32_t d = tmem_base + C::O_COL;
+#pragma unroll
+        for (int k = 0; k < C::BN / 16; ++k) {
+          const uint32_t po = (k >> 2) * C::TILE_BYTES + (k & 3) * 32;
+          umma_f16(d, make_smem_desc_sw128(p_base + po, 16, 1024),
+                   make_smem_desc_sw128(v_base + k * 2048, C::TILE_BYTES, 1024), idesc_o,
+                   (j | k) != 0);
+        }
+        umma_commit(smem_u32(&kv_empty[st]));
+        umma_commit(smem_u32(pv_done));
+      }
+    }
+  } else if (n_tiles > 0) {
+    // ------------------------------ softmax warps -----------------------------
+    const int t = threadIdx.x;          // row within the tile == TMEM lane
+    const int row = q0 + t;             // global query row
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp_idx * 32) << 16);
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      ok = mbar_wait(smem_u32(&s_full[j & 1]), (j >> 1) & 1, abort_flag, p.status,
+                     RB_ERR_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t s_addr = lane_addr + C::S_COL0 + (j & 1) * 128;
+      const int kv0 = j * C::BN;
+      const bool need_mask = (kv0 + C::BN > p.Sk) || (p.causal && kv0 + C::BN - 1 > q0 + off);
+      const int kv_limit = p.causal ? min(p.Sk - 1, row + off) : p.Sk - 1;  // last valid kv index
+      // pass 1: row max
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(s_addr + c * 32, r);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (kv0 + c * 32 + i <= kv_limit) mx = fmaxf(mx, __uint_as_float(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+      }
+      const float m_new = fmaxf(m_used, mx * p.scale_log2);
+      const bool need = m_new > m_used + 8.0f;  // also true on the first tile (m_used = -inf)
+      if (j > 0) {
+        ok = mbar_wait(smem_u32(pv_done), (j - 1) & 1, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_EMPTY);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      if (__any_sync(0xffffffffu, need)) {
+        float alpha = 1.0f;
+        if (need) {
+          alpha = (m_used == -INFINITY) ? 0.0f : exp2f(m_used - m_new);
+          m_used = m_new;
+          l *= alpha;
+        }
+        if (j > 0) {
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(lane_addr + C::O_COL + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32b_x32(lane_addr + C::O_COL + c * 32, r);
+          }
+          tmem_st_wait();
+        }
+      }
+      // pass 2: P = exp2(S*scale - m), row sum, store to swizzled smem
+      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(s_addr + c * 32, r);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
+          float p1 = exp2f(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, neg_m));
+          if (need_mask) {
+            if (kv0 + c * 32 + i > kv_limit) p0 = 0.f;
+            if (kv0 + c * 32 + i + 1 > kv_limit) p1 = 0.f;
+          }
+          l += p0 + p1;
+          T lo = from_f32<T>(p0), hi = from_f32<T>(p1);
+          packed[i >> 1] = (uint32_t)(*reinterpret_cast<uint16_t*>(&lo)) |
+                           ((uint32_t)(*reinterpret_cast<uint16_t*>(&hi)) << 16);
+        }
+        // columns [c*32, c*32+32) -> sub-tile (c>>1), 16-byte chunks ((c&1)*4 .. +4)
+        uint8_t* rowp = sP + (c >> 1) * C::TILE_BYTES + t * 128;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int cc = (c & 1) * 4 + q;
+          *reinterpret_cast<uint4*>(rowp + ((cc ^ (t & 7)) << 4)) =
+              make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(smem_u32(p_ready));
+    }
+    if (ok) {
+      ok = mbar_wait(smem_u32(pv_done), (n_tiles - 1) & 1, abort_flag, p.status,
+                     RB_ERR_TIMEOUT_TMEM_EMPTY);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv_l = l > 0.f ? 1.0f / l : 0.f;
+      T* orow = reinterpret_cast<T*>(p.o) + ((static_cast<long long>(b) * p.Sq + row) * p.H + h) * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(lane_addr + C::O_COL + c * 32, r);
+        tmem_ld_wait();
+        if (row < p.Sq) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 v;
+            T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(__uint_as_float(r[q * 8 + i]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = v;
+          }
+        }
+      }
+      if (row < p.Sq)
+        p.lse[(static_cast<long long>(b) * p.H + h) * p.Sq + row] =
+            (m_used + log2f(l)) * 0.6931471805599453f;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp_idx == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+template <typename T, int HD>
+int launch_fa_fwd(int dtype, const void* q, const void* k, const void* v, const long long* qs,
+                  const long long* ks, const long long* vs, const FaFwdParams& p, cudaStream_t st) {
+  using C = FaFwdCfg<HD>;
+  CUtensorMap tq, tk, tv;
+  auto mk = [&](CUtensorMap* m, const void* base, const long long* s, int S, int heads) {
+    uint64_t dims[4] = {(uint64_t)HD, (uint64_t)S, (uint64_t)heads, (uint64_t)p.B};
+    uint64_t strides[4] = {2, (uint64_t)s[1] * 2, (uint64_t)s[2] * 2, (uint64_t)s[0] * 2};
+    uint32_t box[4] = {64, 128, 1, 1};
+    return rbh::encode_tensor_map(m, dtype, 4, const_cast<void*>(base), dims, strides, box, 1);
+  };
+  int rc = mk(&tq, q, qs, p.Sq, p.H);
+  if (!rc) rc = mk(&tk, k, ks, p.Sk, p.Hkv);
+  if (!rc) rc = mk(&tv, v, vs, p.Sk, p.Hkv);
+  if (rc) return 1000 + rc;
+  auto kern = fa_fwd_kernel<T, HD>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  if (e != cudaSuccess) return 2000 + (int)e;
+  dim3 grid((p.Sq + C::BM - 1) / C::BM, p.H, p.B);
+  kern<<<grid, 192, C::SMEM_BYTES, st>>>(tq, tk, tv, p);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
+}
+
+}  // namespace rb
+
+extern "C" {
+// q/k/v strides are {batch, seq, head} in elements (innermost dim contiguous).
+// o is [B,Sq,H,D] contiguous, lse is [B,H,Sq] fp32.
+int rb_flash_attn_fwd(int dtype, int head_dim, const void* q, const void* k, const void* v,
+                      const long long* q_strides, const long long* k_strides,
+                      const long long* v_strides, void* o, float* lse, int B, int H, int Hkv,
+                      int Sq, int Sk, int causal, float scale, void* stream) {
+  using namespace rb;
+  if (B <= 0 || H <= 0 || Sq <= 0) return 0;
+  FaFwdParams p;
+  p.B = B; p.H = H; p.Hkv = Hkv; p.Sq = Sq; p.Sk = Sk; p.causal = causal;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.o = o; p.lse = lse;
+  p.status = rbh::device_status_word();
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == rbh::DT_BF16) {
+    if (head_dim == 128) return launch_fa_fwd<__nv_bfloat16, 128>(dtype, q, k, v, q_strides, k_strides, v_strides, p, st);
+    if (head_dim == 64) return launch_fa_fwd<__nv_bfloat16, 64>(dtype, q, k, v, q_strides, k_strides, v_strides, p, st);
+  } else if (dtype == rbh::DT_F16) {
+    if (head_dim == 128) return launch_fa_fwd<__half, 128>(dtype, q, k, v, q_strides, k_strides, v_strides, p, st);
+    if (head_dim == 64) return launch_fa_fwd<__half, 64>(dtype, q, k, v, q_strides, k_strides, v_strides, p, st);
+  }
+  return 20;  // unsupported dtype / head_dim
+}
+}

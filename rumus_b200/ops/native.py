@@ -152,6 +152,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
     if bt is None:
         b = b.contiguous()
         bt, ldb = False, N
+    if a.dtype == torch.float32 and path != 2:
+        # the tf32 tensor-core path takes K-major operands only: restage the other layouts
+        if at:
+            a = a.contiguous()
+            at, lda = False, K
+        if not bt:
+            b = b.t().contiguous().t()
+            bt, ldb = True, K
     # kernel convention: a_mn=1 when A is stored [K,M]; b_mn=1 when B is stored [K,N]
     a_mn = 1 if at else 0
     b_mn = 0 if bt else 1
