@@ -78,6 +78,54 @@ def bmm(a, b):
     return _BmmFn.apply(a, b)
 
 
+def _main_grad(p):
+    """Parameters managed by a flat gradient arena carry ``main_grad`` (a view into the arena)
+    and ``grad_accumulate`` (add instead of overwrite).  Weight-gradient GEMMs then write
+    straight into the arena and autograd sees ``None`` for that parameter."""
+    if p is None:
+        return None
+    mg = getattr(p, "main_grad", None)
+    if mg is None:
+        return None
+    return (mg, p)
+
+
+def _wgrad(x2, dy2, mg):
+    if mg is None:
+        return native.gemm(x2.t(), dy2)
+    buf, p = mg
+    acc = getattr(p, "grad_accumulate", False)
+    native.gemm(x2.t(), dy2, out=buf, residual=buf if acc else None)
+    p.grad_accumulate = True
+    return None
+
+
+def _bgrad(dy2, mg):
+    g = native.colsum(dy2)
+    if mg is None:
+        return g
+    buf, p = mg
+    if getattr(p, "grad_accumulate", False):
+        buf.add_(g)
+    else:
+        buf.copy_(g)
+    p.grad_accumulate = True
+    return None
+
+
+def _small_grad(g, mg):
+    """Route a small parameter gradient (norm scale/shift, embeddings) into the arena."""
+    if mg is None or g is None:
+        return g
+    buf, p = mg
+    if getattr(p, "grad_accumulate", False):
+        buf.add_(g.view(buf.shape))
+    else:
+        buf.copy_(g.view(buf.shape))
+    p.grad_accumulate = True
+    return None
+
+
 class _LinearFn(torch.autograd.Function):
     """y = act(x @ W + b) (+ residual); W is [in, out]."""
 
@@ -96,6 +144,8 @@ class _LinearFn(torch.autograd.Function):
         ctx.has_bias = bias is not None
         ctx.has_res = residual is not None
         ctx.x_shape = x.shape
+        ctx.w_main_grad = _main_grad(w)
+        ctx.b_main_grad = _main_grad(bias)
         ctx.save_for_backward(x2, w, pre)
         return y.view(*x.shape[:-1], w.shape[1])
 
@@ -112,9 +162,9 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = native.gemm(dy2, w.t()).view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
-            dw = native.gemm(x2.t(), dy2)
+            dw = _wgrad(x2, dy2, ctx.w_main_grad)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = native.colsum(dy2)
+            db = _bgrad(dy2, ctx.b_main_grad)
         return dx, dw, db, dres, None
 
 
@@ -150,6 +200,7 @@ class _MlpFn(torch.autograd.Function):
         ctx.has_b1 = b1 is not None
         ctx.has_b2 = b2 is not None
         ctx.x_shape = x.shape
+        ctx.mg = (_main_grad(w1), _main_grad(b1), _main_grad(w2), _main_grad(b2))
         ctx.save_for_backward(x2, w1, w2, h, a)
         return y.view(*x.shape[:-1], w2.shape[1])
 
@@ -159,12 +210,13 @@ class _MlpFn(torch.autograd.Function):
         dy2 = dy.reshape(-1, dy.shape[-1])
         if dy2.stride(-1) != 1:
             dy2 = dy2.contiguous()
+        mg_w1, mg_b1, mg_w2, mg_b2 = ctx.mg
         dh = native.gemm(dy2, w2.t(), aux_in=h, dact=ctx.act)
-        dw2 = native.gemm(a.t(), dy2)
-        db2 = native.colsum(dy2) if ctx.has_b2 else None
+        dw2 = _wgrad(a, dy2, mg_w2)
+        db2 = _bgrad(dy2, mg_b2) if ctx.has_b2 else None
         dx = native.gemm(dh, w1.t()).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
-        dw1 = native.gemm(x2.t(), dh)
-        db1 = native.colsum(dh) if ctx.has_b1 else None
+        dw1 = _wgrad(x2, dh, mg_w1)
+        db1 = _bgrad(dh, mg_b1) if ctx.has_b1 else None
         return dx, dw1, db1, dw2, db2, (dy if ctx.has_res else None), None
 
 
@@ -263,6 +315,7 @@ class _NormFn(torch.autograd.Function):
         ctx.rms = rms
         ctx.has_res = residual is not None
         ctx.has_beta = beta is not None
+        ctx.mg = (_main_grad(gamma), _main_grad(beta))
         ctx.save_for_backward(h if h is not None else x, gamma, stats)
         return y, h
 
@@ -271,7 +324,9 @@ class _NormFn(torch.autograd.Function):
         xn, gamma, stats = ctx.saved_tensors
         dx, dg, db = native.norm_bwd(xn, dy, gamma, stats, ctx.rms, dres=dh,
                                      want_beta=ctx.has_beta)
-        return dx, dg, (db if ctx.has_beta else None), (dx if ctx.has_res else None), None, None
+        dg = _small_grad(dg, ctx.mg[0])
+        db = _small_grad(db, ctx.mg[1]) if ctx.has_beta else None
+        return dx, dg, db, (dx if ctx.has_res else None), None, None
 
 
 def layer_norm(x, weight, bias, eps: float = 1e-5, residual=None):
@@ -347,6 +402,48 @@ def cross_entropy_loss(logits: torch.Tensor, targets: torch.Tensor) -> torch.Ten
     return _CrossEntropyFn.apply(logits, targets)
 
 
+class _LmHeadLossFn(torch.autograd.Function):
+    """Vocabulary projection + mean cross entropy.  The logits buffer is overwritten in place by
+    its own gradient inside the cross-entropy kernel, so the [tokens, vocab] matrix exists once."""
+
+    @staticmethod
+    def forward(ctx, x, w, targets):
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        rows = x2.shape[0]
+        logits = native.gemm(x2, w)
+        loss, dlogits = native.cross_entropy(logits, targets.reshape(-1), grad_scale=1.0 / rows,
+                                             loss_scale=1.0 / rows, want_grad=True, inplace=True)
+        ctx.x_shape = x.shape
+        ctx.mg = _main_grad(w)
+        ctx.save_for_backward(x2, w, dlogits)
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        x2, w, dlogits = ctx.saved_tensors
+        dx = native.gemm(dlogits, w.t())
+        dx.mul_(dloss.to(dx.dtype))
+        if ctx.mg is None:
+            dw = native.gemm(x2.t(), dlogits)
+            dw.mul_(dloss.to(dw.dtype))
+        else:
+            # fold the upstream scalar into the (small) activation operand instead of the
+            # [d, vocab] result, then accumulate straight into the arena
+            dw = _wgrad(x2 * dloss.to(x2.dtype), dlogits, ctx.mg)
+        return dx.view(ctx.x_shape), dw, None
+
+
+def lm_head_loss(x, weight_io, targets):
+    """``cross_entropy(x @ weight_io, targets)`` (mean over tokens) without keeping logits and
+    their gradient as two tensors."""
+    if not _is_native(x):
+        logits = x.reshape(-1, x.shape[-1]) @ weight_io
+        return TF.cross_entropy(logits.float(), targets.reshape(-1).long())
+    return _LmHeadLossFn.apply(x, weight_io, targets)
+
+
 def mse_loss(pred, target):
     """reference: tensor/ops.rs:713"""
     return ((pred - target) ** 2).mean()
@@ -367,6 +464,7 @@ class _EmbeddingFn(torch.autograd.Function):
         ctx.seq = seq
         ctx.pos_rows = pos.shape[0] if pos is not None else 0
         ctx.wdtype = weight.dtype
+        ctx.mg = (_main_grad(weight), _main_grad(pos))
         return out
 
     @staticmethod
@@ -378,7 +476,7 @@ class _EmbeddingFn(torch.autograd.Function):
             full = torch.zeros((ctx.pos_rows, dpos.shape[1]), dtype=ctx.wdtype, device=dpos.device)
             full[: ctx.seq] = dpos.to(ctx.wdtype)
             dpos = full
-        return None, dW, dpos
+        return None, _small_grad(dW, ctx.mg[0]), _small_grad(dpos, ctx.mg[1])
 
 
 def embedding(idx: torch.Tensor, weight: torch.Tensor, pos: Optional[torch.Tensor] = None):

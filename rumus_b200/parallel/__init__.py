@@ -1,0 +1,3 @@
+"""Parallelism strategies (reference: rumus/src/nn/{parallel,fsdp}.rs, rumus-distributed/)."""
+from .flat import FlatUnit, build_units, default_units
+from .fsdp import FSDP

@@ -1,0 +1,220 @@
+"""Fully sharded data parallel training over flat per-block arenas.
+
+Reference behaviour (rumus/src/nn/fsdp.rs:63-312, rumus/src/autograd/backward.rs:1101-1242):
+parameters are sharded across ranks, gathered around each linear layer's forward and backward,
+gradients are averaged across ranks and each rank keeps its slice, and an ordinary optimizer then
+updates the shards.  There every transfer goes through host memory and a mutex rendezvous.
+
+Here each sharding unit (embeddings, one transformer block, final norm + head) is one flat bf16
+vector (``flat.FlatUnit``).  Per step and unit:
+
+* backward writes gradients straight into the unit's flat gradient buffer;
+* when the unit's backward has finished (an autograd boundary node fires), the side stream runs
+  **reduce-scatter + sharded Adam** — in ``fused`` mode ONE kernel (``csrc/comm/rs_adam.cu``)
+  that reads this rank's slice of every peer's gradient buffer over NVLink, averages in fp32,
+  applies Adam(W) to the fp32 master shard and moments, and writes the bf16 shard in place;
+* the updated shards are **all-gathered** for the next forward — in ``fused`` mode by copy CTAs
+  that pull peer shards with plain P2P loads (stand-alone kernel, or folded into the unit's first
+  consuming GEMM, ``csrc/comm/ag_gemm.cu``).
+
+``nccl`` mode issues ``reduce_scatter_tensor`` / ``all_gather_into_tensor`` plus the fused flat
+Adam kernel: that is the comparison baseline.  With a world size of 1 no communication happens.
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..ops import native
+from .flat import FlatUnit, build_units, default_units
+
+
+class _Boundary(torch.autograd.Function):
+    """Identity in forward; in backward it tells the engine that every gradient of the unit whose
+    *input* this is has been produced."""
+
+    @staticmethod
+    def forward(ctx, x, engine, unit_idx):
+        ctx.engine, ctx.unit_idx = engine, unit_idx
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        ctx.engine._unit_backward_done(ctx.unit_idx)
+        return g, None, None
+
+
+class FSDP:
+    def __init__(self, model: nn.Module, lr: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999,
+                 eps: float = 1e-8, weight_decay: float = 0.0, adamw: bool = False,
+                 group: Optional[dist.ProcessGroup] = None, mode: Optional[str] = None,
+                 unit_roots: Optional[list] = None, arena=None):
+        self.model = model
+        self.lr, self.beta1, self.beta2, self.eps = lr, beta1, beta2, eps
+        self.weight_decay, self.adamw = weight_decay, adamw
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        mode = mode or os.environ.get("RB_BACKEND", "fused")
+        dev = next(model.parameters()).device
+        if self.world == 1:
+            mode = "local"
+        elif dev.type != "cuda":
+            mode = "cpu"   # gloo ranks: same schedule, collectives through torch.distributed
+        self.mode = mode
+        self.arena = arena
+        alloc = None
+        if mode == "fused":
+            from .symm import SymmArena
+            if self.arena is None:
+                need = sum(p.numel() for p in model.parameters()) * 2 * 2 * 1.05 + (64 << 20)
+                self.arena = SymmArena(int(need), group)
+            alloc = self.arena.alloc_flat
+        self.units: List[FlatUnit] = build_units(model, unit_roots or default_units(model),
+                                                 self.world, self.rank, alloc)
+        self.step_count = 0
+        self._pending: List[int] = []
+        self._cuda = dev.type == "cuda"
+        self.comm_stream = torch.cuda.Stream(device=dev) if self._cuda and self.world > 1 else None
+        self._unit_events = [None] * len(self.units)
+        self._install_boundaries()
+        if mode == "fused":
+            from .fused_fsdp import FusedFsdpComm
+            self.fused = FusedFsdpComm(self)
+        else:
+            self.fused = None
+
+    # ------------------------------------------------------------------ wiring
+    def _install_boundaries(self) -> None:
+        """Route the input of every block (and of the tail) through a boundary node."""
+        blocks = getattr(self.model, "blocks", None)
+        name_to_idx = {u.name: i for i, u in enumerate(self.units)}
+        engine = self
+        if blocks is not None:
+            for i, b in enumerate(blocks):
+                idx = name_to_idx.get(f"blocks.{i}")
+                if idx is None:
+                    continue
+                orig = b.forward
+
+                def fwd(x, *a, _orig=orig, _idx=idx, **kw):
+                    if torch.is_grad_enabled() and x.requires_grad:
+                        x = _Boundary.apply(x, engine, _idx)
+                    return _orig(x, *a, **kw)
+
+                b.forward = fwd
+        tail_idx = name_to_idx.get("tail")
+        ln_final = getattr(self.model, "ln_final", None)
+        if tail_idx is not None and ln_final is not None:
+            orig = ln_final.forward
+
+            def fwd_tail(x, *a, _orig=orig, **kw):
+                if torch.is_grad_enabled() and x.requires_grad:
+                    x = _Boundary.apply(x, engine, tail_idx)
+                return _orig(x, *a, **kw)
+
+            ln_final.forward = fwd_tail
+        self._hooked = {i for n, i in name_to_idx.items() if n.startswith("blocks.") or n == "tail"}
+
+    # ------------------------------------------------------------------ step protocol
+    def zero_grad(self) -> None:
+        for u in self.units:
+            u.begin_step()
+            for p in u.params:
+                p.grad = None
+        self._done = [False] * len(self.units)
+
+    def _unit_backward_done(self, idx: int) -> None:
+        if self._done[idx] or not self._cuda:
+            # CPU ranks get parameter gradients through plain autograd accumulation, which may
+            # run after this node: they finish every unit in step() instead.
+            return
+        self._done[idx] = True
+        self._reduce_and_update(idx)
+
+    def step(self) -> None:
+        """Call after ``loss.backward()``: finishes the units whose backward did not fire a
+        boundary (the embeddings) and makes the updated parameters visible to the next forward."""
+        for i in range(len(self.units) - 1, -1, -1):
+            if not self._done[i]:
+                self._done[i] = True
+                self._reduce_and_update(i)
+        if self.comm_stream is not None:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+        if self.fused is not None:
+            self.fused.end_step()
+        self.step_count += 1
+
+    # ------------------------------------------------------------------ per-unit work
+    def _adam_args(self):
+        return dict(lr=self.lr, beta1=self.beta1, beta2=self.beta2, eps=self.eps,
+                    weight_decay=self.weight_decay, step=self.step_count + 1, adamw=self.adamw)
+
+    def _reduce_and_update(self, idx: int) -> None:
+        u = self.units[idx]
+        u.collect_stray_grads()
+        if self.mode == "local":
+            if self._cuda:
+                native.adam_flat(u.flat_grad, u.master, u.exp_avg, u.exp_avg_sq, u.flat_param,
+                                 **self._adam_args())
+            else:
+                _adam_reference(u.flat_grad.float(), u, **self._adam_args())
+            return
+        if self.mode == "cpu":
+            shard = torch.empty(u.shard_numel, dtype=u.dtype)
+            dist.reduce_scatter_tensor(shard, u.flat_grad, op=dist.ReduceOp.SUM, group=self.group)
+            _adam_reference(shard.float() / self.world, u, **self._adam_args())
+            dist.all_gather_into_tensor(u.flat_param, u.param_shard().clone(), group=self.group)
+            return
+        cur = torch.cuda.current_stream()
+        self.comm_stream.wait_stream(cur)
+        with torch.cuda.stream(self.comm_stream):
+            if self.mode == "fused":
+                self.fused.reduce_scatter_adam(idx)
+                self.fused.all_gather(idx)
+            else:  # nccl baseline
+                shard = u.grad_shard()
+                dist.reduce_scatter_tensor(shard, u.flat_grad, op=dist.ReduceOp.AVG, group=self.group)
+                native.adam_flat(shard, u.master, u.exp_avg, u.exp_avg_sq, u.param_shard(),
+                                 **self._adam_args())
+                dist.all_gather_into_tensor(u.flat_param, u.param_shard(), group=self.group)
+
+    # ------------------------------------------------------------------ state
+    def set_lr(self, lr: float) -> None:
+        self.lr = lr
+
+    def get_lr(self) -> float:
+        return self.lr
+
+    def optimizer_state(self) -> dict:
+        """This rank's shard of the optimizer state (for ``optim-rank{r}.safetensors``)."""
+        out = {}
+        for u in self.units:
+            out[f"{u.name}.master"] = u.master
+            out[f"{u.name}.exp_avg"] = u.exp_avg
+            out[f"{u.name}.exp_avg_sq"] = u.exp_avg_sq
+        return out
+
+    def load_optimizer_state(self, sd: dict) -> None:
+        for u in self.units:
+            u.master.copy_(sd[f"{u.name}.master"])
+            u.exp_avg.copy_(sd[f"{u.name}.exp_avg"])
+            u.exp_avg_sq.copy_(sd[f"{u.name}.exp_avg_sq"])
+            u.param_shard().copy_(u.master)
+        if self.world > 1:
+            for u in self.units:
+                dist.all_gather_into_tensor(u.flat_param, u.param_shard().clone(), group=self.group)
+
+
+def _adam_reference(g32, u: FlatUnit, *, lr, beta1, beta2, eps, weight_decay, step, adamw):
+    m, v, w = u.exp_avg, u.exp_avg_sq, u.master
+    m.mul_(beta1).add_(g32, alpha=1 - beta1)
+    v.mul_(beta2).addcmul_(g32, g32, value=1 - beta2)
+    if adamw:
+        w.mul_(1 - lr * weight_decay)
+    w.sub_(lr * (m / (1 - beta1 ** step)) / ((v / (1 - beta2 ** step)).sqrt() + eps))
+    u.param_shard().copy_(w)
