@@ -34,6 +34,14 @@ int encode_tensor_map(CUtensorMap* out, int dtype, int rank, void* base, const u
                       const uint64_t* strides_bytes, const uint32_t* box, int swizzle_128b) {
   std::call_once(g_encode_once, load_encode);
   if (!g_encode) return -1;
+  // The driver entry point needs a current context on the calling thread.  Threads that have
+  // only been handed a device index (autograd worker threads) get the primary context bound by
+  // their first runtime call; make sure that has happened.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(0);
+    ctx_bound = true;
+  }
   CUtensorMapDataType dt = dtype == DT_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                            : dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                              : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
