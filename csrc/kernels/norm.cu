@@ -335,3 +335,73 @@ int rb_norm_bwd(int dtype, int rms, const void* x, const void* dy, const void* g
 #undef RB_CALL
 }
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the norm backward (declared in rumus_b200_noalloc.h)
+// ---------------------------------------------------------------------------
+#include <mutex>
+#include <stdio.h>
+
+#include "rumus_b200_noalloc.h"
+
+namespace {
+
+constexpr int kNoAllocMaxParts = RB_NORM_BWD_NOALLOC_MAX_PARTIALS;
+constexpr int kNoAllocMaxDim = RB_NORM_BWD_NOALLOC_MAX_DIM;
+
+// Scratch for the per-CTA (d_gamma, d_beta) partial rows: [parts, 2, D] floats, 2 MiB.
+// It lives in the library image, so every GPU that loads the library holds it until exit.
+static __device__ __align__(256) float g_norm_bwd_scratch[kNoAllocMaxParts * 2 * kNoAllocMaxDim];
+
+// In host code `g_norm_bwd_scratch` is only a host-side stand-in for the symbol; the device
+// address has to be looked up per device (with that device current) and cached.
+float* g_noalloc_scratch_addr[16] = {nullptr};
+std::mutex g_noalloc_mu;
+
+}  // namespace
+
+extern "C" int rb_norm_bwd_noalloc_max_dim() { return kNoAllocMaxDim; }
+
+extern "C" int rb_norm_bwd_noalloc(int dtype, int rms, const void* x, const void* dy,
+                                   const void* gamma, const float* stats, const void* dres,
+                                   void* dx, void* dgamma, void* dbeta, long long rows, int D,
+                                   void* stream) {
+  using namespace rb;
+  if (rows <= 0) return 0;
+  if (D <= 0 || D > kNoAllocMaxDim) {
+    fprintf(stderr,
+            "rb_norm_bwd_noalloc: row length %d is outside the built-in scratch (1..%d); use "
+            "rb_norm_bwd with caller-provided scratch instead\n",
+            D, kNoAllocMaxDim);
+    return RB_NOALLOC_ERR_TOO_LARGE;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return RB_NOALLOC_ERR_DEVICE;
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (!g_noalloc_scratch_addr[dev]) {
+      float* p = nullptr;
+      cudaError_t e = cudaGetSymbolAddress((void**)&p, g_norm_bwd_scratch);
+      if (e != cudaSuccess || p == nullptr) {
+        fprintf(stderr, "rb_norm_bwd_noalloc: cudaGetSymbolAddress failed: %s\n",
+                cudaGetErrorString(e));
+        return RB_NOALLOC_ERR_SYMBOL;
+      }
+      g_noalloc_scratch_addr[dev] = p;
+    }
+    scratch = g_noalloc_scratch_addr[dev];
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  int grid = norm_bwd_grid(rows);
+  if (grid > kNoAllocMaxParts) grid = kNoAllocMaxParts;
+#define RB_CALL(T)                                                                               \
+  (rms ? launch_norm_bwd<T, true>(x, dy, gamma, stats, dres, dx, dgamma, dbeta, scratch, grid,  \
+                                  rows, D, st)                                                   \
+       : launch_norm_bwd<T, false>(x, dy, gamma, stats, dres, dx, dgamma, dbeta, scratch, grid, \
+                                   rows, D, st))
+  if (dtype == rbh::DT_BF16) return RB_CALL(__nv_bfloat16);
+  if (dtype == rbh::DT_F16) return RB_CALL(__half);
+  return RB_CALL(float);
+#undef RB_CALL
+}
