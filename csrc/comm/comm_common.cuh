@@ -108,6 +108,22 @@ __device__ __forceinline__ void st_v4(void* p, uint4 v) {
                : "memory");
 }
 
+
+// Copy [lo, hi) bytes (multiples of 16) from peer memory to local memory with the whole CTA,
+// keeping eight 16-byte loads in flight per thread to cover the NVLink round trip.
+__device__ __forceinline__ void copy_range_16(char* dst, const char* src, long long lo, long long hi) {
+  const long long step = (long long)blockDim.x * 16;
+  long long o = lo + (long long)threadIdx.x * 16;
+  for (; o + 7 * step < hi; o += 8 * step) {
+    uint4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = ld_nc_v4(src + o + j * step);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) st_v4(dst + o + j * step, v[j]);
+  }
+  for (; o < hi; o += step) st_v4(dst + o, ld_nc_v4(src + o));
+}
+
 // NVLS: one load returns the sum over all ranks' copies (reduced inside the switch)
 __device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_ptr) {
   uint4 v;

@@ -1,0 +1,443 @@
+// Fused collective + GEMM kernels over the symmetric arena (NVLink P2P), built on the tcgen05
+// GEMM body (csrc/kernels/gemm_tcgen05.cuh):
+//
+//  * ag_gemm  — ALL-GATHER -> GEMM in one launch.  A few "copy" CTAs pull the peers' shards of
+//    the gathered operand into this GPU's own staging buffer with plain P2P loads and publish
+//    per-chunk ready flags; the GEMM CTAs (same kernel) start on tiles / K blocks whose operand
+//    bytes are local already and wait (bounded) on the flags of the rest.  All TMA loads read
+//    LOCAL memory, without multicast.  Two uses:
+//      - tensor-parallel column-parallel linear: the sequence-sharded activation A [M/T, K] of
+//        every rank is gathered along M (flags are checked per output row tile, tiles of this
+//        rank's own rows are scheduled first);
+//      - FSDP: the weight B [K, N] is a slab of the unit's flat parameter vector, gathered along
+//        K (flags are checked per K block, K blocks inside this rank's shard go first).
+//  * gemm_rs  — GEMM -> REDUCE-SCATTER in one launch (row-parallel linear).  GEMM CTAs write
+//    partial output tiles into the local staging buffer and signal the tile's owner rank; a few
+//    "reduce" CTAs on the owner wait for all ranks' signals, read the partial tiles from every
+//    peer over NVLink, add them in fp32 (plus optional bias / residual) and write the rank's
+//    [M/T, N] slab of the result.  Tiles owned by other ranks are computed first.
+//
+// Reference: RowParallelLinear copies the partial output to the host, averages (sic) under a
+// mutex and copies back (rumus-distributed/src/tensor_parallel.rs:69-84); ColumnParallelLinear
+// replicates the input (tensor_parallel.rs:30-36).
+#include "../kernels/gemm_launch.cuh"
+#include "comm_common.cuh"
+
+namespace rb {
+
+struct AgParamsTp {  // same fields as AgParams in fsdp_comm.cu (kept local to this TU)
+  PeerTable peers;
+  long long buf_off, shard_bytes, src_flags_off;
+  int* chunk_flags;
+  long long chunk_bytes;
+  int chunks_per_shard;
+  int epoch;
+  int* status;
+};
+
+__device__ __forceinline__ void ag_copy_role_tp(const AgParamsTp& p, int cta, int n_ctas) {
+  __shared__ int s_ok;
+  const PeerTable& pt = p.peers;
+  char* local = peer_ptr<char>(pt, pt.rank, p.buf_off);
+  for (int k = 1; k < pt.world; ++k) {
+    const int src = (pt.rank + k) % pt.world;
+    if (threadIdx.x == 0) {
+      bool ok = true;
+      if (p.src_flags_off >= 0)
+        ok = wait_flag_sys(peer_ptr<int>(pt, pt.rank, p.src_flags_off) + src, p.epoch, p.status,
+                           RB_ERR_TIMEOUT_FLAG);
+      s_ok = ok ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const char* remote = peer_ptr<char>(pt, src, p.buf_off) + (long long)src * p.shard_bytes;
+    char* dst = local + (long long)src * p.shard_bytes;
+    for (int c = cta; c < p.chunks_per_shard; c += n_ctas) {
+      const long long lo = (long long)c * p.chunk_bytes;
+      const long long hi = min(p.shard_bytes, lo + p.chunk_bytes);
+      copy_range_16(dst, remote, lo, hi);
+      __threadfence();
+      fence_proxy_async();
+      __syncthreads();
+      if (threadIdx.x == 0) st_release_gpu(p.chunk_flags + src * p.chunks_per_shard + c, p.epoch);
+    }
+    __syncthreads();
+  }
+}
+
+struct GatherHooks {
+  const int* chunk_flags;
+  long long shard_bytes, chunk_bytes;
+  int chunks_per_shard, epoch, rank, world;
+  int gather_a;         // 1: rows of A are gathered (checked per M tile); 0: rows of B (per K block)
+  long long row_bytes;  // bytes per gathered row (K*esz for A, N*esz for an N-major B)
+  long long base_off;   // bytes: first row of the operand inside the gathered buffer
+  int rows_per_step;    // 128 (A tile rows) or BK (B rows per K block)
+  int total_rows;       // M or K
+  int first_local_step; // tile / K block where this rank's own shard starts (rotation origin)
+  mutable unsigned long long ready[4];  // chunks already seen ready (<= 256 chunks)
+
+  __device__ __forceinline__ bool range_ready(long long lo, long long hi, volatile int* abort_flag,
+                                              int* status) const {
+    bool waited = false;
+    for (long long b = lo; b < hi;) {
+      const int src = (int)(b / shard_bytes);
+      const long long in_shard = b - (long long)src * shard_bytes;
+      const int c = (int)(in_shard / chunk_bytes);
+      const long long chunk_end = (long long)src * shard_bytes + min(shard_bytes, (long long)(c + 1) * chunk_bytes);
+      if (src != rank && src < world) {
+        const int idx = src * chunks_per_shard + c;
+        const unsigned long long bit = 1ull << (idx & 63);
+        if (!(ready[(idx >> 6) & 3] & bit)) {
+          if (!wait_flag_gpu(chunk_flags + idx, epoch, status, RB_ERR_TIMEOUT_FLAG, abort_flag))
+            return false;
+          ready[(idx >> 6) & 3] |= bit;
+          waited = true;
+        }
+      }
+      b = chunk_end;
+    }
+    if (waited) fence_proxy_async();
+    return true;
+  }
+
+  __device__ __forceinline__ bool before_tile_load(int m_idx, int n_idx, volatile int* abort_flag,
+                                                   int* status) const {
+    if (!gather_a) return true;
+    const long long r0 = (long long)m_idx * rows_per_step;
+    const long long r1 = min((long long)total_rows, r0 + rows_per_step);
+    return range_ready(base_off + r0 * row_bytes, base_off + r1 * row_bytes, abort_flag, status);
+  }
+  __device__ __forceinline__ bool before_k_load(int m_idx, int n_idx, int kb,
+                                                volatile int* abort_flag, int* status) const {
+    if (gather_a) return true;
+    const long long r0 = (long long)kb * rows_per_step;
+    const long long r1 = min((long long)total_rows, r0 + rows_per_step);
+    return range_ready(base_off + r0 * row_bytes, base_off + r1 * row_bytes, abort_flag, status);
+  }
+  __device__ __forceinline__ int map_kb(int kb, int num_kb) const {
+    if (gather_a) return kb;
+    int k = kb + first_local_step;
+    return k >= num_kb ? k - num_kb : k;
+  }
+  __device__ __forceinline__ void after_tile_store(int, int, int) const {}
+  static constexpr bool kCustomRaster = true;
+  __device__ __forceinline__ void raster(int tile, int num_m, int num_n, int& m_idx,
+                                         int& n_idx) const {
+    // grouped raster (8 row tiles per group), rotated so this rank's own rows come first
+    const int group_m = 8;
+    const int group_size = group_m * num_n;
+    const int g = tile / group_size;
+    const int first_m = g * group_m;
+    const int gm = min(num_m - first_m, group_m);
+    const int r = tile - g * group_size;
+    int m = first_m + r % gm;
+    n_idx = r / gm;
+    if (gather_a) {
+      m += first_local_step;
+      if (m >= num_m) m -= num_m;
+    }
+    m_idx = m;
+  }
+};
+
+template <typename T, int BN, bool B_MN>
+__global__ void __launch_bounds__(512, 1)
+    ag_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
+                   const __grid_constant__ CUtensorMap tma_b, const GemmParams gp,
+                   const AgParamsTp ap, GatherHooks hooks, int n_copy_ctas) {
+  extern __shared__ uint8_t smem_raw[];
+  if ((int)blockIdx.x < n_copy_ctas) {
+    ag_copy_role_tp(ap, blockIdx.x, n_copy_ctas);
+    return;
+  }
+  if (threadIdx.x >= 192) return;  // GEMM CTAs use 6 warps; the block size is sized for the copy role
+  hooks.ready[0] = hooks.ready[1] = hooks.ready[2] = hooks.ready[3] = 0ull;
+  gemm_cta_body<T, BN, false, B_MN, GatherHooks>(&tma_a, &tma_b, gp, hooks, smem_raw,
+                                                 blockIdx.x - n_copy_ctas, gridDim.x - n_copy_ctas);
+}
+
+// ---------------------------------------------------------------------------------------------
+struct RsHooks {
+  PeerTable peers;
+  long long tile_flags_off;  // bytes: int[tiles_per_owner][world] on every rank
+  int* tile_counters;        // local int[num_m * num_n], monotonically increasing
+  int epoch, num_n, m_tiles_per_rank;
+
+  __device__ __forceinline__ bool before_tile_load(int, int, volatile int*, int*) const { return true; }
+  __device__ __forceinline__ bool before_k_load(int, int, int, volatile int*, int*) const { return true; }
+  __device__ __forceinline__ int map_kb(int kb, int) const { return kb; }
+  __device__ __forceinline__ void after_tile_store(int m_idx, int n_idx, int quarter) const {
+    __threadfence_system();
+    const int prev = atomicAdd(tile_counters + m_idx * num_n + n_idx, 1);
+    if ((prev & 3) == 3) {
+      const int owner = m_idx / m_tiles_per_rank;
+      const int local_tile = (m_idx - owner * m_tiles_per_rank) * num_n + n_idx;
+      __threadfence_system();
+      st_release_sys(peer_ptr<int>(peers, owner, tile_flags_off) + local_tile * peers.world + peers.rank,
+                     epoch);
+    }
+  }
+  static constexpr bool kCustomRaster = true;
+  __device__ __forceinline__ void raster(int tile, int num_m, int num_n_, int& m_idx,
+                                         int& n_idx) const {
+    const int per_owner = m_tiles_per_rank * num_n_;
+    const int k = tile / per_owner;
+    const int owner = (peers.rank + 1 + k) % peers.world;  // own tiles last
+    const int local = tile - k * per_owner;
+    n_idx = local % num_n_;
+    m_idx = owner * m_tiles_per_rank + local / num_n_;
+  }
+};
+
+struct RsReduceParams {
+  PeerTable peers;
+  long long partial_off;   // bytes: [M, N] partial buffer of T in the arena
+  long long tile_flags_off;
+  void* out;               // [M/T, N] of T (local)
+  const void* bias;        // [N] or null
+  const void* residual;    // [M/T, N] or null
+  int M, N, BN, epoch, num_n, m_tiles_per_rank;
+  int* status;
+};
+
+template <typename T>
+__device__ __forceinline__ void rs_reduce_role(const RsReduceParams& p, int cta, int n_ctas) {
+  __shared__ int s_ok;
+  const PeerTable& pt = p.peers;
+  const int tiles = p.m_tiles_per_rank * p.num_n;
+  const int rows_per_rank = p.M / pt.world;
+  for (int t = cta; t < tiles; t += n_ctas) {
+    if (threadIdx.x == 0) {
+      bool ok = true;
+      const int* f = peer_ptr<int>(pt, pt.rank, p.tile_flags_off) + t * pt.world;
+      for (int r = 0; r < pt.world && ok; ++r)
+        ok = wait_flag_sys(f + r, p.epoch, p.status, RB_ERR_TIMEOUT_FLAG);
+      s_ok = ok ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const int m_local = (t / p.num_n) * 128;
+    const int n0 = (t % p.num_n) * p.BN;
+    const int ncols = min(p.BN, p.N - n0);
+    const int vec_per_row = ncols / 8;
+    const int nrows = min(128, rows_per_rank - m_local);
+    for (int i = threadIdx.x; i < nrows * vec_per_row; i += blockDim.x) {
+      const int r = i / vec_per_row;
+      const int c = n0 + (i - r * vec_per_row) * 8;
+      const long long grow = (long long)pt.rank * rows_per_rank + m_local + r;
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int k = 0; k < pt.world; ++k) {
+        const int src = (pt.rank + k) % pt.world;
+        uint4 raw = ld_nc_v4(peer_ptr<T>(pt, src, p.partial_off) + grow * p.N + c);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += to_f32<T>(e[j]);
+      }
+      if (p.bias) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += to_f32<T>(reinterpret_cast<const T*>(p.bias)[c + j]);
+      }
+      const long long orow = (long long)(m_local + r);
+      if (p.residual) {
+        uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.residual) + orow * p.N + c);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += to_f32<T>(e[j]);
+      }
+      uint4 o;
+      T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) oe[j] = from_f32<T>(acc[j]);
+      *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.out) + orow * p.N + c) = o;
+    }
+    __syncthreads();
+  }
+}
+
+template <typename T, int BN, bool B_MN>
+__global__ void __launch_bounds__(512, 1)
+    gemm_rs_kernel(const __grid_constant__ CUtensorMap tma_a,
+                   const __grid_constant__ CUtensorMap tma_b, const GemmParams gp,
+                   const RsHooks hooks, const RsReduceParams rp, int n_reduce_ctas) {
+  extern __shared__ uint8_t smem_raw[];
+  if ((int)blockIdx.x < n_reduce_ctas) {
+    rs_reduce_role<T>(rp, blockIdx.x, n_reduce_ctas);
+    return;
+  }
+  if (threadIdx.x >= 192) return;
+  gemm_cta_body<T, BN, false, B_MN, RsHooks>(&tma_a, &tma_b, gp, hooks, smem_raw,
+                                             blockIdx.x - n_reduce_ctas, gridDim.x - n_reduce_ctas);
+}
+
+static PeerTable make_table_tp(void* const* bases, int world, int rank) {
+  PeerTable t;
+  for (int i = 0; i < kMaxRanks; ++i) t.base[i] = i < world ? bases[i] : nullptr;
+  t.mc_base = nullptr;
+  t.world = world;
+  t.rank = rank;
+  return t;
+}
+
+template <typename T, bool B_MN>
+int launch_ag_gemm(const GemmArgs& a, const AgParamsTp& ap, const GatherHooks& h, int n_copy,
+                   int gemm_ctas) {
+  constexpr int BN = 256;
+  using C = GemmCfg<T, BN>;
+  CUtensorMap ta, tb;
+  int rc = make_gemm_tensor_maps<T, BN>(a, &ta, &tb);
+  if (rc) return 1000 + rc;
+  auto kern = ag_gemm_kernel<T, BN, B_MN>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  if (e != cudaSuccess) return 2000 + (int)e;
+  const int tiles = ((a.p.M + 127) / 128) * ((a.p.N + BN - 1) / BN);
+  if (gemm_ctas > tiles) gemm_ctas = tiles;
+  kern<<<n_copy + gemm_ctas, 512, C::SMEM_BYTES, a.stream>>>(ta, tb, a.p, ap, h, n_copy);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
+}
+
+template <typename T, bool B_MN>
+int launch_gemm_rs(const GemmArgs& a, const RsHooks& h, const RsReduceParams& rp, int n_red,
+                   int gemm_ctas) {
+  constexpr int BN = 256;
+  using C = GemmCfg<T, BN>;
+  CUtensorMap ta, tb;
+  int rc = make_gemm_tensor_maps<T, BN>(a, &ta, &tb);
+  if (rc) return 1000 + rc;
+  auto kern = gemm_rs_kernel<T, BN, B_MN>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  if (e != cudaSuccess) return 2000 + (int)e;
+  const int tiles = ((a.p.M + 127) / 128) * ((a.p.N + BN - 1) / BN);
+  if (gemm_ctas > tiles) gemm_ctas = tiles;
+  kern<<<n_red + gemm_ctas, 512, C::SMEM_BYTES, a.stream>>>(ta, tb, a.p, h, rp, n_red);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
+}
+
+}  // namespace rb
+
+extern "C" {
+
+// out[M,N] = A[M,K] . B[K,N] (+bias, activation, residual) where ONE operand lives in a gathered
+// staging buffer inside the arena (W shards of `shard_bytes`, this rank's shard already in place):
+//   gather_a = 1: A = staging + a_off (rows gathered along M);  B is a local pointer
+//   gather_a = 0: B = staging + b_off (N-major [K,N], rows gathered along K); A is a local pointer
+// b_mn: 1 = B stored [K,N], 0 = B stored [N,K].   src_flags_off < 0: peers' shards are known ready.
+int rb_ag_gemm(int dtype, void* const* bases, int world, int rank, long long buf_off,
+               long long shard_bytes, long long src_flags_off, int* chunk_flags,
+               long long chunk_bytes, int epoch, int gather_a, long long operand_off,
+               const void* other, long long ld_other, int b_mn, int M, int N, int K, void* out,
+               long long ldc, const void* bias, const void* residual, long long ldr, int act,
+               void* aux_out, int n_copy_ctas, void* stream) {
+  using namespace rb;
+  if (world > kMaxRanks || shard_bytes % 16 != 0) return 30;
+  const int esz = 2;
+  AgParamsTp ap;
+  ap.peers = make_table_tp(bases, world, rank);
+  ap.buf_off = buf_off; ap.shard_bytes = shard_bytes; ap.src_flags_off = src_flags_off;
+  ap.chunk_flags = chunk_flags;
+  ap.chunk_bytes = chunk_bytes;
+  ap.chunks_per_shard = (int)((shard_bytes + chunk_bytes - 1) / chunk_bytes);
+  if (ap.chunks_per_shard * world > 256) return 32;
+  ap.epoch = epoch;
+  ap.status = rbh::device_status_word();
+  char* staging = reinterpret_cast<char*>(bases[rank]) + buf_off;
+  GemmArgs a;
+  a.dtype = dtype; a.a_mn = 0; a.b_mn = b_mn;
+  if (gather_a) {
+    a.A = staging + operand_off; a.lda = K;
+    a.B = other; a.ldb = ld_other;
+  } else {
+    if (!b_mn) return 33;  // a K-gathered weight must be stored [K,N]
+    a.A = other; a.lda = ld_other;
+    a.B = staging + operand_off; a.ldb = N;
+  }
+  a.max_ctas = 0;
+  a.stream = (cudaStream_t)stream;
+  GemmParams& p = a.p;
+  p = GemmParams{};
+  p.M = M; p.N = N; p.K = K; p.out = out; p.ldc = ldc; p.bias = bias; p.residual = residual;
+  p.ldr = ldr; p.act = act; p.aux_out = aux_out; p.ldaux_out = N; p.alpha = 1.f;
+  p.status = ap.status; p.group_m = 8;
+  auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  p.vec_ok = al(out) && (ldc * esz) % 16 == 0 && (!residual || (al(residual) && (ldr * esz) % 16 == 0)) &&
+             (!aux_out || al(aux_out)) && (N * esz) % 16 == 0;
+  if (!al(a.A) || !al(a.B) || (a.lda * esz) % 16 || (a.ldb * esz) % 16) return 10;
+  GatherHooks h;
+  h.chunk_flags = chunk_flags; h.shard_bytes = shard_bytes; h.chunk_bytes = chunk_bytes;
+  h.chunks_per_shard = ap.chunks_per_shard; h.epoch = epoch; h.rank = rank; h.world = world;
+  h.gather_a = gather_a;
+  h.base_off = operand_off;
+  if (gather_a) {
+    h.row_bytes = (long long)K * esz; h.rows_per_step = 128; h.total_rows = M;
+  } else {
+    h.row_bytes = (long long)N * esz; h.rows_per_step = 64; h.total_rows = K;
+  }
+  {
+    // first tile / K block that lies completely inside this rank's shard
+    const long long step_bytes = h.row_bytes * h.rows_per_step;
+    long long lo = (long long)rank * shard_bytes - operand_off;
+    long long s = lo <= 0 ? 0 : (lo + step_bytes - 1) / step_bytes;
+    const int nsteps = (h.total_rows + h.rows_per_step - 1) / h.rows_per_step;
+    h.first_local_step = (int)(s >= nsteps ? 0 : s);
+  }
+  h.ready[0] = h.ready[1] = h.ready[2] = h.ready[3] = 0;
+  int ncopy = n_copy_ctas > 0 ? n_copy_ctas : 16;
+  if (world == 1) ncopy = 0;
+  const int gemm_ctas = rbh::sm_count() - ncopy;
+  if (dtype == rbh::DT_BF16)
+    return b_mn ? launch_ag_gemm<__nv_bfloat16, true>(a, ap, h, ncopy, gemm_ctas)
+                : launch_ag_gemm<__nv_bfloat16, false>(a, ap, h, ncopy, gemm_ctas);
+  if (dtype == rbh::DT_F16)
+    return b_mn ? launch_ag_gemm<__half, true>(a, ap, h, ncopy, gemm_ctas)
+                : launch_ag_gemm<__half, false>(a, ap, h, ncopy, gemm_ctas);
+  return 31;
+}
+
+// Row-parallel linear: out[M/W, N] (this rank's rows) = sum_r A_r[M, K_r] . B_r[K_r, N] (+bias, +residual).
+// partial_off: [M, N] staging buffer of the compute dtype in the arena (same offset on every rank);
+// tile_flags_off: int[(M/W/128) * ceil(N/256) * W] in the arena; tile_counters: local int[M/128 * ceil(N/256)].
+int rb_gemm_rs(int dtype, void* const* bases, int world, int rank, const void* A, long long lda,
+               const void* B, long long ldb, int b_mn, int M, int N, int K, long long partial_off,
+               long long tile_flags_off, int* tile_counters, int epoch, void* out,
+               const void* bias, const void* residual, int n_reduce_ctas, void* stream) {
+  using namespace rb;
+  if (world > kMaxRanks) return 30;
+  if (M % (128 * world) != 0 || N % 8 != 0) return 34;
+  const int esz = 2;
+  GemmArgs a;
+  a.dtype = dtype; a.a_mn = 0; a.b_mn = b_mn; a.A = A; a.lda = lda; a.B = B; a.ldb = ldb;
+  a.max_ctas = 0;
+  a.stream = (cudaStream_t)stream;
+  GemmParams& p = a.p;
+  p = GemmParams{};
+  p.M = M; p.N = N; p.K = K;
+  p.out = reinterpret_cast<char*>(bases[rank]) + partial_off;
+  p.ldc = N; p.alpha = 1.f; p.vec_ok = 1; p.group_m = 8;
+  p.status = rbh::device_status_word();
+  auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (!al(A) || !al(B) || (lda * esz) % 16 || (ldb * esz) % 16 || partial_off % 16) return 10;
+  RsHooks h;
+  h.peers = make_table_tp(bases, world, rank);
+  h.tile_flags_off = tile_flags_off; h.tile_counters = tile_counters; h.epoch = epoch;
+  h.num_n = (N + 255) / 256;
+  h.m_tiles_per_rank = M / world / 128;
+  RsReduceParams rp;
+  rp.peers = h.peers; rp.partial_off = partial_off; rp.tile_flags_off = tile_flags_off;
+  rp.out = out; rp.bias = bias; rp.residual = residual; rp.M = M; rp.N = N; rp.BN = 256;
+  rp.epoch = epoch; rp.num_n = h.num_n; rp.m_tiles_per_rank = h.m_tiles_per_rank;
+  rp.status = p.status;
+  int nred = n_reduce_ctas > 0 ? n_reduce_ctas : 16;
+  const int gemm_ctas = rbh::sm_count() - nred;
+  if (dtype == rbh::DT_BF16)
+    return b_mn ? launch_gemm_rs<__nv_bfloat16, true>(a, h, rp, nred, gemm_ctas)
+                : launch_gemm_rs<__nv_bfloat16, false>(a, h, rp, nred, gemm_ctas);
+  if (dtype == rbh::DT_F16)
+    return b_mn ? launch_gemm_rs<__half, true>(a, h, rp, nred, gemm_ctas)
+                : launch_gemm_rs<__half, false>(a, h, rp, nred, gemm_ctas);
+  return 31;
+}
+}

@@ -57,6 +57,8 @@ struct NoHooks {
                                                 volatile int* abort_flag, int* status) const {
     return true;
   }
+  // Order in which the K blocks of a tile are consumed (a permutation of 0..num_kb-1).
+  __device__ __forceinline__ int map_kb(int kb, int num_kb) const { return kb; }
   // Called by one lane of each epilogue warp after its 32 rows of a tile are stored.
   __device__ __forceinline__ void after_tile_store(int m_idx, int n_idx, int quarter) const {}
   // Maps a linear tile id of this CTA to (m_idx, n_idx); default = grouped raster.
@@ -79,6 +81,12 @@ struct GemmCfg {
   static constexpr int NUM_THREADS = 192;
   static constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
 };
+
+// Barrier over the 192 GEMM threads (warps 0..5).  The fused collective kernels launch wider
+// CTAs whose extra warps have a different role or have exited, so the count is explicit.
+__device__ __forceinline__ void cta_sync_192() {
+  asm volatile("bar.sync 0, 192;" ::: "memory");
+}
 
 template <typename T>
 __device__ __forceinline__ void issue_umma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc,
@@ -222,7 +230,7 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
     tmem_relinquish();
   }
   tc_fence_before();
-  __syncthreads();
+  cta_sync_192();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
@@ -256,7 +264,8 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
         int m_idx, n_idx;
         tile_coords(tile, m_idx, n_idx);
         ok = hooks.before_tile_load(m_idx, n_idx, abort_flag, p.status);
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
+        for (int kbi = 0; kbi < num_kb && ok; ++kbi) {
+          const int kb = hooks.map_kb(kbi, num_kb);
           ok = hooks.before_k_load(m_idx, n_idx, kb, abort_flag, p.status);
           if (!ok) break;
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status,
@@ -382,7 +391,7 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
 
   // ------------------------------ teardown ------------------------------------
   tc_fence_before();
-  __syncthreads();
+  cta_sync_192();
   if (warp_idx == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);

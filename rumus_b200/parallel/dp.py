@@ -1,0 +1,141 @@
+"""Data parallel training: one process per GPU, gradients all-reduced (mean) in buckets.
+
+Reference: ``DataParallel`` replicates a model across devices in one process, scatters the batch,
+gathers outputs on device 0 and re-broadcasts weights every step; ``AllReduceSync`` averages each
+gradient on the host (rumus/src/nn/parallel.rs:24-250).  Here every rank owns its replica and its
+data (SPMD); after backward the flat gradient bucket — which lives in the symmetric arena — is
+all-reduced by ONE kernel that also multiplies by ``1/(loss_scale * world)`` and raises a job-wide
+non-finite flag (``csrc/comm/fsdp_comm.cu: allreduce_unscale_kernel``); identical optimizer steps
+on identical gradients keep the replicas in sync without a broadcast.
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .flat import _round_up
+
+
+class GradBucket:
+    def __init__(self, params: List[nn.Parameter], world: int, alloc):
+        self.params = params
+        dtype = params[0].dtype
+        offs, off = [], 0
+        for p in params:
+            offs.append(off)
+            off += _round_up(p.numel(), 64)
+        self.numel = _round_up(off, 16 * world)
+        self.flat = alloc(self.numel, dtype)
+        self.offsets = offs
+        for p, o in zip(params, offs):
+            p.main_grad = self.flat[o:o + p.numel()].view(p.shape)
+            p.grad_accumulate = False
+
+    def begin_step(self):
+        for p in self.params:
+            p.grad_accumulate = False
+
+    def collect(self):
+        """Gradients that arrived through plain autograd are moved into the bucket and ``p.grad``
+        is re-pointed at the bucket view, so optimizers read reduced values."""
+        for p in self.params:
+            if p.grad is not None and p.grad.data_ptr() != p.main_grad.data_ptr():
+                if p.grad_accumulate:
+                    p.main_grad.add_(p.grad)
+                else:
+                    p.main_grad.copy_(p.grad)
+            p.grad = p.main_grad
+            p.grad_accumulate = True
+
+
+class DataParallel:
+    """``dp = DataParallel(model); loss.backward(); dp.all_reduce_grads(scaler)`` then step."""
+
+    def __init__(self, model: nn.Module, group: Optional[dist.ProcessGroup] = None,
+                 mode: Optional[str] = None, bucket_mb: int = 256, arena=None):
+        self.model = model
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        params = [p for p in model.parameters() if p.requires_grad]
+        dev = params[0].device
+        mode = mode or os.environ.get("RB_BACKEND", "fused")
+        if self.world == 1:
+            mode = "local"
+        elif dev.type != "cuda":
+            mode = "cpu"
+        self.mode = mode
+        self.arena = arena
+        if mode == "fused":
+            from .symm import SymmArena
+            if self.arena is None:
+                need = sum(p.numel() * p.element_size() for p in params) * 1.1 + (16 << 20)
+                self.arena = SymmArena(int(need), group)
+            alloc = lambda n, dt: self.arena.alloc_flat(n, dt)
+        else:
+            alloc = lambda n, dt: torch.zeros(n, dtype=dt, device=dev)
+        # bucket by dtype and size
+        self.buckets: List[GradBucket] = []
+        by_dtype = {}
+        for p in params:
+            by_dtype.setdefault(p.dtype, []).append(p)
+        limit = bucket_mb << 20
+        for dt, ps in by_dtype.items():
+            cur, cur_bytes = [], 0
+            for p in ps:
+                cur.append(p)
+                cur_bytes += p.numel() * p.element_size()
+                if cur_bytes >= limit:
+                    self.buckets.append(GradBucket(cur, self.world, alloc))
+                    cur, cur_bytes = [], 0
+            if cur:
+                self.buckets.append(GradBucket(cur, self.world, alloc))
+        self.epoch = 0
+        self.found_inf = torch.zeros(1, dtype=torch.int32, device=dev)
+        if mode == "fused":
+            a = self.arena
+            self._flags = [(a.alloc_flags(self.world), a.alloc_flags(self.world), a.alloc_flags(self.world))
+                           for _ in self.buckets]
+            self._counters = [a.alloc_local_ints(1) for _ in self.buckets]
+            a.barrier()
+        if self.world > 1:
+            self.broadcast_weights()
+
+    def broadcast_weights(self) -> None:
+        """One-time sync of the replicas (reference: parallel.rs:113-123 does this every step)."""
+        for t in list(self.model.parameters()) + list(self.model.buffers()):
+            dist.broadcast(t.data, src=dist.get_global_rank(self.group, 0) if self.group else 0,
+                           group=self.group)
+
+    def zero_grad(self) -> None:
+        for b in self.buckets:
+            b.begin_step()
+        for p in self.model.parameters():
+            p.grad = None
+
+    def all_reduce_grads(self, inv_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Mean all-reduce of every bucket, fused with the unscale by ``inv_scale`` (device scalar,
+        ``1/loss_scale``).  Returns the job-wide non-finite flag (int32 device tensor)."""
+        self.epoch += 1
+        self.found_inf.zero_()
+        for i, b in enumerate(self.buckets):
+            b.collect()
+            if self.mode == "fused":
+                from . import fused_ops
+                ef, xf, nf = self._flags[i]
+                fused_ops.allreduce_unscale(self.arena, b.flat, enter_flags_off=ef, exit_flags_off=xf,
+                                            inf_flags_off=nf, epoch=self.epoch, inv_scale=inv_scale,
+                                            extra_scale=1.0 / self.world, found_inf=self.found_inf,
+                                            done_counter=self._counters[i])
+            else:
+                if self.world > 1:
+                    dist.all_reduce(b.flat, op=dist.ReduceOp.SUM, group=self.group)
+                s = (float(inv_scale.item()) if inv_scale is not None else 1.0) / self.world
+                b.flat.mul_(s)
+                if not torch.isfinite(b.flat).all():
+                    self.found_inf.fill_(1)
+        return self.found_inf

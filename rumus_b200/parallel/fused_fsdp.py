@@ -1,0 +1,50 @@
+"""Fused-kernel communication for the FSDP engine (see ``fsdp.py`` for the step protocol).
+
+Per sharding unit there are two epoch-flag arrays in the arena (``grad_ready[world]``,
+``param_ready[world]``) and one local completion counter.  At optimizer step ``t`` (1-based):
+
+* ``reduce_scatter_adam(u)`` launches ``rb_rs_adam`` with epoch ``t``: it announces this rank's
+  gradients, waits for every peer's announcement, reduces + updates + rewrites the parameter
+  shard, then announces ``param_ready = t``;
+* ``all_gather(u)`` launches ``rb_all_gather`` with epoch ``t``: per peer it waits for
+  ``param_ready >= t`` and pulls that peer's shard.
+
+Write-after-read safety of the gradient buffers needs no extra barrier: a rank only starts
+writing unit ``u``'s gradients for step ``t+1`` after its own all-gather of ``u`` at step ``t``
+returned, and that returned only after every peer had published ``param_ready = t``, which each
+peer does after it finished reading everybody's gradients of step ``t``.
+"""
+from __future__ import annotations
+
+from . import fused_ops
+
+
+class FusedFsdpComm:
+    def __init__(self, engine):
+        self.e = engine
+        a = engine.arena
+        self.arena = a
+        self.grad_flags = [a.alloc_flags(a.world) for _ in engine.units]
+        self.param_flags = [a.alloc_flags(a.world) for _ in engine.units]
+        self.counters = [a.alloc_local_ints(1) for _ in engine.units]
+        for u in engine.units:
+            assert hasattr(u.flat_param, "arena_offset") and hasattr(u.flat_grad, "arena_offset")
+        a.barrier()
+
+    def reduce_scatter_adam(self, idx: int) -> None:
+        e, u = self.e, self.e.units[idx]
+        fused_ops.rs_adam(self.arena, u.dtype, u.flat_grad.arena_offset, u.flat_param.arena_offset,
+                          u.shard_range[0], u.shard_numel, u.master, u.exp_avg, u.exp_avg_sq,
+                          lr=e.lr, beta1=e.beta1, beta2=e.beta2, eps=e.eps,
+                          weight_decay=e.weight_decay, step=e.step_count + 1, adamw=e.adamw,
+                          grad_flags_off=self.grad_flags[idx], param_flags_off=self.param_flags[idx],
+                          epoch=e.step_count + 1, done_counter=self.counters[idx])
+
+    def all_gather(self, idx: int) -> None:
+        e, u = self.e, self.e.units[idx]
+        esz = u.flat_param.element_size()
+        fused_ops.all_gather(self.arena, u.flat_param.arena_offset, u.shard_numel * esz,
+                             src_flags_off=self.param_flags[idx], epoch=e.step_count + 1)
+
+    def end_step(self) -> None:
+        pass

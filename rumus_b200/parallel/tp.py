@@ -1,0 +1,297 @@
+"""Tensor parallelism with sequence-parallel activations.
+
+Reference: ``ColumnParallelLinear`` (weight ``[K, N/T]``, replicated input, explicit
+``allreduce_grad_x``) and ``RowParallelLinear`` (weight ``[K/T, N]``, partial outputs averaged —
+which is wrong for partial sums — bias on rank 0) in rumus-distributed/src/tensor_parallel.rs:20-86,
+all staged through the host.
+
+Here the activations between a row-parallel output and the next column-parallel input are
+sharded along the token dimension (``[M/T, d]`` per rank), so:
+
+* column-parallel forward  = ALL-GATHER(tokens) -> GEMM          (fused kernel ``rb_ag_gemm``)
+* row-parallel forward     = GEMM -> REDUCE-SCATTER(tokens, SUM) (fused kernel ``rb_gemm_rs``)
+* column-parallel backward = dgrad GEMM -> REDUCE-SCATTER, wgrad on the gathered input
+* row-parallel backward    = ALL-GATHER(dY) -> dgrad GEMM, wgrad on the gathered dY
+
+``mode='nccl'`` runs the same layers with NCCL collectives + separate GEMMs (baseline);
+CPU tensors use ``torch.distributed`` (gloo) and PyTorch math, which is how the sharding logic is
+tested without GPUs.
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..nn.modules import Module, _linear_rng, _uniform
+from ..ops import functional as F
+from ..ops import native
+
+
+class TPContext:
+    """Process group + (for fused mode) arena staging shared by all TP layers of a model."""
+
+    def __init__(self, group: Optional[dist.ProcessGroup] = None, mode: Optional[str] = None,
+                 arena=None, max_tokens: int = 0, max_features: int = 0, dtype=torch.bfloat16):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        mode = mode or os.environ.get("RB_BACKEND", "fused")
+        if self.world == 1:
+            mode = "local"
+        self.mode = mode
+        self.arena = arena
+        self.epoch = 0
+        self.dtype = dtype
+        if mode == "fused":
+            from .symm import SymmArena
+            esz = torch.empty((), dtype=dtype).element_size()
+            stage_bytes = max_tokens * max_features * esz
+            if self.arena is None:
+                self.arena = SymmArena(2 * stage_bytes + (64 << 20), group)
+            a = self.arena
+            self.gather_buf, self.gather_off = a.alloc_bytes(stage_bytes)
+            self.partial_buf, self.partial_off = a.alloc_bytes(stage_bytes)
+            self.chunk_flags = a.alloc_local_ints(256)
+            n_tiles = (max_tokens // 128 + 1) * (max_features // 256 + 1)
+            self.tile_flags_off = a.alloc_flags(n_tiles * self.world)
+            self.tile_counters = a.alloc_local_ints(n_tiles)
+            self.enter_flags = a.alloc_flags(self.world)
+            self.stage_bytes = stage_bytes
+            a.barrier()
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    # ------------------------------------------------------------ collectives (baseline paths)
+    def all_gather_rows(self, x_local: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return x_local
+        out = torch.empty((x_local.shape[0] * self.world, *x_local.shape[1:]), dtype=x_local.dtype,
+                          device=x_local.device)
+        dist.all_gather_into_tensor(out, x_local.contiguous(), group=self.group)
+        return out
+
+    def reduce_scatter_rows(self, x_full: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return x_full
+        out = torch.empty((x_full.shape[0] // self.world, *x_full.shape[1:]), dtype=x_full.dtype,
+                          device=x_full.device)
+        dist.reduce_scatter_tensor(out, x_full.contiguous(), op=dist.ReduceOp.SUM, group=self.group)
+        return out
+
+    def all_reduce(self, x: torch.Tensor, op=dist.ReduceOp.SUM) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_reduce(x, op=op, group=self.group)
+        return x
+
+
+def _mm(a, b):
+    return native.gemm(a, b) if a.is_cuda else a @ b
+
+
+def _fused_ag_gemm(ctx: TPContext, x_local, w, bias=None, act=None):
+    """x_local [M/T, K] (each rank's rows) , w [K, N] logical -> (y [M, N], gathered x [M, K])."""
+    from . import fused_ops
+    a = ctx.arena
+    Ml, K = x_local.shape
+    M = Ml * ctx.world
+    N = w.shape[1]
+    esz = x_local.element_size()
+    shard_bytes = Ml * K * esz
+    assert shard_bytes * ctx.world <= ctx.stage_bytes and shard_bytes % 16 == 0
+    # entry barrier on the staging buffer is implied by the epoch protocol: a peer may only read
+    # my shard after I announced it (src flag) and I only overwrite it after everybody consumed the
+    # previous contents, which the reduce/gather pairing of the layer sequence guarantees;
+    # a host-side group barrier guards the first use.
+    stage = ctx.gather_buf[: shard_bytes * ctx.world].view(x_local.dtype).view(M, K)
+    stage[ctx.rank * Ml:(ctx.rank + 1) * Ml].copy_(x_local)
+    epoch = ctx.next_epoch()
+    _announce(ctx, epoch)
+    chunk = max(1 << 20, (shard_bytes * ctx.world + 255) // 256)
+    chunk = (chunk + 15) // 16 * 16
+    out = torch.empty((M, N), dtype=x_local.dtype, device=x_local.device)
+    fused_ops.ag_gemm(a, buf_off=ctx.gather_off, shard_bytes=shard_bytes, chunk_flags=ctx.chunk_flags,
+                      chunk_bytes=chunk, epoch=epoch, gather_a=True, operand_off=0, other=w, M=M,
+                      N=N, K=K, out=out, src_flags_off=ctx.enter_flags, bias=bias, act=act)
+    return out, stage
+
+
+def _announce(ctx: TPContext, epoch: int) -> None:
+    """Publish 'my shard of the staging buffer holds epoch `epoch`' to every peer (stream ordered)."""
+    from . import fused_ops
+    fused_ops.signal_peers(ctx.arena, ctx.enter_flags, epoch)
+
+
+def _fused_gemm_rs(ctx: TPContext, a_mat, w, bias=None):
+    """a_mat [M, K_local], w [K_local, N] -> y_local [M/T, N] (sum over ranks)."""
+    from . import fused_ops
+    M, K = a_mat.shape
+    N = w.shape[1]
+    out = torch.empty((M // ctx.world, N), dtype=a_mat.dtype, device=a_mat.device)
+    epoch = ctx.next_epoch()
+    fused_ops.gemm_rs(ctx.arena, a_mat, w, partial_off=ctx.partial_off,
+                      tile_flags_off=ctx.tile_flags_off, tile_counters=ctx.tile_counters, epoch=epoch,
+                      out=out, bias=bias)
+    return out
+
+
+class _ColumnParallelFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_local, w, bias, tp: TPContext, act):
+        if tp.mode == "fused" and x_local.is_cuda and _fusable(tp, x_local.shape[0] * tp.world):
+            y, x_full = _fused_ag_gemm(tp, x_local, w, bias, act=None)
+            x_full = x_full.clone()
+        else:
+            x_full = tp.all_gather_rows(x_local)
+            y = _mm(x_full, w)
+            if bias is not None:
+                y = y + bias
+        ctx.tp = tp
+        ctx.has_bias = bias is not None
+        ctx.w_mg = F._main_grad(w)
+        ctx.save_for_backward(x_full, w)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_full, w = ctx.saved_tensors
+        tp = ctx.tp
+        dy = dy.contiguous()
+        if tp.mode == "fused" and dy.is_cuda and _fusable(tp, dy.shape[0]):
+            dx_local = _fused_gemm_rs(tp, dy, w.t())
+        else:
+            dx_local = tp.reduce_scatter_rows(_mm(dy, w.t()))
+        dw = F._wgrad(x_full, dy, ctx.w_mg) if dy.is_cuda else x_full.t() @ dy
+        db = None
+        if ctx.has_bias:
+            db = native.colsum(dy) if dy.is_cuda else dy.sum(0)
+        return dx_local, dw, db, None, None
+
+
+class _RowParallelFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, tp: TPContext):
+        if tp.mode == "fused" and x.is_cuda and _fusable(tp, x.shape[0]):
+            y_local = _fused_gemm_rs(tp, x, w, bias)
+        else:
+            y_local = tp.reduce_scatter_rows(_mm(x, w))
+            if bias is not None:
+                y_local = y_local + bias
+        ctx.tp = tp
+        ctx.has_bias = bias is not None
+        ctx.w_mg = F._main_grad(w)
+        ctx.save_for_backward(x, w)
+        return y_local
+
+    @staticmethod
+    def backward(ctx, dy_local):
+        x, w = ctx.saved_tensors
+        tp = ctx.tp
+        dy_local = dy_local.contiguous()
+        if tp.mode == "fused" and dy_local.is_cuda and _fusable(tp, dy_local.shape[0] * tp.world):
+            dx, dy_full = _fused_ag_gemm(tp, dy_local, w.t())
+        else:
+            dy_full = tp.all_gather_rows(dy_local)
+            dx = _mm(dy_full, w.t())
+        dw = F._wgrad(x, dy_full, ctx.w_mg) if x.is_cuda else x.t() @ dy_full
+        db = None
+        if ctx.has_bias:
+            db = native.colsum(dy_local) if dy_local.is_cuda else dy_local.sum(0)
+        return dx, dw, db, None
+
+
+def _fusable(tp: TPContext, M: int) -> bool:
+    return M % (128 * tp.world) == 0
+
+
+class ColumnParallelLinear(Module):
+    """Weight ``[in, out/T]`` (this rank's output columns).  Input: token-sharded ``[M/T, in]``;
+    output ``[M, out/T]``."""
+
+    def __init__(self, in_features: int, out_features: int, tp: TPContext, bias: bool = True,
+                 device=None, dtype=None):
+        super().__init__()
+        assert out_features % tp.world == 0
+        self.tp = tp
+        self.in_features, self.out_features = in_features, out_features
+        bound = math.sqrt(1.0 / in_features)
+        full = _uniform((in_features, out_features), bound, _linear_rng, device, dtype)
+        n = out_features // tp.world
+        self.weight = nn.Parameter(full[:, tp.rank * n:(tp.rank + 1) * n].contiguous())
+        self.bias = None
+        if bias:
+            fb = _uniform((out_features,), bound, _linear_rng, device, dtype)
+            self.bias = nn.Parameter(fb[tp.rank * n:(tp.rank + 1) * n].contiguous())
+
+    def forward(self, x_local):
+        if self.tp.world == 1:
+            return F.linear(x_local, self.weight, self.bias)
+        return _ColumnParallelFn.apply(x_local, self.weight, self.bias, self.tp, None)
+
+
+class RowParallelLinear(Module):
+    """Weight ``[in/T, out]`` (this rank's input rows).  Input ``[M, in/T]``; output token-sharded
+    ``[M/T, out]``, summed over ranks; the bias is added once (by the reducing owner)."""
+
+    def __init__(self, in_features: int, out_features: int, tp: TPContext, bias: bool = True,
+                 device=None, dtype=None):
+        super().__init__()
+        assert in_features % tp.world == 0
+        self.tp = tp
+        self.in_features, self.out_features = in_features, out_features
+        bound = math.sqrt(1.0 / in_features)
+        full = _uniform((in_features, out_features), bound, _linear_rng, device, dtype)
+        k = in_features // tp.world
+        self.weight = nn.Parameter(full[tp.rank * k:(tp.rank + 1) * k].contiguous())
+        self.bias = nn.Parameter(_uniform((out_features,), bound, _linear_rng, device, dtype)) if bias else None
+
+    def forward(self, x):
+        if self.tp.world == 1:
+            return F.linear(x, self.weight, self.bias)
+        return _RowParallelFn.apply(x, self.weight, self.bias, self.tp)
+
+
+def scatter_rows(x: torch.Tensor, tp: TPContext) -> torch.Tensor:
+    """Take this rank's token slab of a replicated ``[M, d]`` tensor (entering a sequence-parallel
+    region); its backward all-gathers the gradient."""
+    if tp.world == 1:
+        return x
+    return _ScatterRowsFn.apply(x, tp)
+
+
+def gather_rows(x_local: torch.Tensor, tp: TPContext) -> torch.Tensor:
+    if tp.world == 1:
+        return x_local
+    return _GatherRowsFn.apply(x_local, tp)
+
+
+class _ScatterRowsFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        n = x.shape[0] // tp.world
+        return x[tp.rank * n:(tp.rank + 1) * n].contiguous()
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.tp.all_gather_rows(g.contiguous()), None
+
+
+class _GatherRowsFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_local, tp):
+        ctx.tp = tp
+        return tp.all_gather_rows(x_local)
+
+    @staticmethod
+    def backward(ctx, g):
+        n = g.shape[0] // ctx.tp.world
+        # every rank computed the same loss contribution pattern downstream: the gradient of a
+        # gather is the local slab of the (summed) upstream gradient
+        return ctx.tp.reduce_scatter_rows(g.contiguous()), None
