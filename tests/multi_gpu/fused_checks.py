@@ -150,7 +150,7 @@ def main():
     xa = (torch.randn(Mb, Kb, device=dev) * 0.5).bfloat16()
     wref = flat_ref[pad:pad + Kb * Nb].view(Kb, Nb)
     arena.barrier()
-    fused_ops.signal_peers(arena, bflags, 1)
+    fused_ops.signal_peers(arena, bflags, 3)
     outb = torch.empty(Mb, Nb, device=dev, dtype=torch.bfloat16)
     fused_ops.ag_gemm(arena, buf_off=flat_off, shard_bytes=Sb * 2, chunk_flags=chunk_flags,
                       chunk_bytes=32 * 1024, epoch=3, gather_a=False, operand_off=pad * 2, other=xa,
