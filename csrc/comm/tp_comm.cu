@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(512, 1)
     ag_copy_role_tp(ap, blockIdx.x, n_copy_ctas);
     return;
   }
-  if (threadIdx.x >= 192) return;  // GEMM CTAs use 6 warps; the block size is sized for the copy role
+  if (threadIdx.x >= kGemmThreads) return;  // GEMM CTAs use 10 warps; the block is sized for the copy role
   hooks.ready[0] = hooks.ready[1] = hooks.ready[2] = hooks.ready[3] = 0ull;
   gemm_cta_body<T, BN, false, B_MN, GatherHooks>(&tma_a, &tma_b, gp, hooks, smem_raw,
                                                  blockIdx.x - n_copy_ctas, gridDim.x - n_copy_ctas);
@@ -170,7 +170,7 @@ struct RsHooks {
   __device__ __forceinline__ void after_tile_store(int m_idx, int n_idx, int quarter) const {
     __threadfence_system();
     const int prev = atomicAdd(tile_counters + m_idx * num_n + n_idx, 1);
-    if ((prev & 3) == 3) {
+    if ((prev % kGemmEpiWarps) == kGemmEpiWarps - 1) {
       const int owner = m_idx / m_tiles_per_rank;
       const int local_tile = (m_idx - owner * m_tiles_per_rank) * num_n + n_idx;
       __threadfence_system();
@@ -267,7 +267,7 @@ __global__ void __launch_bounds__(512, 1)
     rs_reduce_role<T>(rp, blockIdx.x, n_reduce_ctas);
     return;
   }
-  if (threadIdx.x >= 192) return;
+  if (threadIdx.x >= kGemmThreads) return;
   gemm_cta_body<T, BN, false, B_MN, RsHooks>(&tma_a, &tma_b, gp, hooks, smem_raw,
                                              blockIdx.x - n_reduce_ctas, gridDim.x - n_reduce_ctas);
 }

@@ -215,6 +215,41 @@ __global__ void colsum_partial_kernel(const T* __restrict__ x, float* __restrict
   for (long long r = r0; r < r1; ++r) acc += to_f32<T>(x[r * ld + c]);
   partials[(long long)blockIdx.y * N + c] = acc;
 }
+// vector variant: each thread owns VEC consecutive columns (16-byte loads), 4 rows in flight
+template <typename T>
+__global__ void __launch_bounds__(128)
+    colsum_partial_vec_kernel(const T* __restrict__ x, float* __restrict__ partials, long long rows,
+                              int N, long long ld, int rows_per_slab) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+  if (c >= N) return;
+  const long long r0 = (long long)blockIdx.y * rows_per_slab;
+  const long long r1 = min(rows, r0 + rows_per_slab);
+  float acc[VEC];
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+  long long r = r0;
+  for (; r + 4 <= r1; r += 4) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const uint4*>(x + (r + u) * ld + c);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const T* e = reinterpret_cast<const T*>(&v[u]);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) acc[j] += to_f32<T>(e[j]);
+    }
+  }
+  for (; r < r1; ++r) {
+    uint4 v = *reinterpret_cast<const uint4*>(x + r * ld + c);
+    const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc[j] += to_f32<T>(e[j]);
+  }
+  float* out = partials + (long long)blockIdx.y * N + c;
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) out[j] = acc[j];
+}
 template <typename T>
 __global__ void colsum_final_kernel(const float* __restrict__ partials, int slabs, int N,
                                     T* __restrict__ out) {
@@ -351,8 +386,8 @@ int rb_rope(int dtype, void* x, const long long* pos_ids, long long tokens, int 
 }
 // number of row slabs rb_colsum uses; scratch needed = slabs * N floats
 int rb_colsum_slabs(long long rows) {
-  long long s = (rows + 255) / 256;
-  if (s > 1024) s = 1024;
+  long long s = (rows + 63) / 64;
+  if (s > 512) s = 512;
   if (s < 1) s = 1;
   return (int)s;
 }
@@ -363,8 +398,16 @@ int rb_colsum(int dtype, const void* x, void* out, float* scratch, long long row
   cudaStream_t st = (cudaStream_t)stream;
   const int slabs = rb_colsum_slabs(rows);
   const int rps = (int)((rows + slabs - 1) / slabs);
-  dim3 grid((N + 127) / 128, slabs);
-  RB_DISPATCH_T(dtype, (colsum_partial_kernel<T><<<grid, 128, 0, st>>>((const T*)x, scratch, rows, N, ld, rps)));
+  const int esz = dtype == rbh::DT_F32 ? 4 : 2;
+  const int vec = 16 / esz;
+  const bool vec_ok = (N % vec == 0) && ((ld * esz) % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+  if (vec_ok) {
+    dim3 grid((N / vec + 127) / 128, slabs);
+    RB_DISPATCH_T(dtype, (colsum_partial_vec_kernel<T><<<grid, 128, 0, st>>>((const T*)x, scratch, rows, N, ld, rps)));
+  } else {
+    dim3 grid((N + 127) / 128, slabs);
+    RB_DISPATCH_T(dtype, (colsum_partial_kernel<T><<<grid, 128, 0, st>>>((const T*)x, scratch, rows, N, ld, rps)));
+  }
   RB_DISPATCH_T(dtype, (colsum_final_kernel<T><<<(N + 127) / 128, 128, 0, st>>>(scratch, slabs, N, (T*)out)));
   RB_RET_LAST();
 }

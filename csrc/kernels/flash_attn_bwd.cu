@@ -276,7 +276,7 @@ __global__ void __launch_bounds__(192, 1)
           const int qi = c * 32 + i;
           const int q = q0 + qi;
           const bool valid = kv_ok && q < p.Sq && (!p.causal || kv <= q + off);
-          const float v = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, -sLse[buf * 64 + qi]));
+          const float v = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -sLse[buf * 64 + qi]));
           pr[qi] = valid ? v : 0.f;
         }
       }
@@ -285,10 +285,8 @@ __global__ void __launch_bounds__(192, 1)
         uint8_t* rowp = sPT + t * 128;
 #pragma unroll
         for (int cc = 0; cc < 8; ++cc) {
-          uint4 v;
-          T* e = reinterpret_cast<T*>(&v);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(pr[cc * 8 + i]);
+          const uint4 v = make_uint4(pack2<T>(pr[cc * 8], pr[cc * 8 + 1]), pack2<T>(pr[cc * 8 + 2], pr[cc * 8 + 3]),
+                                     pack2<T>(pr[cc * 8 + 4], pr[cc * 8 + 5]), pack2<T>(pr[cc * 8 + 6], pr[cc * 8 + 7]));
           *reinterpret_cast<uint4*>(rowp + ((cc ^ (t & 7)) << 4)) = v;
         }
       }
@@ -311,10 +309,8 @@ __global__ void __launch_bounds__(192, 1)
         uint8_t* rowp = sdST + t * 128;
 #pragma unroll
         for (int cc = 0; cc < 8; ++cc) {
-          uint4 v;
-          T* e = reinterpret_cast<T*>(&v);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(pr[cc * 8 + i]);
+          const uint4 v = make_uint4(pack2<T>(pr[cc * 8], pr[cc * 8 + 1]), pack2<T>(pr[cc * 8 + 2], pr[cc * 8 + 3]),
+                                     pack2<T>(pr[cc * 8 + 4], pr[cc * 8 + 5]), pack2<T>(pr[cc * 8 + 6], pr[cc * 8 + 7]));
           *reinterpret_cast<uint4*>(rowp + ((cc ^ (t & 7)) << 4)) = v;
         }
       }

@@ -197,21 +197,26 @@ __global__ void __launch_bounds__(192, 1)
       const int kv0 = j * C::BN;
       const bool need_mask = (kv0 + C::BN > p.Sk) || (p.causal && kv0 + C::BN - 1 > q0 + off);
       const int kv_limit = p.causal ? min(p.Sk - 1, row + off) : p.Sk - 1;  // last valid kv index
-      // pass 1: row max
+      // Load the whole S row (4 x 32 columns) once; exponentials are first computed against the
+      // running maximum already in use (m_used).  Only when this tile raises the row maximum by
+      // more than 2^8 (always on the first tile, rarely afterwards) the row is recomputed
+      // against the new maximum and O / l are rescaled.
+      uint32_t sreg[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(s_addr + c * 32, sreg[c]);
+      tmem_ld_wait();
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(s_addr + c * 32, r);
-        tmem_ld_wait();
-        if (need_mask) {
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (kv0 + c * 32 + i <= kv_limit) mx = fmaxf(mx, __uint_as_float(r[i]));
-        } else {
+            if (kv0 + c * 32 + i <= kv_limit) mx = fmaxf(mx, __uint_as_float(sreg[c][i]));
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-        }
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sreg[c][i]));
       }
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       const bool need = m_new > m_used + 8.0f;  // also true on the first tile (m_used = -inf)
@@ -224,7 +229,7 @@ __global__ void __launch_bounds__(192, 1)
       if (__any_sync(0xffffffffu, need)) {
         float alpha = 1.0f;
         if (need) {
-          alpha = (m_used == -INFINITY) ? 0.0f : exp2f(m_used - m_new);
+          alpha = (m_used == -INFINITY) ? 0.0f : fast_exp2(m_used - m_new);
           m_used = m_new;
           l *= alpha;
         }
@@ -241,26 +246,21 @@ __global__ void __launch_bounds__(192, 1)
           tmem_st_wait();
         }
       }
-      // pass 2: P = exp2(S*scale - m), row sum, store to swizzled smem
+      // P = exp2(S*scale - m), row sum, store to swizzled smem
       const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(s_addr + c * 32, r);
-        tmem_ld_wait();
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
-          float p1 = exp2f(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, neg_m));
+          float p0 = fast_exp2(fmaf(__uint_as_float(sreg[c][i]), p.scale_log2, neg_m));
+          float p1 = fast_exp2(fmaf(__uint_as_float(sreg[c][i + 1]), p.scale_log2, neg_m));
           if (need_mask) {
             if (kv0 + c * 32 + i > kv_limit) p0 = 0.f;
             if (kv0 + c * 32 + i + 1 > kv_limit) p1 = 0.f;
           }
           l += p0 + p1;
-          T lo = from_f32<T>(p0), hi = from_f32<T>(p1);
-          packed[i >> 1] = (uint32_t)(*reinterpret_cast<uint16_t*>(&lo)) |
-                           ((uint32_t)(*reinterpret_cast<uint16_t*>(&hi)) << 16);
+          packed[i >> 1] = pack2<T>(p0, p1);
         }
         // columns [c*32, c*32+32) -> sub-tile (c>>1), 16-byte chunks ((c&1)*4 .. +4)
         uint8_t* rowp = sP + (c >> 1) * C::TILE_BYTES + t * 128;

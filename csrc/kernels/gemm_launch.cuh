@@ -18,7 +18,7 @@ struct GemmArgs {
 };
 
 template <typename T, int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
                         const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];

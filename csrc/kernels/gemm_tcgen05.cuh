@@ -14,8 +14,10 @@
 // (rumus/src/backend/gpu/shaders/matmul.wgsl:22) plus separate bias / activation
 // dispatches (shaders/bias.wgsl:20, shaders/unary.wgsl:20); here those are one kernel.
 //
-// Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
-// warps 2..5 = epilogue (TMEM lane quarter = warp_idx % 4).
+// Roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+// warps 2..9 = epilogue (TMEM lane quarter = warp_idx % 4; warps 2..5 take the left half of the
+// tile's columns, warps 6..9 the right half, so an activation-heavy epilogue on a short-K GEMM
+// keeps up with the main loop).
 //
 // `Hooks` lets the fused collective kernels (all-gather -> GEMM, GEMM ->
 // reduce-scatter) reuse this body: the producer asks the hook before loading a
@@ -78,14 +80,17 @@ struct GemmCfg {
   static constexpr int B_BYTES = BN * 128;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int NUM_THREADS = 192;
+  static constexpr int NUM_THREADS = 320;
+  static constexpr int EPI_WARPS = 8;
   static constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-// Barrier over the 192 GEMM threads (warps 0..5).  The fused collective kernels launch wider
+// Barrier over the 320 GEMM threads (warps 0..9).  The fused collective kernels launch wider
 // CTAs whose extra warps have a different role or have exited, so the count is explicit.
-__device__ __forceinline__ void cta_sync_192() {
-  asm volatile("bar.sync 0, 192;" ::: "memory");
+constexpr int kGemmThreads = 320;
+constexpr int kGemmEpiWarps = 8;
+__device__ __forceinline__ void cta_sync_gemm() {
+  asm volatile("bar.sync 0, 320;" ::: "memory");
 }
 
 template <typename T>
@@ -220,7 +225,7 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&tmem_full_bar[s]), 1);
-      mbar_init(smem_u32(&tmem_empty_bar[s]), 4);
+      mbar_init(smem_u32(&tmem_empty_bar[s]), kGemmEpiWarps);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -230,7 +235,7 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
     tmem_relinquish();
   }
   tc_fence_before();
-  cta_sync_192();
+  cta_sync_gemm();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
@@ -349,6 +354,8 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
   } else {
     // ------------------------------ epilogue ----------------------------------
     const int quarter = warp_idx & 3;
+    const int half = (warp_idx - 2) >> 2;           // 0: left half of the columns, 1: right half
+    constexpr int CHUNKS_PER_HALF = BN / 64;        // 32-column chunks per epilogue warp
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -363,7 +370,8 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
       const long long row = static_cast<long long>(m_idx) * BM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int ci = 0; ci < CHUNKS_PER_HALF; ++ci) {
+        const int c = half * CHUNKS_PER_HALF + ci;
         uint32_t r[32];
         tmem_ld_32x32b_x32(taddr + c * 32, r);
         tmem_ld_wait();
@@ -391,7 +399,7 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
 
   // ------------------------------ teardown ------------------------------------
   tc_fence_before();
-  cta_sync_192();
+  cta_sync_gemm();
   if (warp_idx == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);

@@ -36,6 +36,8 @@ __device__ __forceinline__ float ld(const T* p, long long i) {
 
 constexpr int kNormWarps = 8;
 
+__host__ __device__ __forceinline__ int skew(int i) { return i + (i >> 5); }
+
 // ---------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------
@@ -146,10 +148,13 @@ __global__ void __launch_bounds__(kNormWarps * 32)
                     const float* __restrict__ stats, const T* __restrict__ dres,
                     T* __restrict__ dx, float* __restrict__ partials /* [grid,2,D] */,
                     long long rows, int D, int vec_ok) {
-  extern __shared__ float s_acc[];  // [2][D]
+  // [2][D] accumulators, stored skewed (one pad float per 32) so that the 32 lanes of one
+  // shared-memory atomic — addresses lane*VEC + j — fall into 32 different banks
+  extern __shared__ float s_acc[];
+  const int DS = skew(D) + 1;
   float* s_dg = s_acc;
-  float* s_db = s_acc + D;
-  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) s_acc[i] = 0.f;
+  float* s_db = s_acc + DS;
+  for (int i = threadIdx.x; i < 2 * DS; i += blockDim.x) s_acc[i] = 0.f;
   __syncthreads();
   constexpr int VEC = Vec16<T>::N;
   const int lane = threadIdx.x & 31;
@@ -200,8 +205,8 @@ __global__ void __launch_bounds__(kNormWarps * 32)
           float o = rstd * (d * gv.get(j) - c1 - xh * c2);
           if (dres) o += rv.get(j);
           ov.set(j, o);
-          atomicAdd(&s_dg[c + j], d * xh);
-          if (!RMS) atomicAdd(&s_db[c + j], d);
+          atomicAdd(&s_dg[skew(c + j)], d * xh);
+          if (!RMS) atomicAdd(&s_db[skew(c + j)], d);
         }
         *reinterpret_cast<uint4*>(dx + row * D + c) = ov.raw;
       }
@@ -212,14 +217,17 @@ __global__ void __launch_bounds__(kNormWarps * 32)
         float o = rstd * (d * ld(gamma, c) - c1 - xh * c2);
         if (dres) o += ld(dres + row * D, c);
         dx[row * D + c] = from_f32<T>(o);
-        atomicAdd(&s_dg[c], d * xh);
-        if (!RMS) atomicAdd(&s_db[c], d);
+        atomicAdd(&s_dg[skew(c)], d * xh);
+        if (!RMS) atomicAdd(&s_db[skew(c)], d);
       }
     }
   }
   __syncthreads();
   float* out = partials + (long long)blockIdx.x * 2 * D;
-  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) out[i] = s_acc[i];
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    out[i] = s_dg[skew(i)];
+    out[D + i] = s_db[skew(i)];
+  }
 }
 
 // partials [n,2,D] -> dgamma[D], dbeta[D] (dbeta may be null)
@@ -279,7 +287,7 @@ int launch_norm_bwd(const void* x, const void* dy, const void* gamma, const floa
   constexpr int VEC = Vec16<T>::N;
   auto al = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   const int vec = (D % VEC == 0) && al(x) && al(dy) && al(gamma) && al(dres) && al(dx);
-  const size_t smem = (size_t)2 * D * sizeof(float);
+  const size_t smem = (size_t)2 * (skew(D) + 1) * sizeof(float);
   auto kern = norm_bwd_kernel<T, RMS>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

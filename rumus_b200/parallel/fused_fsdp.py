@@ -16,7 +16,12 @@ peer does after it finished reading everybody's gradients of step ``t``.
 """
 from __future__ import annotations
 
+import os
+
 from . import fused_ops
+
+_RS_CTAS = int(os.environ.get("RB_RS_CTAS", "32"))
+_AG_CTAS = int(os.environ.get("RB_AG_CTAS", "16"))
 
 
 class FusedFsdpComm:
@@ -38,13 +43,14 @@ class FusedFsdpComm:
                           lr=e.lr, beta1=e.beta1, beta2=e.beta2, eps=e.eps,
                           weight_decay=e.weight_decay, step=e.step_count + 1, adamw=e.adamw,
                           grad_flags_off=self.grad_flags[idx], param_flags_off=self.param_flags[idx],
-                          epoch=e.step_count + 1, done_counter=self.counters[idx])
+                          epoch=e.step_count + 1, done_counter=self.counters[idx], ctas=_RS_CTAS)
 
     def all_gather(self, idx: int) -> None:
         e, u = self.e, self.e.units[idx]
         esz = u.flat_param.element_size()
         fused_ops.all_gather(self.arena, u.flat_param.arena_offset, u.shard_numel * esz,
-                             src_flags_off=self.param_flags[idx], epoch=e.step_count + 1)
+                             src_flags_off=self.param_flags[idx], epoch=e.step_count + 1,
+                             ctas=_AG_CTAS)
 
     def end_step(self) -> None:
         pass
