@@ -1,0 +1,255 @@
+"""CUDA paths of the vision ops: implicit-GEMM convolution (im2col/col2im kernels around the
+tcgen05 GEMM), BatchNorm2d, max-pool, adaptive average pool.  Activations are kept channels-last
+(NHWC in memory, NCHW in shape) so 1x1 convolutions are plain GEMMs on the activation tensor and
+BatchNorm reduces over contiguous channel vectors.  Kernels: ``csrc/kernels/vision.cu``."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import native
+from ._lib import check, count_launch, ptr, stream_ptr
+
+P, LL, I, F = c_void_p, c_longlong, c_int, c_float
+native.register_signature("rb_im2col_nhwc", [I, P, P] + [I] * 12 + [P])
+native.register_signature("rb_col2im_nhwc", [I, P, P] + [I] * 12 + [P])
+native.register_signature("rb_bn_slabs", [LL])
+native.register_signature("rb_bn_fwd", [I, P, P, P, P, P, P, P, P, P, P, LL, I, F, F, I, I, P])
+native.register_signature("rb_bn_bwd", [I, P, P, P, P, P, P, P, P, P, P, P, P, LL, I, I, I, P])
+native.register_signature("rb_maxpool_fwd", [I, P, P, P] + [I] * 9 + [P])
+native.register_signature("rb_maxpool_bwd", [I, P, P, P] + [I] * 9 + [P])
+native.register_signature("rb_adaptive_avgpool", [I, I, P, P] + [I] * 6 + [P])
+
+
+def _nhwc(x: torch.Tensor) -> torch.Tensor:
+    """[B,C,H,W] (any layout) -> contiguous [B,H,W,C] tensor sharing memory when already channels-last."""
+    return x.permute(0, 2, 3, 1).contiguous()
+
+
+def _as_nchw(y_nhwc: torch.Tensor) -> torch.Tensor:
+    return y_nhwc.permute(0, 3, 1, 2)
+
+
+def _out(n, k, s, p, d=1):
+    return (n + 2 * p - d * (k - 1) - 1) // s + 1
+
+
+def _pad8(k: int, esz: int) -> int:
+    a = 16 // esz
+    return (k + a - 1) // a * a
+
+
+def _im2col(xh, KH, KW, Ho, Wo, stride, pad, dil, Kpad):
+    B, H, W, C = xh.shape
+    cols = torch.empty((B * Ho * Wo, Kpad), dtype=xh.dtype, device=xh.device)
+    check(native.lib().rb_im2col_nhwc(native.dtype_code(xh.dtype), ptr(xh), ptr(cols), B, H, W, C, KH,
+                                      KW, Ho, Wo, stride, pad, dil, Kpad, stream_ptr()), "rb_im2col_nhwc")
+    count_launch()
+    return cols
+
+
+def _col2im(dcols, B, H, W, C, KH, KW, Ho, Wo, stride, pad, dil, Kpad):
+    dx = torch.empty((B, H, W, C), dtype=dcols.dtype, device=dcols.device)
+    check(native.lib().rb_col2im_nhwc(native.dtype_code(dcols.dtype), ptr(dcols), ptr(dx), B, H, W, C,
+                                      KH, KW, Ho, Wo, stride, pad, dil, Kpad, stream_ptr()), "rb_col2im_nhwc")
+    count_launch()
+    return dx
+
+
+def _weight_matrix(weight, Kpad):
+    """[Cout, Cin, KH, KW] -> [Cout, Kpad] with K ordered (kh, kw, c) to match NHWC patches."""
+    Cout, Cin, KH, KW = weight.shape
+    wm = weight.permute(0, 2, 3, 1).reshape(Cout, KH * KW * Cin)
+    if Kpad != wm.shape[1]:
+        wm = torch.nn.functional.pad(wm, (0, Kpad - wm.shape[1]))
+    return wm.contiguous()
+
+
+class Conv2dFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, stride, padding, dilation):
+        B, Cin, H, W = x.shape
+        Cout, _, KH, KW = weight.shape
+        Ho, Wo = _out(H, KH, stride, padding, dilation), _out(W, KW, stride, padding, dilation)
+        xh = _nhwc(x)
+        esz = x.element_size()
+        pointwise = KH == 1 and KW == 1 and stride == 1 and padding == 0 and Cin % (16 // esz) == 0
+        Kpad = Cin if pointwise else _pad8(KH * KW * Cin, esz)
+        cols = xh.view(B * H * W, Cin) if pointwise else _im2col(xh, KH, KW, Ho, Wo, stride, padding,
+                                                                 dilation, Kpad)
+        wm = _weight_matrix(weight, Kpad)
+        y = native.gemm(cols, wm.t(), bias=bias)          # [M, Cout] == NHWC output
+        ctx.geom = (B, H, W, Cin, Cout, KH, KW, Ho, Wo, stride, padding, dilation, Kpad, pointwise)
+        ctx.save_for_backward(xh, wm)
+        ctx.has_bias = bias is not None
+        ctx.w_dtype = weight.dtype
+        return _as_nchw(y.view(B, Ho, Wo, Cout))
+
+    @staticmethod
+    def backward(ctx, dy):
+        xh, wm = ctx.saved_tensors
+        B, H, W, Cin, Cout, KH, KW, Ho, Wo, stride, padding, dilation, Kpad, pointwise = ctx.geom
+        dyh = _nhwc(dy).view(B * Ho * Wo, Cout)
+        dx = dw = db = None
+        cols = xh.view(B * H * W, Cin) if pointwise else _im2col(xh, KH, KW, Ho, Wo, stride, padding,
+                                                                 dilation, Kpad)
+        if ctx.needs_input_grad[1]:
+            dwm = native.gemm(dyh.t(), cols)               # [Cout, Kpad]
+            dw = dwm[:, :KH * KW * Cin].reshape(Cout, KH, KW, Cin).permute(0, 3, 1, 2).contiguous()
+        if ctx.needs_input_grad[0]:
+            dcols = native.gemm(dyh, wm)                   # [M, Kpad]
+            if pointwise:
+                dx = _as_nchw(dcols.view(B, H, W, Cin))
+            else:
+                dx = _as_nchw(_col2im(dcols, B, H, W, Cin, KH, KW, Ho, Wo, stride, padding, dilation, Kpad))
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = native.colsum(dyh)
+        return dx, dw, db, None, None, None
+
+
+class _ConvTranspose2dFn(torch.autograd.Function):
+    """y = col2im(x[M, Cin] @ W[Cin, Cout*K*K]) — the data-gradient path of a convolution."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, stride, padding):
+        B, Cin, H, W = x.shape
+        _, Cout, KH, KW = weight.shape
+        Ho = (H - 1) * stride - 2 * padding + KH
+        Wo = (W - 1) * stride - 2 * padding + KW
+        esz = x.element_size()
+        Kpad = _pad8(KH * KW * Cout, esz)
+        xh = _nhwc(x).view(B * H * W, Cin)
+        wm = weight.permute(0, 2, 3, 1).reshape(Cin, KH * KW * Cout)    # [Cin, (kh,kw,co)]
+        if Kpad != wm.shape[1]:
+            wm = torch.nn.functional.pad(wm, (0, Kpad - wm.shape[1]))
+        wm = wm.contiguous()
+        cols = native.gemm(xh, wm)                                       # [M, Kpad]
+        yh = _col2im(cols, B, Ho, Wo, Cout, KH, KW, H, W, stride, padding, 1, Kpad)
+        if bias is not None:
+            yh = yh + bias
+        ctx.geom = (B, H, W, Cin, Cout, KH, KW, Ho, Wo, stride, padding, Kpad)
+        ctx.has_bias = bias is not None
+        ctx.save_for_backward(xh, wm)
+        return _as_nchw(yh)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xh, wm = ctx.saved_tensors
+        B, H, W, Cin, Cout, KH, KW, Ho, Wo, stride, padding, Kpad = ctx.geom
+        dyh = _nhwc(dy)
+        dcols = _im2col(dyh, KH, KW, H, W, stride, padding, 1, Kpad)     # [B*H*W, Kpad]
+        dx = native.gemm(dcols, wm.t()).view(B, H, W, Cin)
+        dwm = native.gemm(xh.t(), dcols)                                 # [Cin, Kpad]
+        dw = dwm[:, :KH * KW * Cout].reshape(Cin, KH, KW, Cout).permute(0, 3, 1, 2).contiguous()
+        db = native.colsum(dyh.view(-1, Cout)) if ctx.has_bias else None
+        return _as_nchw(dx), dw, db, None, None
+
+
+def conv_transpose2d_cuda(x, weight, bias, stride, padding):
+    return _ConvTranspose2dFn.apply(x, weight, bias, stride, padding)
+
+
+class MaxPool2dFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, k, stride, pad):
+        B, C, H, W = x.shape
+        Ho, Wo = _out(H, k, stride, pad), _out(W, k, stride, pad)
+        xh = _nhwc(x)
+        y = torch.empty((B, Ho, Wo, C), dtype=x.dtype, device=x.device)
+        idx = torch.empty((B, Ho, Wo, C), dtype=torch.int8, device=x.device)
+        check(native.lib().rb_maxpool_fwd(native.dtype_code(x.dtype), ptr(xh), ptr(y), ptr(idx), B, H, W,
+                                          C, k, stride, pad, Ho, Wo, stream_ptr()), "rb_maxpool_fwd")
+        count_launch()
+        ctx.geom = (B, H, W, C, k, stride, pad, Ho, Wo)
+        ctx.save_for_backward(idx)
+        return _as_nchw(y)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (idx,) = ctx.saved_tensors
+        B, H, W, C, k, stride, pad, Ho, Wo = ctx.geom
+        dyh = _nhwc(dy)
+        dx = torch.empty((B, H, W, C), dtype=dy.dtype, device=dy.device)
+        check(native.lib().rb_maxpool_bwd(native.dtype_code(dy.dtype), ptr(dyh), ptr(idx), ptr(dx), B, H,
+                                          W, C, k, stride, pad, Ho, Wo, stream_ptr()), "rb_maxpool_bwd")
+        count_launch()
+        return _as_nchw(dx), None, None, None
+
+
+class AdaptiveAvgPool2dFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, out_size):
+        B, C, H, W = x.shape
+        Ho, Wo = out_size
+        xh = _nhwc(x)
+        y = torch.empty((B, Ho, Wo, C), dtype=x.dtype, device=x.device)
+        check(native.lib().rb_adaptive_avgpool(native.dtype_code(x.dtype), 0, ptr(xh), ptr(y), B, H, W, C,
+                                               Ho, Wo, stream_ptr()), "rb_adaptive_avgpool")
+        count_launch()
+        ctx.geom = (B, H, W, C, Ho, Wo)
+        return _as_nchw(y)
+
+    @staticmethod
+    def backward(ctx, dy):
+        B, H, W, C, Ho, Wo = ctx.geom
+        dyh = _nhwc(dy)
+        dx = torch.empty((B, H, W, C), dtype=dy.dtype, device=dy.device)
+        check(native.lib().rb_adaptive_avgpool(native.dtype_code(dy.dtype), 1, ptr(dyh), ptr(dx), B, H, W,
+                                               C, Ho, Wo, stream_ptr()), "rb_adaptive_avgpool")
+        count_launch()
+        return _as_nchw(dx), None
+
+
+class BatchNorm2dFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, running_mean, running_var, training, momentum, eps, relu,
+                residual):
+        B, C, H, W = x.shape
+        M = B * H * W
+        xh = _nhwc(x)
+        rh = _nhwc(residual) if residual is not None else None
+        y = torch.empty_like(xh)
+        L = native.lib()
+        slabs = L.rb_bn_slabs(M)
+        scratch = torch.empty((slabs, 2, C), dtype=torch.float32, device=x.device)
+        if training:
+            mean = torch.empty(C, dtype=torch.float32, device=x.device)
+            rstd = torch.empty(C, dtype=torch.float32, device=x.device)
+        else:
+            mean = running_mean.float().contiguous()
+            rstd = torch.rsqrt(running_var.float() + eps)
+        w = weight.to(x.dtype).contiguous()
+        b = bias.to(x.dtype).contiguous()
+        check(L.rb_bn_fwd(native.dtype_code(x.dtype), ptr(xh), ptr(rh), ptr(w), ptr(b), ptr(y), ptr(mean),
+                          ptr(rstd), ptr(running_mean) if training else None,
+                          ptr(running_var) if training else None, ptr(scratch), M, C, float(eps),
+                          float(momentum), 1 if relu else 0, 1 if training else 0, stream_ptr()),
+              "rb_bn_fwd")
+        count_launch(3 if training else 1)
+        ctx.geom = (B, C, H, W, relu, training)
+        ctx.has_res = residual is not None
+        ctx.param_dtype = weight.dtype
+        ctx.save_for_backward(xh, y, w, mean, rstd)
+        return _as_nchw(y)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xh, y, w, mean, rstd = ctx.saved_tensors
+        B, C, H, W, relu, training = ctx.geom
+        M = B * H * W
+        dyh = _nhwc(dy)
+        L = native.lib()
+        dx = torch.empty_like(xh)
+        dres = torch.empty_like(xh) if ctx.has_res else None
+        dg = torch.empty(C, dtype=xh.dtype, device=xh.device)
+        db = torch.empty(C, dtype=xh.dtype, device=xh.device)
+        sums = torch.empty(2 * C, dtype=torch.float32, device=xh.device)
+        slabs = L.rb_bn_slabs(M)
+        scratch = torch.empty((slabs, 2, C), dtype=torch.float32, device=xh.device)
+        check(L.rb_bn_bwd(native.dtype_code(xh.dtype), ptr(xh), ptr(dyh), ptr(y), ptr(w), ptr(mean),
+                          ptr(rstd), ptr(dx), ptr(dres), ptr(dg), ptr(db), ptr(sums), ptr(scratch), M, C,
+                          1 if relu else 0, 1 if training else 0, stream_ptr()), "rb_bn_bwd")
+        count_launch(3)
+        return (_as_nchw(dx), dg.to(ctx.param_dtype), db.to(ctx.param_dtype), None, None, None, None,
+                None, None, _as_nchw(dres) if dres is not None else None)
