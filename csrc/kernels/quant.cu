@@ -1,0 +1,291 @@
+// Weight-only quantisation kernels for sm_100a.
+//
+// INT4 (group-wise asymmetric, AWQ/GPTQ-style storage; format of rumus-vision/src/quant.rs:42-126):
+//   packed int32 [Kp/8, N], word (k/8)*N + n, nibble k%8; scales / zero-points [Kp/group, N]
+//   (fp16 or fp32); w[k,n] = (q - zp) * scale.
+//   * int4_gemv: y[M,N] = x[M,K] . dequant(W) for small M (decode): streams the 4-bit weights
+//     once at HBM speed, 16-byte loads (4 columns per thread), split-K across CTAs with fp32
+//     partials in scratch and a deterministic reduce;
+//   * int4_dequant: expands W to a dense 16-bit [K,N] matrix for the tcgen05 GEMM (prefill and
+//     the transposed product used in backward).
+//   Reference kernels: rumus-vision/src/shaders/qmatmul_int4.wgsl:41 (one thread per output,
+//   serial K loop), qmatmul_int4_transpose.wgsl:38.
+//
+// INT8 block format of rumus/src/backend/gpu/shaders/quantize.wgsl:30 / dequantize.wgsl:33 /
+// matmul_q8.wgsl:38: the matrix is laid out column-major, cut into blocks of `bs` values, each
+// block = 4-byte header (f16 scale in the low half) + bs int8 values.
+#include "sm100_common.cuh"
+
+namespace rb {
+
+template <typename TS>
+__device__ __forceinline__ float sc_f32(TS v);
+template <>
+__device__ __forceinline__ float sc_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float sc_f32<__half>(__half v) { return __half2float(v); }
+
+constexpr int kGemvThreads = 128;
+constexpr int kGemvMaxM = 32;
+
+// grid: (ceil(N / (4*128)), splits).  Each thread owns 4 consecutive columns.
+template <typename TX, typename TS>
+__global__ void __launch_bounds__(kGemvThreads)
+    int4_gemv_kernel(const TX* __restrict__ x, const int* __restrict__ packed,
+                     const TS* __restrict__ scales, const TS* __restrict__ zps,
+                     float* __restrict__ partials /* [splits, M, N] */, int M, int N, int K, int Kp,
+                     int group, int k8_per_split) {
+  extern __shared__ float sx[];  // [M][k8_per_split*8] activations of this split
+  const int n0 = (blockIdx.x * kGemvThreads + threadIdx.x) * 4;
+  const int k8_begin = blockIdx.y * k8_per_split;
+  const int k8_end = min(Kp / 8, k8_begin + k8_per_split);
+  const int kspan = (k8_end - k8_begin) * 8;
+  for (int i = threadIdx.x; i < M * kspan; i += blockDim.x) {
+    const int m = i / kspan, kk = i - m * kspan;
+    const int k = k8_begin * 8 + kk;
+    sx[i] = k < K ? to_f32<TX>(x[(long long)m * K + k]) : 0.f;
+  }
+  __syncthreads();
+  if (n0 >= N) return;
+  float acc[kGemvMaxM][4];
+#pragma unroll
+  for (int m = 0; m < kGemvMaxM; ++m)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[m][j] = 0.f;
+  float sc[4] = {0, 0, 0, 0}, zp[4] = {0, 0, 0, 0};
+  int cur_group = -1;
+  const bool full4 = (n0 + 3 < N) && (N % 4 == 0);
+  for (int k8 = k8_begin; k8 < k8_end; ++k8) {
+    const int g = (k8 * 8) / group;
+    if (g != cur_group) {
+      cur_group = g;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = min(n0 + j, N - 1);
+        sc[j] = sc_f32<TS>(scales[(long long)g * N + n]);
+        zp[j] = sc_f32<TS>(zps[(long long)g * N + n]);
+      }
+    }
+    int w[4];
+    if (full4) {
+      const int4 v = *reinterpret_cast<const int4*>(packed + (long long)k8 * N + n0);
+      w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = n0 + j < N ? packed[(long long)k8 * N + n0 + j] : 0;
+    }
+    const float* xs = sx + (k8 - k8_begin) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float wv[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        wv[j] = ((float)((static_cast<unsigned>(w[j]) >> (4 * i)) & 0xF) - zp[j]) * sc[j];
+#pragma unroll
+      for (int m = 0; m < kGemvMaxM; ++m) {
+        if (m < M) {
+          const float xv = xs[m * kspan + i];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[m][j] = fmaf(xv, wv[j], acc[m][j]);
+        }
+      }
+    }
+  }
+  float* out = partials + (long long)blockIdx.y * M * N;
+  for (int m = 0; m < M; ++m)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (n0 + j < N) out[(long long)m * N + n0 + j] = acc[m][j];
+}
+
+template <typename TX>
+__global__ void gemv_reduce_kernel(const float* __restrict__ partials, int splits, long long MN,
+                                   int N, const TX* __restrict__ bias, TX* __restrict__ y) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= MN) return;
+  float a = 0.f;
+  for (int s = 0; s < splits; ++s) a += partials[(long long)s * MN + i];
+  if (bias) a += to_f32<TX>(bias[i % N]);
+  y[i] = from_f32<TX>(a);
+}
+
+// dense[k, n] = (q - zp) * scale  for k < K
+template <typename TO, typename TS>
+__global__ void int4_dequant_kernel(const int* __restrict__ packed, const TS* __restrict__ scales,
+                                    const TS* __restrict__ zps, TO* __restrict__ dense, int N, int K,
+                                    int group) {
+  const long long total = (long long)((K + 7) / 8) * N;
+  const long long gs = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gs) {
+    const int n = (int)(i % N);
+    const int k8 = (int)(i / N);
+    const unsigned w = static_cast<unsigned>(packed[i]);
+    const int g = (k8 * 8) / group;
+    const float sc = sc_f32<TS>(scales[(long long)g * N + n]);
+    const float zp = sc_f32<TS>(zps[(long long)g * N + n]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int k = k8 * 8 + j;
+      if (k < K) dense[(long long)k * N + n] = from_f32<TO>(((float)((w >> (4 * j)) & 0xF) - zp) * sc);
+    }
+  }
+}
+
+// ---- INT8 blocks -------------------------------------------------------------------------
+// src is the [K, N] matrix; block b covers flat column-major elements [b*bs, (b+1)*bs)
+template <typename T>
+__global__ void q8_quantize_kernel(const T* __restrict__ src, unsigned char* __restrict__ dst, int K,
+                                   int N, int bs, long long numel) {
+  const long long b = blockIdx.x;
+  const long long e0 = b * bs;
+  __shared__ float smax[32];
+  float mx = 0.f;
+  for (int i = threadIdx.x; i < bs; i += blockDim.x) {
+    const long long e = e0 + i;
+    if (e < numel) {
+      const long long n = e / K, k = e % K;
+      mx = fmaxf(mx, fabsf(to_f32<T>(src[k * N + n])));
+    }
+  }
+  mx = warp_max(mx);
+  if ((threadIdx.x & 31) == 0) smax[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float r = threadIdx.x < (blockDim.x >> 5) ? smax[threadIdx.x] : 0.f;
+    r = warp_max(r);
+    if (threadIdx.x == 0) smax[0] = r;
+  }
+  __syncthreads();
+  const float absmax = smax[0];
+  const float scale = absmax == 0.f ? 1.f : absmax / 127.f;
+  const float inv = absmax == 0.f ? 0.f : 127.f / absmax;
+  unsigned char* out = dst + b * (4 + bs);
+  if (threadIdx.x == 0) {
+    const __half h = __float2half_rn(scale);
+    const unsigned short bits = *reinterpret_cast<const unsigned short*>(&h);
+    out[0] = bits & 0xFF; out[1] = bits >> 8; out[2] = 0; out[3] = 0;
+  }
+  for (int i = threadIdx.x; i < bs; i += blockDim.x) {
+    const long long e = e0 + i;
+    int q = 0;
+    if (e < numel) {
+      const long long n = e / K, k = e % K;
+      q = max(-128, min(127, __float2int_rn(to_f32<T>(src[k * N + n]) * inv)));
+    }
+    out[4 + i] = (unsigned char)(signed char)q;
+  }
+}
+template <typename T>
+__global__ void q8_dequantize_kernel(const unsigned char* __restrict__ src, T* __restrict__ dst,
+                                     int K, int N, int bs, long long numel) {
+  const long long gs = (long long)gridDim.x * blockDim.x;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < numel; e += gs) {
+    const long long b = e / bs;
+    const int i = (int)(e - b * bs);
+    const unsigned char* blk = src + b * (4 + bs);
+    const unsigned short bits = (unsigned short)blk[0] | ((unsigned short)blk[1] << 8);
+    const float scale = __half2float(*reinterpret_cast<const __half*>(&bits));
+    const float v = (float)(signed char)blk[4 + i] * scale;
+    const long long n = e / K, k = e % K;
+    dst[k * N + n] = from_f32<T>(v);
+  }
+}
+
+}  // namespace rb
+
+extern "C" {
+
+// scratch needed: rb_int4_gemv_splits(K) * M * N floats.
+int rb_int4_gemv_splits(int Kp, int N) {
+  // enough CTAs to fill the machine: columns give N/512 CTAs, the rest comes from K splits
+  const int col_ctas = (N + 511) / 512;
+  int want = (2 * rbh::sm_count() + col_ctas - 1) / col_ctas;
+  const int k8 = Kp / 8;
+  int max_splits = k8 / 16;  // at least 128 rows of K per split
+  if (max_splits < 1) max_splits = 1;
+  if (want > max_splits) want = max_splits;
+  if (want < 1) want = 1;
+  return want;
+}
+
+int rb_int4_gemv(int x_dtype, int scale_dtype, const void* x, const int* packed, const void* scales,
+                 const void* zps, const void* bias, void* y, float* scratch, int M, int N, int K,
+                 int Kp, int group, void* stream) {
+  using namespace rb;
+  if (M <= 0 || N <= 0) return 0;
+  if (M > kGemvMaxM) return 50;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int splits = rb_int4_gemv_splits(Kp, N);
+  int k8_per_split = (Kp / 8 + splits - 1) / splits;
+  // keep splits aligned to groups so a thread's (scale, zp) cache changes at most once per group
+  const int g8 = group / 8;
+  k8_per_split = (k8_per_split + g8 - 1) / g8 * g8;
+  const int real_splits = (Kp / 8 + k8_per_split - 1) / k8_per_split;
+  dim3 grid((N + 4 * kGemvThreads - 1) / (4 * kGemvThreads), real_splits);
+  const size_t smem = (size_t)M * k8_per_split * 8 * sizeof(float);
+#define RB_GEMV(TX, TS)                                                                          \
+  do {                                                                                           \
+    auto kern = int4_gemv_kernel<TX, TS>;                                                        \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    kern<<<grid, kGemvThreads, smem, st>>>((const TX*)x, packed, (const TS*)scales, (const TS*)zps, \
+                                           scratch, M, N, K, Kp, group, k8_per_split);           \
+    gemv_reduce_kernel<TX><<<(unsigned)(((long long)M * N + 255) / 256), 256, 0, st>>>(          \
+        scratch, real_splits, (long long)M * N, N, (const TX*)bias, (TX*)y);                     \
+  } while (0)
+  if (x_dtype == rbh::DT_BF16) {
+    if (scale_dtype == rbh::DT_F16) RB_GEMV(__nv_bfloat16, __half); else RB_GEMV(__nv_bfloat16, float);
+  } else if (x_dtype == rbh::DT_F16) {
+    if (scale_dtype == rbh::DT_F16) RB_GEMV(__half, __half); else RB_GEMV(__half, float);
+  } else {
+    if (scale_dtype == rbh::DT_F16) RB_GEMV(float, __half); else RB_GEMV(float, float);
+  }
+#undef RB_GEMV
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
+}
+
+int rb_int4_dequant(int out_dtype, int scale_dtype, const int* packed, const void* scales,
+                    const void* zps, void* dense, int N, int K, int group, void* stream) {
+  using namespace rb;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long total = (long long)((K + 7) / 8) * N;
+  if (total <= 0) return 0;
+  long long blocks = (total + 255) / 256;
+  const long long cap = (long long)rbh::sm_count() * 32;
+  if (blocks > cap) blocks = cap;
+#define RB_DQ(TO, TS) int4_dequant_kernel<TO, TS><<<(unsigned)blocks, 256, 0, st>>>(packed, (const TS*)scales, (const TS*)zps, (TO*)dense, N, K, group)
+  if (out_dtype == rbh::DT_BF16) { if (scale_dtype == rbh::DT_F16) RB_DQ(__nv_bfloat16, __half); else RB_DQ(__nv_bfloat16, float); }
+  else if (out_dtype == rbh::DT_F16) { if (scale_dtype == rbh::DT_F16) RB_DQ(__half, __half); else RB_DQ(__half, float); }
+  else { if (scale_dtype == rbh::DT_F16) RB_DQ(float, __half); else RB_DQ(float, float); }
+#undef RB_DQ
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
+}
+
+int rb_q8_quantize(int dtype, const void* src, unsigned char* dst, int K, int N, int bs, void* stream) {
+  using namespace rb;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long numel = (long long)K * N;
+  const long long nb = (numel + bs - 1) / bs;
+  if (nb <= 0) return 0;
+  if (dtype == rbh::DT_BF16) q8_quantize_kernel<__nv_bfloat16><<<(unsigned)nb, 64, 0, st>>>((const __nv_bfloat16*)src, dst, K, N, bs, numel);
+  else if (dtype == rbh::DT_F16) q8_quantize_kernel<__half><<<(unsigned)nb, 64, 0, st>>>((const __half*)src, dst, K, N, bs, numel);
+  else q8_quantize_kernel<float><<<(unsigned)nb, 64, 0, st>>>((const float*)src, dst, K, N, bs, numel);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
+}
+int rb_q8_dequantize(int dtype, const unsigned char* src, void* dst, int K, int N, int bs, void* stream) {
+  using namespace rb;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long numel = (long long)K * N;
+  if (numel <= 0) return 0;
+  long long blocks = (numel + 255) / 256;
+  const long long cap = (long long)rbh::sm_count() * 32;
+  if (blocks > cap) blocks = cap;
+  if (dtype == rbh::DT_BF16) q8_dequantize_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(src, (__nv_bfloat16*)dst, K, N, bs, numel);
+  else if (dtype == rbh::DT_F16) q8_dequantize_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(src, (__half*)dst, K, N, bs, numel);
+  else q8_dequantize_kernel<float><<<(unsigned)blocks, 256, 0, st>>>(src, (float*)dst, K, N, bs, numel);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
+}
+}

@@ -1,0 +1,91 @@
+"""CUDA paths of the quantised matmuls (kernels: ``csrc/kernels/quant.cu``).
+
+INT4: ``M <= 32`` rows (decode) run the split-K GEMV that streams the packed weights once;
+larger ``M`` (prefill) expand the weight to a dense 16-bit matrix and run the tcgen05 GEMM.
+INT8 blocks: quantise / dequantise kernels; the matmul dequantises then uses the GEMM.
+"""
+from __future__ import annotations
+
+from ctypes import c_int, c_void_p
+
+import torch
+
+from . import native
+from ._lib import check, count_launch, ptr, stream_ptr
+
+P, I = c_void_p, c_int
+native.register_signature("rb_int4_gemv_splits", [I, I])
+native.register_signature("rb_int4_gemv", [I, I, P, P, P, P, P, P, P, I, I, I, I, I, P])
+native.register_signature("rb_int4_dequant", [I, I, P, P, P, P, I, I, I, P])
+native.register_signature("rb_q8_quantize", [I, P, P, I, I, I, P])
+native.register_signature("rb_q8_dequantize", [I, P, P, I, I, I, P])
+
+GEMV_MAX_M = 32
+
+
+def int4_dequant(qw, dtype: torch.dtype) -> torch.Tensor:
+    dense = torch.empty((qw.k, qw.n), dtype=dtype, device=qw.packed.device)
+    check(native.lib().rb_int4_dequant(native.dtype_code(dtype), native.dtype_code(qw.scales.dtype),
+                                       ptr(qw.packed), ptr(qw.scales), ptr(qw.zero_points), ptr(dense),
+                                       qw.n, qw.k, qw.group_size, stream_ptr()), "rb_int4_dequant")
+    count_launch()
+    return dense
+
+
+def int4_matmul(x: torch.Tensor, qw, bias=None) -> torch.Tensor:
+    """x [M, K] @ dequant(qw) [K, N]."""
+    L = native.lib()
+    M, K = x.shape
+    assert K == qw.k
+    x = x.contiguous()
+    if M <= GEMV_MAX_M:
+        splits = L.rb_int4_gemv_splits(qw.padded_k, qw.n)
+        scratch = torch.empty((splits, M, qw.n), dtype=torch.float32, device=x.device)
+        y = torch.empty((M, qw.n), dtype=x.dtype, device=x.device)
+        check(L.rb_int4_gemv(native.dtype_code(x.dtype), native.dtype_code(qw.scales.dtype), ptr(x),
+                             ptr(qw.packed), ptr(qw.scales), ptr(qw.zero_points), ptr(bias), ptr(y),
+                             ptr(scratch), M, qw.n, K, qw.padded_k, qw.group_size, stream_ptr()),
+              "rb_int4_gemv")
+        count_launch(2)
+        return y
+    dense = int4_dequant(qw, x.dtype)
+    return native.gemm(x, dense, bias=bias)
+
+
+class QMatmulInt4Fn(torch.autograd.Function):
+    """Frozen INT4 weight: only the activation gets a gradient, ``dX = dY @ dequant(W)^T``
+    (reference: rumus-vision/src/shaders/qmatmul_int4_transpose.wgsl:38)."""
+
+    @staticmethod
+    def forward(ctx, x, qw):
+        ctx.qw = qw
+        return int4_matmul(x, qw)
+
+    @staticmethod
+    def backward(ctx, dy):
+        dense = int4_dequant(ctx.qw, dy.dtype)
+        return native.gemm(dy.contiguous(), dense.t()), None
+
+
+def quantize_q8_cuda(weight: torch.Tensor, block_size: int):
+    from ..nn.quant import Q8Tensor
+    k, n = weight.shape
+    w = weight.detach().contiguous()
+    nb = (k * n + block_size - 1) // block_size
+    out = torch.empty(nb * (4 + block_size), dtype=torch.uint8, device=w.device)
+    check(native.lib().rb_q8_quantize(native.dtype_code(w.dtype), ptr(w), ptr(out), k, n, block_size,
+                                      stream_ptr()), "rb_q8_quantize")
+    count_launch()
+    return Q8Tensor(k, n, block_size, out)
+
+
+def dequantize_q8_cuda(q, dtype: torch.dtype) -> torch.Tensor:
+    out = torch.empty((q.k, q.n), dtype=dtype, device=q.data.device)
+    check(native.lib().rb_q8_dequantize(native.dtype_code(dtype), ptr(q.data), ptr(out), q.k, q.n,
+                                        q.block_size, stream_ptr()), "rb_q8_dequantize")
+    count_launch()
+    return out
+
+
+def matmul_q8_cuda(x: torch.Tensor, q) -> torch.Tensor:
+    return native.gemm(x.contiguous(), dequantize_q8_cuda(q, x.dtype))

@@ -1,0 +1,454 @@
+"""Continuous-batching inference engine for Llama-style models with INT4 (AWQ-layout) weights,
+a paged KV cache and tensor parallelism.
+
+The reference server (rumus-serve/src/{scheduler,gpu_worker,model}.rs) batches statically under a
+deadline around a mock model.  Here:
+
+* requests join and leave between steps (C++ scheduler + block allocator,
+  ``csrc/serve/kv_scheduler.cpp``): each step decodes one token for every running sequence and
+  spends the rest of the token budget on prompt chunks of waiting sequences;
+* weights are INT4 group-128 with fp16 scales, sharded Megatron-style across the TP group
+  (qkv / gate-up by output columns, out-proj / down by input rows on group boundaries);
+  decode uses the streaming GEMV kernel, prefill the dequant + tcgen05 GEMM path;
+* attention reads and writes a block-paged KV cache (``csrc/kernels/paged_attention.cu``); whole
+  prompts run through the FlashAttention forward kernel;
+* the two partial-sum reductions per layer are all-reduces over the TP group (fused arena kernel
+  or NCCL).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import time
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..models.llama import LlamaConfig
+from ..nn.quant import QuantizedTensor, qmatmul_int4
+from ..ops import _lib, functional as F, native
+from ..ops._lib import check, count_launch, ptr, stream_ptr
+
+P, LL, I, Fl = c_void_p, c_longlong, c_int, c_float
+native.register_signature("rb_paged_decode_splits", [I])
+native.register_signature("rb_paged_decode_attn", [I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, Fl, P])
+native.register_signature("rb_kv_append", [I, P, P, LL, P, P, P, I, I, P])
+native.register_signature("rb_argmax", [I, P, LL, I, I, P, P, P])
+
+
+# --------------------------------------------------------------------------- host scheduler
+class Scheduler:
+    """ctypes face of the C++ continuous-batching scheduler / block allocator."""
+
+    def __init__(self, num_blocks: int, block_size: int, max_batch: int, token_budget: int):
+        L = _lib.host_lib()
+        L.rbs_create.restype = c_void_p
+        L.rbs_create.argtypes = [c_int] * 4
+        L.rbs_destroy.argtypes = [c_void_p]
+        L.rbs_add_request.argtypes = [c_void_p, c_longlong, c_int, c_int]
+        L.rbs_schedule.argtypes = [c_void_p] + [c_void_p] * 6 + [c_int]
+        L.rbs_commit.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                 c_void_p, c_int]
+        L.rbs_block_table.argtypes = [c_void_p, c_longlong, c_void_p, c_int]
+        L.rbs_context_len.argtypes = [c_void_p, c_longlong]
+        L.rbs_abort.argtypes = [c_void_p, c_longlong]
+        for n in ("rbs_num_free_blocks", "rbs_num_waiting", "rbs_num_running"):
+            getattr(L, n).argtypes = [c_void_p]
+        L.rbs_num_preemptions.restype = c_longlong
+        L.rbs_num_preemptions.argtypes = [c_void_p]
+        self.L = L
+        self.h = c_void_p(L.rbs_create(num_blocks, block_size, max_batch, token_budget))
+        self.cap = max(max_batch, 64) * 4
+        self.block_size = block_size
+
+    def __del__(self):
+        try:
+            self.L.rbs_destroy(self.h)
+        except Exception:
+            pass
+
+    def add(self, rid: int, prompt_len: int, max_new: int) -> int:
+        return self.L.rbs_add_request(self.h, rid, prompt_len, max_new)
+
+    def schedule(self):
+        cap = self.cap
+        dec = (c_longlong * cap)(); pre = (c_longlong * cap)()
+        ps = (c_int * cap)(); pl = (c_int * cap)()
+        nd, npf = c_int(0), c_int(0)
+        self.L.rbs_schedule(self.h, dec, ctypes.byref(nd), pre, ps, pl, ctypes.byref(npf), cap)
+        return ([dec[i] for i in range(nd.value)],
+                [(pre[i], ps[i], pl[i]) for i in range(npf.value)])
+
+    def commit(self, decode_ids, prefills, eos_ids=()):
+        cap = self.cap
+        dec = (c_longlong * max(1, len(decode_ids)))(*decode_ids)
+        pre = (c_longlong * max(1, len(prefills)))(*[p[0] for p in prefills])
+        pl = (c_int * max(1, len(prefills)))(*[p[2] for p in prefills])
+        eos = (c_longlong * max(1, len(eos_ids)))(*eos_ids)
+        fin = (c_longlong * cap)()
+        n = self.L.rbs_commit(self.h, dec, len(decode_ids), pre, pl, len(prefills), eos, len(eos_ids),
+                              fin, cap)
+        return [fin[i] for i in range(n)]
+
+    def block_table(self, rid: int, max_blocks: int) -> List[int]:
+        out = (c_int * max_blocks)()
+        n = self.L.rbs_block_table(self.h, rid, out, max_blocks)
+        return [out[i] for i in range(max(0, min(n, max_blocks)))]
+
+    def context_len(self, rid: int) -> int:
+        return self.L.rbs_context_len(self.h, rid)
+
+    def free_blocks(self) -> int:
+        return self.L.rbs_num_free_blocks(self.h)
+
+    def num_waiting(self) -> int:
+        return self.L.rbs_num_waiting(self.h)
+
+    def num_running(self) -> int:
+        return self.L.rbs_num_running(self.h)
+
+    def preemptions(self) -> int:
+        return int(self.L.rbs_num_preemptions(self.h))
+
+
+# --------------------------------------------------------------------------- model
+@dataclass
+class ServeConfig:
+    model: LlamaConfig
+    group_size: int = 128
+    block_size: int = 64
+    num_blocks: int = 4096
+    max_batch: int = 64
+    token_budget: int = 4096
+    dtype: torch.dtype = torch.bfloat16
+    scale_dtype: torch.dtype = torch.float16
+    comm_mode: str = "nccl"
+
+
+class _Layer:
+    pass
+
+
+class Int4LlamaShard:
+    """This rank's shard of an INT4-quantised Llama: random-init weights generated per layer and
+    quantised on the fly (``seed`` makes every rank draw the same full matrices before slicing)."""
+
+    def __init__(self, cfg: ServeConfig, device, rank: int = 0, world: int = 1, seed: int = 0):
+        m = cfg.model
+        self.cfg, self.device, self.rank, self.world = cfg, device, rank, world
+        assert m.num_heads % world == 0 and m.num_kv_heads % world == 0
+        hd = m.d_model // m.num_heads
+        self.hd = hd
+        self.h_local, self.hkv_local = m.num_heads // world, m.num_kv_heads // world
+        ffn_local = m.ffn_dim // world
+        # row-parallel K splits must fall on quantisation-group boundaries
+        assert (self.h_local * hd) % cfg.group_size == 0 and ffn_local % cfg.group_size == 0 or world == 1
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        std = 0.02
+
+        def rnd(*shape):
+            return torch.randn(*shape, generator=g) * std
+
+        def q(w):
+            return QuantizedTensor.from_f32(w, cfg.group_size, cfg.scale_dtype).to(device)
+
+        self.emb = rnd(m.vocab_size, m.d_model).to(cfg.dtype).to(device)
+        self.layers: List[_Layer] = []
+        r, W = rank, world
+        for _ in range(m.num_layers):
+            L = _Layer()
+            wq, wk, wv = rnd(m.d_model, m.num_heads * hd), rnd(m.d_model, m.num_kv_heads * hd), \
+                rnd(m.d_model, m.num_kv_heads * hd)
+            ql, kl = self.h_local * hd, self.hkv_local * hd
+            L.qkv = q(torch.cat([wq[:, r * ql:(r + 1) * ql], wk[:, r * kl:(r + 1) * kl],
+                                 wv[:, r * kl:(r + 1) * kl]], dim=1))
+            wo = rnd(m.num_heads * hd, m.d_model)
+            L.out = q(wo[r * ql:(r + 1) * ql])
+            wg, wu = rnd(m.d_model, m.ffn_dim), rnd(m.d_model, m.ffn_dim)
+            L.gate_up = q(torch.cat([wg[:, r * ffn_local:(r + 1) * ffn_local],
+                                     wu[:, r * ffn_local:(r + 1) * ffn_local]], dim=1))
+            wd = rnd(m.ffn_dim, m.d_model)
+            L.down = q(wd[r * ffn_local:(r + 1) * ffn_local])
+            L.ln1 = torch.ones(m.d_model, dtype=cfg.dtype, device=device)
+            L.ln2 = torch.ones(m.d_model, dtype=cfg.dtype, device=device)
+            self.layers.append(L)
+        self.ln_f = torch.ones(m.d_model, dtype=cfg.dtype, device=device)
+        vloc = m.vocab_size // world
+        self.vocab_local = vloc
+        self.head = rnd(m.d_model, m.vocab_size)[:, r * vloc:(r + 1) * vloc].contiguous().to(cfg.dtype).to(device)
+
+
+class PagedKVCache:
+    def __init__(self, cfg: ServeConfig, hkv_local: int, hd: int, device):
+        n, bs = cfg.num_blocks, cfg.block_size
+        self.block_size = bs
+        self.k = [torch.zeros((n, bs, hkv_local, hd), dtype=cfg.dtype, device=device)
+                  for _ in range(cfg.model.num_layers)]
+        self.v = [torch.zeros((n, bs, hkv_local, hd), dtype=cfg.dtype, device=device)
+                  for _ in range(cfg.model.num_layers)]
+
+    def append(self, layer: int, k_src, v_src, slots):
+        """k_src/v_src: [T, Hkv*D] row views (possibly strided); slots: int64 [T]."""
+        kc, vc = self.k[layer], self.v[layer]
+        row = kc.shape[2] * kc.shape[3]
+        if k_src.is_cuda:
+            check(native.lib().rb_kv_append(native.dtype_code(kc.dtype), ptr(k_src), ptr(v_src),
+                                            k_src.stride(0), ptr(slots), ptr(kc), ptr(vc),
+                                            k_src.shape[0], row, stream_ptr()), "rb_kv_append")
+            count_launch()
+        else:
+            kc.view(-1, row)[slots] = k_src
+            vc.view(-1, row)[slots] = v_src
+
+
+def paged_decode_attention(q, k_cache, v_cache, block_tables, ctx_lens, scale: float, max_ctx: int):
+    """q [B, H, D]; returns [B, H, D]."""
+    B, H, D = q.shape
+    Hkv = k_cache.shape[2]
+    if q.is_cuda:
+        L = native.lib()
+        splits = L.rb_paged_decode_splits(int(max_ctx))
+        so = torch.empty((B, H, splits, D), dtype=torch.float32, device=q.device)
+        sml = torch.empty((B, H, splits, 2), dtype=torch.float32, device=q.device)
+        out = torch.empty_like(q)
+        check(L.rb_paged_decode_attn(native.dtype_code(q.dtype), ptr(q), ptr(k_cache), ptr(v_cache),
+                                     ptr(block_tables), ptr(ctx_lens), ptr(out), ptr(so), ptr(sml), B, H,
+                                     Hkv, D, k_cache.shape[1], block_tables.shape[1], splits,
+                                     float(scale), stream_ptr()), "rb_paged_decode_attn")
+        count_launch(2)
+        return out
+    outs = []
+    bs = k_cache.shape[1]
+    for b in range(B):
+        n = int(ctx_lens[b])
+        idx = torch.arange(n)
+        blk = block_tables[b, idx // bs].long()
+        kk = k_cache[blk, idx % bs].float()   # [n, Hkv, D]
+        vv = v_cache[blk, idx % bs].float()
+        rep = H // Hkv
+        kk, vv = kk.repeat_interleave(rep, 1), vv.repeat_interleave(rep, 1)
+        s = torch.einsum("hd,nhd->hn", q[b].float(), kk) * scale
+        outs.append(torch.einsum("hn,nhd->hd", torch.softmax(s, -1), vv).to(q.dtype))
+    return torch.stack(outs)
+
+
+def greedy_sample(logits: torch.Tensor):
+    """Row argmax -> (ids int64 [B], max values fp32 [B])."""
+    if logits.is_cuda:
+        B, V = logits.shape
+        ids = torch.empty(B, dtype=torch.int64, device=logits.device)
+        vals = torch.empty(B, dtype=torch.float32, device=logits.device)
+        check(native.lib().rb_argmax(native.dtype_code(logits.dtype), ptr(logits), logits.stride(0), B, V,
+                                     ptr(ids), ptr(vals), stream_ptr()), "rb_argmax")
+        count_launch()
+        return ids, vals
+    vals, ids = logits.float().max(dim=-1)
+    return ids, vals
+
+
+def _rope(x, positions, heads, hd, theta):
+    """x [T, heads*hd] rotated in place by absolute positions [T]."""
+    T = x.shape[0]
+    if x.is_cuda:
+        native.rope_(x, T, 1, heads, hd, 0, theta, False, pos_ids=positions)
+        return x
+    xr = x.view(T, heads, hd).float()
+    half = hd // 2
+    inv = theta ** (-2.0 * torch.arange(half, dtype=torch.float32) / hd)
+    ang = positions.float()[:, None] * inv[None]
+    cs, sn = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    a, b = xr[..., :half], xr[..., half:]
+    x.copy_(torch.cat([a * cs - b * sn, b * cs + a * sn], -1).reshape(T, heads * hd).to(x.dtype))
+    return x
+
+
+@dataclass
+class Request:
+    rid: int
+    prompt: List[int]
+    max_new: int
+    arrival: float = 0.0
+    first_token_time: Optional[float] = None
+    finish_time: Optional[float] = None
+    output: List[int] = field(default_factory=list)
+
+
+class Engine:
+    def __init__(self, cfg: ServeConfig, device=None, group: Optional[dist.ProcessGroup] = None, seed: int = 0):
+        self.cfg = cfg
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = device or torch.device("cpu")
+        self.model = Int4LlamaShard(cfg, self.device, self.rank, self.world, seed)
+        self.cache = PagedKVCache(cfg, self.model.hkv_local, self.model.hd, self.device)
+        self.sched = Scheduler(cfg.num_blocks, cfg.block_size, cfg.max_batch, cfg.token_budget)
+        self.requests: Dict[int, Request] = {}
+        self.max_blocks = (cfg.model.seq_len + 512 + cfg.block_size - 1) // cfg.block_size
+        self.steps = 0
+        self.tokens_out = 0
+        self._ar = None
+        if self.world > 1 and cfg.comm_mode == "fused" and self.device.type == "cuda":
+            from ..parallel.symm import SymmArena
+            self.arena = SymmArena(64 << 20, group)
+            n = cfg.token_budget * cfg.model.d_model
+            self._ar_buf, _ = self.arena.alloc(n, cfg.dtype)
+            self._ar_flags = (self.arena.alloc_flags(self.world), self.arena.alloc_flags(self.world),
+                              self.arena.alloc_flags(self.world))
+            self._ar_cnt = self.arena.alloc_local_ints(1)
+            self._ar_found = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self._ar_epoch = 0
+            self.arena.barrier()
+            self._ar = True
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, rid: int, prompt: List[int], max_new: int, arrival: Optional[float] = None) -> bool:
+        if self.sched.add(rid, len(prompt), max_new) != 0:
+            return False
+        self.requests[rid] = Request(rid, list(prompt), max_new, arrival if arrival is not None else time.time())
+        return True
+
+    def has_work(self) -> bool:
+        return self.sched.num_waiting() + self.sched.num_running() > 0
+
+    # ------------------------------------------------------------------ TP all-reduce
+    def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return x
+        if self._ar:
+            from ..parallel import fused_ops
+            n = x.numel()
+            pad = (-n) % (8 * self.world)
+            buf = self._ar_buf[: n + pad]
+            buf[:n].copy_(x.reshape(-1))
+            if pad:
+                buf[n:].zero_()
+            self._ar_epoch += 1
+            ef, xf, nf = self._ar_flags
+            fused_ops.allreduce_unscale(self.arena, buf, enter_flags_off=ef, exit_flags_off=xf,
+                                        inf_flags_off=nf, epoch=self._ar_epoch, found_inf=self._ar_found,
+                                        done_counter=self._ar_cnt, ctas=8)
+            return buf[:n].view(x.shape).clone()
+        dist.all_reduce(x, group=self.group)
+        return x
+
+    # ------------------------------------------------------------------ forward
+    def _forward(self, tokens: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, attend):
+        """tokens/positions/slots: [T].  ``attend(layer, q [T,H,D], k [T,Hkv,D], v) -> [T,H,D]``
+        runs after this step's K/V were appended to the cache.  Returns hidden [T, d]."""
+        m, md = self.cfg.model, self.model
+        hd, H, Hkv = md.hd, md.h_local, md.hkv_local
+        x = F.embedding(tokens, md.emb)
+        T = x.shape[0]
+        for li, L in enumerate(md.layers):
+            h = F.rms_norm(x, L.ln1, m.rms_eps)
+            qkv = qmatmul_int4(h, L.qkv)
+            q = qkv[:, : H * hd]
+            k = qkv[:, H * hd: (H + Hkv) * hd]
+            v = qkv[:, (H + Hkv) * hd:]
+            _rope(q, positions, H, hd, m.rope_theta)
+            _rope(k, positions, Hkv, hd, m.rope_theta)
+            self.cache.append(li, k, v, slots)
+            o = attend(li, q.reshape(T, H, hd), k.reshape(T, Hkv, hd), v.reshape(T, Hkv, hd))
+            a = self._all_reduce(qmatmul_int4(o.reshape(T, H * hd).contiguous(), L.out))
+            x = x + a
+            h2 = F.rms_norm(x, L.ln2, m.rms_eps)
+            gu = qmatmul_int4(h2, L.gate_up)
+            d = self._all_reduce(qmatmul_int4(F.swiglu(gu), L.down))
+            x = x + d
+        return F.rms_norm(x, md.ln_f, m.rms_eps)
+
+    def _logits_argmax(self, hidden: torch.Tensor) -> torch.Tensor:
+        md = self.model
+        logits = native.gemm(hidden.contiguous(), md.head) if hidden.is_cuda else hidden @ md.head
+        ids, vals = greedy_sample(logits)
+        if self.world == 1:
+            return ids
+        ids = ids + self.rank * md.vocab_local
+        allv = [torch.empty_like(vals) for _ in range(self.world)]
+        alli = [torch.empty_like(ids) for _ in range(self.world)]
+        dist.all_gather(allv, vals, group=self.group)
+        dist.all_gather(alli, ids, group=self.group)
+        best = torch.stack(allv).argmax(dim=0)
+        return torch.stack(alli).gather(0, best[None]).squeeze(0)
+
+    def _slots(self, rid: int, start: int, n: int) -> torch.Tensor:
+        bs = self.cfg.block_size
+        table = self.sched.block_table(rid, self.max_blocks)
+        pos = torch.arange(start, start + n)
+        blk = torch.tensor(table, dtype=torch.int64)[pos // bs]
+        return (blk * bs + pos % bs).to(self.device)
+
+    # ------------------------------------------------------------------ one engine step
+    def step(self) -> List[int]:
+        """Runs one scheduling step; returns the ids of requests that finished."""
+        decode_ids, prefills = self.sched.schedule()
+        if not decode_ids and not prefills:
+            return []
+        dev, scale = self.device, 1.0 / math.sqrt(self.model.hd)
+        now_tokens: Dict[int, int] = {}
+        # ---- prompt chunks (one forward per sequence; whole prompts use FlashAttention directly)
+        for rid, start, n in prefills:
+            req = self.requests[rid]
+            seq = req.prompt + req.output   # a preempted sequence re-prefills what it had generated
+            toks = torch.tensor(seq[start:start + n], dtype=torch.int64, device=dev)
+            pos = torch.arange(start, start + n, dtype=torch.int64, device=dev)
+            slots = self._slots(rid, start, n)
+            table = torch.tensor(self.sched.block_table(rid, self.max_blocks), dtype=torch.int64, device=dev)
+
+            def attend(li, q, k, v, start=start, n=n, table=table):
+                if start == 0:
+                    return F.flash_attention(q[None], k[None], v[None], True, scale)[0]
+                # continuation chunk: keys/values of the prefix come from the paged cache
+                idx = torch.arange(0, start + n, device=dev)
+                bs = self.cfg.block_size
+                kk = self.cache.k[li][table[idx // bs], idx % bs]
+                vv = self.cache.v[li][table[idx // bs], idx % bs]
+                return F.flash_attention(q[None], kk[None], vv[None], True, scale)[0]
+
+            hidden = self._forward(toks, pos, slots, attend)
+            if start + n >= len(seq):
+                now_tokens[rid] = int(self._logits_argmax(hidden[-1:])[0])
+        # ---- decode batch
+        if decode_ids:
+            B = len(decode_ids)
+            last = [self.requests[r].output[-1] if self.requests[r].output else self.requests[r].prompt[-1]
+                    for r in decode_ids]
+            ctx = [len(self.requests[r].prompt) + len(self.requests[r].output) for r in decode_ids]
+            toks = torch.tensor(last, dtype=torch.int64, device=dev)
+            pos = torch.tensor([c - 1 for c in ctx], dtype=torch.int64, device=dev)
+            tables = torch.zeros((B, self.max_blocks), dtype=torch.int32)
+            slots = []
+            bs = self.cfg.block_size
+            for i, r in enumerate(decode_ids):
+                t = self.sched.block_table(r, self.max_blocks)
+                tables[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
+                slots.append(t[(ctx[i] - 1) // bs] * bs + (ctx[i] - 1) % bs)
+            tables = tables.to(dev)
+            slots_t = torch.tensor(slots, dtype=torch.int64, device=dev)
+            ctx_t = torch.tensor(ctx, dtype=torch.int32, device=dev)
+            max_ctx = max(ctx)
+
+            def attend_dec(li, q, k, v):
+                return paged_decode_attention(q.contiguous(), self.cache.k[li], self.cache.v[li], tables,
+                                              ctx_t, scale, max_ctx)
+
+            hidden = self._forward(toks, pos, slots_t, attend_dec)
+            ids = self._logits_argmax(hidden)
+            for r, t in zip(decode_ids, ids.tolist()):
+                now_tokens[r] = int(t)
+        t_now = time.time()
+        for rid, tok in now_tokens.items():
+            req = self.requests[rid]
+            if req.first_token_time is None:
+                req.first_token_time = t_now
+            req.output.append(tok)
+            self.tokens_out += 1
+        finished = self.sched.commit(decode_ids, prefills)
+        for rid in finished:
+            self.requests[rid].finish_time = t_now
+        self.steps += 1
+        return finished

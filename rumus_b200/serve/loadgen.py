@@ -1,0 +1,93 @@
+"""Poisson load generator / serving benchmark.
+
+Drives an ``Engine`` in-process with requests whose arrival times follow a Poisson process
+(default 32 req/s), prompt lengths U[128, 2048] and output lengths U[128, 512], random token ids —
+the serving configuration of the benchmark suite.  Reports generated tokens/s and the p50
+time-to-first-token.  Under tensor parallelism every rank runs the same schedule (same seed) and
+rank 0 reports.
+
+    python -m rumus_b200.serve.loadgen --requests 64            (1 GPU, scaled-down model)
+    torchrun --nproc-per-node 8 -m rumus_b200.serve.loadgen --model 7b --requests 256
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import random
+import time
+
+import torch
+import torch.distributed as dist
+
+from ..models.llama import LlamaConfig
+from .engine import Engine, ServeConfig
+
+
+def run(engine: Engine, n_requests: int, rate: float, prompt_rng=(128, 2048), out_rng=(128, 512),
+        seed: int = 0, vocab: int = 32000):
+    rnd = random.Random(seed)
+    t, arrivals = 0.0, []
+    for i in range(n_requests):
+        t += rnd.expovariate(rate)
+        arrivals.append((t, i + 1, [rnd.randrange(vocab) for _ in range(rnd.randint(*prompt_rng))],
+                         rnd.randint(*out_rng)))
+    t0 = time.time()
+    nxt, done, ttft = 0, 0, []
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    while done < n_requests:
+        now = time.time() - t0
+        while nxt < n_requests and arrivals[nxt][0] <= now:
+            a = arrivals[nxt]
+            engine.add_request(a[1], a[2], a[3], arrival=t0 + a[0])
+            nxt += 1
+        if not engine.has_work():
+            time.sleep(min(0.001, max(0.0, arrivals[nxt][0] - now)) if nxt < n_requests else 0.001)
+            continue
+        for rid in engine.step():
+            r = engine.requests.pop(rid)
+            ttft.append((r.first_token_time - r.arrival) * 1e3)
+            done += 1
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    wall = time.time() - t0
+    ttft.sort()
+    return {"requests": n_requests, "wall_s": wall, "generated_tokens": engine.tokens_out,
+            "tok_per_s": engine.tokens_out / wall, "ttft_p50_ms": ttft[len(ttft) // 2],
+            "ttft_p99_ms": ttft[min(len(ttft) - 1, int(len(ttft) * 0.99))], "steps": engine.steps,
+            "preemptions": engine.sched.preemptions()}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="small", choices=["small", "7b"])
+    ap.add_argument("--requests", type=int, default=64)
+    ap.add_argument("--rate", type=float, default=32.0)
+    ap.add_argument("--comm", default="nccl")
+    a = ap.parse_args(argv)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local) if torch.cuda.is_available() else torch.device("cpu")
+    if dev.type == "cuda":
+        torch.cuda.set_device(dev)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl" if dev.type == "cuda" else "gloo")
+    mc = LlamaConfig.llama_7b() if a.model == "7b" else LlamaConfig(
+        vocab_size=32000, seq_len=4096, d_model=1024, num_heads=8, num_kv_heads=8, num_layers=4, ffn_dim=2816)
+    cfg = ServeConfig(model=mc, num_blocks=8192 if a.model == "7b" else 2048, max_batch=128,
+                      token_budget=8192, comm_mode=a.comm,
+                      dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32,
+                      scale_dtype=torch.float16 if dev.type == "cuda" else torch.float32)
+    eng = Engine(cfg, dev)
+    res = run(eng, a.requests, a.rate, vocab=mc.vocab_size)
+    if int(os.environ.get("RANK", "0")) == 0:
+        res.update({"model": a.model, "tp": world, "rate_req_s": a.rate, "weights": "INT4 g128 fp16 scales"})
+        print(json.dumps(res))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
