@@ -1,0 +1,225 @@
+"""Distributed logic on CPU ranks (gloo): FSDP sharding/step, tensor parallel layers, 1F1B pipeline,
+TP x PP Llama, data parallel — each compared with the single-process computation."""
+import torch
+import torch.distributed as dist
+
+from dist_utils import run_ranks
+
+
+# ------------------------------------------------------------------ FSDP
+def _fsdp_worker(rank, world):
+    from rumus_b200.models import GPT, GPTConfig
+    from rumus_b200.parallel import FSDP
+    cfg = GPTConfig(vocab_size=64, seq_len=16, d_model=32, num_heads=2, num_layers=2, ffn_dim=64)
+    torch.manual_seed(0)
+    model = GPT(cfg)
+    eng = FSDP(model, lr=1e-2)
+    assert eng.mode == "cpu" and eng.world == world
+    g = torch.Generator().manual_seed(5)
+    data = torch.randint(0, 64, (3, world * 2, 17), generator=g)
+    for step in range(3):
+        tok = data[step, rank * 2:(rank + 1) * 2]
+        eng.zero_grad()
+        loss = model(tok[:, :-1], tok[:, 1:])
+        loss.backward()
+        eng.step()
+    return {k: v.clone() for k, v in model.state_dict().items()}
+
+
+def test_fsdp_matches_single_process():
+    from rumus_b200.models import GPT, GPTConfig
+    from rumus_b200.optim import Adam
+    world = 2
+    states = run_ranks(_fsdp_worker, world)
+    for k in states[0]:
+        assert torch.equal(states[0][k], states[1][k]), k       # replicas agree after all-gather
+    cfg = GPTConfig(vocab_size=64, seq_len=16, d_model=32, num_heads=2, num_layers=2, ffn_dim=64)
+    torch.manual_seed(0)
+    ref = GPT(cfg)
+    opt = Adam(ref.parameters(), lr=1e-2)
+    g = torch.Generator().manual_seed(5)
+    data = torch.randint(0, 64, (3, world * 2, 17), generator=g)
+    for step in range(3):
+        opt.zero_grad()
+        ref(data[step][:, :-1], data[step][:, 1:]).backward()
+        opt.step()
+    rs = ref.state_dict()
+    for k in rs:
+        if k.endswith("k_proj.bias"):
+            continue   # exact gradient is zero (softmax ignores a key bias): Adam amplifies rounding noise
+        assert torch.allclose(states[0][k], rs[k], atol=2e-5), k
+
+
+# ------------------------------------------------------------------ TP layers
+def _tp_worker(rank, world):
+    from rumus_b200.parallel.tp import ColumnParallelLinear, RowParallelLinear, TPContext, scatter_rows, gather_rows
+    tp = TPContext(mode="nccl")
+    torch.manual_seed(1)
+    w1 = torch.randn(16, 32) * 0.2
+    w2 = torch.randn(32, 16) * 0.2
+    b2 = torch.randn(16) * 0.1
+    x = torch.randn(8, 16)
+    col = ColumnParallelLinear(16, 32, tp, bias=False)
+    row = RowParallelLinear(32, 16, tp, bias=True)
+    n = 32 // world
+    with torch.no_grad():
+        col.weight.copy_(w1[:, rank * n:(rank + 1) * n])
+        row.weight.copy_(w2[rank * n:(rank + 1) * n])
+        row.bias.copy_(b2)
+    xs = x.clone().requires_grad_(True)
+    y_local = row(torch.relu(col(scatter_rows(xs, tp))))
+    y = gather_rows(y_local, tp)
+    (y ** 2).sum().backward()
+    xr = x.clone().requires_grad_(True)
+    w1r, w2r = w1.clone().requires_grad_(True), w2.clone().requires_grad_(True)
+    yr = torch.relu(xr @ w1r) @ w2r + b2
+    (yr ** 2).sum().backward()
+    assert torch.allclose(y, yr, atol=1e-5)
+    # every rank seeds the loss on the full gathered output, so input grads arrive summed T times
+    assert torch.allclose(xs.grad, xr.grad * world, atol=1e-4)
+    assert torch.allclose(col.weight.grad, w1r.grad[:, rank * n:(rank + 1) * n] * world, atol=1e-4)
+    assert torch.allclose(row.weight.grad, w2r.grad[rank * n:(rank + 1) * n] * world, atol=1e-4)
+    return True
+
+
+def test_tensor_parallel_linear_pair():
+    assert all(run_ranks(_tp_worker, 2))
+
+
+# ------------------------------------------------------------------ pipeline
+def _pp_worker(rank, world):
+    from rumus_b200.parallel.pp import PipelineStage, one_f_one_b_order
+    torch.manual_seed(2)
+    w = [torch.randn(8, 8) * 0.3 for _ in range(world)]
+    mine = w[rank].clone().requires_grad_(True)
+    M = 4
+    g = torch.Generator().manual_seed(3)
+    xs = [torch.randn(5, 8, generator=g) for _ in range(M)]
+    ts = [torch.randn(5, 8, generator=g) for _ in range(M)]
+    last = rank == world - 1
+
+    def fwd(inp):
+        if last:
+            x, t = inp
+            return ((torch.tanh(x @ mine) - t) ** 2).mean()
+        return torch.tanh(inp @ mine)
+
+    st = PipelineStage(fwd, rank, world, rank - 1 if rank > 0 else None, rank + 1 if not last else None,
+                       (5, 8), torch.float32, torch.device("cpu"))
+    log = []
+    loss = st.run(xs if rank == 0 else ts, ops_log=log)
+    assert log == one_f_one_b_order(rank, world, M)
+    # single-process reference
+    ws = [t.clone().requires_grad_(True) for t in w]
+    tot = 0
+    for x, t in zip(xs, ts):
+        h = x
+        for wi in ws:
+            h = torch.tanh(h @ wi)
+        tot = tot + ((h - t) ** 2).mean() / M
+    tot.backward()
+    assert torch.allclose(mine.grad, ws[rank].grad, atol=1e-6)
+    if last:
+        assert torch.allclose(loss, tot.detach(), atol=1e-6)
+    return True
+
+
+def test_pipeline_1f1b_matches_sequential():
+    assert all(run_ranks(_pp_worker, 3))
+
+
+def test_1f1b_order_properties():
+    from rumus_b200.parallel.pp import one_f_one_b_order
+    for P in (2, 4):
+        for M in (1, 4, 8):
+            for s in range(P):
+                ops = one_f_one_b_order(s, P, M)
+                assert [m for k, m in ops if k == "F"] == list(range(M))
+                assert [m for k, m in ops if k == "B"] == list(range(M))
+                live = peak = 0
+                for k, _ in ops:
+                    live += 1 if k == "F" else -1
+                    peak = max(peak, live)
+                assert peak <= min(P - s, M)     # bounded activation memory: the point of 1F1B
+
+
+# ------------------------------------------------------------------ TP x PP Llama
+def _tp_pp_worker(rank, world):
+    from rumus_b200.models import Llama, LlamaConfig
+    from rumus_b200.models.llama_parallel import ParallelLlamaStage
+    from rumus_b200.parallel.pp import PipelineStage
+    from rumus_b200.parallel.topology import build_topology
+    from rumus_b200.parallel.tp import TPContext
+    topo = build_topology(tp=2, pp=2)
+    cfg = LlamaConfig(vocab_size=64, seq_len=8, d_model=32, num_heads=2, num_kv_heads=2, num_layers=2,
+                      ffn_dim=64)
+    torch.manual_seed(11)
+    dense = Llama(cfg)
+    tp = TPContext(group=topo.tp_group, mode="nccl")
+    stage = ParallelLlamaStage(cfg, tp, topo.pp_idx, 2)
+    stage.load_dense(dense.state_dict())
+    B, S, M = 2, 8, 2
+    stage.set_microbatch_shape(B, S)
+    g = torch.Generator().manual_seed(12)
+    toks = [torch.randint(0, 64, (B, S + 1), generator=g) for _ in range(M)]
+    first, last = topo.pp_idx == 0, topo.pp_idx == 1
+    mbs = [t[:, :-1] for t in toks] if first else [t[:, 1:] for t in toks]
+    ps = PipelineStage(stage, topo.pp_idx, 2, topo.prev_stage_rank, topo.next_stage_rank,
+                       (B * S // 2, cfg.d_model), torch.float32, torch.device("cpu"))
+    loss = ps.run(mbs)
+    ref = sum(dense(t[:, :-1], t[:, 1:]) for t in toks) / M
+    ref.backward()
+    if last:
+        assert torch.allclose(loss, ref.detach(), atol=1e-5), (loss, ref)
+    # gradient of this rank's shard of the first block's down projection
+    per = cfg.num_layers // 2
+    gd = dense.blocks[topo.pp_idx * per].mlp.down_proj.weight.grad
+    f = cfg.ffn_dim // 2
+    mine = stage.blocks[0].down.weight.grad
+    assert torch.allclose(mine, gd[topo.tp_idx * f:(topo.tp_idx + 1) * f], atol=1e-5)
+    return True
+
+
+def test_llama_tp2_pp2_matches_dense():
+    assert all(run_ranks(_tp_pp_worker, 4))
+
+
+# ------------------------------------------------------------------ DP
+def _dp_worker(rank, world):
+    from rumus_b200.parallel.dp import DataParallel
+    import rumus_b200.nn as rnn
+    torch.manual_seed(20 + rank)      # different init per rank: broadcast must sync them
+    m = torch.nn.Sequential(rnn.Linear(6, 5), torch.nn.ReLU(), rnn.Linear(5, 2))
+    dp = DataParallel(m)
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(world * 3, 6, generator=g)
+    dp.zero_grad()
+    (m(x[rank * 3:(rank + 1) * 3]) ** 2).mean().backward()
+    found = dp.all_reduce_grads()
+    assert int(found.item()) == 0
+    return [p.detach().clone() for p in m.parameters()], [p.grad.clone() for p in m.parameters()], x
+
+
+def test_data_parallel_mean_gradients():
+    outs = run_ranks(_dp_worker, 2)
+    (p0, g0, x), (p1, g1, _) = outs
+    for a, b in zip(p0, p1):
+        assert torch.equal(a, b)
+    for a, b in zip(g0, g1):
+        assert torch.allclose(a, b, atol=1e-6)
+    import rumus_b200.nn as rnn
+    m = torch.nn.Sequential(rnn.Linear(6, 5), torch.nn.ReLU(), rnn.Linear(5, 2))
+    with torch.no_grad():
+        for p, v in zip(m.parameters(), p0):
+            p.copy_(v)
+    (m(x) ** 2).mean().backward()
+    for p, gref in zip(m.parameters(), g0):
+        assert torch.allclose(p.grad, gref, atol=1e-6)
+
+
+def test_topology_groups():
+    from rumus_b200.parallel.topology import groups_for
+    g = groups_for(8, tp=4, pp=2)
+    assert g["tp"] == [[0, 1, 2, 3], [4, 5, 6, 7]] and g["pp"][0] == [0, 4] and g["dp_size"] == 1
+    g = groups_for(8, tp=2, pp=2)
+    assert g["dp"][0] == [0, 4] and len(g["tp"]) == 4
