@@ -311,6 +311,15 @@ __global__ void signal_peers_kernel(PeerTable pt, long long flags_off, int epoch
   }
 }
 
+// Waits (bounded by `budget_ns`) for *flag >= epoch.  Used by the failure-detection tests: with a
+// flag that nothing sets the wait runs out, the status word gets RB_ERR_TIMEOUT_FLAG and the
+// kernel returns normally.
+__global__ void wait_flag_probe_kernel(const int* flag, int epoch, unsigned long long budget_ns,
+                                       int* status, int* result) {
+  if (threadIdx.x == 0 && blockIdx.x == 0)
+    *result = wait_flag_sys(flag, epoch, status, RB_ERR_TIMEOUT_FLAG, nullptr, budget_ns) ? 1 : 0;
+}
+
 static PeerTable make_table(void* const* bases, void* mc_base, int world, int rank) {
   PeerTable t;
   for (int i = 0; i < kMaxRanks; ++i) t.base[i] = i < world ? bases[i] : nullptr;
@@ -346,6 +355,14 @@ int rb_rs_adam(int dtype, void* const* bases, void* mc_base, int world, int rank
   if (dtype == rbh::DT_BF16) rs_adam_kernel<__nv_bfloat16><<<ctas, 512, 0, st>>>(p);
   else if (dtype == rbh::DT_F16) rs_adam_kernel<__half><<<ctas, 512, 0, st>>>(p);
   else return 31;
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
+}
+
+int rb_wait_flag_probe(const int* flag, int epoch, long long budget_ms, int* result, void* stream) {
+  using namespace rb;
+  wait_flag_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(
+      flag, epoch, (unsigned long long)budget_ms * 1000000ull, rbh::device_status_word(), result);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 3000 + (int)e;
 }

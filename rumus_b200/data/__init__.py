@@ -1,0 +1,5 @@
+"""Data engine (reference: rumus/src/data/): Dataset / DataItem / DataLoader and the `.rrec`
+record format."""
+from .dataset import DataItem, Dataset, TensorDataset, SyntheticTokens, SyntheticImages
+from .dataloader import DataLoader, collate
+from .record import RecordWriter, RecordDataset

@@ -1,0 +1,77 @@
+"""Observability: JSONL metrics sink per rank, device-side timers, NVTX ranges.
+
+The reference has none of this beyond ``eprintln!`` in the server and ``Trainer::epoch_avg_loss``
+(rumus/src/train.rs:78-85)."""
+from __future__ import annotations
+
+import contextlib
+import json
+import os
+import time
+from typing import Optional
+
+import torch
+
+
+class MetricsLogger:
+    """Appends one JSON object per ``log`` call to ``{dir}/metrics-rank{r}.jsonl``."""
+
+    def __init__(self, directory: Optional[str], rank: int = 0):
+        self.path = None
+        if directory:
+            os.makedirs(directory, exist_ok=True)
+            self.path = os.path.join(directory, f"metrics-rank{rank}.jsonl")
+        self.rank = rank
+
+    def log(self, **kv) -> dict:
+        rec = {"ts": time.time(), "rank": self.rank}
+        for k, v in kv.items():
+            if isinstance(v, torch.Tensor):
+                v = v.item() if v.numel() == 1 else v.tolist()
+            rec[k] = v
+        if self.path:
+            with open(self.path, "a") as f:
+                f.write(json.dumps(rec) + "\n")
+        return rec
+
+
+class DeviceTimer:
+    """CUDA-event timer on the current stream (wall clock on CPU)."""
+
+    def __init__(self):
+        self.cuda = torch.cuda.is_available()
+        self.t0 = None
+
+    def __enter__(self):
+        if self.cuda:
+            self.e0, self.e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        else:
+            self.t0 = time.perf_counter()
+        return self
+
+    def __exit__(self, *exc):
+        if self.cuda:
+            self.e1.record()
+            self.e1.synchronize()
+            self.ms = self.e0.elapsed_time(self.e1)
+        else:
+            self.ms = (time.perf_counter() - self.t0) * 1e3
+        return False
+
+
+@contextlib.contextmanager
+def trace_range(name: str):
+    """NVTX range (shows up in profiler timelines); no-op without CUDA."""
+    if torch.cuda.is_available():
+        torch.cuda.nvtx.range_push(name)
+        try:
+            yield
+        finally:
+            torch.cuda.nvtx.range_pop()
+    else:
+        yield
+
+
+def peak_memory_gb() -> float:
+    return torch.cuda.max_memory_allocated() / 2 ** 30 if torch.cuda.is_available() else 0.0

@@ -1,0 +1,138 @@
+"""CPU tests: C++ oracle vs PyTorch, data engine, graph, ONNX export, JIT, custom ops, checkpoints."""
+import os
+
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as TF
+
+import rumus_b200.nn as rnn
+from rumus_b200 import oracle
+from rumus_b200.ops import functional as F
+
+
+def test_cpu_oracle_agrees_with_pytorch():
+    torch.manual_seed(0)
+    a, b = torch.randn(7, 5), torch.randn(5, 9)
+    assert torch.allclose(oracle.matmul(a, b), a @ b, atol=1e-5)
+    x = torch.randn(6, 11)
+    assert torch.allclose(oracle.unary("gelu", x), TF.gelu(x, approximate="tanh"), atol=1e-6)
+    assert torch.allclose(oracle.unary("leaky_relu", x, 0.1), TF.leaky_relu(x, 0.1))
+    assert torch.allclose(oracle.softmax(x), torch.softmax(x, -1), atol=1e-6)
+    w, bb = torch.randn(11), torch.randn(11)
+    y, save = oracle.layer_norm(x, w, bb)
+    assert torch.allclose(y, TF.layer_norm(x, (11,), w, bb), atol=1e-5)
+    xr = x.clone().requires_grad_(True); wr = w.clone().requires_grad_(True); br = bb.clone().requires_grad_(True)
+    g = torch.randn(6, 11)
+    TF.layer_norm(xr, (11,), wr, br).backward(g)
+    dx, dw, db = oracle.layer_norm_backward(x, w, g, save)
+    assert torch.allclose(dx, xr.grad, atol=1e-5) and torch.allclose(dw, wr.grad, atol=1e-5)
+    t = torch.randint(0, 11, (6,))
+    loss, grad = oracle.cross_entropy(x, t)
+    xr = x.clone().requires_grad_(True)
+    lr = TF.cross_entropy(xr, t); lr.backward()
+    assert abs(loss - lr.item()) < 1e-5 and torch.allclose(grad, xr.grad, atol=1e-6)
+    img, k = torch.randn(2, 3, 9, 8), torch.randn(4, 3, 3, 3)
+    assert torch.allclose(oracle.conv2d(img, k, None, 2, 1, 1), TF.conv2d(img, k, None, 2, 1), atol=1e-4)
+    q, kk, v = torch.randn(3, 10, 8), torch.randn(3, 10, 8), torch.randn(3, 10, 8)
+    ref = F.sdpa_reference(q[:, :, None], kk[:, :, None], v[:, :, None], True)[:, :, 0]
+    assert torch.allclose(oracle.flash_attention(q, kk, v, True), ref, atol=1e-5)
+    from rumus_b200.nn.quant import QuantizedTensor
+    qw = QuantizedTensor.from_f32(torch.randn(64, 6), 32)
+    xm = torch.randn(3, 64)
+    assert torch.allclose(oracle.qmatmul_int4(xm, qw), xm @ qw.dequantize(), atol=1e-4)
+
+
+def test_dropout_matches_reference_hash_on_cpu_oracle():
+    x = torch.ones(4096)
+    y = oracle.dropout(x, 0.25, 99)
+    keep = (y != 0).float().mean().item()
+    assert abs(keep - 0.75) < 0.03 and torch.allclose(y[y != 0], torch.tensor(1 / 0.75))
+
+
+def test_data_engine(tmp_path):
+    from rumus_b200.data import DataLoader, RecordDataset, RecordWriter, SyntheticTokens, TensorDataset
+    p = str(tmp_path / "d.rrec")
+    w = RecordWriter.create(p)
+    xs = [torch.randn(3, 5) for _ in range(7)]
+    ys = [torch.randn(2).half() for _ in range(7)]
+    for x, y in zip(xs, ys):
+        w.append(x, y)
+    w.finish()
+    raw = open(p, "rb").read()
+    assert raw[:4] == b"RREC" and len(raw) % 4 == 0
+    for force_py in (False, True):
+        ds = RecordDataset(p, force_python=force_py)
+        assert len(ds) == 7
+        for i in range(7):
+            it = ds.get(i)
+            assert torch.equal(it.input, xs[i]) and torch.equal(it.target, ys[i]) and it.target.dtype == torch.float16
+    ds = TensorDataset(torch.arange(10).float()[:, None], torch.arange(10).float())
+    for workers in (0, 3):
+        dl = DataLoader(ds, 4, shuffle=False, drop_last=False, num_workers=workers)
+        got = torch.cat([b.input[:, 0] for b in dl])
+        assert torch.equal(got, torch.arange(10).float()) and len(dl) == 3
+    dl = DataLoader(ds, 4, shuffle=True, drop_last=True, num_workers=2)
+    seen = torch.cat([b.target for b in dl])
+    assert seen.numel() == 8 and len(set(seen.tolist())) == 8
+    # early teardown of a threaded iterator must not hang
+    it = iter(DataLoader(ds, 1, num_workers=2, prefetch_factor=1))
+    next(it); del it
+    st = SyntheticTokens(4, 16, 100, seed=0)
+    a = st.get(1)
+    assert torch.equal(a.input[1:], a.target[:-1])
+
+
+def test_graph_spmm_and_oracle():
+    from rumus_b200.graph import Graph
+    g = Graph.new(5, [0, 1, 2, 3, 0], [1, 2, 3, 4, 4], [1., 2., 3., 4., 5.])
+    x = torch.randn(5, 3, requires_grad=True)
+    y = g.spmm(x)
+    y.sum().backward()
+    A = g.adj.dense()
+    assert torch.allclose(y, A @ x) and torch.allclose(x.grad, A.t() @ torch.ones(5, 3))
+    assert torch.allclose(oracle.spmm(g.adj, x.detach()), A @ x.detach(), atol=1e-6)
+
+
+def test_onnx_export_structure(tmp_path):
+    from rumus_b200.io.onnx_export import export_onnx, parse_model
+
+    class M(rnn.Module):
+        def __init__(self):
+            super().__init__()
+            self.hidden, self.output = rnn.Linear(2, 8), rnn.Linear(8, 1)
+
+        def forward(self, x):
+            return self.output(F.relu(self.hidden(x)))
+
+    m = M()
+    p = str(tmp_path / "m.onnx")
+    pm = parse_model(export_onnx(m, [torch.randn(4, 2)], p))
+    assert os.path.getsize(p) > 0
+    assert (pm["ir_version"], pm["producer_name"], pm["opset"]) == (9, "rumus", 17)
+    assert [n["op_type"] for n in pm["nodes"]] == ["Gemm", "Relu", "Gemm"]
+    assert pm["initializers"]["hidden.weight"].shape == (2, 8)
+    assert torch.allclose(torch.from_numpy(pm["initializers"]["hidden.weight"].copy()), m.hidden.weight.detach())
+    cnn = nn.Sequential(rnn.Conv2d(1, 4, 3, 1, 1), nn.ReLU(), rnn.MaxPool2d(2), rnn.Flatten(), rnn.Linear(64, 4))
+    pm = parse_model(export_onnx(cnn, [torch.randn(2, 1, 8, 8)]))
+    assert [n["op_type"] for n in pm["nodes"]] == ["Conv", "Relu", "MaxPool", "Flatten", "Gemm"]
+    assert pm["initializers"]["0.weight"].shape == (4, 1, 3, 3)
+
+
+def test_jit_fused_chain_cpu_and_codegen():
+    from rumus_b200 import jit
+    a, b = torch.randn(100), torch.randn(100)
+    y = jit.compile(lambda x, z: ((x + z) * x).relu() * 0.5 + z.gelu(), a, b)
+    assert torch.allclose(y, torch.relu((a + b) * a) * 0.5 + TF.gelu(b, approximate="tanh"), atol=1e-6)
+    src, entry = jit.generate_cuda(2, [("add", 0, 1), ("relu", 2), ("scale", 3, 2.0)], torch.bfloat16, 4)
+    assert entry == "fused_kernel" and "fmaxf(v2, 0.0f)" in src and "float s0" in src
+
+
+def test_custom_op_cpu_path_and_backward():
+    from rumus_b200.ext import CustomOp, custom_forward
+    op = CustomOp("square_plus", "", "k", 2, lambda shapes: shapes[0], cpu_fn=lambda a, b: a * a + b,
+                  backward=lambda g, ins, out: (2 * ins[0] * g, g))
+    a = torch.randn(5, requires_grad=True); b = torch.randn(5, requires_grad=True)
+    y = custom_forward(op, a, b)
+    y.sum().backward()
+    assert torch.allclose(y, a * a + b) and torch.allclose(a.grad, 2 * a.detach()) and torch.allclose(b.grad, torch.ones(5))
