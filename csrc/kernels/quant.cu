@@ -161,9 +161,8 @@ __global__ void q8_quantize_kernel(const T* __restrict__ src, unsigned char* __r
   const float inv = absmax == 0.f ? 0.f : 127.f / absmax;
   unsigned char* out = dst + b * (4 + bs);
   if (threadIdx.x == 0) {
-    const __half h = __float2half_rn(scale);
-    const unsigned short bits = *reinterpret_cast<const unsigned short*>(&h);
-    out[0] = bits & 0xFF; out[1] = bits >> 8; out[2] = 0; out[3] = 0;
+    // 4-byte header: f16 scale in the low half, zero in the high half (blocks are 4-byte aligned)
+    *reinterpret_cast<uint32_t*>(out) = (uint32_t)__half_as_ushort(__float2half_rn(scale));
   }
   for (int i = threadIdx.x; i < bs; i += blockDim.x) {
     const long long e = e0 + i;

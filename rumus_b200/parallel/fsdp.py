@@ -52,13 +52,15 @@ class FSDP:
     def __init__(self, model: nn.Module, lr: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999,
                  eps: float = 1e-8, weight_decay: float = 0.0, adamw: bool = False,
                  group: Optional[dist.ProcessGroup] = None, mode: Optional[str] = None,
-                 unit_roots: Optional[list] = None, arena=None):
+                 unit_roots: Optional[list] = None, arena=None, local_only: bool = False):
         self.model = model
         self.lr, self.beta1, self.beta2, self.eps = lr, beta1, beta2, eps
         self.weight_decay, self.adamw = weight_decay, adamw
         self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        # ``local_only``: no sharding (the parameters of a tensor/pipeline-parallel stage are
+        # already this rank's own); the engine is then just the flat-arena fused optimizer
+        self.world = dist.get_world_size(group) if dist.is_initialized() and not local_only else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() and not local_only else 0
         mode = mode or os.environ.get("RB_BACKEND", "fused")
         dev = next(model.parameters()).device
         if self.world == 1:
