@@ -345,7 +345,7 @@ int rb_ag_gemm(int dtype, void* const* bases, int world, int rank, long long buf
   ap.epoch = epoch;
   ap.status = rbh::device_status_word();
   char* staging = reinterpret_cast<char*>(bases[rank]) + buf_off;
-  GemmArgs a;
+  GemmArgs a{};
   a.dtype = dtype; a.a_mn = 0; a.b_mn = b_mn;
   if (gather_a) {
     a.A = staging + operand_off; a.lda = K;
@@ -362,6 +362,7 @@ int rb_ag_gemm(int dtype, void* const* bases, int world, int rank, long long buf
   p.M = M; p.N = N; p.K = K; p.out = out; p.ldc = ldc; p.bias = bias; p.residual = residual;
   p.ldr = ldr; p.act = act; p.aux_out = aux_out; p.ldaux_out = N; p.alpha = 1.f;
   p.status = ap.status; p.group_m = 8;
+  p.sched = rbh::dynamic_tiles() ? rbh::next_sched_slot() : nullptr;
   auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   p.vec_ok = al(out) && (ldc * esz) % 16 == 0 && (!residual || (al(residual) && (ldr * esz) % 16 == 0)) &&
              (!aux_out || al(aux_out)) && (N * esz) % 16 == 0;
@@ -408,7 +409,7 @@ int rb_gemm_rs(int dtype, void* const* bases, int world, int rank, const void* A
   if (world > kMaxRanks) return 30;
   if (M % (128 * world) != 0 || N % 8 != 0) return 34;
   const int esz = 2;
-  GemmArgs a;
+  GemmArgs a{};
   a.dtype = dtype; a.a_mn = 0; a.b_mn = b_mn; a.A = A; a.lda = lda; a.B = B; a.ldb = ldb;
   a.max_ctas = 0;
   a.stream = (cudaStream_t)stream;
@@ -418,6 +419,7 @@ int rb_gemm_rs(int dtype, void* const* bases, int world, int rank, const void* A
   p.out = reinterpret_cast<char*>(bases[rank]) + partial_off;
   p.ldc = N; p.alpha = 1.f; p.vec_ok = 1; p.group_m = 8;
   p.status = rbh::device_status_word();
+  p.sched = rbh::dynamic_tiles() ? rbh::next_sched_slot() : nullptr;
   auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   if (!al(A) || !al(B) || (lda * esz) % 16 || (ldb * esz) % 16 || partial_off % 16) return 10;
   RsHooks h;

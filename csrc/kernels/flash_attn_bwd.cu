@@ -1,7 +1,7 @@
 // FlashAttention backward for sm_100a (tcgen05 + TMEM + TMA), head_dim 128.
 //
-// One CTA owns a 128-row K/V tile of one (batch, kv-head) and sweeps the query
-// tiles (64 rows each) that attend to it.  All five GEMMs of a tile pair run on
+// One CTA (14 warps: 8 softmax, 4 dQ drain, 1 TMA, 1 MMA) owns a 128-row K/V tile of
+// one (batch, kv-head) and sweeps the query tiles (64 rows each) that attend to it.  All five GEMMs of a tile pair run on
 // tcgen05 with M = 128 by working on transposed score tiles:
 //
 //   S^T  [kv x q] = K . Q^T                 (recomputed)
@@ -41,18 +41,27 @@ struct FaBwdCfg {
   static constexpr int Q_TILE = 64 * 128 * 2;     // [64 x 128] = 16 KB (2 sub-tiles of 8 KB)
   static constexpr int Q_SUB = 64 * 128;          // 8 KB
   static constexpr int PT_BYTES = 128 * 128;      // [128 kv x 64 q] = 16 KB
-  static constexpr int STAGES = 2;
-  static constexpr int SMEM_BYTES = 2 * KV_TILE + STAGES * 2 * Q_TILE + 2 * PT_BYTES +
-                                    2 * 2 * 64 * 4 /*lse,delta x2 stages*/ + 1024 + 256;
-  static constexpr int COL_ST = 0, COL_DPT = 64, COL_DQT = 128, COL_DV = 256, COL_DK = 384;
+  static constexpr int STAGES = 3;                // Q / dO ring
+  static constexpr int SMEM_BYTES = 2 * KV_TILE + STAGES * 2 * Q_TILE + 2 * 2 * PT_BYTES +
+                                    2 * 2 * 64 * 4 /*lse,delta x2 buffers*/ + 1024 + 256;
+  // TMEM columns.  S^T is double buffered; dP^T and dQ^T of one iteration share a buffer (dP^T has
+  // been consumed by the time dS^T exists), and that shared buffer is double buffered as well.
+  static constexpr int COL_ST = 0, COL_DPD = 128, COL_DV = 256, COL_DK = 384;
+  // warp roles
+  static constexpr int SOFTMAX_WARPS = 8, DRAIN_WARP0 = 8, TMA_WARP = 12, MMA_WARP = 13;
+  static constexpr int THREADS = 14 * 32;
 };
+static_assert(FaBwdCfg::SMEM_BYTES <= 227 * 1024, "shared memory budget");
 
-__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-
+// Pipeline (b = it & 1, s = it % 3):
+//   MMA warp      scores(it+1) -> S^T[b^1], dP^T[b^1]   |  wait P^T/dS^T(it)  |  dV, dK, dQ^T(it)
+//   softmax x8    S^T[b] -> P^T[b] (smem), dP^T[b] -> dS^T[b] (smem)           (two warps per lane
+//                 quarter, 32 query columns each)
+//   drain x4      dQ^T[b] -> red.add into the fp32 dQ buffer
+// so the exponentials of tile it+1, the accumulate GEMMs of tile it and the dQ atomics of tile
+// it-1 run at the same time.
 template <typename T>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(FaBwdCfg::THREADS, 1)
     fa_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                   const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
                   const FaBwdParams p) {
@@ -64,21 +73,22 @@ __global__ void __launch_bounds__(192, 1)
   uint8_t* sV = sK + C::KV_TILE;
   uint8_t* sQ = sV + C::KV_TILE;               // [STAGES][Q_TILE]
   uint8_t* sdO = sQ + C::STAGES * C::Q_TILE;   // [STAGES][Q_TILE]
-  uint8_t* sPT = sdO + C::STAGES * C::Q_TILE;
-  uint8_t* sdST = sPT + C::PT_BYTES;
-  float* sLse = reinterpret_cast<float*>(sdST + C::PT_BYTES);  // [2][64]
-  float* sDelta = sLse + 2 * 64;                                // [2][64]
+  uint8_t* sPT = sdO + C::STAGES * C::Q_TILE;  // [2][PT_BYTES]
+  uint8_t* sdST = sPT + 2 * C::PT_BYTES;       // [2][PT_BYTES]
+  float* sLse = reinterpret_cast<float*>(sdST + 2 * C::PT_BYTES);  // [2][64]
+  float* sDelta = sLse + 2 * 64;                                    // [2][64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sDelta + 2 * 64);
-  uint64_t* kv_full = bars;        // 1
-  uint64_t* q_full = bars + 1;     // [2]
-  uint64_t* q_empty = bars + 3;    // [2]
-  uint64_t* st_full = bars + 5;
-  uint64_t* dpt_full = bars + 6;
-  uint64_t* pds_ready = bars + 7;
-  uint64_t* dq_full = bars + 8;
-  uint64_t* dq_free = bars + 9;
-  uint64_t* all_done = bars + 10;
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* kv_full = bars;         // 1
+  uint64_t* q_full = bars + 1;      // [3]
+  uint64_t* q_empty = bars + 4;     // [3]
+  uint64_t* st_full = bars + 7;     // [2]
+  uint64_t* dpt_full = bars + 9;    // [2]
+  uint64_t* pds_ready = bars + 11;  // [2]
+  uint64_t* dq_full = bars + 13;    // [2]
+  uint64_t* dq_free = bars + 15;    // [2]
+  uint64_t* stat_full = bars + 17;  // [2]
+  uint64_t* all_done = bars + 19;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
   const int warp_idx = threadIdx.x >> 5;
@@ -103,20 +113,23 @@ __global__ void __launch_bounds__(192, 1)
     prefetch_tensormap(&tv);
     prefetch_tensormap(&tdo);
     mbar_init(smem_u32(kv_full), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(smem_u32(&q_full[s]), 1);
       mbar_init(smem_u32(&q_empty[s]), 1);
     }
-    mbar_init(smem_u32(st_full), 1);
-    mbar_init(smem_u32(dpt_full), 1);
-    mbar_init(smem_u32(pds_ready), 128);
-    mbar_init(smem_u32(dq_full), 1);
-    mbar_init(smem_u32(dq_free), 128);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&st_full[s]), 1);
+      mbar_init(smem_u32(&dpt_full[s]), 1);
+      mbar_init(smem_u32(&pds_ready[s]), C::SOFTMAX_WARPS * 32);
+      mbar_init(smem_u32(&dq_full[s]), 1);
+      mbar_init(smem_u32(&dq_free[s]), 128);
+      mbar_init(smem_u32(&stat_full[s]), 128);
+    }
     mbar_init(smem_u32(all_done), 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp_idx == 5) {
+  if (warp_idx == C::MMA_WARP) {
     tmem_alloc(smem_u32(tmem_ptr_smem), 512);
     tmem_relinquish();
   }
@@ -132,7 +145,7 @@ __global__ void __launch_bounds__(192, 1)
     q0 = (q_tile_start + ti) * C::BQ;
   };
 
-  if (warp_idx == 4) {
+  if (warp_idx == C::TMA_WARP) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0 && n_iters > 0) {
       mbar_arrive_expect_tx(smem_u32(kv_full), 2 * C::KV_TILE);
@@ -142,10 +155,10 @@ __global__ void __launch_bounds__(192, 1)
         tma_load_4d(smem_u32(sV + s * C::KV_SUB), &tv, smem_u32(kv_full), s * 64, kv0, hkv, b);
       }
       bool ok = true;
+      int st = 0;
+      uint32_t ph = 0;
       for (int it = 0; it < n_iters && ok; ++it) {
-        const int st = it & 1;
-        ok = mbar_wait(smem_u32(&q_empty[st]), ((it >> 1) & 1) ^ 1, abort_flag, p.status,
-                       RB_ERR_TIMEOUT_EMPTY);
+        ok = mbar_wait(smem_u32(&q_empty[st]), ph ^ 1, abort_flag, p.status, RB_ERR_TIMEOUT_EMPTY);
         if (!ok) break;
         int qh, q0;
         iter_coords(it, qh, q0);
@@ -156,11 +169,15 @@ __global__ void __launch_bounds__(192, 1)
           tma_load_4d(smem_u32(sQ + st * C::Q_TILE + s * C::Q_SUB), &tq, bar, s * 64, q0, qh, b);
           tma_load_4d(smem_u32(sdO + st * C::Q_TILE + s * C::Q_SUB), &tdo, bar, s * 64, q0, qh, b);
         }
+        if (++st == C::STAGES) {
+          st = 0;
+          ph ^= 1;
+        }
       }
       if (!ok)
         for (int i = 0; i < 64; ++i) __nanosleep(10000);
     }
-  } else if (warp_idx == 5) {
+  } else if (warp_idx == C::MMA_WARP) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0 && n_iters > 0) {
       constexpr int F = UmmaFormat<T>::value;
@@ -168,43 +185,66 @@ __global__ void __launch_bounds__(192, 1)
       constexpr uint32_t idesc_acc = make_idesc(F, 0, 1, 128, 128);  // P^T(A,Kmaj) x dO(B,N-maj)
       constexpr uint32_t idesc_dq = make_idesc(F, 1, 1, 128, 64);    // K^T(A,M-maj) x dS^T(B,N-maj)
       const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV);
-      const uint32_t pt_base = smem_u32(sPT), dst_base = smem_u32(sdST);
       bool ok = mbar_wait(smem_u32(kv_full), 0, abort_flag, p.status, RB_ERR_TIMEOUT_FULL);
-      auto issue_scores = [&](int it) {
-        const int st = it & 1;
+      // S^T and dP^T of tile `it` from Q/dO stage `st` into TMEM buffer it & 1
+      auto issue_scores = [&](int it, int st) {
+        const int buf = it & 1;
         const uint32_t q_base = smem_u32(sQ + st * C::Q_TILE);
         const uint32_t do_base = smem_u32(sdO + st * C::Q_TILE);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {  // K dim = head_dim 128
           const uint32_t oa = (k >> 2) * C::KV_SUB + (k & 3) * 32;
           const uint32_t ob = (k >> 2) * C::Q_SUB + (k & 3) * 32;
-          umma_f16(tmem_base + C::COL_ST, make_smem_desc_sw128(k_base + oa, 16, 1024),
+          umma_f16(tmem_base + C::COL_ST + buf * 64, make_smem_desc_sw128(k_base + oa, 16, 1024),
                    make_smem_desc_sw128(q_base + ob, 16, 1024), idesc_st, k != 0);
         }
-        umma_commit(smem_u32(st_full));
+        umma_commit(smem_u32(&st_full[buf]));
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t oa = (k >> 2) * C::KV_SUB + (k & 3) * 32;
           const uint32_t ob = (k >> 2) * C::Q_SUB + (k & 3) * 32;
-          umma_f16(tmem_base + C::COL_DPT, make_smem_desc_sw128(v_base + oa, 16, 1024),
+          umma_f16(tmem_base + C::COL_DPD + buf * 64, make_smem_desc_sw128(v_base + oa, 16, 1024),
                    make_smem_desc_sw128(do_base + ob, 16, 1024), idesc_st, k != 0);
         }
-        umma_commit(smem_u32(dpt_full));
+        umma_commit(smem_u32(&dpt_full[buf]));
       };
       if (ok) {
         ok = mbar_wait(smem_u32(&q_full[0]), 0, abort_flag, p.status, RB_ERR_TIMEOUT_FULL);
         if (ok) {
           tc_fence_after();
-          issue_scores(0);
+          issue_scores(0, 0);
         }
       }
+      int st = 0;            // Q/dO stage of tile `it`
+      uint32_t st_ph = 0;    // its ring phase
       for (int it = 0; it < n_iters && ok; ++it) {
-        const int st = it & 1;
-        ok = mbar_wait(smem_u32(pds_ready), it & 1, abort_flag, p.status, RB_ERR_TIMEOUT_FLAG);
+        const int buf = it & 1;
+        const uint32_t bph = (it >> 1) & 1;
+        int st_n = st + 1;
+        uint32_t ph_n = st_ph;
+        if (st_n == C::STAGES) {
+          st_n = 0;
+          ph_n ^= 1;
+        }
+        if (it + 1 < n_iters) {
+          ok = mbar_wait(smem_u32(&q_full[st_n]), ph_n, abort_flag, p.status, RB_ERR_TIMEOUT_FULL);
+          if (!ok) break;
+          if (it >= 1) {
+            // the dP^T/dQ^T buffer of tile it+1 last held dQ^T of tile it-1: wait for its drain
+            ok = mbar_wait(smem_u32(&dq_free[buf ^ 1]), ((it - 1) >> 1) & 1, abort_flag, p.status,
+                           RB_ERR_TIMEOUT_TMEM_EMPTY);
+            if (!ok) break;
+          }
+          tc_fence_after();
+          issue_scores(it + 1, st_n);
+        }
+        ok = mbar_wait(smem_u32(&pds_ready[buf]), bph, abort_flag, p.status, RB_ERR_TIMEOUT_FLAG);
         if (!ok) break;
         tc_fence_after();
         const uint32_t q_base = smem_u32(sQ + st * C::Q_TILE);
         const uint32_t do_base = smem_u32(sdO + st * C::Q_TILE);
+        const uint32_t pt_base = smem_u32(sPT + buf * C::PT_BYTES);
+        const uint32_t dst_base = smem_u32(sdST + buf * C::PT_BYTES);
         // dV += P^T . dO ; dK += dS^T . Q      (K dim = 64 query rows -> 4 steps)
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -218,165 +258,210 @@ __global__ void __launch_bounds__(192, 1)
                    make_smem_desc_sw128(q_base + k * 2048, C::Q_SUB, 1024), idesc_acc,
                    (it | k) != 0);
         }
-        // dQ^T = K^T . dS^T  (K dim = 128 kv rows -> 8 steps); needs the previous dQ^T drained
-        if (it > 0) {
-          ok = mbar_wait(smem_u32(dq_free), (it - 1) & 1, abort_flag, p.status,
-                         RB_ERR_TIMEOUT_TMEM_EMPTY);
-          if (!ok) break;
-          tc_fence_after();
-        }
+        // dQ^T = K^T . dS^T  (K dim = 128 kv rows -> 8 steps) into the buffer dP^T(it) occupied
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          umma_f16(tmem_base + C::COL_DQT,
+          umma_f16(tmem_base + C::COL_DPD + buf * 64,
                    make_smem_desc_sw128(k_base + k * 2048, C::KV_SUB, 1024),
                    make_smem_desc_sw128(dst_base + k * 2048, C::PT_BYTES, 1024), idesc_dq, k != 0);
         }
-        umma_commit(smem_u32(dq_full));
+        umma_commit(smem_u32(&dq_full[buf]));
         umma_commit(smem_u32(&q_empty[st]));
-        if (it + 1 < n_iters) {
-          ok = mbar_wait(smem_u32(&q_full[(it + 1) & 1]), ((it + 1) >> 1) & 1, abort_flag, p.status,
-                         RB_ERR_TIMEOUT_FULL);
-          if (!ok) break;
-          tc_fence_after();
-          issue_scores(it + 1);
-        }
+        st = st_n;
+        st_ph = ph_n;
       }
       if (ok) umma_commit(smem_u32(all_done));
     }
-  } else if (n_iters > 0) {
-    // ------------------------------ compute warps ------------------------------
-    const int t = threadIdx.x;  // kv row within tile == TMEM lane (also d index for dQ^T)
+  } else if (warp_idx >= C::DRAIN_WARP0 && warp_idx < C::DRAIN_WARP0 + 4) {
+    // ------------------------------ dQ drain warps ------------------------------
+    if (n_iters > 0) {
+      const int t = (warp_idx & 3) * 32 + lane;  // TMEM lane == d index of dQ^T
+      const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp_idx & 3) * 32) << 16);
+      bool ok = true;
+      for (int it = 0; it < n_iters; ++it) {
+        const int buf = it & 1;
+        int qh, q0;
+        iter_coords(it, qh, q0);
+        ok = mbar_wait(smem_u32(&dq_full[buf]), (it >> 1) & 1, abort_flag, p.status,
+                       RB_ERR_TIMEOUT_TMEM_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        float* dq_base =
+            p.dq_accum + ((static_cast<long long>(b) * p.Sq + q0) * p.H + qh) * C::HD + t;
+        const long long qstride = static_cast<long long>(p.H) * C::HD;
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32b_x32(lane_addr + C::COL_DPD + buf * 64, r0);
+        tmem_ld_32x32b_x32(lane_addr + C::COL_DPD + buf * 64 + 32, r1);
+        tmem_ld_wait();
+        // the values are in registers: hand the TMEM buffer back before the atomics
+        tc_fence_before();
+        mbar_arrive(smem_u32(&dq_free[buf]));
+        if (q0 + C::BQ <= p.Sq) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) atomicAdd(dq_base + i * qstride, __uint_as_float(r0[i]));
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            atomicAdd(dq_base + (32 + i) * qstride, __uint_as_float(r1[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (q0 + i < p.Sq) atomicAdd(dq_base + i * qstride, __uint_as_float(r0[i]));
+            if (q0 + 32 + i < p.Sq)
+              atomicAdd(dq_base + (32 + i) * qstride, __uint_as_float(r1[i]));
+          }
+        }
+      }
+    }
+  } else if (warp_idx < C::SOFTMAX_WARPS && n_iters > 0) {
+    // ------------------------------ softmax warps ------------------------------
+    const int tid = threadIdx.x;                // 0..255
+    const int t = (warp_idx & 3) * 32 + lane;   // kv row within tile == TMEM lane
+    const int half = warp_idx >> 2;             // which 32 query columns
     const int kv = kv0 + t;
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp_idx * 32) << 16);
-    bool ok = true;
-    for (int it = 0; it < n_iters; ++it) {
+    const bool kv_ok = kv < p.Sk;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp_idx & 3) * 32) << 16);
+    // threads 0..63 fetch lse (scaled to base 2), threads 64..127 fetch delta, one tile ahead
+    auto fetch_stat = [&](int it) -> float {
+      if (tid >= 128 || it >= n_iters) return 0.f;
       int qh, q0;
       iter_coords(it, qh, q0);
+      const int q = q0 + (tid & 63);
+      if (q >= p.Sq) return 0.f;
+      const long long idx = (static_cast<long long>(b) * p.H + qh) * p.Sq + q;
+      return tid < 64 ? p.lse[idx] * 1.4426950408889634f : p.delta[idx];
+    };
+    auto store_stat = [&](int buf, float v) {
+      if (tid < 64) sLse[buf * 64 + tid] = v;
+      else if (tid < 128) sDelta[buf * 64 + tid - 64] = v;
+    };
+    store_stat(0, fetch_stat(0));
+    if (tid < 128) mbar_arrive(smem_u32(&stat_full[0]));
+    bool ok = true;
+    for (int it = 0; it < n_iters; ++it) {
       const int buf = it & 1;
-      if (t < 64) {
-        const int q = q0 + t;
-        const long long idx = (static_cast<long long>(b) * p.H + qh) * p.Sq + q;
-        sLse[buf * 64 + t] = q < p.Sq ? p.lse[idx] * 1.4426950408889634f : 0.f;
-        sDelta[buf * 64 + t] = q < p.Sq ? p.delta[idx] : 0.f;
-      }
-      named_bar_sync(1, 128);
-      ok = mbar_wait(smem_u32(st_full), it & 1, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL);
+      const uint32_t bph = (it >> 1) & 1;
+      int qh, q0;
+      iter_coords(it, qh, q0);
+      const float next_stat = fetch_stat(it + 1);
+      ok = mbar_wait(smem_u32(&stat_full[buf]), bph, abort_flag, p.status, RB_ERR_TIMEOUT_FLAG);
+      ok = ok && mbar_wait(smem_u32(&st_full[buf]), bph, abort_flag, p.status,
+                           RB_ERR_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      float pr[64];
-      const bool kv_ok = kv < p.Sk;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      const float* lse_t = sLse + buf * 64 + half * 32;
+      const float* delta_t = sDelta + buf * 64 + half * 32;
+      // no masking needed when the whole tile is in range and below the causal diagonal
+      const bool full_tile = kv0 + C::BKV <= p.Sk && q0 + C::BQ <= p.Sq &&
+                             (!p.causal || kv0 + C::BKV - 1 <= q0 + off);
+      float pr[32];
+      {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(lane_addr + C::COL_ST + c * 32, r);
+        tmem_ld_32x32b_x32(lane_addr + C::COL_ST + buf * 64 + half * 32, r);
         tmem_ld_wait();
+        if (full_tile) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int qi = c * 32 + i;
-          const int q = q0 + qi;
-          const bool valid = kv_ok && q < p.Sq && (!p.causal || kv <= q + off);
-          const float v = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -sLse[buf * 64 + qi]));
-          pr[qi] = valid ? v : 0.f;
+          for (int i = 0; i < 32; ++i)
+            pr[i] = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -lse_t[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int q = q0 + half * 32 + i;
+            const bool valid = kv_ok && q < p.Sq && (!p.causal || kv <= q + off);
+            const float v = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -lse_t[i]));
+            pr[i] = valid ? v : 0.f;
+          }
         }
       }
-      // P^T row -> smem (8 chunks of 16 bytes, swizzled)
+      if (it >= 2) {
+        // P^T / dS^T buffers of tile it-2 must have been consumed by its accumulate GEMMs
+        ok = mbar_wait(smem_u32(&dq_full[buf]), ((it - 2) >> 1) & 1, abort_flag, p.status,
+                       RB_ERR_TIMEOUT_TMEM_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      // this thread's 32 columns of P^T row t -> smem (4 chunks of 16 bytes, swizzled)
       {
-        uint8_t* rowp = sPT + t * 128;
+        uint8_t* rowp = sPT + buf * C::PT_BYTES + t * 128;
 #pragma unroll
-        for (int cc = 0; cc < 8; ++cc) {
-          const uint4 v = make_uint4(pack2<T>(pr[cc * 8], pr[cc * 8 + 1]), pack2<T>(pr[cc * 8 + 2], pr[cc * 8 + 3]),
-                                     pack2<T>(pr[cc * 8 + 4], pr[cc * 8 + 5]), pack2<T>(pr[cc * 8 + 6], pr[cc * 8 + 7]));
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const int cc = half * 4 + c4;
+          const uint4 v = make_uint4(pack2<T>(pr[c4 * 8], pr[c4 * 8 + 1]),
+                                     pack2<T>(pr[c4 * 8 + 2], pr[c4 * 8 + 3]),
+                                     pack2<T>(pr[c4 * 8 + 4], pr[c4 * 8 + 5]),
+                                     pack2<T>(pr[c4 * 8 + 6], pr[c4 * 8 + 7]));
           *reinterpret_cast<uint4*>(rowp + ((cc ^ (t & 7)) << 4)) = v;
         }
       }
-      ok = mbar_wait(smem_u32(dpt_full), it & 1, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL);
+      ok = mbar_wait(smem_u32(&dpt_full[buf]), bph, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(lane_addr + C::COL_DPT + c * 32, r);
+        tmem_ld_32x32b_x32(lane_addr + C::COL_DPD + buf * 64 + half * 32, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int qi = c * 32 + i;
-          pr[qi] = pr[qi] * (__uint_as_float(r[i]) - sDelta[buf * 64 + qi]) * p.scale;
-        }
+        for (int i = 0; i < 32; ++i)
+          pr[i] = pr[i] * (__uint_as_float(r[i]) - delta_t[i]) * p.scale;
       }
       {
-        uint8_t* rowp = sdST + t * 128;
+        uint8_t* rowp = sdST + buf * C::PT_BYTES + t * 128;
 #pragma unroll
-        for (int cc = 0; cc < 8; ++cc) {
-          const uint4 v = make_uint4(pack2<T>(pr[cc * 8], pr[cc * 8 + 1]), pack2<T>(pr[cc * 8 + 2], pr[cc * 8 + 3]),
-                                     pack2<T>(pr[cc * 8 + 4], pr[cc * 8 + 5]), pack2<T>(pr[cc * 8 + 6], pr[cc * 8 + 7]));
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const int cc = half * 4 + c4;
+          const uint4 v = make_uint4(pack2<T>(pr[c4 * 8], pr[c4 * 8 + 1]),
+                                     pack2<T>(pr[c4 * 8 + 2], pr[c4 * 8 + 3]),
+                                     pack2<T>(pr[c4 * 8 + 4], pr[c4 * 8 + 5]),
+                                     pack2<T>(pr[c4 * 8 + 6], pr[c4 * 8 + 7]));
           *reinterpret_cast<uint4*>(rowp + ((cc ^ (t & 7)) << 4)) = v;
         }
       }
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(smem_u32(pds_ready));
-      // drain dQ^T: lane t holds d = t, 64 query columns
-      ok = mbar_wait(smem_u32(dq_full), it & 1, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      float* dq_base = p.dq_accum + ((static_cast<long long>(b) * p.Sq + q0) * p.H + qh) * C::HD + t;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(lane_addr + C::COL_DQT + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int qi = c * 32 + i;
-          if (q0 + qi < p.Sq)
-            atomicAdd(dq_base + static_cast<long long>(qi) * p.H * C::HD, __uint_as_float(r[i]));
+      mbar_arrive(smem_u32(&pds_ready[buf]));
+      // statistics of the next tile go to buffer buf^1, last read in tile it-1: every softmax
+      // thread has left that tile once its P^T/dS^T barrier has completed
+      if (warp_idx < 4 && it + 1 < n_iters) {
+        if (it >= 1) {
+          ok = mbar_wait(smem_u32(&pds_ready[buf ^ 1]), ((it - 1) >> 1) & 1, abort_flag, p.status,
+                         RB_ERR_TIMEOUT_FLAG);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
         }
+        store_stat(buf ^ 1, next_stat);
+        mbar_arrive(smem_u32(&stat_full[buf ^ 1]));
       }
-      tc_fence_before();
-      mbar_arrive(smem_u32(dq_free));
     }
     if (ok) {
       ok = mbar_wait(smem_u32(all_done), 0, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
+      // warps 0-3 store dV, warps 4-7 store dK
       tc_fence_after();
       const long long orow = ((static_cast<long long>(b) * p.Sk + kv) * p.Hkv + hkv) * C::HD;
-      T* dkp = reinterpret_cast<T*>(p.dk) + orow;
-      T* dvp = reinterpret_cast<T*>(p.dv) + orow;
+      T* outp = reinterpret_cast<T*>(half == 0 ? p.dv : p.dk) + orow;
+      const uint32_t col0 = half == 0 ? C::COL_DV : C::COL_DK;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(lane_addr + C::COL_DV + c * 32, r);
+        tmem_ld_32x32b_x32(lane_addr + col0 + c * 32, r);
         tmem_ld_wait();
-        if (kv < p.Sk) {
+        if (kv_ok) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint4 v;
             T* e = reinterpret_cast<T*>(&v);
 #pragma unroll
             for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(__uint_as_float(r[q * 8 + i]));
-            *reinterpret_cast<uint4*>(dvp + c * 32 + q * 8) = v;
-          }
-        }
-        tmem_ld_32x32b_x32(lane_addr + C::COL_DK + c * 32, r);
-        tmem_ld_wait();
-        if (kv < p.Sk) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 v;
-            T* e = reinterpret_cast<T*>(&v);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(__uint_as_float(r[q * 8 + i]));
-            *reinterpret_cast<uint4*>(dkp + c * 32 + q * 8) = v;
+            *reinterpret_cast<uint4*>(outp + c * 32 + q * 8) = v;
           }
         }
       }
     }
-  } else {
+  } else if (n_iters == 0) {
     // no query tile attends to this K/V tile: gradients are zero
     const int t = threadIdx.x;
     const int kv = kv0 + t;
@@ -392,7 +477,7 @@ __global__ void __launch_bounds__(192, 1)
 
   tc_fence_before();
   __syncthreads();
-  if (warp_idx == 5) {
+  if (warp_idx == C::MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -447,7 +532,7 @@ int launch_fa_bwd(int dtype, const void* q, const void* k, const void* v, const 
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   if (e != cudaSuccess) return 2000 + (int)e;
   dim3 grid((p.Sk + C::BKV - 1) / C::BKV, p.Hkv, p.B);
-  kern<<<grid, 192, C::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+  kern<<<grid, C::THREADS, C::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
   e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 3000 + (int)e;
 }

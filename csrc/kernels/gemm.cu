@@ -97,7 +97,7 @@ int rb_gemm(int dtype, int a_mn, int b_mn, const void* A, long long lda, const v
             float alpha, int path, int bn, int max_ctas, int* path_used, void* stream) {
   using namespace rb;
   if (M <= 0 || N <= 0) return 0;
-  GemmArgs a;
+  GemmArgs a{};
   a.dtype = dtype; a.a_mn = a_mn; a.b_mn = b_mn; a.A = A; a.lda = lda; a.B = B; a.ldb = ldb;
   a.max_ctas = max_ctas;
   a.stream = (cudaStream_t)stream;
@@ -107,6 +107,7 @@ int rb_gemm(int dtype, int a_mn, int b_mn, const void* A, long long lda, const v
   p.ldaux_in = ldaux_in; p.act = act; p.dact = dact; p.out_f32 = out_f32; p.alpha = alpha;
   p.status = rbh::device_status_word();
   p.group_m = 8;
+  p.sched = rbh::dynamic_tiles() ? rbh::next_sched_slot() : nullptr;
   const int esz = dtype == rbh::DT_F32 ? 4 : 2;
   const int osz = out_f32 ? 4 : esz;
   p.vec_ok = aligned16(out) && (ldc * osz) % 16 == 0 &&
@@ -143,7 +144,7 @@ int rb_bmm_simt(int dtype, int a_mn, int b_mn, const void* A, long long lda, lon
                 void* out, long long ldc, long long scb, int out_f32, float alpha, void* stream) {
   using namespace rb;
   if (M <= 0 || N <= 0 || batch <= 0) return 0;
-  GemmArgs a;
+  GemmArgs a{};
   a.dtype = dtype; a.a_mn = a_mn; a.b_mn = b_mn; a.A = A; a.lda = lda; a.B = B; a.ldb = ldb;
   a.max_ctas = 0;
   a.stream = (cudaStream_t)stream;

@@ -45,6 +45,7 @@ struct GemmParams {
   float alpha;
   int* status;           // device status word
   int group_m;           // raster group (m-tiles walked before advancing n)
+  int* sched;            // device int[2] {next tile, finished CTAs} for dynamic tile scheduling, or null
 };
 
 struct NoHooks {
@@ -82,11 +83,12 @@ struct GemmCfg {
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int NUM_THREADS = 320;
   static constexpr int EPI_WARPS = 8;
-  static constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 384 /*barriers, scheduler ring*/;
 };
 
 // Barrier over the 320 GEMM threads (warps 0..9).  The fused collective kernels launch wider
 // CTAs whose extra warps have a different role or have exited, so the count is explicit.
+constexpr int kSchedSlots = 4;
 constexpr int kGemmThreads = 320;
 constexpr int kGemmEpiWarps = 8;
 __device__ __forceinline__ void cta_sync_gemm() {
@@ -210,8 +212,11 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
   uint64_t* empty_bar = bars + STAGES;
   uint64_t* tmem_full_bar = bars + 2 * STAGES;
   uint64_t* tmem_empty_bar = bars + 2 * STAGES + 2;
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint64_t* sched_full = bars + 2 * STAGES + 4;    // [kSchedSlots] producer -> MMA / epilogue
+  uint64_t* sched_empty = sched_full + kSchedSlots;  // [kSchedSlots]
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(sched_empty + kSchedSlots);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+  volatile int* tile_ring = abort_flag + 1;           // [kSchedSlots] tile ids, -1 = no more work
 
   const int warp_idx = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -226,6 +231,10 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&tmem_full_bar[s]), 1);
       mbar_init(smem_u32(&tmem_empty_bar[s]), kGemmEpiWarps);
+    }
+    for (int s = 0; s < kSchedSlots; ++s) {
+      mbar_init(smem_u32(&sched_full[s]), 1);
+      mbar_init(smem_u32(&sched_empty[s]), 1 + kGemmEpiWarps);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -265,7 +274,30 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = cta_rank; tile < total_tiles && ok; tile += num_ctas) {
+      int static_tile = cta_rank, slot = 0;
+      uint32_t slot_phase = 0;
+      while (ok) {
+        // Tile source: a device-wide atomic counter when p.sched is set (CTAs that start late —
+        // e.g. because a communication kernel holds some SMs — simply take fewer tiles), else
+        // the static stride.  The id is handed to the MMA and epilogue warps through a small ring.
+        int tile;
+        if (p.sched) {
+          tile = atomicAdd(p.sched, 1);
+        } else {
+          tile = static_tile;
+          static_tile += num_ctas;
+        }
+        if (tile >= total_tiles) tile = -1;
+        ok = mbar_wait(smem_u32(&sched_empty[slot]), slot_phase ^ 1, abort_flag, p.status,
+                       RB_ERR_TIMEOUT_EMPTY);
+        if (!ok) break;
+        tile_ring[slot] = tile;
+        mbar_arrive(smem_u32(&sched_full[slot]));
+        if (++slot == kSchedSlots) {
+          slot = 0;
+          slot_phase ^= 1;
+        }
+        if (tile < 0) break;
         int m_idx, n_idx;
         tile_coords(tile, m_idx, n_idx);
         ok = hooks.before_tile_load(m_idx, n_idx, abort_flag, p.status);
@@ -314,7 +346,19 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = cta_rank; tile < total_tiles && ok; tile += num_ctas) {
+      int slot = 0;
+      uint32_t slot_phase = 0;
+      while (ok) {
+        ok = mbar_wait(smem_u32(&sched_full[slot]), slot_phase, abort_flag, p.status,
+                       RB_ERR_TIMEOUT_FULL);
+        if (!ok) break;
+        const int tile = tile_ring[slot];
+        mbar_arrive(smem_u32(&sched_empty[slot]));
+        if (++slot == kSchedSlots) {
+          slot = 0;
+          slot_phase ^= 1;
+        }
+        if (tile < 0) break;
         ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status,
                        RB_ERR_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
@@ -359,7 +403,21 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = cta_rank; tile < total_tiles && ok; tile += num_ctas) {
+    int slot = 0;
+    uint32_t slot_phase = 0;
+    while (ok) {
+      ok = mbar_wait(smem_u32(&sched_full[slot]), slot_phase, abort_flag, p.status,
+                     RB_ERR_TIMEOUT_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const int tile = tile_ring[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sched_empty[slot]));
+      if (++slot == kSchedSlots) {
+        slot = 0;
+        slot_phase ^= 1;
+      }
+      if (tile < 0) break;
       int m_idx, n_idx;
       tile_coords(tile, m_idx, n_idx);
       ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status,
@@ -403,6 +461,15 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
   if (warp_idx == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && p.sched) {
+    // the last CTA to leave re-arms the scheduler words for the next launch that uses this slot
+    const int prev = atomicAdd(p.sched + 1, 1);
+    if (prev == num_ctas - 1) {
+      p.sched[0] = 0;
+      p.sched[1] = 0;
+      __threadfence();
+    }
   }
 }
 

@@ -4,6 +4,8 @@
 #include "sm100_common.cuh"
 
 #include <cudaTypedefs.h>
+#include <atomic>
+#include <cstdlib>
 #include <mutex>
 #include <stdio.h>
 
@@ -85,6 +87,33 @@ int read_and_clear_status() {
   return v;
 }
 
+int* next_sched_slot() {
+  static std::atomic<unsigned> counter{0};
+  static int* g_sched[kMaxDevices] = {nullptr};
+  constexpr int kSlots = 256;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= kMaxDevices) return nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_sched[dev]) {
+      int* p = nullptr;
+      if (cudaMalloc(&p, kSlots * 2 * sizeof(int)) != cudaSuccess) return nullptr;
+      cudaMemset(p, 0, kSlots * 2 * sizeof(int));
+      g_sched[dev] = p;
+    }
+  }
+  return g_sched[dev] + 2 * (counter.fetch_add(1) % kSlots);
+}
+
+bool dynamic_tiles() {
+  static const bool on = [] {
+    const char* e = std::getenv("RB_GEMM_DYNAMIC");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 int sm_count() {
   int dev = 0;
   cudaGetDevice(&dev);
@@ -105,5 +134,5 @@ extern "C" {
 int rb_read_status() { return rbh::read_and_clear_status(); }
 int rb_sm_count() { return rbh::sm_count(); }
 // Make sure the status word exists (call once per device before graph capture).
-int rb_init_device() { return rbh::device_status_word() ? 0 : -1; }
+int rb_init_device() { return (rbh::device_status_word() && rbh::next_sched_slot()) ? 0 : -1; }
 }

@@ -425,4 +425,10 @@ int read_and_clear_status();
 
 int sm_count();
 
+// A pair of zero-initialised ints {next tile, finished CTAs} for one dynamically scheduled GEMM
+// launch.  Slots rotate (256 of them) so launches that overlap on the device never share one.
+int* next_sched_slot();
+// Whether tensor-core GEMMs take tiles from the atomic counter (env RB_GEMM_DYNAMIC, default on).
+bool dynamic_tiles();
+
 }  // namespace rbh
