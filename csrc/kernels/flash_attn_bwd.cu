@@ -26,8 +26,9 @@ struct FaBwdParams {
   int B, H, Hkv, Sq, Sk;
   int causal;
   float scale, scale_log2;
-  const float* lse;    // [B,H,Sq]
-  const float* delta;  // [B,H,Sq]  rowsum(dO * O)
+  const float* lse2;   // [B,H,sq_pad]  log-sum-exp in base-2 units (lse * log2 e)
+  const float* delta;  // [B,H,sq_pad]  rowsum(dO * O)
+  int sq_pad;          // row stride of both, a multiple of 64; padding holds finite values
   float* dq_accum;     // [B,Sq,H,128] fp32, zero-initialised
   void* dk;            // [B,Sk,Hkv,128]
   void* dv;            // [B,Sk,Hkv,128]
@@ -42,10 +43,14 @@ struct FaBwdCfg {
   static constexpr int Q_SUB = 64 * 128;          // 8 KB
   static constexpr int PT_BYTES = 128 * 128;      // [128 kv x 64 q] = 16 KB
   static constexpr int STAGES = 3;                // Q / dO ring
-  static constexpr int SMEM_BYTES = 2 * KV_TILE + STAGES * 2 * Q_TILE + 2 * 2 * PT_BYTES +
-                                    2 * 2 * 64 * 4 /*lse,delta x2 buffers*/ + 1024 + 256;
+  static constexpr int SMEM_BYTES = 2 * KV_TILE + STAGES * 2 * Q_TILE + 2 * PT_BYTES +
+                                    STAGES * 2 * 64 * 4 /*lse2, delta per stage*/ + 1024 + 256;
   // TMEM columns.  S^T is double buffered; dP^T and dQ^T of one iteration share a buffer (dP^T has
   // been consumed by the time dS^T exists), and that shared buffer is double buffered as well.
+  // Once a softmax warp has read its 32 fp32 columns of S^T it writes P^T (16-bit, two values per
+  // column) over the first 16 of them and dS^T over the last 16: the dV and dK GEMMs take their A
+  // operand from there, which keeps 48 KB per tile off the shared-memory port (the port, not the
+  // tensor pipe, is what limits this kernel).
   static constexpr int COL_ST = 0, COL_DPD = 128, COL_DV = 256, COL_DK = 384;
   // warp roles
   static constexpr int SOFTMAX_WARPS = 8, DRAIN_WARP0 = 8, TMA_WARP = 12, MMA_WARP = 13;
@@ -73,25 +78,22 @@ __global__ void __launch_bounds__(FaBwdCfg::THREADS, 1)
   uint8_t* sV = sK + C::KV_TILE;
   uint8_t* sQ = sV + C::KV_TILE;               // [STAGES][Q_TILE]
   uint8_t* sdO = sQ + C::STAGES * C::Q_TILE;   // [STAGES][Q_TILE]
-  uint8_t* sPT = sdO + C::STAGES * C::Q_TILE;  // [2][PT_BYTES]
-  uint8_t* sdST = sPT + 2 * C::PT_BYTES;       // [2][PT_BYTES]
-  float* sLse = reinterpret_cast<float*>(sdST + 2 * C::PT_BYTES);  // [2][64]
-  float* sDelta = sLse + 2 * 64;                                    // [2][64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sDelta + 2 * 64);
+  uint8_t* sdST = sdO + C::STAGES * C::Q_TILE;  // [2][PT_BYTES]  (B operand of the dQ^T GEMM)
+  float* sStat = reinterpret_cast<float*>(sdST + 2 * C::PT_BYTES);  // [STAGES][lse2 64 | delta 64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + C::STAGES * 128);
   uint64_t* kv_full = bars;         // 1
   uint64_t* q_full = bars + 1;      // [3]
   uint64_t* q_empty = bars + 4;     // [3]
   uint64_t* st_full = bars + 7;     // [2]
   uint64_t* dpt_full = bars + 9;    // [2]
-  uint64_t* pds_ready = bars + 11;  // [2]
+  uint64_t* pds_ready = bars + 11;  // [2]  P^T, dS^T of the tile are in place
   uint64_t* dq_full = bars + 13;    // [2]
   uint64_t* dq_free = bars + 15;    // [2]
-  uint64_t* stat_full = bars + 17;  // [2]
   uint64_t* all_done = bars + 19;
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
-  const int warp_idx = threadIdx.x >> 5;
+  const int warp_idx = uniform_warp_idx();
   const int lane = threadIdx.x & 31;
   const int kv_tile = blockIdx.x;
   const int hkv = blockIdx.y, b = blockIdx.z;
@@ -123,7 +125,6 @@ __global__ void __launch_bounds__(FaBwdCfg::THREADS, 1)
       mbar_init(smem_u32(&pds_ready[s]), C::SOFTMAX_WARPS * 32);
       mbar_init(smem_u32(&dq_full[s]), 1);
       mbar_init(smem_u32(&dq_free[s]), 128);
-      mbar_init(smem_u32(&stat_full[s]), 128);
     }
     mbar_init(smem_u32(all_done), 1);
     *abort_flag = 0;
@@ -163,7 +164,13 @@ __global__ void __launch_bounds__(FaBwdCfg::THREADS, 1)
         int qh, q0;
         iter_coords(it, qh, q0);
         const uint32_t bar = smem_u32(&q_full[st]);
-        mbar_arrive_expect_tx(bar, 2 * C::Q_TILE);
+        mbar_arrive_expect_tx(bar, 2 * C::Q_TILE + 2 * 64 * 4);
+        {
+          // this tile's 64 row statistics ride on the same barrier
+          const long long srow = (static_cast<long long>(b) * p.H + qh) * p.sq_pad + q0;
+          bulk_load_1d(smem_u32(sStat + st * 128), p.lse2 + srow, 64 * 4, bar);
+          bulk_load_1d(smem_u32(sStat + st * 128 + 64), p.delta + srow, 64 * 4, bar);
+        }
 #pragma unroll
         for (int s = 0; s < C::SUB; ++s) {
           tma_load_4d(smem_u32(sQ + st * C::Q_TILE + s * C::Q_SUB), &tq, bar, s * 64, q0, qh, b);
@@ -179,7 +186,7 @@ __global__ void __launch_bounds__(FaBwdCfg::THREADS, 1)
     }
   } else if (warp_idx == C::MMA_WARP) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0 && n_iters > 0) {
+    if (n_iters > 0) {   // whole warp; one elected lane issues each instruction
       constexpr int F = UmmaFormat<T>::value;
       constexpr uint32_t idesc_st = make_idesc(F, 0, 0, 128, 64);    // K(A,Kmaj) x Q(B,Kmaj)
       constexpr uint32_t idesc_acc = make_idesc(F, 0, 1, 128, 128);  // P^T(A,Kmaj) x dO(B,N-maj)
@@ -191,22 +198,19 @@ __global__ void __launch_bounds__(FaBwdCfg::THREADS, 1)
         const int buf = it & 1;
         const uint32_t q_base = smem_u32(sQ + st * C::Q_TILE);
         const uint32_t do_base = smem_u32(sdO + st * C::Q_TILE);
+        // the two accumulators are interleaved: back-to-back MMAs into one accumulator would
+        // each wait for the previous one's write-back
 #pragma unroll
         for (int k = 0; k < 8; ++k) {  // K dim = head_dim 128
           const uint32_t oa = (k >> 2) * C::KV_SUB + (k & 3) * 32;
           const uint32_t ob = (k >> 2) * C::Q_SUB + (k & 3) * 32;
-          umma_f16(tmem_base + C::COL_ST + buf * 64, make_smem_desc_sw128(k_base + oa, 16, 1024),
+          umma_f16_w(tmem_base + C::COL_ST + buf * 64, make_smem_desc_sw128(k_base + oa, 16, 1024),
                    make_smem_desc_sw128(q_base + ob, 16, 1024), idesc_st, k != 0);
-        }
-        umma_commit(smem_u32(&st_full[buf]));
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t oa = (k >> 2) * C::KV_SUB + (k & 3) * 32;
-          const uint32_t ob = (k >> 2) * C::Q_SUB + (k & 3) * 32;
-          umma_f16(tmem_base + C::COL_DPD + buf * 64, make_smem_desc_sw128(v_base + oa, 16, 1024),
+          umma_f16_w(tmem_base + C::COL_DPD + buf * 64, make_smem_desc_sw128(v_base + oa, 16, 1024),
                    make_smem_desc_sw128(do_base + ob, 16, 1024), idesc_st, k != 0);
         }
-        umma_commit(smem_u32(&dpt_full[buf]));
+        umma_commit_w(smem_u32(&st_full[buf]));
+        umma_commit_w(smem_u32(&dpt_full[buf]));
       };
       if (ok) {
         ok = mbar_wait(smem_u32(&q_full[0]), 0, abort_flag, p.status, RB_ERR_TIMEOUT_FULL);
@@ -243,34 +247,32 @@ __global__ void __launch_bounds__(FaBwdCfg::THREADS, 1)
         tc_fence_after();
         const uint32_t q_base = smem_u32(sQ + st * C::Q_TILE);
         const uint32_t do_base = smem_u32(sdO + st * C::Q_TILE);
-        const uint32_t pt_base = smem_u32(sPT + buf * C::PT_BYTES);
         const uint32_t dst_base = smem_u32(sdST + buf * C::PT_BYTES);
-        // dV += P^T . dO ; dK += dS^T . Q      (K dim = 64 query rows -> 4 steps)
+        const uint32_t pt_tmem = tmem_base + C::COL_ST + buf * 64;
+        // dV += P^T . dO ; dK += dS^T . Q      (K dim = 64 query rows -> 4 steps; A from TMEM:
+        // query columns [32h, 32h+32) live packed in columns 32h + {0..15} (P^T) / {16..31} (dS^T))
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          umma_f16(tmem_base + C::COL_DV, make_smem_desc_sw128(pt_base + k * 32, 16, 1024),
-                   make_smem_desc_sw128(do_base + k * 2048, C::Q_SUB, 1024), idesc_acc,
-                   (it | k) != 0);
-        }
+          umma_f16_ts_w(tmem_base + C::COL_DV, pt_tmem + (k >> 1) * 32 + (k & 1) * 8,
+                      make_smem_desc_sw128(do_base + k * 2048, C::Q_SUB, 1024), idesc_acc,
+                      (it | k) != 0);
+          umma_f16_ts_w(tmem_base + C::COL_DK, pt_tmem + 16 + (k >> 1) * 32 + (k & 1) * 8,
+                      make_smem_desc_sw128(q_base + k * 2048, C::Q_SUB, 1024), idesc_acc,
+                      (it | k) != 0);
+          // dQ^T = K^T . dS^T  (K dim = 128 kv rows -> 8 steps) into the buffer dP^T(it) occupied
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          umma_f16(tmem_base + C::COL_DK, make_smem_desc_sw128(dst_base + k * 32, 16, 1024),
-                   make_smem_desc_sw128(q_base + k * 2048, C::Q_SUB, 1024), idesc_acc,
-                   (it | k) != 0);
+          for (int k2 = 2 * k; k2 < 2 * k + 2; ++k2)
+            umma_f16_w(tmem_base + C::COL_DPD + buf * 64,
+                     make_smem_desc_sw128(k_base + k2 * 2048, C::KV_SUB, 1024),
+                     make_smem_desc_sw128(dst_base + k2 * 2048, C::PT_BYTES, 1024), idesc_dq,
+                     k2 != 0);
         }
-        // dQ^T = K^T . dS^T  (K dim = 128 kv rows -> 8 steps) into the buffer dP^T(it) occupied
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          umma_f16(tmem_base + C::COL_DPD + buf * 64,
-                   make_smem_desc_sw128(k_base + k * 2048, C::KV_SUB, 1024),
-                   make_smem_desc_sw128(dst_base + k * 2048, C::PT_BYTES, 1024), idesc_dq, k != 0);
-        }
-        umma_commit(smem_u32(&dq_full[buf]));
-        umma_commit(smem_u32(&q_empty[st]));
+        umma_commit_w(smem_u32(&dq_full[buf]));
+        umma_commit_w(smem_u32(&q_empty[st]));
         st = st_n;
         st_ph = ph_n;
       }
-      if (ok) umma_commit(smem_u32(all_done));
+      if (ok) umma_commit_w(smem_u32(all_done));
     }
   } else if (warp_idx >= C::DRAIN_WARP0 && warp_idx < C::DRAIN_WARP0 + 4) {
     // ------------------------------ dQ drain warps ------------------------------
@@ -315,84 +317,60 @@ __global__ void __launch_bounds__(FaBwdCfg::THREADS, 1)
     }
   } else if (warp_idx < C::SOFTMAX_WARPS && n_iters > 0) {
     // ------------------------------ softmax warps ------------------------------
-    const int tid = threadIdx.x;                // 0..255
     const int t = (warp_idx & 3) * 32 + lane;   // kv row within tile == TMEM lane
     const int half = warp_idx >> 2;             // which 32 query columns
     const int kv = kv0 + t;
     const bool kv_ok = kv < p.Sk;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp_idx & 3) * 32) << 16);
-    // threads 0..63 fetch lse (scaled to base 2), threads 64..127 fetch delta, one tile ahead
-    auto fetch_stat = [&](int it) -> float {
-      if (tid >= 128 || it >= n_iters) return 0.f;
-      int qh, q0;
-      iter_coords(it, qh, q0);
-      const int q = q0 + (tid & 63);
-      if (q >= p.Sq) return 0.f;
-      const long long idx = (static_cast<long long>(b) * p.H + qh) * p.Sq + q;
-      return tid < 64 ? p.lse[idx] * 1.4426950408889634f : p.delta[idx];
-    };
-    auto store_stat = [&](int buf, float v) {
-      if (tid < 64) sLse[buf * 64 + tid] = v;
-      else if (tid < 128) sDelta[buf * 64 + tid - 64] = v;
-    };
-    store_stat(0, fetch_stat(0));
-    if (tid < 128) mbar_arrive(smem_u32(&stat_full[0]));
     bool ok = true;
+    int stage = 0;   // Q/dO/statistics ring slot of tile `it`
     for (int it = 0; it < n_iters; ++it) {
       const int buf = it & 1;
       const uint32_t bph = (it >> 1) & 1;
       int qh, q0;
       iter_coords(it, qh, q0);
-      const float next_stat = fetch_stat(it + 1);
-      ok = mbar_wait(smem_u32(&stat_full[buf]), bph, abort_flag, p.status, RB_ERR_TIMEOUT_FLAG);
-      ok = ok && mbar_wait(smem_u32(&st_full[buf]), bph, abort_flag, p.status,
-                           RB_ERR_TIMEOUT_TMEM_FULL);
+      // S^T complete implies the tile's TMA stage (and with it the statistics) has landed
+      ok = mbar_wait(smem_u32(&st_full[buf]), bph, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const float* lse_t = sLse + buf * 64 + half * 32;
-      const float* delta_t = sDelta + buf * 64 + half * 32;
+      const float4* lse_t = reinterpret_cast<const float4*>(sStat + stage * 128 + half * 32);
+      const float4* delta_t = reinterpret_cast<const float4*>(sStat + stage * 128 + 64 + half * 32);
+      if (++stage == C::STAGES) stage = 0;
       // no masking needed when the whole tile is in range and below the causal diagonal
       const bool full_tile = kv0 + C::BKV <= p.Sk && q0 + C::BQ <= p.Sq &&
                              (!p.causal || kv0 + C::BKV - 1 <= q0 + off);
+      const uint32_t st_addr = lane_addr + C::COL_ST + buf * 64 + half * 32;
       float pr[32];
       {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(lane_addr + C::COL_ST + buf * 64 + half * 32, r);
+        tmem_ld_32x32b_x32(st_addr, r);
         tmem_ld_wait();
-        if (full_tile) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            pr[i] = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -lse_t[i]));
-        } else {
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 l4 = lse_t[i4];
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int i = i4 * 4 + j;
+            pr[i] = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -ls[j]));
+          }
+        }
+        if (!full_tile) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int q = q0 + half * 32 + i;
             const bool valid = kv_ok && q < p.Sq && (!p.causal || kv <= q + off);
-            const float v = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -lse_t[i]));
-            pr[i] = valid ? v : 0.f;
+            pr[i] = valid ? pr[i] : 0.f;
           }
         }
       }
-      if (it >= 2) {
-        // P^T / dS^T buffers of tile it-2 must have been consumed by its accumulate GEMMs
-        ok = mbar_wait(smem_u32(&dq_full[buf]), ((it - 2) >> 1) & 1, abort_flag, p.status,
-                       RB_ERR_TIMEOUT_TMEM_FULL);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-      }
-      // this thread's 32 columns of P^T row t -> smem (4 chunks of 16 bytes, swizzled)
+      // P^T (16-bit pairs) over this warp's first 16 S^T columns
       {
-        uint8_t* rowp = sPT + buf * C::PT_BYTES + t * 128;
+        uint32_t pk[16];
 #pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) {
-          const int cc = half * 4 + c4;
-          const uint4 v = make_uint4(pack2<T>(pr[c4 * 8], pr[c4 * 8 + 1]),
-                                     pack2<T>(pr[c4 * 8 + 2], pr[c4 * 8 + 3]),
-                                     pack2<T>(pr[c4 * 8 + 4], pr[c4 * 8 + 5]),
-                                     pack2<T>(pr[c4 * 8 + 6], pr[c4 * 8 + 7]));
-          *reinterpret_cast<uint4*>(rowp + ((cc ^ (t & 7)) << 4)) = v;
-        }
+        for (int i = 0; i < 16; ++i) pk[i] = pack2<T>(pr[2 * i], pr[2 * i + 1]);
+        tmem_st_32x32b_x16(st_addr, pk);
       }
       ok = mbar_wait(smem_u32(&dpt_full[buf]), bph, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
@@ -403,36 +381,41 @@ __global__ void __launch_bounds__(FaBwdCfg::THREADS, 1)
         tmem_ld_32x32b_x32(lane_addr + C::COL_DPD + buf * 64 + half * 32, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          pr[i] = pr[i] * (__uint_as_float(r[i]) - delta_t[i]) * p.scale;
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 d4 = delta_t[i4];
+          const float ds[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int i = i4 * 4 + j;
+            pr[i] = pr[i] * (__uint_as_float(r[i]) - ds[j]) * p.scale;
+          }
+        }
+      }
+      if (it >= 2) {
+        // the dS^T shared buffer of tile it-2 must have been consumed by its dQ^T GEMM
+        ok = mbar_wait(smem_u32(&dq_full[buf]), ((it - 2) >> 1) & 1, abort_flag, p.status,
+                       RB_ERR_TIMEOUT_TMEM_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
       }
       {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pk[i] = pack2<T>(pr[2 * i], pr[2 * i + 1]);
+        // dS^T: TMEM copy (A of the dK GEMM) and swizzled shared copy (B of the dQ^T GEMM)
+        tmem_st_32x32b_x16(st_addr + 16, pk);
         uint8_t* rowp = sdST + buf * C::PT_BYTES + t * 128;
 #pragma unroll
         for (int c4 = 0; c4 < 4; ++c4) {
           const int cc = half * 4 + c4;
-          const uint4 v = make_uint4(pack2<T>(pr[c4 * 8], pr[c4 * 8 + 1]),
-                                     pack2<T>(pr[c4 * 8 + 2], pr[c4 * 8 + 3]),
-                                     pack2<T>(pr[c4 * 8 + 4], pr[c4 * 8 + 5]),
-                                     pack2<T>(pr[c4 * 8 + 6], pr[c4 * 8 + 7]));
-          *reinterpret_cast<uint4*>(rowp + ((cc ^ (t & 7)) << 4)) = v;
+          *reinterpret_cast<uint4*>(rowp + ((cc ^ (t & 7)) << 4)) =
+              make_uint4(pk[c4 * 4], pk[c4 * 4 + 1], pk[c4 * 4 + 2], pk[c4 * 4 + 3]);
         }
       }
+      tmem_st_wait();
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(smem_u32(&pds_ready[buf]));
-      // statistics of the next tile go to buffer buf^1, last read in tile it-1: every softmax
-      // thread has left that tile once its P^T/dS^T barrier has completed
-      if (warp_idx < 4 && it + 1 < n_iters) {
-        if (it >= 1) {
-          ok = mbar_wait(smem_u32(&pds_ready[buf ^ 1]), ((it - 1) >> 1) & 1, abort_flag, p.status,
-                         RB_ERR_TIMEOUT_FLAG);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-        }
-        store_stat(buf ^ 1, next_stat);
-        mbar_arrive(smem_u32(&stat_full[buf ^ 1]));
-      }
     }
     if (ok) {
       ok = mbar_wait(smem_u32(all_done), 0, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL);
@@ -483,11 +466,14 @@ __global__ void __launch_bounds__(FaBwdCfg::THREADS, 1)
   }
 }
 
-// delta[b,h,q] = sum_d dO[b,q,h,d] * O[b,q,h,d]   (one warp per row)
+// delta[b,h,q] = sum_d dO[b,q,h,d] * O[b,q,h,d] and lse2 = lse * log2(e), both written with the
+// padded row stride the main kernel's bulk loads use   (one warp per row)
 template <typename T>
 __global__ void fa_bwd_delta_kernel(const T* __restrict__ o, const T* __restrict__ dout,
                                     long long do_sb, long long do_ss, long long do_sh,
-                                    float* __restrict__ delta, int B, int H, int Sq, int HD) {
+                                    const float* __restrict__ lse, float* __restrict__ delta,
+                                    float* __restrict__ lse2, int B, int H, int Sq, int sq_pad,
+                                    int HD) {
   const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const long long total = static_cast<long long>(B) * Sq * H;
@@ -501,20 +487,26 @@ __global__ void fa_bwd_delta_kernel(const T* __restrict__ o, const T* __restrict
   float acc = 0.f;
   for (int d = lane; d < HD; d += 32) acc += to_f32<T>(op[d]) * to_f32<T>(dp[d]);
   acc = warp_sum(acc);
-  if (lane == 0) delta[(static_cast<long long>(b) * H + h) * Sq + q] = acc;
+  if (lane == 0) {
+    const long long row = static_cast<long long>(b) * H + h;
+    delta[row * sq_pad + q] = acc;
+    lse2[row * sq_pad + q] = lse[row * Sq + q] * 1.4426950408889634f;
+  }
 }
 
 template <typename T>
 int launch_fa_bwd(int dtype, const void* q, const void* k, const void* v, const void* o,
                   const void* dout, const long long* qs, const long long* ks, const long long* vs,
-                  const long long* dos, float* delta, const FaBwdParams& p, cudaStream_t st) {
+                  const long long* dos, const float* lse, float* stats, const FaBwdParams& p,
+                  cudaStream_t st) {
   using C = FaBwdCfg;
   {
     const long long rows = static_cast<long long>(p.B) * p.Sq * p.H;
     const int threads = 256;
     const long long blocks = (rows * 32 + threads - 1) / threads;
     fa_bwd_delta_kernel<T><<<(unsigned)blocks, threads, 0, st>>>(
-        (const T*)o, (const T*)dout, dos[0], dos[1], dos[2], delta, p.B, p.H, p.Sq, C::HD);
+        (const T*)o, (const T*)dout, dos[0], dos[1], dos[2], lse, stats,
+        stats + static_cast<long long>(p.B) * p.H * p.sq_pad, p.B, p.H, p.Sq, p.sq_pad, C::HD);
   }
   CUtensorMap tq, tk, tv, tdo;
   auto mk = [&](CUtensorMap* m, const void* base, const long long* s, int S, int heads, int rows) {
@@ -542,11 +534,13 @@ int launch_fa_bwd(int dtype, const void* q, const void* k, const void* v, const 
 extern "C" {
 // head_dim must be 128.  Strides are {batch, seq, head} in elements.
 // o is [B,Sq,H,128] contiguous; dq_accum is fp32 [B,Sq,H,128] and must be zero on entry;
-// delta is fp32 scratch [B,H,Sq]; dk/dv are [B,Sk,Hkv,128] contiguous.
+// stats is fp32 scratch of 2*B*H*sq_pad elements, sq_pad = Sq rounded up to a multiple of 64,
+// zero on entry (the kernel fills delta and the base-2 log-sum-exp; the padding must stay finite);
+// dk/dv are [B,Sk,Hkv,128] contiguous.
 int rb_flash_attn_bwd(int dtype, int head_dim, const void* q, const void* k, const void* v,
                       const void* o, const void* dout, const float* lse, const long long* q_strides,
                       const long long* k_strides, const long long* v_strides,
-                      const long long* do_strides, float* delta, float* dq_accum, void* dk,
+                      const long long* do_strides, float* stats, float* dq_accum, void* dk,
                       void* dv, int B, int H, int Hkv, int Sq, int Sk, int causal, float scale,
                       void* stream) {
   using namespace rb;
@@ -556,13 +550,16 @@ int rb_flash_attn_bwd(int dtype, int head_dim, const void* q, const void* k, con
   p.B = B; p.H = H; p.Hkv = Hkv; p.Sq = Sq; p.Sk = Sk; p.causal = causal;
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
-  p.lse = lse; p.delta = delta; p.dq_accum = dq_accum; p.dk = dk; p.dv = dv;
+  p.sq_pad = (Sq + 63) / 64 * 64;
+  p.delta = stats;
+  p.lse2 = stats + static_cast<long long>(B) * H * p.sq_pad;
+  p.dq_accum = dq_accum; p.dk = dk; p.dv = dv;
   p.status = rbh::device_status_word();
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == rbh::DT_BF16)
-    return launch_fa_bwd<__nv_bfloat16>(dtype, q, k, v, o, dout, q_strides, k_strides, v_strides, do_strides, delta, p, st);
+    return launch_fa_bwd<__nv_bfloat16>(dtype, q, k, v, o, dout, q_strides, k_strides, v_strides, do_strides, lse, stats, p, st);
   if (dtype == rbh::DT_F16)
-    return launch_fa_bwd<__half>(dtype, q, k, v, o, dout, q_strides, k_strides, v_strides, do_strides, delta, p, st);
+    return launch_fa_bwd<__half>(dtype, q, k, v, o, dout, q_strides, k_strides, v_strides, do_strides, lse, stats, p, st);
   return 20;
 }
 }

@@ -55,7 +55,8 @@ def fa_backward(q, k, v, o, lse, dout, causal: bool, scale: float):
     dq32 = torch.zeros((B, Sq, H, D), dtype=torch.float32, device=q.device)
     dk = torch.empty((B, Sk, Hkv, D), dtype=q.dtype, device=q.device)
     dv = torch.empty((B, Sk, Hkv, D), dtype=q.dtype, device=q.device)
-    delta = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
+    sq_pad = (Sq + 63) // 64 * 64
+    delta = torch.zeros((2, B, H, sq_pad), dtype=torch.float32, device=q.device)  # delta | lse*log2e
     qs, ks, vs, dos = _strides3(q), _strides3(k), _strides3(v), _strides3(dout)
     rc = L.rb_flash_attn_bwd(native.dtype_code(q.dtype), D, ptr(q), ptr(k), ptr(v), ptr(o),
                              ptr(dout), ptr(lse), ctypes.addressof(qs), ctypes.addressof(ks),
