@@ -37,7 +37,8 @@ struct FaFwdCfg {
   static constexpr int KV_BYTES = SUB * TILE_BYTES;  // per K or V tile
   static constexpr int P_BYTES = 2 * TILE_BYTES;     // [128 x 128]
   static constexpr int STAGES = 2;
-  static constexpr int SMEM_BYTES = Q_BYTES + STAGES * 2 * KV_BYTES + P_BYTES + 1024 + 256;
+  static constexpr int P_BUFS = 2;   // P double buffered: softmax(j+1) overlaps P(j).V(j)
+  static constexpr int SMEM_BYTES = Q_BYTES + STAGES * 2 * KV_BYTES + P_BUFS * P_BYTES + 1024 + 256;
   static constexpr int TMEM_COLS = 512;
   static constexpr int S_COL0 = 0;       // S buffers at columns [0,128) and [128,256)
   static constexpr int O_COL = 256;      // O at [256, 256+HD)
@@ -55,17 +56,17 @@ __global__ void __launch_bounds__(192, 1)
   uint8_t* sK = sQ + C::Q_BYTES;                       // [STAGES][KV_BYTES]
   uint8_t* sV = sK + C::STAGES * C::KV_BYTES;          // [STAGES][KV_BYTES]
   uint8_t* sP = sV + C::STAGES * C::KV_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::P_BUFS * C::P_BYTES);
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;    // [2]
   uint64_t* kv_empty = bars + 3;   // [2]
   uint64_t* s_full = bars + 5;     // [2]
-  uint64_t* p_ready = bars + 7;
-  uint64_t* pv_done = bars + 8;
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* p_ready = bars + 7;    // [2]
+  uint64_t* pv_done = bars + 9;    // [2]
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
-  const int warp_idx = threadIdx.x >> 5;
+  const int warp_idx = uniform_warp_idx();
   const int lane = threadIdx.x & 31;
   const int q_tile = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal tiles first
   const int h = blockIdx.y, b = blockIdx.z;
@@ -88,8 +89,10 @@ __global__ void __launch_bounds__(192, 1)
       mbar_init(smem_u32(&kv_empty[s]), 1);
       mbar_init(smem_u32(&s_full[s]), 1);
     }
-    mbar_init(smem_u32(p_ready), 128);
-    mbar_init(smem_u32(pv_done), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&p_ready[s]), 128);
+      mbar_init(smem_u32(&pv_done[s]), 1);
+    }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -130,7 +133,7 @@ __global__ void __launch_bounds__(192, 1)
     }
   } else if (warp_idx == 5) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0 && n_tiles > 0) {
+    if (n_tiles > 0) {   // whole warp; one elected lane issues each instruction
       constexpr uint32_t idesc_s = make_idesc(UmmaFormat<T>::value, 0, 0, 128, 128);
       constexpr uint32_t idesc_o = make_idesc(UmmaFormat<T>::value, 0, 1, 128, HD);
       bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, p.status, RB_ERR_TIMEOUT_FULL);
@@ -142,10 +145,10 @@ __global__ void __launch_bounds__(192, 1)
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t o = (k >> 2) * C::TILE_BYTES + (k & 3) * 32;
-          umma_f16(d, make_smem_desc_sw128(q_base + o, 16, 1024),
+          umma_f16_w(d, make_smem_desc_sw128(q_base + o, 16, 1024),
                    make_smem_desc_sw128(k_base + o, 16, 1024), idesc_s, k != 0);
         }
-        umma_commit(smem_u32(&s_full[j & 1]));
+        umma_commit_w(smem_u32(&s_full[j & 1]));
       };
       if (ok) {
         ok = mbar_wait(smem_u32(&kv_full[0]), 0, abort_flag, p.status, RB_ERR_TIMEOUT_FULL);
@@ -162,22 +165,23 @@ __global__ void __launch_bounds__(192, 1)
           tc_fence_after();
           issue_s(j + 1);
         }
-        ok = mbar_wait(smem_u32(p_ready), j & 1, abort_flag, p.status, RB_ERR_TIMEOUT_FLAG);
+        ok = mbar_wait(smem_u32(&p_ready[j & 1]), (j >> 1) & 1, abort_flag, p.status,
+                       RB_ERR_TIMEOUT_FLAG);
         if (!ok) break;
         tc_fence_after();
         const int st = j & 1;
-        const uint32_t p_base = smem_u32(sP);
+        const uint32_t p_base = smem_u32(sP + (j & 1) * C::P_BYTES);
         const uint32_t v_base = smem_u32(sV + st * C::KV_BYTES);
         const uint32_t d = tmem_base + C::O_COL;
 #pragma unroll
         for (int k = 0; k < C::BN / 16; ++k) {
           const uint32_t po = (k >> 2) * C::TILE_BYTES + (k & 3) * 32;
-          umma_f16(d, make_smem_desc_sw128(p_base + po, 16, 1024),
+          umma_f16_w(d, make_smem_desc_sw128(p_base + po, 16, 1024),
                    make_smem_desc_sw128(v_base + k * 2048, C::TILE_BYTES, 1024), idesc_o,
                    (j | k) != 0);
         }
-        umma_commit(smem_u32(&kv_empty[st]));
-        umma_commit(smem_u32(pv_done));
+        umma_commit_w(smem_u32(&kv_empty[st]));
+        umma_commit_w(smem_u32(&pv_done[j & 1]));
       }
     }
   } else if (n_tiles > 0) {
@@ -220,13 +224,22 @@ __global__ void __launch_bounds__(192, 1)
       }
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       const bool need = m_new > m_used + 8.0f;  // also true on the first tile (m_used = -inf)
-      if (j > 0) {
-        ok = mbar_wait(smem_u32(pv_done), (j - 1) & 1, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_EMPTY);
+      if (j >= 2) {
+        // the P buffer of tile j-2 must have been consumed
+        ok = mbar_wait(smem_u32(&pv_done[j & 1]), ((j - 2) >> 1) & 1, abort_flag, p.status,
+                       RB_ERR_TIMEOUT_TMEM_EMPTY);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        tc_fence_after();
       }
       if (__any_sync(0xffffffffu, need)) {
+        if (j > 0) {
+          // O is rescaled in place: the previous P.V must have retired
+          ok = mbar_wait(smem_u32(&pv_done[(j - 1) & 1]), ((j - 1) >> 1) & 1, abort_flag, p.status,
+                         RB_ERR_TIMEOUT_TMEM_EMPTY);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+        }
         float alpha = 1.0f;
         if (need) {
           alpha = (m_used == -INFINITY) ? 0.0f : fast_exp2(m_used - m_new);
@@ -263,7 +276,7 @@ __global__ void __launch_bounds__(192, 1)
           packed[i >> 1] = pack2<T>(p0, p1);
         }
         // columns [c*32, c*32+32) -> sub-tile (c>>1), 16-byte chunks ((c&1)*4 .. +4)
-        uint8_t* rowp = sP + (c >> 1) * C::TILE_BYTES + t * 128;
+        uint8_t* rowp = sP + (j & 1) * C::P_BYTES + (c >> 1) * C::TILE_BYTES + t * 128;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int cc = (c & 1) * 4 + q;
@@ -273,11 +286,11 @@ __global__ void __launch_bounds__(192, 1)
       }
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(smem_u32(p_ready));
+      mbar_arrive(smem_u32(&p_ready[j & 1]));
     }
     if (ok) {
-      ok = mbar_wait(smem_u32(pv_done), (n_tiles - 1) & 1, abort_flag, p.status,
-                     RB_ERR_TIMEOUT_TMEM_EMPTY);
+      ok = mbar_wait(smem_u32(&pv_done[(n_tiles - 1) & 1]), ((n_tiles - 1) >> 1) & 1, abort_flag,
+                     p.status, RB_ERR_TIMEOUT_TMEM_EMPTY);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {

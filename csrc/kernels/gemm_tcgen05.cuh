@@ -103,6 +103,15 @@ __device__ __forceinline__ void issue_umma(uint32_t d, uint64_t a, uint64_t b, u
   else
     umma_f16(d, a, b, idesc, acc);
 }
+// whole-warp form: one elected lane issues (see umma_f16_w)
+template <typename T>
+__device__ __forceinline__ void issue_umma_w(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc,
+                                             uint32_t acc) {
+  if constexpr (sizeof(T) == 4)
+    umma_tf32_w(d, a, b, idesc, acc);
+  else
+    umma_f16_w(d, a, b, idesc, acc);
+}
 
 __device__ __forceinline__ float apply_act(float v, int act) {
   switch (act) {
@@ -218,7 +227,7 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
   volatile int* tile_ring = abort_flag + 1;           // [kSchedSlots] tile ids, -1 = no more work
 
-  const int warp_idx = threadIdx.x >> 5;
+  const int warp_idx = uniform_warp_idx();
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -339,7 +348,7 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
     }
   } else if (warp_idx == 1) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
+    {   // whole warp, uniform control flow; one elected lane issues each MMA / commit
       constexpr uint32_t idesc = make_idesc(UmmaFormat<T>::value, A_MN ? 1 : 0, B_MN ? 1 : 0, BM, BN);
       int stage = 0;
       uint32_t phase = 0;
@@ -353,7 +362,8 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
                        RB_ERR_TIMEOUT_FULL);
         if (!ok) break;
         const int tile = tile_ring[slot];
-        mbar_arrive(smem_u32(&sched_empty[slot]));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sched_empty[slot]));
         if (++slot == kSchedSlots) {
           slot = 0;
           slot_phase ^= 1;
@@ -379,16 +389,16 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
             const uint64_t bdesc =
                 B_MN ? make_smem_desc_sw128(b_base + k * UMMA_K * 128, BK * 128, 1024)
                      : make_smem_desc_sw128(b_base + k * 32, 16, 1024);
-            issue_umma<T>(tmem_d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            issue_umma_w<T>(tmem_d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(smem_u32(&empty_bar[stage]));
+          umma_commit_w(smem_u32(&empty_bar[stage]));
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        umma_commit(smem_u32(&tmem_full_bar[acc]));
+        umma_commit_w(smem_u32(&tmem_full_bar[acc]));
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1;
