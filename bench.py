@@ -98,6 +98,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--mode", default=None, help="fused | nccl (multi-GPU communication path)")
+    ap.add_argument("--phases", action="store_true", help="also report forward/backward/tail device times")
     ap.add_argument("--layers", type=int, default=None, help="debug only: invalidates the number")
     ap.add_argument("--seqs-per-gpu", type=int, default=8)
     args = ap.parse_args()
@@ -189,6 +190,33 @@ def main():
     ms_e2e, _, _, last_e2e = timed(train_step_e2e, host_tokens[args.warmup:])
     e2e_value = tokens / (ms_e2e / 1e3)
 
+    phases = None
+    if args.phases:
+        # per-phase device times of a few extra steps (forward / backward / optimizer+comm tail)
+        acc = [0.0, 0.0, 0.0]
+        n_ph = 3
+        for i in range(n_ph):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            sync_all()
+            tok = dev_tokens[args.warmup + i % max(1, args.steps)]
+            engine.zero_grad()
+            if i == n_ph - 1 and world > 1 and hasattr(engine, "start_trace"):
+                engine.start_trace()
+            ev[0].record()
+            loss = model(tok[:, :-1], tok[:, 1:])
+            ev[1].record()
+            loss.backward()
+            ev[2].record()
+            engine.step()
+            ev[3].record()
+            torch.cuda.synchronize()
+            for k in range(3):
+                acc[k] += ev[k].elapsed_time(ev[k + 1]) / n_ph
+        phases = {"forward_ms": acc[0], "backward_ms": acc[1], "step_tail_ms": acc[2]}
+        if world > 1 and hasattr(engine, "stop_trace"):
+            tr = engine.stop_trace(ev[0])
+            phases["unit_trace_ms"] = [[n, round(a, 2), round(b_, 2), round(c, 2)] for n, a, b_, c in tr]
+
     if rank == 0:
         flops = cfg.flops_per_token() * B * S
         out = {
@@ -211,6 +239,8 @@ def main():
             "final_loss": float(last_loss.item()) if last_loss is not None else None,
             "device_status": status,
         }
+        if phases:
+            out["phases"] = phases
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

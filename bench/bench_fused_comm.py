@@ -1,0 +1,91 @@
+"""Times the fused FSDP communication kernels against NCCL + the flat Adam kernel on one sharding
+unit (run under torchrun, one rank per GPU):
+
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 bench/bench_fused_comm.py
+
+CUDA-event timing on the launching stream, max over ranks, 3 warm-ups; the unit (default 100M bf16
+parameters, i.e. 200 MB of gradients) is larger than the 126 MB L2.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from rumus_b200.ops import native  # noqa: E402
+from rumus_b200.parallel import fused_ops  # noqa: E402
+from rumus_b200.parallel.symm import SymmArena  # noqa: E402
+
+
+def timed(fn, iters=8, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ts = []
+    for _ in range(iters):
+        dist.barrier()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(); fn(); e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    t = torch.tensor([ts[len(ts) // 2]], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+def main():
+    rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    native.lib().rb_init_device()
+    P = int(os.environ.get("UNIT_NUMEL", str(100 * 1024 * 1024))) // (8 * world) * (8 * world)
+    S = P // world
+    arena = SymmArena(4 * P + (64 << 20))
+    g = arena.alloc_flat(P, torch.bfloat16); w = arena.alloc_flat(P, torch.bfloat16)
+    g.normal_(); w.normal_()
+    master = w[rank * S:(rank + 1) * S].float(); m = torch.zeros_like(master); v = torch.zeros_like(master)
+    gf, pf = arena.alloc_flags(world), arena.alloc_flags(world)
+    cnt = arena.alloc_local_ints(1)
+    arena.barrier()
+    epoch = [0]
+    res = {}
+    for threads_ctas in [(64, 16), (148, 32), (296, 148)]:
+        rs_ctas, ag_ctas = threads_ctas
+
+        def rs():
+            epoch[0] += 1
+            fused_ops.rs_adam(arena, torch.bfloat16, g.arena_offset, w.arena_offset, rank * S, S, master, m, v,
+                              lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0, step=1,
+                              adamw=False, grad_flags_off=gf, param_flags_off=pf, epoch=epoch[0],
+                              done_counter=cnt, ctas=rs_ctas)
+
+        def ag():
+            # the flags of the last rs() epoch are already set: this times the copy alone
+            fused_ops.all_gather(arena, w.arena_offset, S * 2, src_flags_off=pf, epoch=epoch[0], ctas=ag_ctas)
+
+        res[f"fused rs_adam ctas={rs_ctas}"] = timed(rs)
+        res[f"fused all_gather ctas={ag_ctas}"] = timed(ag)
+    shard = torch.empty(S, dtype=torch.bfloat16, device=dev)
+    res["nccl reduce_scatter"] = timed(lambda: dist.reduce_scatter_tensor(shard, g, op=dist.ReduceOp.AVG))
+    res["adam_flat (shard)"] = timed(lambda: native.adam_flat(shard, master, m, v, w[rank * S:(rank + 1) * S],
+                                                              lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8,
+                                                              weight_decay=0.0, step=1, adamw=False))
+    res["nccl all_gather"] = timed(lambda: dist.all_gather_into_tensor(w, w[rank * S:(rank + 1) * S]))
+    if rank == 0:
+        print(f"unit {P / 1e6:.0f}M bf16 params, world {world}, status {native.read_status()}")
+        peer_bytes = (world - 1) * S * 2
+        for k, t in res.items():
+            print(f"  {k:34s} {t * 1e3:9.1f} us   ({peer_bytes / t / 1e6:7.1f} GB/s of peer traffic per GPU)")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -19,8 +19,24 @@
 // (rumus/src/nn/fsdp.rs:139-167, rumus/src/autograd/backward.rs:1157-1241); data-parallel
 // averaging maps every gradient to the host (rumus/src/nn/parallel.rs:151-250).
 #include "comm_common.cuh"
+#include <cstdlib>
 
 namespace rb {
+
+// Threads per communication CTA (env RB_COMM_THREADS, default 512).  Measured on 2 GPUs with a
+// 105M-parameter unit: 148 CTAs x 512 threads run reduce-scatter+Adam in 346 us (NCCL
+// reduce-scatter + the flat Adam kernel: 556 us); 256 threads need 296 CTAs for the same time.
+static int comm_threads() {
+  static const int n = [] {
+    const char* e = std::getenv("RB_COMM_THREADS");
+    int v = e ? std::atoi(e) : 512;
+    if (v < 64) v = 64;
+    if (v > 512) v = 512;
+    return v / 32 * 32;
+  }();
+  return n;
+}
+
 
 struct RsAdamParams {
   PeerTable peers;
@@ -75,56 +91,82 @@ __global__ void __launch_bounds__(512) rs_adam_kernel(const RsAdamParams p) {
   const float gs = (p.grad_scale ? *p.grad_scale : 1.f) / (float)pt.world;
   const float rbc1 = 1.f / p.bc1, rbc2 = 1.f / p.bc2;
   const long long nvec = p.shard_n / 8;
-  const long long stride = (long long)gridDim.x * blockDim.x;
   TG* my_param = peer_ptr<TG>(pt, pt.rank, p.param_off) + p.shard_lo;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
-    float g[8];
+  // Each thread handles kUnroll vectors of 8 elements per trip and issues the kUnroll peer loads of
+  // one source back to back: a peer load takes microseconds, so the bytes in flight per thread
+  // decide the NVLink bandwidth this kernel reaches.
+  constexpr int kUnroll = 4;
+  const long long trip = (long long)gridDim.x * blockDim.x * kUnroll;
+  for (long long base = (long long)blockIdx.x * blockDim.x * kUnroll + threadIdx.x; base < nvec;
+       base += trip) {
+    float g[kUnroll][8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) g[j] = 0.f;
-    const long long eoff = p.shard_lo + i * 8;
+    for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g[u][j] = 0.f;
     if (p.use_multimem) {
-      const char* mc = reinterpret_cast<const char*>(pt.mc_base) + p.grad_off + eoff * (long long)sizeof(TG);
-      uint4 raw = multimem_ld_reduce_16<TG>(mc);
-      unpack8<TG>(raw, g);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const long long i = base + (long long)u * blockDim.x;
+        if (i < nvec) {
+          const char* mc = reinterpret_cast<const char*>(pt.mc_base) + p.grad_off +
+                           (p.shard_lo + i * 8) * (long long)sizeof(TG);
+          unpack8<TG>(multimem_ld_reduce_16<TG>(mc), g[u]);
+        }
+      }
     } else {
       for (int k = 0; k < pt.world; ++k) {
         const int r = (pt.rank + k) % pt.world;
-        uint4 raw = ld_nc_v4(peer_ptr<TG>(pt, r, p.grad_off) + eoff);
-        float f[8];
-        unpack8<TG>(raw, f);
+        const TG* src = peer_ptr<TG>(pt, r, p.grad_off) + p.shard_lo;
+        uint4 raw[kUnroll];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) g[j] += f[j];
+        for (int u = 0; u < kUnroll; ++u) {
+          const long long i = base + (long long)u * blockDim.x;
+          raw[u] = i < nvec ? ld_nc_v4(src + i * 8) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          float f[8];
+          unpack8<TG>(raw[u], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) g[u][j] += f[j];
+        }
       }
     }
     if (skip) continue;
-    float4 pv[2], mv[2], vv[2];
-    pv[0] = *reinterpret_cast<float4*>(p.master + i * 8);
-    pv[1] = *reinterpret_cast<float4*>(p.master + i * 8 + 4);
-    mv[0] = *reinterpret_cast<float4*>(p.m + i * 8);
-    mv[1] = *reinterpret_cast<float4*>(p.m + i * 8 + 4);
-    vv[0] = *reinterpret_cast<float4*>(p.v + i * 8);
-    vv[1] = *reinterpret_cast<float4*>(p.v + i * 8 + 4);
-    float* pp = &pv[0].x;
-    float* mp = &mv[0].x;
-    float* vp = &vv[0].x;
-    uint4 outv;
-    TG* oe = reinterpret_cast<TG*>(&outv);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float grad = g[j] * gs;
-      mp[j] = p.beta1 * mp[j] + (1.f - p.beta1) * grad;
-      vp[j] = p.beta2 * vp[j] + (1.f - p.beta2) * grad * grad;
-      if (p.adamw) pp[j] -= p.lr * p.weight_decay * pp[j];
-      pp[j] -= p.lr * (mp[j] * rbc1) / (sqrtf(vp[j] * rbc2) + p.eps);
-      oe[j] = from_f32<TG>(pp[j]);
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long i = base + (long long)u * blockDim.x;
+      if (i >= nvec) break;
+      float4 pv[2], mv[2], vv[2];
+      pv[0] = *reinterpret_cast<float4*>(p.master + i * 8);
+      pv[1] = *reinterpret_cast<float4*>(p.master + i * 8 + 4);
+      mv[0] = *reinterpret_cast<float4*>(p.m + i * 8);
+      mv[1] = *reinterpret_cast<float4*>(p.m + i * 8 + 4);
+      vv[0] = *reinterpret_cast<float4*>(p.v + i * 8);
+      vv[1] = *reinterpret_cast<float4*>(p.v + i * 8 + 4);
+      float* pp = &pv[0].x;
+      float* mp = &mv[0].x;
+      float* vp = &vv[0].x;
+      uint4 outv;
+      TG* oe = reinterpret_cast<TG*>(&outv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float grad = g[u][j] * gs;
+        mp[j] = p.beta1 * mp[j] + (1.f - p.beta1) * grad;
+        vp[j] = p.beta2 * vp[j] + (1.f - p.beta2) * grad * grad;
+        if (p.adamw) pp[j] -= p.lr * p.weight_decay * pp[j];
+        pp[j] -= p.lr * (mp[j] * rbc1) / (sqrtf(vp[j] * rbc2) + p.eps);
+        oe[j] = from_f32<TG>(pp[j]);
+      }
+      *reinterpret_cast<float4*>(p.master + i * 8) = pv[0];
+      *reinterpret_cast<float4*>(p.master + i * 8 + 4) = pv[1];
+      *reinterpret_cast<float4*>(p.m + i * 8) = mv[0];
+      *reinterpret_cast<float4*>(p.m + i * 8 + 4) = mv[1];
+      *reinterpret_cast<float4*>(p.v + i * 8) = vv[0];
+      *reinterpret_cast<float4*>(p.v + i * 8 + 4) = vv[1];
+      *reinterpret_cast<uint4*>(my_param + i * 8) = outv;
     }
-    *reinterpret_cast<float4*>(p.master + i * 8) = pv[0];
-    *reinterpret_cast<float4*>(p.master + i * 8 + 4) = pv[1];
-    *reinterpret_cast<float4*>(p.m + i * 8) = mv[0];
-    *reinterpret_cast<float4*>(p.m + i * 8 + 4) = mv[1];
-    *reinterpret_cast<float4*>(p.v + i * 8) = vv[0];
-    *reinterpret_cast<float4*>(p.v + i * 8 + 4) = vv[1];
-    *reinterpret_cast<uint4*>(my_param + i * 8) = outv;
   }
   // last CTA to finish publishes "my parameter shard is updated"
   __threadfence_system();
@@ -320,6 +362,23 @@ __global__ void wait_flag_probe_kernel(const int* flag, int epoch, unsigned long
     *result = wait_flag_sys(flag, epoch, status, RB_ERR_TIMEOUT_FLAG, nullptr, budget_ns) ? 1 : 0;
 }
 
+// One-warp gate launched in front of a many-CTA worker kernel on the same stream: optionally
+// publishes this rank's flag, then waits (bounded) for every peer's flag.  The worker repeats the
+// same checks and finds them satisfied, so no worker CTA ever sits on an SM waiting for a peer
+// that is still computing: while this rank is ahead of its peers only this warp is resident.
+__global__ void flag_gate_kernel(PeerTable pt, long long flags_off, int epoch, int do_signal,
+                                 int* status) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  if (do_signal) {
+    __threadfence_system();
+    for (int r = 0; r < pt.world; ++r)
+      st_release_sys(peer_ptr<int>(pt, r, flags_off) + pt.rank, epoch);
+  }
+  for (int r = 0; r < pt.world; ++r)
+    if (!wait_flag_sys(peer_ptr<int>(pt, pt.rank, flags_off) + r, epoch, status, RB_ERR_TIMEOUT_FLAG))
+      return;
+}
+
 static PeerTable make_table(void* const* bases, void* mc_base, int world, int rank) {
   PeerTable t;
   for (int i = 0; i < kMaxRanks; ++i) t.base[i] = i < world ? bases[i] : nullptr;
@@ -352,8 +411,9 @@ int rb_rs_adam(int dtype, void* const* bases, void* mc_base, int world, int rank
   p.status = rbh::device_status_word();
   if (ctas <= 0) ctas = 32;
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == rbh::DT_BF16) rs_adam_kernel<__nv_bfloat16><<<ctas, 512, 0, st>>>(p);
-  else if (dtype == rbh::DT_F16) rs_adam_kernel<__half><<<ctas, 512, 0, st>>>(p);
+  flag_gate_kernel<<<1, 32, 0, st>>>(p.peers, grad_flags_off, epoch, 1, p.status);
+  if (dtype == rbh::DT_BF16) rs_adam_kernel<__nv_bfloat16><<<ctas, comm_threads(), 0, st>>>(p);
+  else if (dtype == rbh::DT_F16) rs_adam_kernel<__half><<<ctas, comm_threads(), 0, st>>>(p);
   else return 31;
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 3000 + (int)e;
@@ -386,12 +446,21 @@ int rb_all_gather(void* const* bases, int world, int rank, long long buf_off, lo
   p.peers = make_table(bases, nullptr, world, rank);
   p.buf_off = buf_off; p.shard_bytes = shard_bytes; p.src_flags_off = src_flags_off;
   p.chunk_flags = chunk_flags;
-  p.chunk_bytes = chunk_bytes > 0 ? chunk_bytes : shard_bytes;
+  if (ctas <= 0) ctas = 16;
+  if (chunk_bytes <= 0) {
+    // no consumer is waiting on chunk flags: cut each shard into about four pieces per CTA so
+    // that every CTA copies (a single piece would leave the whole copy to CTA 0)
+    chunk_bytes = (shard_bytes / ((long long)ctas * 4) + 4095) / 4096 * 4096;
+    if (chunk_bytes < 65536) chunk_bytes = 65536;
+  }
+  p.chunk_bytes = chunk_bytes;
   p.chunks_per_shard = (int)((shard_bytes + p.chunk_bytes - 1) / p.chunk_bytes);
   p.epoch = epoch;
   p.status = rbh::device_status_word();
   if (ctas <= 0) ctas = 16;
-  all_gather_kernel<<<ctas, 512, 0, (cudaStream_t)stream>>>(p);
+  if (src_flags_off >= 0)
+    flag_gate_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(p.peers, src_flags_off, epoch, 0, p.status);
+  all_gather_kernel<<<ctas, comm_threads(), 0, (cudaStream_t)stream>>>(p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 3000 + (int)e;
 }
@@ -413,9 +482,9 @@ int rb_allreduce_unscale(int dtype, void* const* bases, void* mc_base, int world
   p.status = rbh::device_status_word();
   if (ctas <= 0) ctas = 32;
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == rbh::DT_BF16) allreduce_unscale_kernel<__nv_bfloat16><<<ctas, 512, 0, st>>>(p);
-  else if (dtype == rbh::DT_F16) allreduce_unscale_kernel<__half><<<ctas, 512, 0, st>>>(p);
-  else allreduce_unscale_kernel<float><<<ctas, 512, 0, st>>>(p);
+  if (dtype == rbh::DT_BF16) allreduce_unscale_kernel<__nv_bfloat16><<<ctas, comm_threads(), 0, st>>>(p);
+  else if (dtype == rbh::DT_F16) allreduce_unscale_kernel<__half><<<ctas, comm_threads(), 0, st>>>(p);
+  else allreduce_unscale_kernel<float><<<ctas, comm_threads(), 0, st>>>(p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 3000 + (int)e;
 }

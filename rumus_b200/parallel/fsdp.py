@@ -81,8 +81,13 @@ class FSDP:
         self.step_count = 0
         self._pending: List[int] = []
         self._cuda = dev.type == "cuda"
-        self.comm_stream = torch.cuda.Stream(device=dev) if self._cuda and self.world > 1 else None
+        # highest priority: when SM resources free up, pending communication CTAs are placed before
+        # the next compute kernel's, so the collectives run in the shadow of the backward pass
+        # instead of piling up behind it
+        self.comm_stream = (torch.cuda.Stream(device=dev, priority=-1)
+                            if self._cuda and self.world > 1 else None)
         self._unit_events = [None] * len(self.units)
+        self._trace = None
         self._install_boundaries()
         if mode == "fused":
             from .fused_fsdp import FusedFsdpComm
@@ -121,6 +126,7 @@ class FSDP:
 
             ln_final.forward = fwd_tail
         self._hooked = {i for n, i in name_to_idx.items() if n.startswith("blocks.") or n == "tail"}
+        self._first_hooked = min(self._hooked) if self._hooked else -1
 
     # ------------------------------------------------------------------ step protocol
     def zero_grad(self) -> None:
@@ -136,7 +142,9 @@ class FSDP:
             # run after this node: they finish every unit in step() instead.
             return
         self._done[idx] = True
-        self._reduce_and_update(idx)
+        # after the first block's backward only the embedding gradient is left to compute: from
+        # here on the communication kernels have the GPU to themselves
+        self._reduce_and_update(idx, tail=(idx == self._first_hooked))
 
     def step(self) -> None:
         """Call after ``loss.backward()``: finishes the units whose backward did not fire a
@@ -144,7 +152,7 @@ class FSDP:
         for i in range(len(self.units) - 1, -1, -1):
             if not self._done[i]:
                 self._done[i] = True
-                self._reduce_and_update(i)
+                self._reduce_and_update(i, tail=True)
         if self.comm_stream is not None:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
         if self.fused is not None:
@@ -156,7 +164,7 @@ class FSDP:
         return dict(lr=self.lr, beta1=self.beta1, beta2=self.beta2, eps=self.eps,
                     weight_decay=self.weight_decay, step=self.step_count + 1, adamw=self.adamw)
 
-    def _reduce_and_update(self, idx: int) -> None:
+    def _reduce_and_update(self, idx: int, tail: bool = False) -> None:
         u = self.units[idx]
         u.collect_stray_grads()
         if self.mode == "local":
@@ -173,17 +181,39 @@ class FSDP:
             dist.all_gather_into_tensor(u.flat_param, u.param_shard().clone(), group=self.group)
             return
         cur = torch.cuda.current_stream()
+        trace = self._trace
+        if trace is not None:
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            ev[0].record(cur)
+            trace.append((u.name, ev))
         self.comm_stream.wait_stream(cur)
         with torch.cuda.stream(self.comm_stream):
+            if trace is not None:
+                ev[1].record(self.comm_stream)
             if self.mode == "fused":
-                self.fused.reduce_scatter_adam(idx)
-                self.fused.all_gather(idx)
+                self.fused.reduce_scatter_adam(idx, tail)
+                self.fused.all_gather(idx, tail)
             else:  # nccl baseline
                 shard = u.grad_shard()
                 dist.reduce_scatter_tensor(shard, u.flat_grad, op=dist.ReduceOp.AVG, group=self.group)
                 native.adam_flat(shard, u.master, u.exp_avg, u.exp_avg_sq, u.param_shard(),
                                  **self._adam_args())
                 dist.all_gather_into_tensor(u.flat_param, u.param_shard(), group=self.group)
+            if trace is not None:
+                ev[2].record(self.comm_stream)
+
+    def start_trace(self) -> None:
+        """Record, for every unit of the following steps, when its backward finished (compute
+        stream) and when its reduce-scatter/update/all-gather started and ended (side stream)."""
+        self._trace = []
+
+    def stop_trace(self, origin: "torch.cuda.Event"):
+        """Returns ``[(unit, backward_done_ms, comm_start_ms, comm_end_ms)]`` relative to ``origin``."""
+        torch.cuda.synchronize()
+        out = [(n, origin.elapsed_time(e[0]), origin.elapsed_time(e[1]), origin.elapsed_time(e[2]))
+               for n, e in (self._trace or [])]
+        self._trace = None
+        return out
 
     # ------------------------------------------------------------------ state
     def set_lr(self, lr: float) -> None:

@@ -20,8 +20,13 @@ import os
 
 from . import fused_ops
 
-_RS_CTAS = int(os.environ.get("RB_RS_CTAS", "32"))
-_AG_CTAS = int(os.environ.get("RB_AG_CTAS", "16"))
+# CTAs per communication kernel while the backward pass is still running on the compute stream
+# (few, so the persistent GEMMs keep their SMs) and once it has finished (nothing left to overlap
+# with: use the whole GPU).
+_RS_CTAS = int(os.environ.get("RB_RS_CTAS", "148"))
+_AG_CTAS = int(os.environ.get("RB_AG_CTAS", "32"))
+_TAIL_RS_CTAS = int(os.environ.get("RB_TAIL_RS_CTAS", "296"))
+_TAIL_AG_CTAS = int(os.environ.get("RB_TAIL_AG_CTAS", "148"))
 
 
 class FusedFsdpComm:
@@ -36,21 +41,22 @@ class FusedFsdpComm:
             assert hasattr(u.flat_param, "arena_offset") and hasattr(u.flat_grad, "arena_offset")
         a.barrier()
 
-    def reduce_scatter_adam(self, idx: int) -> None:
+    def reduce_scatter_adam(self, idx: int, tail: bool = False) -> None:
         e, u = self.e, self.e.units[idx]
         fused_ops.rs_adam(self.arena, u.dtype, u.flat_grad.arena_offset, u.flat_param.arena_offset,
                           u.shard_range[0], u.shard_numel, u.master, u.exp_avg, u.exp_avg_sq,
                           lr=e.lr, beta1=e.beta1, beta2=e.beta2, eps=e.eps,
                           weight_decay=e.weight_decay, step=e.step_count + 1, adamw=e.adamw,
                           grad_flags_off=self.grad_flags[idx], param_flags_off=self.param_flags[idx],
-                          epoch=e.step_count + 1, done_counter=self.counters[idx], ctas=_RS_CTAS)
+                          epoch=e.step_count + 1, done_counter=self.counters[idx],
+                          ctas=_TAIL_RS_CTAS if tail else _RS_CTAS)
 
-    def all_gather(self, idx: int) -> None:
+    def all_gather(self, idx: int, tail: bool = False) -> None:
         e, u = self.e, self.e.units[idx]
         esz = u.flat_param.element_size()
         fused_ops.all_gather(self.arena, u.flat_param.arena_offset, u.shard_numel * esz,
                              src_flags_off=self.param_flags[idx], epoch=e.step_count + 1,
-                             ctas=_AG_CTAS)
+                             ctas=_TAIL_AG_CTAS if tail else _AG_CTAS)
 
     def end_step(self) -> None:
         pass

@@ -34,7 +34,7 @@ def rs_adam(arena: SymmArena, dtype, grad_off, param_off, shard_lo, shard_n, mas
                       ptr(grad_scale), ptr(skip), grad_flags_off, param_flags_off, epoch,
                       ptr(done_counter), 1 if arena.mc_ptr else 0, ctas, stream_ptr())
     check(rc, "rb_rs_adam")
-    count_launch()
+    count_launch(2)   # flag gate + worker
 
 
 def signal_peers(arena: SymmArena, flags_off: int, epoch: int):
@@ -51,7 +51,7 @@ def all_gather(arena: SymmArena, buf_off: int, shard_bytes: int, *, src_flags_of
     rc = L.rb_all_gather(arena.bases(), arena.world, arena.rank, buf_off, shard_bytes, src_flags_off,
                          ptr(chunk_flags), chunk_bytes, epoch, ctas, stream_ptr())
     check(rc, "rb_all_gather")
-    count_launch()
+    count_launch(2 if src_flags_off >= 0 else 1)
 
 
 def allreduce_unscale(arena: SymmArena, buf: torch.Tensor, *, enter_flags_off, exit_flags_off,
