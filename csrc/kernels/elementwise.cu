@@ -251,13 +251,22 @@ __global__ void __launch_bounds__(128)
   for (int j = 0; j < VEC; ++j) out[j] = acc[j];
 }
 template <typename T>
-__global__ void colsum_final_kernel(const float* __restrict__ partials, int slabs, int N,
-                                    T* __restrict__ out) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= N) return;
+__global__ void __launch_bounds__(256)
+    colsum_final_kernel(const float* __restrict__ partials, int slabs, int N, T* __restrict__ out) {
+  // 32 columns x 8 slab slices per CTA, folded through shared memory
+  __shared__ float sa[8][33];
+  const int cx = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float acc = 0.f;
-  for (int s = 0; s < slabs; ++s) acc += partials[(long long)s * N + c];
-  out[c] = from_f32<T>(acc);
+  if (c < N)
+    for (int s = slice; s < slabs; s += 8) acc += partials[(long long)s * N + c];
+  sa[slice][cx] = acc;
+  __syncthreads();
+  if (slice == 0 && c < N) {
+#pragma unroll
+    for (int k = 1; k < 8; ++k) acc += sa[k][cx];
+    out[c] = from_f32<T>(acc);
+  }
 }
 
 inline unsigned ew_grid(long long n, int threads) {
@@ -408,7 +417,7 @@ int rb_colsum(int dtype, const void* x, void* out, float* scratch, long long row
     dim3 grid((N + 127) / 128, slabs);
     RB_DISPATCH_T(dtype, (colsum_partial_kernel<T><<<grid, 128, 0, st>>>((const T*)x, scratch, rows, N, ld, rps)));
   }
-  RB_DISPATCH_T(dtype, (colsum_final_kernel<T><<<(N + 127) / 128, 128, 0, st>>>(scratch, slabs, N, (T*)out)));
+  RB_DISPATCH_T(dtype, (colsum_final_kernel<T><<<(N + 31) / 32, 256, 0, st>>>(scratch, slabs, N, (T*)out)));
   RB_RET_LAST();
 }
 }

@@ -30,8 +30,9 @@ struct FaBwdParams {
   const float* delta;  // [B,H,sq_pad]  rowsum(dO * O)
   int sq_pad;          // row stride of both, a multiple of 64; padding holds finite values
   float* dq_accum;     // [B,Sq,H,128] fp32, zero-initialised
-  void* dk;            // [B,Sk,Hkv,128]
-  void* dv;            // [B,Sk,Hkv,128]
+  void* dk;            // [B,Sk,Hkv,128] with element strides dkv_sb / dkv_ss / dkv_sh
+  void* dv;            // same strides as dk
+  long long dkv_sb, dkv_ss, dkv_sh;
   int* status;
 };
 
@@ -424,7 +425,7 @@ __global__ void __launch_bounds__(FaBwdCfg::THREADS, 1)
     if (ok) {
       // warps 0-3 store dV, warps 4-7 store dK
       tc_fence_after();
-      const long long orow = ((static_cast<long long>(b) * p.Sk + kv) * p.Hkv + hkv) * C::HD;
+      const long long orow = static_cast<long long>(b) * p.dkv_sb + kv * p.dkv_ss + hkv * p.dkv_sh;
       T* outp = reinterpret_cast<T*>(half == 0 ? p.dv : p.dk) + orow;
       const uint32_t col0 = half == 0 ? C::COL_DV : C::COL_DK;
 #pragma unroll 1
@@ -449,7 +450,7 @@ __global__ void __launch_bounds__(FaBwdCfg::THREADS, 1)
     const int t = threadIdx.x;
     const int kv = kv0 + t;
     if (t < 128 && kv < p.Sk) {
-      const long long orow = ((static_cast<long long>(b) * p.Sk + kv) * p.Hkv + hkv) * C::HD;
+      const long long orow = static_cast<long long>(b) * p.dkv_sb + kv * p.dkv_ss + hkv * p.dkv_sh;
       uint4 z = make_uint4(0, 0, 0, 0);
       for (int c = 0; c < C::HD / 8; ++c) {
         *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.dk) + orow + c * 8) = z;
@@ -467,31 +468,59 @@ __global__ void __launch_bounds__(FaBwdCfg::THREADS, 1)
 }
 
 // delta[b,h,q] = sum_d dO[b,q,h,d] * O[b,q,h,d] and lse2 = lse * log2(e), both written with the
-// padded row stride the main kernel's bulk loads use   (one warp per row)
+// padded row stride the main kernel's bulk loads use.  HD = 128: half a warp per row, one 16-byte
+// load of each tensor per lane.  Also converts nothing else: dq conversion is fa_dq_cast_kernel.
 template <typename T>
 __global__ void fa_bwd_delta_kernel(const T* __restrict__ o, const T* __restrict__ dout,
                                     long long do_sb, long long do_ss, long long do_sh,
                                     const float* __restrict__ lse, float* __restrict__ delta,
-                                    float* __restrict__ lse2, int B, int H, int Sq, int sq_pad,
-                                    int HD) {
-  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+                                    float* __restrict__ lse2, int B, int H, int Sq, int sq_pad) {
+  const long long hw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
+  const int l16 = threadIdx.x & 15;
   const long long total = static_cast<long long>(B) * Sq * H;
-  if (warp >= total) return;
-  const int h = warp % H;
-  const long long bq = warp / H;
+  const bool live = hw < total;
+  const long long r = live ? hw : 0;
+  const int h = r % H;
+  const long long bq = r / H;
   const int q = bq % Sq;
   const int b = bq / Sq;
-  const T* op = o + warp * HD;
-  const T* dp = dout + b * do_sb + q * do_ss + h * do_sh;
   float acc = 0.f;
-  for (int d = lane; d < HD; d += 32) acc += to_f32<T>(op[d]) * to_f32<T>(dp[d]);
-  acc = warp_sum(acc);
-  if (lane == 0) {
+  if (live) {
+    const uint4 ov = *reinterpret_cast<const uint4*>(o + r * 128 + l16 * 8);
+    const uint4 dv = *reinterpret_cast<const uint4*>(dout + b * do_sb + q * do_ss + h * do_sh + l16 * 8);
+    const T* oe = reinterpret_cast<const T*>(&ov);
+    const T* de = reinterpret_cast<const T*>(&dv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += to_f32<T>(oe[j]) * to_f32<T>(de[j]);
+  }
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (live && l16 == 0) {
     const long long row = static_cast<long long>(b) * H + h;
     delta[row * sq_pad + q] = acc;
     lse2[row * sq_pad + q] = lse[row * Sq + q] * 1.4426950408889634f;
   }
+}
+
+// dq (fp32 accumulation buffer [B,Sq,H,128]) -> T with element strides {sb, ss, sh}
+template <typename T>
+__global__ void fa_dq_cast_kernel(const float* __restrict__ dq32, T* __restrict__ dq, long long sb,
+                                  long long ss, long long sh, int B, int Sq, int H) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;  // 8 elements each
+  const long long total = static_cast<long long>(B) * Sq * H * 16;
+  if (i >= total) return;
+  const int c = i & 15;
+  const long long r = i >> 4;
+  const int h = r % H;
+  const long long bq = r / H;
+  const int q = bq % Sq;
+  const int b = bq / Sq;
+  const float4 a0 = *reinterpret_cast<const float4*>(dq32 + i * 8);
+  const float4 a1 = *reinterpret_cast<const float4*>(dq32 + i * 8 + 4);
+  uint4 v;
+  v.x = pack2<T>(a0.x, a0.y); v.y = pack2<T>(a0.z, a0.w);
+  v.z = pack2<T>(a1.x, a1.y); v.w = pack2<T>(a1.z, a1.w);
+  *reinterpret_cast<uint4*>(dq + b * sb + q * ss + h * sh + c * 8) = v;
 }
 
 template <typename T>
@@ -503,10 +532,10 @@ int launch_fa_bwd(int dtype, const void* q, const void* k, const void* v, const 
   {
     const long long rows = static_cast<long long>(p.B) * p.Sq * p.H;
     const int threads = 256;
-    const long long blocks = (rows * 32 + threads - 1) / threads;
+    const long long blocks = (rows * 16 + threads - 1) / threads;
     fa_bwd_delta_kernel<T><<<(unsigned)blocks, threads, 0, st>>>(
         (const T*)o, (const T*)dout, dos[0], dos[1], dos[2], lse, stats,
-        stats + static_cast<long long>(p.B) * p.H * p.sq_pad, p.B, p.H, p.Sq, p.sq_pad, C::HD);
+        stats + static_cast<long long>(p.B) * p.H * p.sq_pad, p.B, p.H, p.Sq, p.sq_pad);
   }
   CUtensorMap tq, tk, tv, tdo;
   auto mk = [&](CUtensorMap* m, const void* base, const long long* s, int S, int heads, int rows) {
@@ -536,13 +565,14 @@ extern "C" {
 // o is [B,Sq,H,128] contiguous; dq_accum is fp32 [B,Sq,H,128] and must be zero on entry;
 // stats is fp32 scratch of 2*B*H*sq_pad elements, sq_pad = Sq rounded up to a multiple of 64,
 // zero on entry (the kernel fills delta and the base-2 log-sum-exp; the padding must stay finite);
-// dk/dv are [B,Sk,Hkv,128] contiguous.
+// dk/dv are [B,Sk,Hkv,128] views with element strides dkv_strides = {batch, seq, head}
+// (rows of 128 contiguous, 16-byte aligned).
 int rb_flash_attn_bwd(int dtype, int head_dim, const void* q, const void* k, const void* v,
                       const void* o, const void* dout, const float* lse, const long long* q_strides,
                       const long long* k_strides, const long long* v_strides,
                       const long long* do_strides, float* stats, float* dq_accum, void* dk,
-                      void* dv, int B, int H, int Hkv, int Sq, int Sk, int causal, float scale,
-                      void* stream) {
+                      void* dv, const long long* dkv_strides, int B, int H, int Hkv, int Sq, int Sk,
+                      int causal, float scale, void* stream) {
   using namespace rb;
   if (head_dim != 128) return 20;
   if (B <= 0 || H <= 0 || Sq <= 0 || Sk <= 0) return 0;
@@ -554,6 +584,7 @@ int rb_flash_attn_bwd(int dtype, int head_dim, const void* q, const void* k, con
   p.delta = stats;
   p.lse2 = stats + static_cast<long long>(B) * H * p.sq_pad;
   p.dq_accum = dq_accum; p.dk = dk; p.dv = dv;
+  p.dkv_sb = dkv_strides[0]; p.dkv_ss = dkv_strides[1]; p.dkv_sh = dkv_strides[2];
   p.status = rbh::device_status_word();
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == rbh::DT_BF16)
@@ -561,5 +592,24 @@ int rb_flash_attn_bwd(int dtype, int head_dim, const void* q, const void* k, con
   if (dtype == rbh::DT_F16)
     return launch_fa_bwd<__half>(dtype, q, k, v, o, dout, q_strides, k_strides, v_strides, do_strides, lse, stats, p, st);
   return 20;
+}
+
+// dq32 [B,Sq,H,128] fp32 contiguous -> dq (dtype) with element strides {batch, seq, head}
+int rb_fa_dq_cast(int dtype, const float* dq32, void* dq, const long long* strides, int B, int Sq,
+                  int H, void* stream) {
+  using namespace rb;
+  const long long total = static_cast<long long>(B) * Sq * H * 16;
+  if (total <= 0) return 0;
+  const int threads = 256;
+  const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == rbh::DT_BF16)
+    fa_dq_cast_kernel<__nv_bfloat16><<<blocks, threads, 0, st>>>(dq32, (__nv_bfloat16*)dq, strides[0], strides[1], strides[2], B, Sq, H);
+  else if (dtype == rbh::DT_F16)
+    fa_dq_cast_kernel<__half><<<blocks, threads, 0, st>>>(dq32, (__half*)dq, strides[0], strides[1], strides[2], B, Sq, H);
+  else
+    return 20;
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
 }
 }

@@ -209,19 +209,21 @@ __global__ void __launch_bounds__(192, 1)
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(s_addr + c * 32, sreg[c]);
       tmem_ld_wait();
-      float mx = -INFINITY;
+      // four independent chains (one warp per scheduler: nothing else hides the fmax latency)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (kv0 + c * 32 + i <= kv_limit) mx = fmaxf(mx, __uint_as_float(sreg[c][i]));
+            if (kv0 + c * 32 + i <= kv_limit) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sreg[c][i]));
       } else {
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sreg[c][i]));
+          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sreg[c][i]));
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       const bool need = m_new > m_used + 8.0f;  // also true on the first tile (m_used = -inf)
       if (j >= 2) {
@@ -261,6 +263,7 @@ __global__ void __launch_bounds__(192, 1)
       }
       // P = exp2(S*scale - m), row sum, store to swizzled smem
       const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t packed[16];
@@ -272,7 +275,7 @@ __global__ void __launch_bounds__(192, 1)
             if (kv0 + c * 32 + i > kv_limit) p0 = 0.f;
             if (kv0 + c * 32 + i + 1 > kv_limit) p1 = 0.f;
           }
-          l += p0 + p1;
+          l4[(i >> 1) & 3] += p0 + p1;
           packed[i >> 1] = pack2<T>(p0, p1);
         }
         // columns [c*32, c*32+32) -> sub-tile (c>>1), 16-byte chunks ((c&1)*4 .. +4)
@@ -284,6 +287,7 @@ __global__ void __launch_bounds__(192, 1)
               make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
         }
       }
+      l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(smem_u32(&p_ready[j & 1]));

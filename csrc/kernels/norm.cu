@@ -230,19 +230,171 @@ __global__ void __launch_bounds__(kNormWarps * 32)
   }
 }
 
+// Column-owner variant used when rows are 16-byte vectors and D <= 128 * VEC * NCHUNK: a group of
+// 128 threads works on one row, thread t owning the 16-byte chunks t, t+128, ... of every row
+// the group visits.  x and dy stay in registers between the two row reductions and the dx pass,
+// and d_gamma / d_beta accumulate in registers (no shared-memory atomics); the four groups of a
+// CTA fold their accumulators through shared memory once at the end.
+constexpr int kColGroupThreads = 128;
+
+// kColGroups row groups per CTA: 4 while the accumulators fit 128 registers, 2 for wider rows
+template <typename T, bool RMS, int NCHUNK, int kColGroups>
+__global__ void __launch_bounds__(kColGroups* kColGroupThreads)
+    norm_bwd_cols_kernel(const T* __restrict__ x, const T* __restrict__ dy,
+                         const T* __restrict__ gamma, const float* __restrict__ stats,
+                         const T* __restrict__ dres, T* __restrict__ dx,
+                         float* __restrict__ partials /* [grid,2,D] */, long long rows, int D) {
+  constexpr int VEC = Vec16<T>::N;
+  extern __shared__ float s_fold[];                       // [2][D]
+  __shared__ float s_red[2][kColGroups][4][2];            // [buffer][group][warp][c1,c2]
+  const int grp = threadIdx.x / kColGroupThreads;
+  const int tg = threadIdx.x % kColGroupThreads;
+  const int wg = tg >> 5, lane = tg & 31;
+  float acc_g[NCHUNK][VEC], acc_b[NCHUNK][VEC];
+  Vec16<T> gv[NCHUNK];
+#pragma unroll
+  for (int i = 0; i < NCHUNK; ++i) {
+    const int c = (i * kColGroupThreads + tg) * VEC;
+    gv[i].raw = c < D ? *reinterpret_cast<const uint4*>(gamma + c) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc_g[i][j] = acc_b[i][j] = 0.f;
+  }
+  const float inv_d = 1.f / (float)D;
+  int buf = 0;
+  const long long row_step = (long long)gridDim.x * kColGroups;
+  // every group runs the same number of trips so that the named barrier below stays matched
+  const long long trips = (rows + row_step - 1) / row_step;
+  // software pipeline: the next row's x / dy are requested before the current row is reduced
+  Vec16<T> xn[NCHUNK], dn[NCHUNK];
+  auto fetch = [&](long long row) {
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i) {
+      const int c = (i * kColGroupThreads + tg) * VEC;
+      if (row < rows && c < D) {
+        xn[i].raw = *reinterpret_cast<const uint4*>(x + row * D + c);
+        dn[i].raw = *reinterpret_cast<const uint4*>(dy + row * D + c);
+      } else {
+        xn[i].raw = make_uint4(0, 0, 0, 0);
+        dn[i].raw = make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  fetch((long long)blockIdx.x * kColGroups + grp);
+  for (long long trip = 0; trip < trips; ++trip) {
+    const long long row = trip * row_step + (long long)blockIdx.x * kColGroups + grp;
+    const bool live = row < rows;
+    Vec16<T> xv[NCHUNK], dv[NCHUNK];
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i) {
+      xv[i] = xn[i];
+      dv[i] = dn[i];
+    }
+    if (trip + 1 < trips) fetch(row + row_step);
+    float mean = 0.f, rstd = 0.f;
+    if (live) {
+      mean = RMS ? 0.f : stats[row * 2];
+      rstd = stats[row * 2 + 1];
+    }
+    float c1 = 0.f, c2 = 0.f;  // sum(dy*g), sum(dy*g*xhat)
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i)
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const float xh = (xv[i].get(j) - mean) * rstd;
+        const float dg = dv[i].get(j) * gv[i].get(j);
+        c1 += dg;
+        c2 += dg * xh;
+      }
+    c1 = warp_sum(c1);
+    c2 = warp_sum(c2);
+    if (lane == 0) {
+      s_red[buf][grp][wg][0] = c1;
+      s_red[buf][grp][wg][1] = c2;
+    }
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(kColGroupThreads) : "memory");
+    c1 = (s_red[buf][grp][0][0] + s_red[buf][grp][1][0] + s_red[buf][grp][2][0] +
+          s_red[buf][grp][3][0]) * inv_d;
+    c2 = (s_red[buf][grp][0][1] + s_red[buf][grp][1][1] + s_red[buf][grp][2][1] +
+          s_red[buf][grp][3][1]) * inv_d;
+    buf ^= 1;
+    if (RMS) c1 = 0.f;
+    if (live) {
+#pragma unroll
+      for (int i = 0; i < NCHUNK; ++i) {
+        const int c = (i * kColGroupThreads + tg) * VEC;
+        if (c < D) {
+          Vec16<T> rv, ov;
+          if (dres) rv.raw = *reinterpret_cast<const uint4*>(dres + row * D + c);
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) {
+            const float xh = (xv[i].get(j) - mean) * rstd;
+            const float d = dv[i].get(j);
+            float o = rstd * (d * gv[i].get(j) - c1 - xh * c2);
+            if (dres) o += rv.get(j);
+            ov.set(j, o);
+            acc_g[i][j] += d * xh;
+            acc_b[i][j] += d;
+          }
+          *reinterpret_cast<uint4*>(dx + row * D + c) = ov.raw;
+        }
+      }
+    }
+  }
+  // fold the four groups: group 0 stores, the others add in turn
+  for (int gsel = 0; gsel < kColGroups; ++gsel) {
+    if (grp == gsel) {
+#pragma unroll
+      for (int i = 0; i < NCHUNK; ++i) {
+        const int c = (i * kColGroupThreads + tg) * VEC;
+        if (c < D) {
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) {
+            if (gsel == 0) {
+              s_fold[c + j] = acc_g[i][j];
+              s_fold[D + c + j] = acc_b[i][j];
+            } else {
+              s_fold[c + j] += acc_g[i][j];
+              s_fold[D + c + j] += acc_b[i][j];
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  float* out = partials + (long long)blockIdx.x * 2 * D;
+  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) out[i] = s_fold[i];
+}
+
 // partials [n,2,D] -> dgamma[D], dbeta[D] (dbeta may be null)
 template <typename T>
-__global__ void norm_bwd_reduce_kernel(const float* __restrict__ partials, int n, int D,
-                                       T* __restrict__ dgamma, T* __restrict__ dbeta) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= D) return;
+__global__ void __launch_bounds__(256)
+    norm_bwd_reduce_kernel(const float* __restrict__ partials, int n, int D,
+                           T* __restrict__ dgamma, T* __restrict__ dbeta) {
+  // 32 columns x 8 row slices per CTA: each slice strides over the partial rows, then the
+  // slices fold through shared memory
+  __shared__ float sg[8][33], sb[8][33];
+  const int cx = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float g = 0.f, b = 0.f;
-  for (int i = 0; i < n; ++i) {
-    g += partials[(long long)i * 2 * D + c];
-    b += partials[(long long)i * 2 * D + D + c];
+  if (c < D) {
+    for (int i = slice; i < n; i += 8) {
+      g += partials[(long long)i * 2 * D + c];
+      b += partials[(long long)i * 2 * D + D + c];
+    }
   }
-  dgamma[c] = from_f32<T>(g);
-  if (dbeta) dbeta[c] = from_f32<T>(b);
+  sg[slice][cx] = g;
+  sb[slice][cx] = b;
+  __syncthreads();
+  if (slice == 0 && c < D) {
+#pragma unroll
+    for (int k = 1; k < 8; ++k) {
+      g += sg[k][cx];
+      b += sb[k][cx];
+    }
+    dgamma[c] = from_f32<T>(g);
+    if (dbeta) dbeta[c] = from_f32<T>(b);
+  }
 }
 
 template <typename T, bool RMS>
@@ -287,6 +439,22 @@ int launch_norm_bwd(const void* x, const void* dy, const void* gamma, const floa
   constexpr int VEC = Vec16<T>::N;
   auto al = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   const int vec = (D % VEC == 0) && al(x) && al(dy) && al(gamma) && al(dres) && al(dx);
+  const int chunks = (D + kColGroupThreads * VEC - 1) / (kColGroupThreads * VEC);
+  if (vec && chunks <= 4) {
+    const size_t fold = (size_t)2 * D * sizeof(float);
+#define RB_COLS(N, G)                                                                            \
+  norm_bwd_cols_kernel<T, RMS, N, G><<<grid, G * kColGroupThreads, fold, st>>>(                  \
+      (const T*)x, (const T*)dy, (const T*)gamma, stats, (const T*)dres, (T*)dx, partials, rows, D)
+    if (chunks == 1) RB_COLS(1, 4);
+    else if (chunks == 2) RB_COLS(2, 4);
+    else if (chunks == 3) RB_COLS(3, 2);
+    else RB_COLS(4, 2);
+#undef RB_COLS
+    norm_bwd_reduce_kernel<T><<<(D + 31) / 32, 256, 0, st>>>(partials, grid, D, (T*)dgamma,
+                                                             RMS ? nullptr : (T*)dbeta);
+    cudaError_t e2 = cudaGetLastError();
+    return e2 == cudaSuccess ? 0 : 3000 + (int)e2;
+  }
   const size_t smem = (size_t)2 * (skew(D) + 1) * sizeof(float);
   auto kern = norm_bwd_kernel<T, RMS>;
   if (smem > 48 * 1024) {
@@ -295,7 +463,7 @@ int launch_norm_bwd(const void* x, const void* dy, const void* gamma, const floa
   }
   kern<<<grid, kNormWarps * 32, smem, st>>>((const T*)x, (const T*)dy, (const T*)gamma, stats,
                                             (const T*)dres, (T*)dx, partials, rows, D, vec);
-  norm_bwd_reduce_kernel<T><<<(D + 255) / 256, 256, 0, st>>>(partials, grid, D, (T*)dgamma,
+  norm_bwd_reduce_kernel<T><<<(D + 31) / 32, 256, 0, st>>>(partials, grid, D, (T*)dgamma,
                                                            RMS ? nullptr : (T*)dbeta);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 3000 + (int)e;

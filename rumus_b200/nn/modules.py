@@ -200,6 +200,11 @@ class MultiheadAttention(Module):
         H, Hkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         if self.rope_theta is not None:
             qkv = F.rope_qkv(qkv, S, H, Hkv, hd, self.rope_theta)
+        if (mask is None and hd == 128 and qkv.is_cuda
+                and qkv.dtype in (torch.bfloat16, torch.float16) and qkv.data_ptr() % 16 == 0):
+            # packed path: the backward kernels write d_q / d_k / d_v into one d_qkv buffer
+            o = F.flash_attention_packed(qkv, H, Hkv, self.causal)
+            return self.out_proj(o.reshape(B, S, self.d_model), residual=residual)
         q, k, v = qkv.split(self._splits(), dim=-1)
         q = q.view(B, S, H, hd)
         k = k.view(B, S, Hkv, hd)

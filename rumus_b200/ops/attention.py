@@ -13,8 +13,9 @@ from ._lib import check, count_launch, ptr, stream_ptr
 
 P, LL, I, F = c_void_p, c_longlong, c_int, c_float
 native.register_signature("rb_flash_attn_fwd", [I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, P])
-native.register_signature("rb_flash_attn_bwd", [I, I, P, P, P, P, P, P, P, P, P, P, P, P, P, P,
+native.register_signature("rb_flash_attn_bwd", [I, I, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P,
                                                 I, I, I, I, I, I, F, P])
+native.register_signature("rb_fa_dq_cast", [I, P, P, P, I, I, I, P])
 
 
 def _strides3(t: torch.Tensor):
@@ -46,26 +47,36 @@ def fa_forward(q, k, v, causal: bool, scale: float):
     return o, lse, (q, k, v)
 
 
-def fa_backward(q, k, v, o, lse, dout, causal: bool, scale: float):
+def fa_backward(q, k, v, o, lse, dout, causal: bool, scale: float, out=None):
+    """dq, dk, dv.  ``out`` may give three preallocated [B,S,heads,128] views (e.g. slices of one
+    packed d_qkv buffer): the kernels write straight into them."""
     L = native.lib()
     B, Sq, H, D = q.shape
     _, Sk, Hkv, _ = k.shape
     if not _tma_ok(dout):
         dout = dout.contiguous()
     dq32 = torch.zeros((B, Sq, H, D), dtype=torch.float32, device=q.device)
-    dk = torch.empty((B, Sk, Hkv, D), dtype=q.dtype, device=q.device)
-    dv = torch.empty((B, Sk, Hkv, D), dtype=q.dtype, device=q.device)
+    if out is None:
+        dq = torch.empty((B, Sq, H, D), dtype=q.dtype, device=q.device)
+        dk = torch.empty((B, Sk, Hkv, D), dtype=q.dtype, device=q.device)
+        dv = torch.empty((B, Sk, Hkv, D), dtype=q.dtype, device=q.device)
+    else:
+        dq, dk, dv = out
+    assert dk.stride() == dv.stride() and dk.stride(3) == 1 and dq.stride(3) == 1
     sq_pad = (Sq + 63) // 64 * 64
-    delta = torch.zeros((2, B, H, sq_pad), dtype=torch.float32, device=q.device)  # delta | lse*log2e
+    stats = torch.zeros((2, B, H, sq_pad), dtype=torch.float32, device=q.device)  # delta | lse*log2e
     qs, ks, vs, dos = _strides3(q), _strides3(k), _strides3(v), _strides3(dout)
+    dkvs, dqs = _strides3(dk), _strides3(dq)
     rc = L.rb_flash_attn_bwd(native.dtype_code(q.dtype), D, ptr(q), ptr(k), ptr(v), ptr(o),
                              ptr(dout), ptr(lse), ctypes.addressof(qs), ctypes.addressof(ks),
-                             ctypes.addressof(vs), ctypes.addressof(dos), ptr(delta), ptr(dq32),
-                             ptr(dk), ptr(dv), B, H, Hkv, Sq, Sk, 1 if causal else 0, float(scale),
-                             stream_ptr())
+                             ctypes.addressof(vs), ctypes.addressof(dos), ptr(stats), ptr(dq32),
+                             ptr(dk), ptr(dv), ctypes.addressof(dkvs), B, H, Hkv, Sq, Sk,
+                             1 if causal else 0, float(scale), stream_ptr())
     check(rc, "rb_flash_attn_bwd")
-    count_launch(2)
-    dq = native.cast(dq32, q.dtype)
+    rc = L.rb_fa_dq_cast(native.dtype_code(q.dtype), ptr(dq32), ptr(dq), ctypes.addressof(dqs),
+                         B, Sq, H, stream_ptr())
+    check(rc, "rb_fa_dq_cast")
+    count_launch(3)
     return dq, dk, dv
 
 
@@ -85,6 +96,44 @@ class _FlashAttnFn(torch.autograd.Function):
         else:
             dq, dk, dv = _composed_backward(q, k, v, dout, ctx.causal, ctx.scale)
         return dq, dk, dv, None, None
+
+
+class _FlashAttnPackedFn(torch.autograd.Function):
+    """Attention on the packed projection output ``qkv [B, S, (H + 2*Hkv) * 128]``: the backward
+    kernels write d_q, d_k, d_v into the three slices of one d_qkv buffer (no concatenation)."""
+
+    @staticmethod
+    def forward(ctx, qkv, heads, kv_heads, causal, scale):
+        B, S, _ = qkv.shape
+        hd = 128
+        q, k, v = qkv.split([heads * hd, kv_heads * hd, kv_heads * hd], dim=-1)
+        q, k, v = q.view(B, S, heads, hd), k.view(B, S, kv_heads, hd), v.view(B, S, kv_heads, hd)
+        o, lse, _ = fa_forward(q, k, v, causal, scale)
+        ctx.causal, ctx.scale, ctx.heads, ctx.kv_heads = causal, scale, heads, kv_heads
+        ctx.save_for_backward(qkv, o, lse)
+        return o
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, o, lse = ctx.saved_tensors
+        B, S, _ = qkv.shape
+        H, Hkv, hd = ctx.heads, ctx.kv_heads, 128
+        sizes = [H * hd, Hkv * hd, Hkv * hd]
+        q, k, v = qkv.split(sizes, dim=-1)
+        q, k, v = q.view(B, S, H, hd), k.view(B, S, Hkv, hd), v.view(B, S, Hkv, hd)
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = dqkv.split(sizes, dim=-1)
+        out = (dq.view(B, S, H, hd), dk.view(B, S, Hkv, hd), dv.view(B, S, Hkv, hd))
+        fa_backward(q, k, v, o, lse, dout, ctx.causal, ctx.scale, out=out)
+        return dqkv, None, None, None, None
+
+
+def flash_attention_packed(qkv, heads: int, kv_heads: int, causal: bool = True,
+                           scale: Optional[float] = None):
+    """``qkv`` is the fused projection output, head_dim 128, CUDA, 16-bit, 16-byte aligned rows."""
+    if scale is None:
+        scale = 1.0 / math.sqrt(128)
+    return _FlashAttnPackedFn.apply(qkv, heads, kv_heads, causal, scale)
 
 
 def _composed_backward(q, k, v, dout, causal, scale):

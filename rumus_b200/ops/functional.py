@@ -590,6 +590,15 @@ def sdpa_reference(q, k, v, causal: bool, scale: Optional[float] = None):
     return (p @ vf).permute(0, 2, 1, 3).to(q.dtype)
 
 
+def flash_attention_packed(qkv, heads: int, kv_heads: int, causal: bool = True,
+                           scale: Optional[float] = None):
+    """Attention over the fused projection output ``[B, S, (heads + 2*kv_heads) * 128]`` (CUDA,
+    16-bit): same result as splitting and calling ``flash_attention``, without the gradient
+    concatenation."""
+    from .attention import flash_attention_packed as _packed
+    return _packed(qkv, heads, kv_heads, causal, scale)
+
+
 def flash_attention(q, k, v, causal: bool = True, scale: Optional[float] = None):
     """Memory-efficient attention on ``[B, S, H, d]`` tensors (strided views of a fused qkv
     projection are fine).  Reference: tensor/ops.rs:2685 (forward-only there; it falls back to

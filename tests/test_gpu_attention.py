@@ -53,3 +53,31 @@ def test_flash_attention_backward(B, S, H, Hkv, causal):
     assert _rel(q.grad, qr.grad) < 3e-2, _rel(q.grad, qr.grad)
     assert _rel(k.grad, kr.grad) < 3e-2, _rel(k.grad, kr.grad)
     assert _rel(v.grad, vr.grad) < 3e-2, _rel(v.grad, vr.grad)
+
+
+@pytest.mark.parametrize("B,S,H,Hkv,causal", [(2, 256, 4, 4, True), (1, 200, 4, 2, True), (1, 130, 2, 2, False)])
+def test_flash_attention_packed_matches_split(B, S, H, Hkv, causal):
+    """Packed-qkv attention (gradients written into one d_qkv buffer) against the split form."""
+    from rumus_b200.ops import functional as F
+    torch.manual_seed(3)
+    D = 128
+    W = (H + 2 * Hkv) * D
+    base = (torch.randn(B, S, W, device="cuda") * 0.6).bfloat16()
+    a = base.clone().requires_grad_(True)
+    b = base.clone().requires_grad_(True)
+    o1 = F.flash_attention_packed(a, H, Hkv, causal)
+    q, k, v = b.split([H * D, Hkv * D, Hkv * D], dim=-1)
+    o2 = F.flash_attention(q.view(B, S, H, D), k.view(B, S, Hkv, D), v.view(B, S, Hkv, D), causal)
+    assert torch.equal(o1, o2)
+    g = torch.randn_like(o1)
+    o1.backward(g)
+    o2.backward(g)
+    assert _rel(a.grad, b.grad) < 1e-3, _rel(a.grad, b.grad)
+    ref = base.float().requires_grad_(True)
+    qf, kf, vf = ref.split([H * D, Hkv * D, Hkv * D], dim=-1)
+    kf4, vf4 = kf.view(B, S, Hkv, D), vf.view(B, S, Hkv, D)
+    if Hkv != H:
+        kf4 = kf4.repeat_interleave(H // Hkv, dim=2)
+        vf4 = vf4.repeat_interleave(H // Hkv, dim=2)
+    F.sdpa_reference(qf.view(B, S, H, D), kf4, vf4, causal).backward(g.float())
+    assert _rel(a.grad, ref.grad) < 3e-2, _rel(a.grad, ref.grad)
