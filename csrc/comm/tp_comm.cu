@@ -149,12 +149,19 @@ __global__ void __launch_bounds__(512, 1)
   extern __shared__ uint8_t smem_raw[];
   if ((int)blockIdx.x < n_copy_ctas) {
     ag_copy_role_tp(ap, blockIdx.x, n_copy_ctas);
-    return;
+    // with the dynamic tile scheduler a copy CTA joins the GEMM once its share is gathered
+    // (its SM would otherwise idle for the rest of the kernel)
+    if (gp.sched == nullptr) return;
+    asm volatile("bar.sync 2, 512;" ::: "memory");
   }
   if (threadIdx.x >= kGemmThreads) return;  // GEMM CTAs use 10 warps; the block is sized for the copy role
   hooks.ready[0] = hooks.ready[1] = hooks.ready[2] = hooks.ready[3] = 0ull;
-  gemm_cta_body<T, BN, false, B_MN, GatherHooks>(&tma_a, &tma_b, gp, hooks, smem_raw,
-                                                 blockIdx.x - n_copy_ctas, gridDim.x - n_copy_ctas);
+  if (gp.sched != nullptr)
+    gemm_cta_body<T, BN, false, B_MN, GatherHooks>(&tma_a, &tma_b, gp, hooks, smem_raw, blockIdx.x,
+                                                   gridDim.x);
+  else
+    gemm_cta_body<T, BN, false, B_MN, GatherHooks>(&tma_a, &tma_b, gp, hooks, smem_raw,
+                                                   blockIdx.x - n_copy_ctas, gridDim.x - n_copy_ctas);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -222,36 +229,59 @@ __device__ __forceinline__ void rs_reduce_role(const RsReduceParams& p, int cta,
     const int ncols = min(p.BN, p.N - n0);
     const int vec_per_row = ncols / 8;
     const int nrows = min(128, rows_per_rank - m_local);
-    for (int i = threadIdx.x; i < nrows * vec_per_row; i += blockDim.x) {
-      const int r = i / vec_per_row;
-      const int c = n0 + (i - r * vec_per_row) * 8;
-      const long long grow = (long long)pt.rank * rows_per_rank + m_local + r;
-      float acc[8];
+    // kU vectors per thread and trip, the kU loads of one source issued back to back: a peer
+    // load takes microseconds, so the bytes in flight per thread set the reducer's bandwidth
+    constexpr int kU = 4;
+    const int nvec = nrows * vec_per_row;
+    for (int i0 = threadIdx.x; i0 < nvec; i0 += blockDim.x * kU) {
+      float acc[kU][8];
+      long long goff[kU];
+      int cc[kU], rr[kU];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int u = 0; u < kU; ++u) {
+        const int i = i0 + u * blockDim.x;
+        const int r = i < nvec ? i / vec_per_row : 0;
+        rr[u] = r;
+        cc[u] = n0 + ((i < nvec ? i : 0) - r * vec_per_row) * 8;
+        goff[u] = ((long long)pt.rank * rows_per_rank + m_local + r) * p.N + cc[u];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+      }
       for (int k = 0; k < pt.world; ++k) {
         const int src = (pt.rank + k) % pt.world;
-        uint4 raw = ld_nc_v4(peer_ptr<T>(pt, src, p.partial_off) + grow * p.N + c);
-        const T* e = reinterpret_cast<const T*>(&raw);
+        const T* base = peer_ptr<T>(pt, src, p.partial_off);
+        uint4 raw[kU];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] += to_f32<T>(e[j]);
+        for (int u = 0; u < kU; ++u)
+          raw[u] = (i0 + u * (int)blockDim.x) < nvec ? ld_nc_v4(base + goff[u]) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const T* e = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[u][j] += to_f32<T>(e[j]);
+        }
       }
-      if (p.bias) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] += to_f32<T>(reinterpret_cast<const T*>(p.bias)[c + j]);
+      for (int u = 0; u < kU; ++u) {
+        if (i0 + u * (int)blockDim.x >= nvec) break;
+        const int c = cc[u];
+        if (p.bias) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[u][j] += to_f32<T>(reinterpret_cast<const T*>(p.bias)[c + j]);
+        }
+        const long long orow = (long long)(m_local + rr[u]);
+        if (p.residual) {
+          uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.residual) + orow * p.N + c);
+          const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[u][j] += to_f32<T>(e[j]);
+        }
+        uint4 o;
+        T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) oe[j] = from_f32<T>(acc[u][j]);
+        *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.out) + orow * p.N + c) = o;
       }
-      const long long orow = (long long)(m_local + r);
-      if (p.residual) {
-        uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.residual) + orow * p.N + c);
-        const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] += to_f32<T>(e[j]);
-      }
-      uint4 o;
-      T* oe = reinterpret_cast<T*>(&o);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) oe[j] = from_f32<T>(acc[j]);
-      *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.out) + orow * p.N + c) = o;
     }
     __syncthreads();
   }
@@ -263,6 +293,17 @@ __global__ void __launch_bounds__(512, 1)
                    const __grid_constant__ CUtensorMap tma_b, const GemmParams gp,
                    const RsHooks hooks, const RsReduceParams rp, int n_reduce_ctas) {
   extern __shared__ uint8_t smem_raw[];
+  if (n_reduce_ctas == 0) {
+    // unified mode: every CTA computes tiles until the scheduler runs dry (tiles owned by the
+    // other ranks first), then every CTA reduces a share of this rank's own tiles.  No SM is
+    // parked on a flag while there is still GEMM work, and the reduction runs at full width.
+    if (threadIdx.x < kGemmThreads)
+      gemm_cta_body<T, BN, false, B_MN, RsHooks>(&tma_a, &tma_b, gp, hooks, smem_raw, blockIdx.x,
+                                                 gridDim.x);
+    asm volatile("bar.sync 2, 512;" ::: "memory");
+    rs_reduce_role<T>(rp, blockIdx.x, gridDim.x);
+    return;
+  }
   if ((int)blockIdx.x < n_reduce_ctas) {
     rs_reduce_role<T>(rp, blockIdx.x, n_reduce_ctas);
     return;
@@ -432,7 +473,7 @@ int rb_gemm_rs(int dtype, void* const* bases, int world, int rank, const void* A
   rp.out = out; rp.bias = bias; rp.residual = residual; rp.M = M; rp.N = N; rp.BN = 256;
   rp.epoch = epoch; rp.num_n = h.num_n; rp.m_tiles_per_rank = h.m_tiles_per_rank;
   rp.status = p.status;
-  int nred = n_reduce_ctas > 0 ? n_reduce_ctas : 16;
+  int nred = n_reduce_ctas > 0 ? n_reduce_ctas : 0;   // 0: unified mode (see gemm_rs_kernel)
   const int gemm_ctas = rbh::sm_count() - nred;
   if (dtype == rbh::DT_BF16)
     return b_mn ? launch_gemm_rs<__nv_bfloat16, true>(a, h, rp, nred, gemm_ctas)

@@ -100,7 +100,7 @@ def ag_gemm(arena: SymmArena, *, buf_off: int, shard_bytes: int, chunk_flags: to
 
 def gemm_rs(arena: SymmArena, a: torch.Tensor, b: torch.Tensor, *, partial_off: int,
             tile_flags_off: int, tile_counters: torch.Tensor, epoch: int, out: torch.Tensor,
-            bias=None, residual=None, n_reduce_ctas: int = 16):
+            bias=None, residual=None, n_reduce_ctas: int = 0):
     """GEMM -> reduce-scatter in one launch: ``out [M/W, N]`` = this rank's rows of ``sum_r a_r @ b_r``."""
     L = native.lib()
     M, K = a.shape
