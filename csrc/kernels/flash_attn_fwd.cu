@@ -2,8 +2,10 @@
 //
 // One CTA owns a 128-row query tile of one (batch, head).  K/V tiles of 128 rows
 // stream through a 2-stage TMA ring.  S = Q K^T and O += P V run on tcgen05 with
-// S (double buffered) and O living in TMEM; four softmax warps own one query row
-// per thread (TMEM lane == row), keep the running max / sum in registers, write
+// S (double buffered) and O living in TMEM; eight softmax warps, two per 32-row
+// quarter: each thread owns one query row (TMEM lane == row) and half of the tile's
+// 128 key columns, the two halves agree on the row maximum through shared memory,
+// keep the running max / partial sum in registers, write
 // P as bf16/fp16 into a 128B-swizzled shared tile that the second MMA consumes,
 // and rescale O in TMEM only when the running max moved by more than 2^8 (lazy
 // rescale).  exp is exp2 with the softmax scale folded in.  LSE is saved for the
@@ -45,7 +47,7 @@ struct FaFwdCfg {
 };
 
 template <typename T, int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
     fa_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                   const __grid_constant__ CUtensorMap tv, const FaFwdParams p) {
   using C = FaFwdCfg<HD>;
@@ -58,19 +60,23 @@ __global__ void __launch_bounds__(192, 1)
   uint8_t* sP = sV + C::STAGES * C::KV_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::P_BUFS * C::P_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;    // [2]
-  uint64_t* kv_empty = bars + 3;   // [2]
+  uint64_t* kv_full = bars + 1;    // [2] K tile landed
+  uint64_t* kv_empty = bars + 3;   // [2] K slot free again (its S GEMM retired)
   uint64_t* s_full = bars + 5;     // [2]
   uint64_t* p_ready = bars + 7;    // [2]
   uint64_t* pv_done = bars + 9;    // [2]
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* max_bar = bars + 11;   // [2] both column halves have published their row maxima
+  uint64_t* sum_bar = bars + 13;   // the two partial row sums are published (once, at the end)
+  uint64_t* v_full = bars + 14;    // [2] V tile landed
+  uint64_t* v_empty = bars + 16;   // [2] V slot free again (its P.V GEMM retired)
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
   const int warp_idx = uniform_warp_idx();
   const int lane = threadIdx.x & 31;
   const int q_tile = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal tiles first
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int hkv = h / (p.H / p.Hkv);
+  const int h_idx = blockIdx.y, b = blockIdx.z;
+  const int hkv = h_idx / (p.H / p.Hkv);
   const int q0 = q_tile * C::BM;
   const int off = p.Sk - p.Sq;
   int n_tiles = (p.Sk + C::BN - 1) / C::BN;
@@ -87,16 +93,20 @@ __global__ void __launch_bounds__(192, 1)
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&kv_full[s]), 1);
       mbar_init(smem_u32(&kv_empty[s]), 1);
+      mbar_init(smem_u32(&v_full[s]), 1);
+      mbar_init(smem_u32(&v_empty[s]), 1);
       mbar_init(smem_u32(&s_full[s]), 1);
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(smem_u32(&p_ready[s]), 128);
+      mbar_init(smem_u32(&p_ready[s]), 256);
       mbar_init(smem_u32(&pv_done[s]), 1);
+      mbar_init(smem_u32(&max_bar[s]), 256);
     }
+    mbar_init(smem_u32(sum_bar), 256);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp_idx == 5) {
+  if (warp_idx == 9) {
     tmem_alloc(smem_u32(tmem_ptr_smem), C::TMEM_COLS);
     tmem_relinquish();
   }
@@ -105,33 +115,40 @@ __global__ void __launch_bounds__(192, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
-  if (warp_idx == 4) {
+  if (warp_idx == 8) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0 && n_tiles > 0) {
       mbar_arrive_expect_tx(smem_u32(q_full), C::Q_BYTES);
 #pragma unroll
       for (int s = 0; s < C::SUB; ++s)
-        tma_load_4d(smem_u32(sQ + s * C::TILE_BYTES), &tq, smem_u32(q_full), s * 64, q0, h, b);
+        tma_load_4d(smem_u32(sQ + s * C::TILE_BYTES), &tq, smem_u32(q_full), s * 64, q0, h_idx, b);
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
+        // K and V travel on separate barriers: a K slot is free as soon as the S GEMM that read it
+        // has retired, one P.V earlier than the V slot, which lets K(j) arrive before S(j) is due
         ok = mbar_wait(smem_u32(&kv_empty[st]), ph ^ 1, abort_flag, p.status, RB_ERR_TIMEOUT_EMPTY);
         if (!ok) break;
-        const uint32_t bar = smem_u32(&kv_full[st]);
-        mbar_arrive_expect_tx(bar, 2 * C::KV_BYTES);
+        const uint32_t kbar = smem_u32(&kv_full[st]);
+        mbar_arrive_expect_tx(kbar, C::KV_BYTES);
 #pragma unroll
-        for (int s = 0; s < C::SUB; ++s) {
-          tma_load_4d(smem_u32(sK + st * C::KV_BYTES + s * C::TILE_BYTES), &tk, bar, s * 64,
+        for (int s = 0; s < C::SUB; ++s)
+          tma_load_4d(smem_u32(sK + st * C::KV_BYTES + s * C::TILE_BYTES), &tk, kbar, s * 64,
                       j * C::BN, hkv, b);
-          tma_load_4d(smem_u32(sV + st * C::KV_BYTES + s * C::TILE_BYTES), &tv, bar, s * 64,
+        ok = mbar_wait(smem_u32(&v_empty[st]), ph ^ 1, abort_flag, p.status, RB_ERR_TIMEOUT_EMPTY);
+        if (!ok) break;
+        const uint32_t vbar = smem_u32(&v_full[st]);
+        mbar_arrive_expect_tx(vbar, C::KV_BYTES);
+#pragma unroll
+        for (int s = 0; s < C::SUB; ++s)
+          tma_load_4d(smem_u32(sV + st * C::KV_BYTES + s * C::TILE_BYTES), &tv, vbar, s * 64,
                       j * C::BN, hkv, b);
-        }
       }
       if (!ok)
         for (int i = 0; i < 64; ++i) __nanosleep(10000);
     }
-  } else if (warp_idx == 5) {
+  } else if (warp_idx == 9) {
     // ------------------------------ MMA issuer --------------------------------
     if (n_tiles > 0) {   // whole warp; one elected lane issues each instruction
       constexpr uint32_t idesc_s = make_idesc(UmmaFormat<T>::value, 0, 0, 128, 128);
@@ -149,6 +166,7 @@ __global__ void __launch_bounds__(192, 1)
                    make_smem_desc_sw128(k_base + o, 16, 1024), idesc_s, k != 0);
         }
         umma_commit_w(smem_u32(&s_full[j & 1]));
+        umma_commit_w(smem_u32(&kv_empty[st]));
       };
       if (ok) {
         ok = mbar_wait(smem_u32(&kv_full[0]), 0, abort_flag, p.status, RB_ERR_TIMEOUT_FULL);
@@ -168,8 +186,10 @@ __global__ void __launch_bounds__(192, 1)
         ok = mbar_wait(smem_u32(&p_ready[j & 1]), (j >> 1) & 1, abort_flag, p.status,
                        RB_ERR_TIMEOUT_FLAG);
         if (!ok) break;
-        tc_fence_after();
         const int st = j & 1;
+        ok = mbar_wait(smem_u32(&v_full[st]), (j >> 1) & 1, abort_flag, p.status, RB_ERR_TIMEOUT_FULL);
+        if (!ok) break;
+        tc_fence_after();
         const uint32_t p_base = smem_u32(sP + (j & 1) * C::P_BYTES);
         const uint32_t v_base = smem_u32(sV + st * C::KV_BYTES);
         const uint32_t d = tmem_base + C::O_COL;
@@ -180,55 +200,70 @@ __global__ void __launch_bounds__(192, 1)
                    make_smem_desc_sw128(v_base + k * 2048, C::TILE_BYTES, 1024), idesc_o,
                    (j | k) != 0);
         }
-        umma_commit_w(smem_u32(&kv_empty[st]));
+        umma_commit_w(smem_u32(&v_empty[st]));
         umma_commit_w(smem_u32(&pv_done[j & 1]));
       }
     }
   } else if (n_tiles > 0) {
     // ------------------------------ softmax warps -----------------------------
-    const int t = threadIdx.x;          // row within the tile == TMEM lane
-    const int row = q0 + t;             // global query row
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp_idx * 32) << 16);
-    float m_used = -INFINITY, l = 0.f;
+    const int h = warp_idx >> 2;                 // which half of the tile's key columns
+    const int t = (warp_idx & 3) * 32 + lane;    // row within the tile == TMEM lane
+    const int row = q0 + t;                      // global query row
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp_idx & 3) * 32) << 16);
+    constexpr int COL_X = C::O_COL + 128;        // spare TMEM columns: per-row scalars of the two halves
+    constexpr int O_CHUNKS = HD / 64;            // 32-column chunks of O per half
+    float m_used = -INFINITY, l = 0.f;           // l: this half's partial row sum
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      ok = mbar_wait(smem_u32(&s_full[j & 1]), (j >> 1) & 1, abort_flag, p.status,
-                     RB_ERR_TIMEOUT_TMEM_FULL);
+      const int jb = j & 1;
+      const uint32_t jph = (j >> 1) & 1;
+      ok = mbar_wait(smem_u32(&s_full[jb]), jph, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t s_addr = lane_addr + C::S_COL0 + (j & 1) * 128;
+      const uint32_t s_addr = lane_addr + C::S_COL0 + jb * 128 + h * 64;
       const int kv0 = j * C::BN;
+      const int kvh0 = kv0 + h * 64;               // first key column of this half
       const bool need_mask = (kv0 + C::BN > p.Sk) || (p.causal && kv0 + C::BN - 1 > q0 + off);
       const int kv_limit = p.causal ? min(p.Sk - 1, row + off) : p.Sk - 1;  // last valid kv index
-      // Load the whole S row (4 x 32 columns) once; exponentials are first computed against the
-      // running maximum already in use (m_used).  Only when this tile raises the row maximum by
-      // more than 2^8 (always on the first tile, rarely afterwards) the row is recomputed
-      // against the new maximum and O / l are rescaled.
-      uint32_t sreg[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(s_addr + c * 32, sreg[c]);
+      // This half's 64 columns of the S row are loaded once.  Exponentials are first taken against
+      // the running maximum already in use; only when the tile raises the row maximum by more
+      // than 2^8 (always on the first tile, rarely afterwards) O and l are rescaled.
+      uint32_t sreg[2][32];
+      tmem_ld_32x32b_x32(s_addr, sreg[0]);
+      tmem_ld_32x32b_x32(s_addr + 32, sreg[1]);
       tmem_ld_wait();
-      // four independent chains (one warp per scheduler: nothing else hides the fmax latency)
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (kv0 + c * 32 + i <= kv_limit) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sreg[c][i]));
+            if (kvh0 + c * 32 + i <= kv_limit)
+              mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sreg[c][i]));
       } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sreg[c][i]));
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // the other half's maximum of the same row (through a spare TMEM column of this lane)
+      tmem_st_32x32b_x1(lane_addr + COL_X + jb * 2 + h, __float_as_uint(mx));
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&max_bar[jb]));
+      ok = mbar_wait(smem_u32(&max_bar[jb]), jph, abort_flag, p.status, RB_ERR_TIMEOUT_FLAG);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      mx = fmaxf(mx, __uint_as_float(tmem_ld_32x32b_x1(lane_addr + COL_X + jb * 2 + (h ^ 1))));
+      tmem_ld_wait();
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       const bool need = m_new > m_used + 8.0f;  // also true on the first tile (m_used = -inf)
       if (j >= 2) {
         // the P buffer of tile j-2 must have been consumed
-        ok = mbar_wait(smem_u32(&pv_done[j & 1]), ((j - 2) >> 1) & 1, abort_flag, p.status,
+        ok = mbar_wait(smem_u32(&pv_done[jb]), ((j - 2) >> 1) & 1, abort_flag, p.status,
                        RB_ERR_TIMEOUT_TMEM_EMPTY);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -249,40 +284,41 @@ __global__ void __launch_bounds__(192, 1)
           l *= alpha;
         }
         if (j > 0) {
+          // each half rescales its own half of the O columns
 #pragma unroll 1
-          for (int c = 0; c < HD / 32; ++c) {
+          for (int c = 0; c < O_CHUNKS; ++c) {
             uint32_t r[32];
-            tmem_ld_32x32b_x32(lane_addr + C::O_COL + c * 32, r);
+            const uint32_t o_addr = lane_addr + C::O_COL + h * (HD / 2) + c * 32;
+            tmem_ld_32x32b_x32(o_addr, r);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32b_x32(lane_addr + C::O_COL + c * 32, r);
+            tmem_st_32x32b_x32(o_addr, r);
           }
           tmem_st_wait();
         }
       }
-      // P = exp2(S*scale - m), row sum, store to swizzled smem
+      // P = exp2(S*scale - m), partial row sum, store to swizzled smem (sub-tile h of buffer jb)
       const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint8_t* rowp = sP + jb * C::P_BYTES + h * C::TILE_BYTES + t * 128;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float p0 = fast_exp2(fmaf(__uint_as_float(sreg[c][i]), p.scale_log2, neg_m));
           float p1 = fast_exp2(fmaf(__uint_as_float(sreg[c][i + 1]), p.scale_log2, neg_m));
           if (need_mask) {
-            if (kv0 + c * 32 + i > kv_limit) p0 = 0.f;
-            if (kv0 + c * 32 + i + 1 > kv_limit) p1 = 0.f;
+            if (kvh0 + c * 32 + i > kv_limit) p0 = 0.f;
+            if (kvh0 + c * 32 + i + 1 > kv_limit) p1 = 0.f;
           }
           l4[(i >> 1) & 3] += p0 + p1;
           packed[i >> 1] = pack2<T>(p0, p1);
         }
-        // columns [c*32, c*32+32) -> sub-tile (c>>1), 16-byte chunks ((c&1)*4 .. +4)
-        uint8_t* rowp = sP + (j & 1) * C::P_BYTES + (c >> 1) * C::TILE_BYTES + t * 128;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const int cc = (c & 1) * 4 + q;
+          const int cc = c * 4 + q;
           *reinterpret_cast<uint4*>(rowp + ((cc ^ (t & 7)) << 4)) =
               make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
         }
@@ -290,7 +326,7 @@ __global__ void __launch_bounds__(192, 1)
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(smem_u32(&p_ready[j & 1]));
+      mbar_arrive(smem_u32(&p_ready[jb]));
     }
     if (ok) {
       ok = mbar_wait(smem_u32(&pv_done[(n_tiles - 1) & 1]), ((n_tiles - 1) >> 1) & 1, abort_flag,
@@ -299,12 +335,25 @@ __global__ void __launch_bounds__(192, 1)
     }
     if (ok) {
       tc_fence_after();
+      // total row sum = the two halves' partial sums
+      tmem_st_32x32b_x1(lane_addr + COL_X + 4 + h, __float_as_uint(l));
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(smem_u32(sum_bar));
+      ok = mbar_wait(smem_u32(sum_bar), 0, abort_flag, p.status, RB_ERR_TIMEOUT_FLAG);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      l += __uint_as_float(tmem_ld_32x32b_x1(lane_addr + COL_X + 4 + (h ^ 1)));
+      tmem_ld_wait();
       const float inv_l = l > 0.f ? 1.0f / l : 0.f;
-      T* orow = reinterpret_cast<T*>(p.o) + ((static_cast<long long>(b) * p.Sq + row) * p.H + h) * HD;
+      T* orow = reinterpret_cast<T*>(p.o) + ((static_cast<long long>(b) * p.Sq + row) * p.H + h_idx) * HD +
+                h * (HD / 2);
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = 0; c < O_CHUNKS; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(lane_addr + C::O_COL + c * 32, r);
+        tmem_ld_32x32b_x32(lane_addr + C::O_COL + h * (HD / 2) + c * 32, r);
         tmem_ld_wait();
         if (row < p.Sq) {
 #pragma unroll
@@ -317,15 +366,15 @@ __global__ void __launch_bounds__(192, 1)
           }
         }
       }
-      if (row < p.Sq)
-        p.lse[(static_cast<long long>(b) * p.H + h) * p.Sq + row] =
+      if (h == 0 && row < p.Sq)
+        p.lse[(static_cast<long long>(b) * p.H + h_idx) * p.Sq + row] =
             (m_used + log2f(l)) * 0.6931471805599453f;
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp_idx == 5) {
+  if (warp_idx == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
@@ -350,7 +399,7 @@ int launch_fa_fwd(int dtype, const void* q, const void* k, const void* v, const 
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   if (e != cudaSuccess) return 2000 + (int)e;
   dim3 grid((p.Sq + C::BM - 1) / C::BM, p.H, p.B);
-  kern<<<grid, 192, C::SMEM_BYTES, st>>>(tq, tk, tv, p);
+  kern<<<grid, 320, C::SMEM_BYTES, st>>>(tq, tk, tv, p);
   e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 3000 + (int)e;
 }
