@@ -94,7 +94,8 @@ int rb_gemm(int dtype, int a_mn, int b_mn, const void* A, long long lda, const v
             long long ldb, int M, int N, int K, void* out, long long ldc, int out_f32,
             const void* bias, const void* residual, long long ldr, void* aux_out,
             long long ldaux_out, const void* aux_in, long long ldaux_in, int act, int dact,
-            float alpha, int path, int bn, int max_ctas, int* path_used, void* stream) {
+            float alpha, int path, int bn, int max_ctas, int split_k, int* path_used,
+            void* stream) {
   using namespace rb;
   if (M <= 0 || N <= 0) return 0;
   GemmArgs a{};
@@ -107,6 +108,7 @@ int rb_gemm(int dtype, int a_mn, int b_mn, const void* A, long long lda, const v
   p.ldaux_in = ldaux_in; p.act = act; p.dact = dact; p.out_f32 = out_f32; p.alpha = alpha;
   p.status = rbh::device_status_word();
   p.group_m = 8;
+  p.split_k = 1;
   p.sched = rbh::dynamic_tiles() ? rbh::next_sched_slot() : nullptr;
   const int esz = dtype == rbh::DT_F32 ? 4 : 2;
   const int osz = out_f32 ? 4 : esz;
@@ -132,6 +134,16 @@ int rb_gemm(int dtype, int a_mn, int b_mn, const void* A, long long lda, const v
   if (bn == 0) {
     const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
     bn = (N <= 128 || tiles256 < rbh::sm_count()) ? 128 : 256;
+  }
+  if (split_k > 1) {
+    // split-K adds into a zero-initialised fp32 output and has no fused epilogue
+    if (!out_f32 || bias || residual || aux_out || aux_in || act || dact) return 12;
+    const int bk = dtype == rbh::DT_F32 ? 32 : 64;
+    const int num_kb = (K + bk - 1) / bk;
+    if (split_k > num_kb) split_k = num_kb;
+    const int kb_per = (num_kb + split_k - 1) / split_k;
+    split_k = (num_kb + kb_per - 1) / kb_per;   // no empty slice
+    p.split_k = split_k;
   }
   if (dtype == rbh::DT_BF16) return launch_gemm_bf16(a, bn);
   if (dtype == rbh::DT_F16) return launch_gemm_f16(a, bn);

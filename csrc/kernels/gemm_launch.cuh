@@ -79,7 +79,8 @@ int launch_gemm_one(const GemmArgs& a) {
   const int num_n = (a.p.N + BN - 1) / BN;
   int ctas = rbh::sm_count();
   if (a.max_ctas > 0 && a.max_ctas < ctas) ctas = a.max_ctas;
-  const int grid = num_m * num_n < ctas ? num_m * num_n : ctas;
+  const int items = num_m * num_n * (a.p.split_k > 1 ? a.p.split_k : 1);
+  const int grid = items < ctas ? items : ctas;
   kern<<<grid, C::NUM_THREADS, C::SMEM_BYTES, a.stream>>>(ta, tb, a.p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 3000 + (int)e;

@@ -46,6 +46,8 @@ struct GemmParams {
   int* status;           // device status word
   int group_m;           // raster group (m-tiles walked before advancing n)
   int* sched;            // device int[2] {next tile, finished CTAs} for dynamic tile scheduling, or null
+  int split_k;           // > 1: K is cut into this many slices, every (tile, slice) is a work item and
+                         // the epilogue adds into a zero-initialised fp32 output (no bias/act/residual)
 };
 
 struct NoHooks {
@@ -203,6 +205,26 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
   store_row32<OT>(reinterpret_cast<OT*>(p.out), p.ldc, row, col, ncols_valid, vec, v);
 }
 
+// split-K epilogue: out (fp32) += alpha * acc, 16-byte vector reductions where the row allows
+__device__ __forceinline__ void epilogue_chunk_atomic(const GemmParams& p, const uint32_t* acc_bits,
+                                                      long long row, int col, int ncols_valid) {
+  float* o = reinterpret_cast<float*>(p.out) + row * p.ldc + col;
+  if (p.vec_ok && ncols_valid == 32) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + i * 4),
+                   "f"(__uint_as_float(acc_bits[i * 4]) * p.alpha),
+                   "f"(__uint_as_float(acc_bits[i * 4 + 1]) * p.alpha),
+                   "f"(__uint_as_float(acc_bits[i * 4 + 2]) * p.alpha),
+                   "f"(__uint_as_float(acc_bits[i * 4 + 3]) * p.alpha)
+                   : "memory");
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < ncols_valid) atomicAdd(o + i, __uint_as_float(acc_bits[i]) * p.alpha);
+  }
+}
+
 template <typename T, int BN, bool A_MN, bool B_MN, typename Hooks>
 __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
                                               const GemmParams& p, const Hooks& hooks,
@@ -260,7 +282,9 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
   const int num_m = (p.M + BM - 1) / BM;
   const int num_n = (p.N + BN - 1) / BN;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int total_tiles = num_m * num_n;
+  const int split_k = p.split_k > 1 ? p.split_k : 1;
+  const int kb_per = (num_kb + split_k - 1) / split_k;   // K blocks per slice (no slice is empty)
+  const int total_tiles = num_m * num_n * split_k;      // work items: (tile, K slice)
   const int group_m = p.group_m > 0 ? p.group_m : 8;
 
   auto tile_coords = [&](int tile, int& m_idx, int& n_idx) {
@@ -308,9 +332,11 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
         }
         if (tile < 0) break;
         int m_idx, n_idx;
-        tile_coords(tile, m_idx, n_idx);
+        const int ks = tile % split_k;
+        tile_coords(tile / split_k, m_idx, n_idx);
+        const int kb_end = min(num_kb, (ks + 1) * kb_per);
         ok = hooks.before_tile_load(m_idx, n_idx, abort_flag, p.status);
-        for (int kbi = 0; kbi < num_kb && ok; ++kbi) {
+        for (int kbi = ks * kb_per; kbi < kb_end && ok; ++kbi) {
           const int kb = hooks.map_kb(kbi, num_kb);
           ok = hooks.before_k_load(m_idx, n_idx, kb, abort_flag, p.status);
           if (!ok) break;
@@ -374,7 +400,9 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int ks = tile % split_k;
+        const int kb_n = min(num_kb, (ks + 1) * kb_per) - ks * kb_per;
+        for (int kb = 0; kb < kb_n; ++kb) {
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status,
                          RB_ERR_TIMEOUT_FULL);
           if (!ok) break;
@@ -429,7 +457,7 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
       }
       if (tile < 0) break;
       int m_idx, n_idx;
-      tile_coords(tile, m_idx, n_idx);
+      tile_coords(tile / split_k, m_idx, n_idx);
       ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status,
                      RB_ERR_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
@@ -446,7 +474,9 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
         const int col = n_idx * BN + c * 32;
         const int ncols_valid = min(32, p.N - col);
         if (row < p.M && ncols_valid > 0) {
-          if (p.out_f32)
+          if (split_k > 1)
+            epilogue_chunk_atomic(p, r, row, col, ncols_valid);
+          else if (p.out_f32)
             epilogue_chunk<T, float>(p, r, row, col, ncols_valid);
           else
             epilogue_chunk<T, T>(p, r, row, col, ncols_valid);

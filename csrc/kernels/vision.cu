@@ -74,6 +74,77 @@ __global__ void col2im_nhwc_kernel(const T* __restrict__ dcols, T* __restrict__ 
   }
 }
 
+// 16-byte forms for 16-bit types with C % 8 == 0 and Kpad == KH*KW*C: one thread moves 8 channels.
+template <typename T>
+__global__ void im2col_nhwc_vec8_kernel(const T* __restrict__ x, T* __restrict__ cols, int B, int H,
+                                        int W, int C, int KH, int KW, int Ho, int Wo, int stride,
+                                        int pad, int dil) {
+  const int C8 = C >> 3;
+  const int K8 = KH * KW * C8;                       // 16-byte chunks per cols row
+  const long long total = (long long)B * Ho * Wo * K8;
+  const long long gs = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gs) {
+    const int k8 = (int)(i % K8);
+    const long long m = i / K8;
+    const int c8 = k8 % C8;
+    const int kk = k8 / C8;
+    const int kw = kk % KW, kh = kk / KW;
+    const int ow = (int)(m % Wo);
+    const long long t = m / Wo;
+    const int oh = (int)(t % Ho);
+    const int b = (int)(t / Ho);
+    const int ih = oh * stride - pad + kh * dil;
+    const int iw = ow * stride - pad + kw * dil;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (ih >= 0 && ih < H && iw >= 0 && iw < W)
+      v = *reinterpret_cast<const uint4*>(x + (((long long)b * H + ih) * W + iw) * C + c8 * 8);
+    reinterpret_cast<uint4*>(cols)[i] = v;
+  }
+}
+
+template <typename T>
+__global__ void col2im_nhwc_vec8_kernel(const T* __restrict__ dcols, T* __restrict__ dx, int B, int H,
+                                        int W, int C, int KH, int KW, int Ho, int Wo, int stride,
+                                        int pad, int dil) {
+  const int C8 = C >> 3;
+  const long long Kdim = (long long)KH * KW * C;
+  const long long total = (long long)B * H * W * C8;
+  const long long gs = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gs) {
+    const int c8 = (int)(i % C8);
+    long long t = i / C8;
+    const int iw = (int)(t % W);
+    t /= W;
+    const int ih = (int)(t % H);
+    const int b = (int)(t / H);
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int kh = 0; kh < KH; ++kh) {
+      const int nh = ih + pad - kh * dil;
+      if (nh < 0 || nh % stride) continue;
+      const int oh = nh / stride;
+      if (oh >= Ho) continue;
+      for (int kw = 0; kw < KW; ++kw) {
+        const int nw = iw + pad - kw * dil;
+        if (nw < 0 || nw % stride) continue;
+        const int ow = nw / stride;
+        if (ow >= Wo) continue;
+        const long long m = ((long long)b * Ho + oh) * Wo + ow;
+        const uint4 v = *reinterpret_cast<const uint4*>(dcols + m * Kdim + (kh * KW + kw) * C + c8 * 8);
+        const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += to_f32<T>(e[j]);
+      }
+    }
+    uint4 o;
+    T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) oe[j] = from_f32<T>(acc[j]);
+    reinterpret_cast<uint4*>(dx)[i] = o;
+  }
+}
+
 // ---------------------------------------------------------------------------------- batch norm
 // stage 1: per-slab partial sums over rows of an [M, C] matrix: partials[slab][0][c] = sum x,
 // partials[slab][1][c] = sum x^2  (or, in backward, sum dy' and sum dy'*xhat)
@@ -183,6 +254,255 @@ __global__ void bn_bwd_apply_kernel(const T* __restrict__ x, const T* __restrict
       o = g * d;
     }
     dx[i] = from_f32<T>(o);
+  }
+}
+
+// ------------------------------------------------------------------ batch norm, 16-byte forms
+// For 16-bit types with C % 8 == 0 and a power-of-two number of 8-channel groups (every ResNet
+// layer): one thread owns 8 consecutive channels and moves them with one 16-byte access.
+template <typename T>
+__device__ __forceinline__ void unpack8f(const uint4& v, float* f) {
+  const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) f[j] = to_f32<T>(e[j]);
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack8f(const float* f) {
+  uint4 v;
+  T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) e[j] = from_f32<T>(f[j]);
+  return v;
+}
+
+// 256 threads = cgb channel groups x (256 / cgb) row lanes; partial sums per slab as in
+// bn_partial_kernel.  cgb = min(C / 8, 32).
+template <typename T, bool BWD>
+__global__ void __launch_bounds__(256)
+    bn_partial_vec8_kernel(const T* __restrict__ x, const T* __restrict__ dy,
+                           const T* __restrict__ y, const float* __restrict__ mean,
+                           const float* __restrict__ rstd, float* __restrict__ partials,
+                           long long M, int C, int rows_per_slab, int relu, int cgb) {
+  __shared__ float s_acc[256][17];
+  const int tx = threadIdx.x % cgb, ty = threadIdx.x / cgb;
+  const int lanes = 256 / cgb;
+  const int c0 = (blockIdx.x * cgb + tx) * 8;
+  const long long r0 = (long long)blockIdx.y * rows_per_slab;
+  const long long r1 = min(M, r0 + rows_per_slab);
+  float a[8], b[8], mu[8], rs[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    a[j] = b[j] = 0.f;
+    mu[j] = BWD ? mean[c0 + j] : 0.f;
+    rs[j] = BWD ? rstd[c0 + j] : 1.f;
+  }
+  for (long long r = r0 + ty; r < r1; r += lanes) {
+    float xv[8];
+    unpack8f<T>(*reinterpret_cast<const uint4*>(x + r * C + c0), xv);
+    if (!BWD) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        a[j] += xv[j];
+        b[j] += xv[j] * xv[j];
+      }
+    } else {
+      float d[8];
+      unpack8f<T>(*reinterpret_cast<const uint4*>(dy + r * C + c0), d);
+      if (relu) {
+        float yv[8];
+        unpack8f<T>(*reinterpret_cast<const uint4*>(y + r * C + c0), yv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (yv[j] <= 0.f) d[j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        a[j] += d[j];
+        b[j] += d[j] * (xv[j] - mu[j]) * rs[j];
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    s_acc[threadIdx.x][j] = a[j];
+    s_acc[threadIdx.x][8 + j] = b[j];
+  }
+  __syncthreads();
+  if (ty == 0) {
+    for (int l = 1; l < lanes; ++l)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        a[j] += s_acc[l * cgb + tx][j];
+        b[j] += s_acc[l * cgb + tx][8 + j];
+      }
+    float* pa = partials + ((long long)blockIdx.y * 2) * C + c0;
+    float* pb = partials + ((long long)blockIdx.y * 2 + 1) * C + c0;
+    *reinterpret_cast<float4*>(pa) = make_float4(a[0], a[1], a[2], a[3]);
+    *reinterpret_cast<float4*>(pa + 4) = make_float4(a[4], a[5], a[6], a[7]);
+    *reinterpret_cast<float4*>(pb) = make_float4(b[0], b[1], b[2], b[3]);
+    *reinterpret_cast<float4*>(pb + 4) = make_float4(b[4], b[5], b[6], b[7]);
+  }
+}
+
+// Sums the slab partials of 32 channels with 8 slab slices per CTA; out2[0][c], out2[1][c] (smem)
+__device__ __forceinline__ void bn_fold_partials(const float* __restrict__ partials, int slabs,
+                                                 int C, int c, int slice, int cx, float& s,
+                                                 float& q, float (*ss)[33], float (*sq)[33]) {
+  s = 0.f;
+  q = 0.f;
+  if (c < C)
+    for (int i = slice; i < slabs; i += 8) {
+      s += partials[((long long)i * 2) * C + c];
+      q += partials[((long long)i * 2 + 1) * C + c];
+    }
+  ss[slice][cx] = s;
+  sq[slice][cx] = q;
+  __syncthreads();
+  if (slice == 0) {
+#pragma unroll
+    for (int k = 1; k < 8; ++k) {
+      s += ss[k][cx];
+      q += sq[k][cx];
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    bn_finalize_fwd_par_kernel(const float* __restrict__ partials, int slabs, int C, long long M,
+                               float eps, float momentum, float* __restrict__ mean,
+                               float* __restrict__ rstd, float* __restrict__ running_mean,
+                               float* __restrict__ running_var) {
+  __shared__ float ss[8][33], sq[8][33];
+  const int cx = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
+  float s, q;
+  bn_fold_partials(partials, slabs, C, c, slice, cx, s, q, ss, sq);
+  if (slice != 0 || c >= C) return;
+  const float mu = s / (float)M;
+  const float var = fmaxf(q / (float)M - mu * mu, 0.f);
+  mean[c] = mu;
+  rstd[c] = rsqrtf(var + eps);
+  if (running_mean) {
+    running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * mu;
+    running_var[c] = (1.f - momentum) * running_var[c] + momentum * var;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+    bn_finalize_bwd_par_kernel(const float* __restrict__ partials, int slabs, int C,
+                               float* __restrict__ sums, T* __restrict__ dgamma,
+                               T* __restrict__ dbeta) {
+  __shared__ float ss[8][33], sq[8][33];
+  const int cx = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
+  float s, q;
+  bn_fold_partials(partials, slabs, C, c, slice, cx, s, q, ss, sq);
+  if (slice != 0 || c >= C) return;
+  sums[c] = s;
+  sums[C + c] = q;
+  dbeta[c] = from_f32<T>(s);
+  dgamma[c] = from_f32<T>(q);
+}
+
+// Per-channel coefficients live in shared memory (computed once per CTA): reading mean / rstd /
+// gamma / beta per element from global memory cost 16 scattered 4-byte loads per 8 channels and
+// made these kernels L1-bound at ~1.8 TB/s.
+//   forward:  y = relu(x * a + b + res),  a = rstd * gamma,  b = beta - mean * a
+template <typename T>
+__global__ void bn_apply_vec8_kernel(const T* __restrict__ x, const T* __restrict__ res,
+                                     const T* __restrict__ gamma, const T* __restrict__ beta,
+                                     const float* __restrict__ mean, const float* __restrict__ rstd,
+                                     T* __restrict__ y, long long n8, int C, int relu) {
+  extern __shared__ float s_coef[];   // [2][C]
+  float* sa = s_coef;
+  float* sb = s_coef + C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float a = rstd[c] * to_f32<T>(gamma[c]);
+    sa[c] = a;
+    sb[c] = to_f32<T>(beta[c]) - mean[c] * a;
+  }
+  __syncthreads();
+  const int CG = C >> 3;
+  const long long gs = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += gs) {
+    const int c0 = (int)(i % CG) * 8;
+    float xv[8], rv[8];
+    unpack8f<T>(reinterpret_cast<const uint4*>(x)[i], xv);
+    if (res) unpack8f<T>(reinterpret_cast<const uint4*>(res)[i], rv);
+    const float4 a0 = *reinterpret_cast<const float4*>(sa + c0), a1 = *reinterpret_cast<const float4*>(sa + c0 + 4);
+    const float4 b0 = *reinterpret_cast<const float4*>(sb + c0), b1 = *reinterpret_cast<const float4*>(sb + c0 + 4);
+    const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float v = fmaf(xv[j], av[j], bv[j]);
+      if (res) v += rv[j];
+      if (relu) v = fmaxf(v, 0.f);
+      xv[j] = v;
+    }
+    reinterpret_cast<uint4*>(y)[i] = pack8f<T>(xv);
+  }
+}
+
+//   backward: dx = A * d + Bc * x + Cc with d = dy masked by the ReLU, and (training)
+//   A = gamma*rstd, Bc = -A*rstd*S2/M, Cc = -A*S1/M - Bc*mean;  (eval) Bc = Cc = 0
+template <typename T>
+__global__ void bn_bwd_apply_vec8_kernel(const T* __restrict__ x, const T* __restrict__ dy,
+                                         const T* __restrict__ y, const T* __restrict__ gamma,
+                                         const float* __restrict__ mean,
+                                         const float* __restrict__ rstd,
+                                         const float* __restrict__ sums, T* __restrict__ dx,
+                                         T* __restrict__ dres, long long n8, int C, long long M,
+                                         int relu, int training) {
+  extern __shared__ float s_coef[];   // [3][C]
+  float* sA = s_coef;
+  float* sB = s_coef + C;
+  float* sC = s_coef + 2 * C;
+  const float invM = 1.f / (float)M;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float rs = rstd[c];
+    const float A = to_f32<T>(gamma[c]) * rs;
+    float Bc = 0.f, Cc = 0.f;
+    if (training) {
+      Bc = -A * rs * sums[C + c] * invM;
+      Cc = -A * sums[c] * invM - Bc * mean[c];
+    }
+    sA[c] = A;
+    sB[c] = Bc;
+    sC[c] = Cc;
+  }
+  __syncthreads();
+  const int CG = C >> 3;
+  const long long gs = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += gs) {
+    const int c0 = (int)(i % CG) * 8;
+    float d[8], o[8];
+    unpack8f<T>(reinterpret_cast<const uint4*>(dy)[i], d);
+    if (relu) {
+      float yv[8];
+      unpack8f<T>(reinterpret_cast<const uint4*>(y)[i], yv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (yv[j] <= 0.f) d[j] = 0.f;
+    }
+    if (dres) reinterpret_cast<uint4*>(dres)[i] = pack8f<T>(d);
+    const float4 A0 = *reinterpret_cast<const float4*>(sA + c0), A1 = *reinterpret_cast<const float4*>(sA + c0 + 4);
+    const float Av[8] = {A0.x, A0.y, A0.z, A0.w, A1.x, A1.y, A1.z, A1.w};
+    if (training) {
+      float xv[8];
+      unpack8f<T>(reinterpret_cast<const uint4*>(x)[i], xv);
+      const float4 B0 = *reinterpret_cast<const float4*>(sB + c0), B1 = *reinterpret_cast<const float4*>(sB + c0 + 4);
+      const float4 C0 = *reinterpret_cast<const float4*>(sC + c0), C1 = *reinterpret_cast<const float4*>(sC + c0 + 4);
+      const float Bv[8] = {B0.x, B0.y, B0.z, B0.w, B1.x, B1.y, B1.z, B1.w};
+      const float Cv[8] = {C0.x, C0.y, C0.z, C0.w, C1.x, C1.y, C1.z, C1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = fmaf(Av[j], d[j], fmaf(Bv[j], xv[j], Cv[j]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = Av[j] * d[j];
+    }
+    reinterpret_cast<uint4*>(dx)[i] = pack8f<T>(o);
   }
 }
 
@@ -304,6 +624,9 @@ inline unsigned vgrid(long long n) {
   if ((dtype) == rbh::DT_BF16) { using T = __nv_bfloat16; CALL; }        \
   else if ((dtype) == rbh::DT_F16) { using T = __half; CALL; }           \
   else { using T = float; CALL; }
+#define RB_DISPATCH_16(dtype, CALL)                            \
+  if ((dtype) == rbh::DT_BF16) { using T = __nv_bfloat16; CALL; } \
+  else { using T = __half; CALL; }
 #define RB_RET_LAST()                                 \
   do {                                                \
     cudaError_t e__ = cudaGetLastError();             \
@@ -318,6 +641,15 @@ int rb_im2col_nhwc(int dtype, const void* x, void* cols, int B, int H, int W, in
   cudaStream_t st = (cudaStream_t)stream;
   const long long n = (long long)B * Ho * Wo * Kpad;
   if (n <= 0) return 0;
+  const bool a16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(cols)) & 15) == 0;
+  if (dtype != rbh::DT_F32 && C % 8 == 0 && Kpad == KH * KW * C && a16) {
+    const long long n8 = n / 8;
+    if (dtype == rbh::DT_BF16)
+      im2col_nhwc_vec8_kernel<__nv_bfloat16><<<vgrid(n8), 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)cols, B, H, W, C, KH, KW, Ho, Wo, stride, pad, dil);
+    else
+      im2col_nhwc_vec8_kernel<__half><<<vgrid(n8), 256, 0, st>>>((const __half*)x, (__half*)cols, B, H, W, C, KH, KW, Ho, Wo, stride, pad, dil);
+    RB_RET_LAST();
+  }
   RB_DISPATCH_T(dtype, (im2col_nhwc_kernel<T><<<vgrid(n), 256, 0, st>>>((const T*)x, (T*)cols, B, H, W, C, KH, KW, Ho, Wo, stride, pad, dil, Kpad)));
   RB_RET_LAST();
 }
@@ -327,6 +659,15 @@ int rb_col2im_nhwc(int dtype, const void* dcols, void* dx, int B, int H, int W, 
   cudaStream_t st = (cudaStream_t)stream;
   const long long n = (long long)B * H * W * C;
   if (n <= 0) return 0;
+  const bool a16 = ((reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(dcols)) & 15) == 0;
+  if (dtype != rbh::DT_F32 && C % 8 == 0 && Kpad == KH * KW * C && a16) {
+    const long long n8 = n / 8;
+    if (dtype == rbh::DT_BF16)
+      col2im_nhwc_vec8_kernel<__nv_bfloat16><<<vgrid(n8), 256, 0, st>>>((const __nv_bfloat16*)dcols, (__nv_bfloat16*)dx, B, H, W, C, KH, KW, Ho, Wo, stride, pad, dil);
+    else
+      col2im_nhwc_vec8_kernel<__half><<<vgrid(n8), 256, 0, st>>>((const __half*)dcols, (__half*)dx, B, H, W, C, KH, KW, Ho, Wo, stride, pad, dil);
+    RB_RET_LAST();
+  }
   RB_DISPATCH_T(dtype, (col2im_nhwc_kernel<T><<<vgrid(n), 256, 0, st>>>((const T*)dcols, (T*)dx, B, H, W, C, KH, KW, Ho, Wo, stride, pad, dil, Kpad)));
   RB_RET_LAST();
 }
@@ -343,14 +684,29 @@ int rb_bn_fwd(int dtype, const void* x, const void* res, const void* gamma, cons
   using namespace rb;
   cudaStream_t st = (cudaStream_t)stream;
   if (M <= 0) return 0;
+  const int cg = C / 8;
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  const bool vec8 = dtype != rbh::DT_F32 && C % 8 == 0 && C <= 4096 && (cg & (cg - 1)) == 0 && al16(x) &&
+                    al16(res) && al16(gamma) && al16(beta) && al16(y);
+  const int cgb = cg < 32 ? cg : 32;
   if (training) {
     const int slabs = rb_bn_slabs(M);
     const int rps = (int)((M + slabs - 1) / slabs);
-    dim3 grid((C + 63) / 64, slabs);
-    RB_DISPATCH_T(dtype, (bn_partial_kernel<T, false><<<grid, 64, 0, st>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, scratch, M, C, rps, 0)));
-    bn_finalize_fwd_kernel<<<(C + 127) / 128, 128, 0, st>>>(scratch, slabs, C, M, eps, momentum, mean, rstd, running_mean, running_var);
+    if (vec8) {
+      dim3 grid(cg / cgb, slabs);
+      RB_DISPATCH_16(dtype, (bn_partial_vec8_kernel<T, false><<<grid, 256, 0, st>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, scratch, M, C, rps, 0, cgb)));
+      bn_finalize_fwd_par_kernel<<<(C + 31) / 32, 256, 0, st>>>(scratch, slabs, C, M, eps, momentum, mean, rstd, running_mean, running_var);
+    } else {
+      dim3 grid((C + 63) / 64, slabs);
+      RB_DISPATCH_T(dtype, (bn_partial_kernel<T, false><<<grid, 64, 0, st>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, scratch, M, C, rps, 0)));
+      bn_finalize_fwd_kernel<<<(C + 127) / 128, 128, 0, st>>>(scratch, slabs, C, M, eps, momentum, mean, rstd, running_mean, running_var);
+    }
   }
-  RB_DISPATCH_T(dtype, (bn_apply_kernel<T><<<vgrid(M * C), 256, 0, st>>>((const T*)x, (const T*)res, (const T*)gamma, (const T*)beta, mean, rstd, (T*)y, M * C, C, relu)));
+  if (vec8) {
+    RB_DISPATCH_16(dtype, (bn_apply_vec8_kernel<T><<<vgrid(M * cg), 256, 2 * C * sizeof(float), st>>>((const T*)x, (const T*)res, (const T*)gamma, (const T*)beta, mean, rstd, (T*)y, M * cg, C, relu)));
+  } else {
+    RB_DISPATCH_T(dtype, (bn_apply_kernel<T><<<vgrid(M * C), 256, 0, st>>>((const T*)x, (const T*)res, (const T*)gamma, (const T*)beta, mean, rstd, (T*)y, M * C, C, relu)));
+  }
   RB_RET_LAST();
 }
 // sums: [2*C] fp32 scratch; scratch: slabs*2*C floats
@@ -362,6 +718,18 @@ int rb_bn_bwd(int dtype, const void* x, const void* dy, const void* y, const voi
   if (M <= 0) return 0;
   const int slabs = rb_bn_slabs(M);
   const int rps = (int)((M + slabs - 1) / slabs);
+  const int cg = C / 8;
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  const bool vec8 = dtype != rbh::DT_F32 && C % 8 == 0 && C <= 4096 && (cg & (cg - 1)) == 0 && al16(x) &&
+                    al16(dy) && al16(y) && al16(gamma) && al16(dx) && al16(dres);
+  if (vec8) {
+    const int cgb = cg < 32 ? cg : 32;
+    dim3 grid(cg / cgb, slabs);
+    RB_DISPATCH_16(dtype, (bn_partial_vec8_kernel<T, true><<<grid, 256, 0, st>>>((const T*)x, (const T*)dy, (const T*)y, mean, rstd, scratch, M, C, rps, relu, cgb)));
+    RB_DISPATCH_16(dtype, (bn_finalize_bwd_par_kernel<T><<<(C + 31) / 32, 256, 0, st>>>(scratch, slabs, C, sums, (T*)dgamma, (T*)dbeta)));
+    RB_DISPATCH_16(dtype, (bn_bwd_apply_vec8_kernel<T><<<vgrid(M * cg), 256, 3 * C * sizeof(float), st>>>((const T*)x, (const T*)dy, (const T*)y, (const T*)gamma, mean, rstd, sums, (T*)dx, (T*)dres, M * cg, C, M, relu, training)));
+    RB_RET_LAST();
+  }
   dim3 grid((C + 63) / 64, slabs);
   RB_DISPATCH_T(dtype, (bn_partial_kernel<T, true><<<grid, 64, 0, st>>>((const T*)x, (const T*)dy, (const T*)y, mean, rstd, scratch, M, C, rps, relu)));
   RB_DISPATCH_T(dtype, (bn_finalize_bwd_kernel<T><<<(C + 127) / 128, 128, 0, st>>>(scratch, slabs, C, sums, (T*)dgamma, (T*)dbeta)));

@@ -47,7 +47,7 @@ def _L():
 def _declare(lib) -> None:
     P, LL, I, F = c_void_p, c_longlong, c_int, c_float
     lib.rb_gemm.argtypes = [I, I, I, P, LL, P, LL, I, I, I, P, LL, I, P, P, LL, P, LL, P, LL, I, I,
-                            F, I, I, I, P, P]
+                            F, I, I, I, I, P, P]
     lib.rb_bmm_simt.argtypes = [I, I, I, P, LL, LL, P, LL, LL, I, I, I, I, P, LL, LL, I, F, P]
     lib.rb_norm_fwd.argtypes = [I, I, P, P, P, P, P, P, P, LL, I, F, P]
     lib.rb_norm_bwd_partials.argtypes = [LL]
@@ -127,17 +127,33 @@ def _mat_major(t: torch.Tensor):
     return None, None
 
 
+_SM_COUNT = None
+
+
+def sm_count() -> int:
+    """SMs of the current device (cached)."""
+    global _SM_COUNT
+    if _SM_COUNT is None:
+        _SM_COUNT = int(_L().rb_sm_count())
+    return _SM_COUNT
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
          act: Optional[str] = None, residual: Optional[torch.Tensor] = None,
          aux_out: bool = False, aux_in: Optional[torch.Tensor] = None, dact: Optional[str] = None,
          out_dtype: Optional[torch.dtype] = None, alpha: float = 1.0,
-         out: Optional[torch.Tensor] = None, path: int = 0, bn: int = 0, max_ctas: int = 0):
+         out: Optional[torch.Tensor] = None, path: int = 0, bn: int = 0, max_ctas: int = 0,
+         split_k: int = 0):
     """``out = dact'(aux_in) * act(alpha * a @ b + bias) + residual``.
 
     ``a`` is logical [M,K], ``b`` logical [K,N]; either may be a transposed view
     (``x.t()``) — the storage order is passed to the kernel as the operand's
     "major", nothing is copied.  Returns ``out`` or ``(out, pre_activation)``
     when ``aux_out``.
+
+    ``split_k`` (0 = automatic): when the output has far fewer tiles than the GPU has SMs and K
+    is long (weight gradients of convolutions: M, N a few hundred, K = batch x pixels), K is cut
+    into slices that run as separate work items adding into an fp32 buffer.
     """
     L = _L()
     assert a.is_cuda and b.is_cuda and a.dtype == b.dtype
@@ -178,13 +194,32 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
         assert residual.dtype == odt and residual.shape == (M, N) and residual.stride(1) == 1
     if aux_in is not None:
         assert aux_in.dtype == odt and aux_in.shape == (M, N) and aux_in.stride(1) == 1
+    plain = bias is None and act is None and not aux_out and aux_in is None and dact is None
+    if split_k == 0 and plain and path != 2 and K >= 4096:
+        tiles = ((M + 127) // 128) * ((N + 127) // 128)
+        sms = sm_count()
+        if tiles * 2 <= sms:
+            split_k = max(1, min(sms // tiles, K // 1024))
+    if split_k > 1 and plain:
+        ws = torch.zeros((M, N), dtype=torch.float32, device=a.device)
+        used = c_int(0)
+        rc = L.rb_gemm(dt, a_mn, b_mn, ptr(a), lda, ptr(b), ldb, M, N, K, ptr(ws), N, 1, None, None, 0,
+                       None, N, None, 0, 0, 0, float(alpha), path, bn, max_ctas, split_k,
+                       ctypes.addressof(used), stream_ptr())
+        check(rc, "rb_gemm")
+        count_launch()
+        gemm.last_path = used.value
+        if residual is not None:
+            ws.add_(residual)
+        out.copy_(ws)
+        return out
     used = c_int(0)
     rc = L.rb_gemm(dt, a_mn, b_mn, ptr(a), lda, ptr(b), ldb, M, N, K, ptr(out), out.stride(0) if M > 1 else N,
                    out_f32, ptr(bias), ptr(residual),
                    (residual.stride(0) if M > 1 else N) if residual is not None else 0,
                    ptr(pre), N, ptr(aux_in),
                    (aux_in.stride(0) if M > 1 else N) if aux_in is not None else 0,
-                   ACT_CODES[act], ACT_CODES[dact], float(alpha), path, bn, max_ctas,
+                   ACT_CODES[act], ACT_CODES[dact], float(alpha), path, bn, max_ctas, 1,
                    ctypes.addressof(used), stream_ptr())
     check(rc, "rb_gemm")
     count_launch()

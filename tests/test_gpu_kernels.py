@@ -59,6 +59,22 @@ def test_gemm_large_persistent(bn):
     assert _rel_err(out32, ref) < 5e-3
 
 
+@pytest.mark.parametrize("split_k", [0, 3, 7])
+def test_gemm_split_k_weight_gradient_shape(split_k):
+    """Few output tiles, long K (convolution weight gradients): K slices as separate work items."""
+    native = _native()
+    M, N, K = 200, 136, 12544   # 2 x 2 tiles of 128; K = 196 K-blocks of 64
+    x = torch.randn(K, M, device="cuda").half()
+    dy = torch.randn(K, N, device="cuda").half()
+    ref = x.float().t() @ dy.float()
+    out = native.gemm(x.t(), dy, path=1, split_k=split_k)
+    assert out.dtype == torch.float16
+    assert _rel_err(out, ref) < 5e-3
+    acc = torch.randn(M, N, device="cuda").half()
+    out2 = native.gemm(x.t(), dy, path=1, split_k=split_k, out=acc.clone(), residual=acc)
+    assert _rel_err(out2, ref + acc.float()) < 5e-3
+
+
 def test_gemm_epilogues():
     native = _native()
     M, N, K = 384, 512, 256

@@ -18,6 +18,7 @@ def _rel(a, b):
     dict(B=3, Cin=32, Cout=64, H=8, W=8, k=1, s=1, p=0, d=1),
     dict(B=2, Cin=16, Cout=24, H=9, W=9, k=1, s=2, p=0, d=1),
     dict(B=1, Cin=8, Cout=8, H=12, W=12, k=3, s=2, p=2, d=2),
+    dict(B=4, Cin=64, Cout=64, H=28, W=28, k=3, s=1, p=1, d=1),   # vector im2col / col2im, split-K wgrad
 ])
 def test_conv2d_fwd_bwd(dtype, tol, cfg):
     from rumus_b200.ops import vision as V
@@ -77,6 +78,36 @@ def test_batch_norm2d(relu, use_res):
     ye = V.batch_norm2d(x.detach(), w.detach(), b.detach(), rm, rv, False, 0.1, 1e-5)
     yer = V.batch_norm2d(xs[0].detach(), xs[1].detach(), xs[2].detach(), rmc, rvc, False, 0.1, 1e-5)
     assert _rel(ye.cpu(), yer) < 1e-4
+
+
+@pytest.mark.parametrize("C,relu,use_res", [(64, True, True), (256, False, False), (16, True, False)])
+def test_batch_norm2d_half_vector_path(C, relu, use_res):
+    """fp16 channels-last batch norm with C % 8 == 0 (16-byte kernels) against the fp32 CPU form."""
+    from rumus_b200.ops import vision as V
+    torch.manual_seed(5)
+    B, H, W = 6, 9, 11
+    x32 = torch.randn(B, C, H, W)
+    r32 = torch.randn(B, C, H, W) if use_res else None
+    w32, b32 = 1 + 0.1 * torch.randn(C), 0.1 * torch.randn(C)
+    g32 = torch.randn(B, C, H, W)
+    cl = dict(memory_format=torch.channels_last)
+    x = x32.cuda().half().contiguous(**cl).requires_grad_(True)
+    res = r32.cuda().half().contiguous(**cl).requires_grad_(True) if use_res else None
+    w = w32.cuda().half().requires_grad_(True)
+    b = b32.cuda().half().requires_grad_(True)
+    rm, rv = torch.zeros(C, device="cuda"), torch.ones(C, device="cuda")
+    y = V.batch_norm2d(x, w, b, rm, rv, True, 0.1, 1e-5, relu=relu, residual=res)
+    y.backward(g32.cuda().half().contiguous(**cl))
+    xs = [t.detach().float().cpu().requires_grad_(True) for t in (x, w, b)]
+    rc = res.detach().float().cpu().requires_grad_(True) if use_res else None
+    yr = V.batch_norm2d(xs[0], xs[1], xs[2], torch.zeros(C), torch.ones(C), True, 0.1, 1e-5,
+                        relu=relu, residual=rc)
+    yr.backward(g32.half().float())
+    assert _rel(y.float().cpu(), yr) < 3e-3
+    assert _rel(x.grad.float().cpu(), xs[0].grad) < 1e-2
+    assert _rel(w.grad.float().cpu(), xs[1].grad) < 1e-2 and _rel(b.grad.float().cpu(), xs[2].grad) < 1e-2
+    if use_res:
+        assert _rel(res.grad.float().cpu(), rc.grad) < 3e-3
 
 
 def test_pools():
