@@ -65,6 +65,8 @@ def main(argv=None):
     ap.add_argument("--requests", type=int, default=64)
     ap.add_argument("--rate", type=float, default=32.0)
     ap.add_argument("--comm", default="nccl")
+    ap.add_argument("--num-blocks", type=int, default=0,
+                    help="KV-cache blocks per rank (0: sized to at most 35%% of device memory)")
     a = ap.parse_args(argv)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -76,14 +78,22 @@ def main(argv=None):
         dist.init_process_group("nccl" if dev.type == "cuda" else "gloo")
     mc = LlamaConfig.llama_7b() if a.model == "7b" else LlamaConfig(
         vocab_size=32000, seq_len=4096, d_model=1024, num_heads=8, num_kv_heads=8, num_layers=4, ffn_dim=2816)
-    cfg = ServeConfig(model=mc, num_blocks=8192 if a.model == "7b" else 2048, max_batch=128,
+    num_blocks = a.num_blocks or (8192 if a.model == "7b" else 2048)
+    if dev.type == "cuda" and not a.num_blocks:
+        # bound the KV cache: block bytes = tokens x layers x (K and V) x local kv heads x head dim x 2 B
+        block_size = ServeConfig.__dataclass_fields__["block_size"].default
+        per_block = block_size * mc.num_layers * 2 * max(1, mc.num_kv_heads // world) * (mc.d_model // mc.num_heads) * 2
+        cap = int(0.35 * torch.cuda.get_device_properties(dev).total_memory / per_block)
+        num_blocks = max(64, min(num_blocks, cap))
+    cfg = ServeConfig(model=mc, num_blocks=num_blocks, max_batch=128,
                       token_budget=8192, comm_mode=a.comm,
                       dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32,
                       scale_dtype=torch.float16 if dev.type == "cuda" else torch.float32)
     eng = Engine(cfg, dev)
     res = run(eng, a.requests, a.rate, vocab=mc.vocab_size)
     if int(os.environ.get("RANK", "0")) == 0:
-        res.update({"model": a.model, "tp": world, "rate_req_s": a.rate, "weights": "INT4 g128 fp16 scales"})
+        res.update({"model": a.model, "tp": world, "rate_req_s": a.rate, "weights": "INT4 g128 fp16 scales",
+                    "kv_blocks": num_blocks})
         print(json.dumps(res))
     if world > 1:
         dist.destroy_process_group()

@@ -13,7 +13,7 @@ def _rel(a, b):
     return ((a - b).norm() / (b.norm() + 1e-12)).item()
 
 
-@pytest.mark.parametrize("M", [1, 7, 32, 200])
+@pytest.mark.parametrize("M", [1, 7, 32, 45, 128, 200])
 @pytest.mark.parametrize("K,N", [(4096, 1536), (1000, 264)])
 def test_int4_matmul(M, K, N):
     from rumus_b200.nn.quant import QuantizedTensor, qmatmul_int4
