@@ -28,28 +28,33 @@ __device__ __forceinline__ float sc_f32<__half>(__half v) { return __half2float(
 constexpr int kGemvThreads = 128;
 constexpr int kGemvMaxM = 32;
 
-// grid: (ceil(N / (4*128)), splits).  Each thread owns 4 consecutive columns.
-template <typename TX, typename TS>
+// grid: (ceil(N / (4*128)), splits).  Each thread owns 4 consecutive columns and MT rows of x
+// (MT = the launch's row bucket 1/2/4/8/16/32, so the accumulators stay in registers and no work
+// is predicated away for small batches).  Per 8 packed k values a thread dequantises its 32
+// weights once and then, per row, reads the 8 activations with two 16-byte shared loads and does
+// 32 FMAs.
+template <typename TX, typename TS, int MT>
 __global__ void __launch_bounds__(kGemvThreads)
     int4_gemv_kernel(const TX* __restrict__ x, const int* __restrict__ packed,
                      const TS* __restrict__ scales, const TS* __restrict__ zps,
                      float* __restrict__ partials /* [splits, M, N] */, int M, int N, int K, int Kp,
                      int group, int k8_per_split) {
-  extern __shared__ float sx[];  // [M][k8_per_split*8] activations of this split
+  extern __shared__ __align__(16) float sx[];  // [M][k8_per_split*8] activations of this split
   const int n0 = (blockIdx.x * kGemvThreads + threadIdx.x) * 4;
   const int k8_begin = blockIdx.y * k8_per_split;
   const int k8_end = min(Kp / 8, k8_begin + k8_per_split);
-  const int kspan = (k8_end - k8_begin) * 8;
-  for (int i = threadIdx.x; i < M * kspan; i += blockDim.x) {
-    const int m = i / kspan, kk = i - m * kspan;
+  const int kspan = k8_per_split * 8;          // row pitch in shared memory (a multiple of 8)
+  const int klive = (k8_end - k8_begin) * 8;
+  for (int i = threadIdx.x; i < M * klive; i += blockDim.x) {
+    const int m = i / klive, kk = i - m * klive;
     const int k = k8_begin * 8 + kk;
-    sx[i] = k < K ? to_f32<TX>(x[(long long)m * K + k]) : 0.f;
+    sx[m * kspan + kk] = k < K ? to_f32<TX>(x[(long long)m * K + k]) : 0.f;
   }
   __syncthreads();
   if (n0 >= N) return;
-  float acc[kGemvMaxM][4];
+  float acc[MT][4];
 #pragma unroll
-  for (int m = 0; m < kGemvMaxM; ++m)
+  for (int m = 0; m < MT; ++m)
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[m][j] = 0.f;
   float sc[4] = {0, 0, 0, 0}, zp[4] = {0, 0, 0, 0};
@@ -74,28 +79,35 @@ __global__ void __launch_bounds__(kGemvThreads)
 #pragma unroll
       for (int j = 0; j < 4; ++j) w[j] = n0 + j < N ? packed[(long long)k8 * N + n0 + j] : 0;
     }
-    const float* xs = sx + (k8 - k8_begin) * 8;
+    float wv[8][4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float wv[4];
+    for (int i = 0; i < 8; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j)
-        wv[j] = ((float)((static_cast<unsigned>(w[j]) >> (4 * i)) & 0xF) - zp[j]) * sc[j];
+        wv[i][j] = ((float)((static_cast<unsigned>(w[j]) >> (4 * i)) & 0xF) - zp[j]) * sc[j];
+    const float* xs = sx + (k8 - k8_begin) * 8;
 #pragma unroll
-      for (int m = 0; m < kGemvMaxM; ++m) {
-        if (m < M) {
-          const float xv = xs[m * kspan + i];
+    for (int m = 0; m < MT; ++m) {
+      if (m < M) {
+        const float4 x0 = *reinterpret_cast<const float4*>(xs + m * kspan);
+        const float4 x1 = *reinterpret_cast<const float4*>(xs + m * kspan + 4);
+        const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll
-          for (int j = 0; j < 4; ++j) acc[m][j] = fmaf(xv, wv[j], acc[m][j]);
-        }
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[m][j] = fmaf(xv[i], wv[i][j], acc[m][j]);
       }
     }
   }
   float* out = partials + (long long)blockIdx.y * M * N;
-  for (int m = 0; m < M; ++m)
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (n0 + j < N) out[(long long)m * N + n0 + j] = acc[m][j];
+  for (int m = 0; m < MT; ++m) {
+    if (m < M) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (n0 + j < N) out[(long long)m * N + n0 + j] = acc[m][j];
+    }
+  }
 }
 
 template <typename TX>
@@ -222,12 +234,21 @@ int rb_int4_gemv(int x_dtype, int scale_dtype, const void* x, const int* packed,
   const int real_splits = (Kp / 8 + k8_per_split - 1) / k8_per_split;
   dim3 grid((N + 4 * kGemvThreads - 1) / (4 * kGemvThreads), real_splits);
   const size_t smem = (size_t)M * k8_per_split * 8 * sizeof(float);
-#define RB_GEMV(TX, TS)                                                                          \
+#define RB_GEMV_MT(TX, TS, MT_)                                                                   \
   do {                                                                                           \
-    auto kern = int4_gemv_kernel<TX, TS>;                                                        \
+    auto kern = int4_gemv_kernel<TX, TS, MT_>;                                                   \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     kern<<<grid, kGemvThreads, smem, st>>>((const TX*)x, packed, (const TS*)scales, (const TS*)zps, \
                                            scratch, M, N, K, Kp, group, k8_per_split);           \
+  } while (0)
+#define RB_GEMV(TX, TS)                                                                          \
+  do {                                                                                           \
+    if (M <= 1) RB_GEMV_MT(TX, TS, 1);                                                           \
+    else if (M <= 2) RB_GEMV_MT(TX, TS, 2);                                                      \
+    else if (M <= 4) RB_GEMV_MT(TX, TS, 4);                                                      \
+    else if (M <= 8) RB_GEMV_MT(TX, TS, 8);                                                      \
+    else if (M <= 16) RB_GEMV_MT(TX, TS, 16);                                                    \
+    else RB_GEMV_MT(TX, TS, 32);                                                                 \
     gemv_reduce_kernel<TX><<<(unsigned)(((long long)M * N + 255) / 256), 256, 0, st>>>(          \
         scratch, real_splits, (long long)M * N, N, (const TX*)bias, (TX*)y);                     \
   } while (0)
@@ -238,6 +259,7 @@ int rb_int4_gemv(int x_dtype, int scale_dtype, const void* x, const int* packed,
   } else {
     if (scale_dtype == rbh::DT_F16) RB_GEMV(float, __half); else RB_GEMV(float, float);
   }
+#undef RB_GEMV_MT
 #undef RB_GEMV
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 3000 + (int)e;

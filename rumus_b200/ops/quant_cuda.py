@@ -20,7 +20,8 @@ native.register_signature("rb_int4_dequant", [I, I, P, P, P, P, I, I, I, P])
 native.register_signature("rb_q8_quantize", [I, P, P, I, I, I, P])
 native.register_signature("rb_q8_dequantize", [I, P, P, I, I, I, P])
 
-GEMV_MAX_M = 32
+GEMV_MAX_M = 32            # rows one GEMV launch handles (accumulators in registers)
+GEMV_CHUNKED_MAX_M = 32    # batches up to this size use (chunks of) the GEMV; larger ones dequantise + GEMM
 
 
 def int4_dequant(qw, dtype: torch.dtype) -> torch.Tensor:
@@ -38,15 +39,19 @@ def int4_matmul(x: torch.Tensor, qw, bias=None) -> torch.Tensor:
     M, K = x.shape
     assert K == qw.k
     x = x.contiguous()
-    if M <= GEMV_MAX_M:
+    if M <= GEMV_CHUNKED_MAX_M:
+        # decode batches: the packed weights are streamed once per 32 rows
         splits = L.rb_int4_gemv_splits(qw.padded_k, qw.n)
-        scratch = torch.empty((splits, M, qw.n), dtype=torch.float32, device=x.device)
         y = torch.empty((M, qw.n), dtype=x.dtype, device=x.device)
-        check(L.rb_int4_gemv(native.dtype_code(x.dtype), native.dtype_code(qw.scales.dtype), ptr(x),
-                             ptr(qw.packed), ptr(qw.scales), ptr(qw.zero_points), ptr(bias), ptr(y),
-                             ptr(scratch), M, qw.n, K, qw.padded_k, qw.group_size, stream_ptr()),
-              "rb_int4_gemv")
-        count_launch(2)
+        scratch = torch.empty((splits, min(M, GEMV_MAX_M), qw.n), dtype=torch.float32, device=x.device)
+        for r0 in range(0, M, GEMV_MAX_M):
+            rows = min(GEMV_MAX_M, M - r0)
+            check(L.rb_int4_gemv(native.dtype_code(x.dtype), native.dtype_code(qw.scales.dtype),
+                                 ptr(x[r0:r0 + rows]), ptr(qw.packed), ptr(qw.scales),
+                                 ptr(qw.zero_points), ptr(bias), ptr(y[r0:r0 + rows]), ptr(scratch),
+                                 rows, qw.n, K, qw.padded_k, qw.group_size, stream_ptr()),
+                  "rb_int4_gemv")
+            count_launch(2)
         return y
     dense = int4_dequant(qw, x.dtype)
     return native.gemm(x, dense, bias=bias)
