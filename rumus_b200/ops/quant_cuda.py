@@ -21,7 +21,9 @@ native.register_signature("rb_q8_quantize", [I, P, P, I, I, I, P])
 native.register_signature("rb_q8_dequantize", [I, P, P, I, I, I, P])
 
 GEMV_MAX_M = 32            # rows one GEMV launch handles (accumulators in registers)
-GEMV_CHUNKED_MAX_M = 32    # batches up to this size use (chunks of) the GEMV; larger ones dequantise + GEMM
+GEMV_CHUNKED_MAX_M = 8     # batches up to this size use the GEMV; larger ones dequantise + tcgen05 GEMM
+                           # (measured crossover on K 4096 x N 12288: GEMV 81 us at 8 rows, 118 us at 16;
+                           # dequantise + GEMM 85-97 us for any batch up to 128)
 
 
 def int4_dequant(qw, dtype: torch.dtype) -> torch.Tensor:

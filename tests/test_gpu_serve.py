@@ -29,6 +29,24 @@ def test_int4_matmul(M, K, N):
     assert _rel(x.grad, gref) < 1e-2
 
 
+@pytest.mark.parametrize("M", [2, 5, 16, 32, 70])
+def test_int4_gemv_all_row_buckets(M, monkeypatch):
+    """The streaming GEMV at every row bucket (and chunked above 32 rows), whatever the dispatch
+    threshold currently is."""
+    from rumus_b200.nn.quant import QuantizedTensor
+    from rumus_b200.ops import quant_cuda as Q
+    monkeypatch.setattr(Q, "GEMV_CHUNKED_MAX_M", 128)
+    torch.manual_seed(M)
+    K, N = 1160, 520     # K is not a multiple of the group size, N not of 512
+    w = torch.randn(K, N) * 0.05
+    q = QuantizedTensor.from_f32(w, 128, torch.float16).to("cuda")
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    y = Q.int4_matmul(x, q, bias)
+    ref = x.float() @ q.dequantize(torch.float32) + bias.float()
+    assert _rel(y, ref) < 1e-2
+
+
 def test_q8_roundtrip_and_matmul():
     from rumus_b200.nn.quant import dequantize_q8, matmul_q8, quantize_q8
     torch.manual_seed(0)
