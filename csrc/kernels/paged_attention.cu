@@ -13,8 +13,24 @@ namespace rb {
 
 constexpr int kPaWarps = 4;
 
-// grid (H, B, splits), 128 threads.  D = 128: every lane owns 4 consecutive dims.
+// grid (H, B, splits), 128 threads.  D = 128: eight lanes share one token (16 dims = two 16-byte
+// loads of K and of V per lane), so a warp works on four tokens at once and every 8-lane group
+// carries its own online-softmax state; two tokens per group are in flight per trip.  (One token
+// per warp with 8-byte loads left the kernel latency bound at about half the HBM rate.)
 // partial_o [B,H,splits,D] fp32, partial_ml [B,H,splits,2] (running max in log2 domain, sum).
+template <typename T>
+__device__ __forceinline__ void pa_load16(const T* p, float* f) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p);
+  const uint4 b = *reinterpret_cast<const uint4*>(p + 8);
+  const T* ea = reinterpret_cast<const T*>(&a);
+  const T* eb = reinterpret_cast<const T*>(&b);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    f[j] = to_f32<T>(ea[j]);
+    f[8 + j] = to_f32<T>(eb[j]);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kPaWarps * 32)
     paged_decode_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
@@ -23,62 +39,92 @@ __global__ void __launch_bounds__(kPaWarps * 32)
                              float* __restrict__ partial_ml, int H, int Hkv, int block_size,
                              int max_blocks, int splits, float scale_log2) {
   constexpr int D = 128;
+  constexpr int G = kPaWarps * 4;   // token groups per CTA
   const int h = blockIdx.x, b = blockIdx.y, sp = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int grp = lane >> 3, sub = lane & 7;
+  const int gid = warp * 4 + grp;
   const int hkv = h / (H / Hkv);
   const int ctx = ctx_lens[b];
   const int per = (ctx + splits - 1) / splits;
   const int t0 = sp * per, t1 = min(ctx, t0 + per);
-  float qv[4];
-  {
-    const uint2 raw = *reinterpret_cast<const uint2*>(q + ((long long)b * H + h) * D + lane * 4);
-    const T* e = reinterpret_cast<const T*>(&raw);
+  float qv[16];
+  pa_load16<T>(q + ((long long)b * H + h) * D + sub * 16, qv);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) qv[j] = to_f32<T>(e[j]) * scale_log2;
-  }
-  float m = -INFINITY, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int j = 0; j < 16; ++j) qv[j] *= scale_log2;
+  float m = -INFINITY, l = 0.f, acc[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) acc[j] = 0.f;
   const int* table = block_tables + (long long)b * max_blocks;
-  for (int t = t0 + warp; t < t1; t += kPaWarps) {
+  auto row_base = [&](int t) -> long long {
     const int blk = table[t / block_size];
-    const long long base = (((long long)blk * block_size + (t % block_size)) * Hkv + hkv) * D + lane * 4;
-    const uint2 kr = *reinterpret_cast<const uint2*>(k_cache + base);
-    const uint2 vr = *reinterpret_cast<const uint2*>(v_cache + base);
-    const T* ke = reinterpret_cast<const T*>(&kr);
-    const T* ve = reinterpret_cast<const T*>(&vr);
-    float s = 0.f;
+    return (((long long)blk * block_size + (t % block_size)) * Hkv + hkv) * D + sub * 16;
+  };
+  // every lane runs every trip (the shuffles are warp wide); out-of-range tokens are skipped
+  for (int tb = t0; tb < t1; tb += 2 * G) {
+    const int ta = tb + gid, tc = tb + G + gid;
+    const bool va = ta < t1, vc = tc < t1;
+    float ka[16], vaa[16], kc[16], vcc[16];
+    if (va) {
+      const long long base = row_base(ta);
+      pa_load16<T>(k_cache + base, ka);
+      pa_load16<T>(v_cache + base, vaa);
+    }
+    if (vc) {
+      const long long base = row_base(tc);
+      pa_load16<T>(k_cache + base, kc);
+      pa_load16<T>(v_cache + base, vcc);
+    }
+    float sa = 0.f, sc = 0.f;
+    if (va) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) s += qv[j] * to_f32<T>(ke[j]);
-    s = warp_sum(s);
-    const float mn = fmaxf(m, s);
-    const float corr = fast_exp2(m - mn);
-    const float p = fast_exp2(s - mn);
-    l = l * corr + p;
+      for (int j = 0; j < 16; ++j) sa = fmaf(qv[j], ka[j], sa);
+    }
+    if (vc) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[j] = acc[j] * corr + p * to_f32<T>(ve[j]);
-    m = mn;
+      for (int j = 0; j < 16; ++j) sc = fmaf(qv[j], kc[j], sc);
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+      sa += __shfl_xor_sync(0xffffffffu, sa, o);
+      sc += __shfl_xor_sync(0xffffffffu, sc, o);
+    }
+    if (va) {
+      const float mn = fmaxf(m, vc ? fmaxf(sa, sc) : sa);
+      const float corr = fast_exp2(m - mn);   // m = -inf on the first token: exp2(-inf) = 0
+      const float pa = fast_exp2(sa - mn);
+      const float pc = vc ? fast_exp2(sc - mn) : 0.f;
+      l = l * corr + pa + pc;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        float v = acc[j] * corr + pa * vaa[j];
+        if (vc) v = fmaf(pc, vcc[j], v);
+        acc[j] = v;
+      }
+      m = mn;
+    }
   }
-  // merge the warps of this CTA
-  __shared__ float s_m[kPaWarps], s_l[kPaWarps], s_acc[kPaWarps][D];
-  if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
+  // merge the 16 token groups of this CTA
+  __shared__ float s_m[G], s_l[G], s_acc[G][D];
+  if (sub == 0) { s_m[gid] = m; s_l[gid] = l; }
 #pragma unroll
-  for (int j = 0; j < 4; ++j) s_acc[warp][lane * 4 + j] = acc[j];
+  for (int j = 0; j < 16; ++j) s_acc[gid][sub * 16 + j] = acc[j];
   __syncthreads();
-  if (warp == 0) {
+  {
+    const int d = threadIdx.x;   // 128 threads, one output dim each
     float gm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kPaWarps; ++w) gm = fmaxf(gm, s_m[w]);
-    float gl = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int g = 0; g < G; ++g) gm = fmaxf(gm, s_m[g]);
+    float gl = 0.f, o = 0.f;
 #pragma unroll
-    for (int w = 0; w < kPaWarps; ++w) {
-      const float f = s_m[w] == -INFINITY ? 0.f : fast_exp2(s_m[w] - gm);
-      gl += s_l[w] * f;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) o[j] += s_acc[w][lane * 4 + j] * f;
+    for (int g = 0; g < G; ++g) {
+      const float f = s_m[g] == -INFINITY ? 0.f : fast_exp2(s_m[g] - gm);
+      gl += s_l[g] * f;
+      o += s_acc[g][d] * f;
     }
     const long long pi = ((long long)b * H + h) * splits + sp;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) partial_o[pi * D + lane * 4 + j] = o[j];
-    if (lane == 0) { partial_ml[pi * 2] = gm; partial_ml[pi * 2 + 1] = gl; }
+    partial_o[pi * D + d] = o;
+    if (d == 0) { partial_ml[pi * 2] = gm; partial_ml[pi * 2 + 1] = gl; }
   }
 }
 

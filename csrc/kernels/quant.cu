@@ -154,6 +154,44 @@ __global__ void int4_dequant_kernel(const int* __restrict__ packed, const TS* __
   }
 }
 
+// 16-bit outputs with N % 8 == 0: one thread dequantises 8 columns x 8 k rows (two 16-byte loads of
+// packed words, eight 16-byte stores) instead of one column with 2-byte stores.
+template <typename TO, typename TS>
+__global__ void int4_dequant_vec8_kernel(const int* __restrict__ packed, const TS* __restrict__ scales,
+                                         const TS* __restrict__ zps, TO* __restrict__ dense, int N,
+                                         int K, int group) {
+  const int N8 = N >> 3;
+  const long long total = (long long)((K + 7) / 8) * N8;
+  const long long gs = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gs) {
+    const int n0 = (int)(i % N8) * 8;
+    const int k8 = (int)(i / N8);
+    const int4 w0 = *reinterpret_cast<const int4*>(packed + (long long)k8 * N + n0);
+    const int4 w1 = *reinterpret_cast<const int4*>(packed + (long long)k8 * N + n0 + 4);
+    const unsigned w[8] = {(unsigned)w0.x, (unsigned)w0.y, (unsigned)w0.z, (unsigned)w0.w,
+                           (unsigned)w1.x, (unsigned)w1.y, (unsigned)w1.z, (unsigned)w1.w};
+    const int g = (k8 * 8) / group;
+    float sc[8], zp[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      sc[c] = sc_f32<TS>(scales[(long long)g * N + n0 + c]);
+      zp[c] = sc_f32<TS>(zps[(long long)g * N + n0 + c]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int k = k8 * 8 + j;
+      if (k < K) {
+        uint4 o;
+        TO* e = reinterpret_cast<TO*>(&o);
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          e[c] = from_f32<TO>(((float)((w[c] >> (4 * j)) & 0xF) - zp[c]) * sc[c]);
+        *reinterpret_cast<uint4*>(dense + (long long)k * N + n0) = o;
+      }
+    }
+  }
+}
+
 // ---- INT8 blocks -------------------------------------------------------------------------
 // src is the [K, N] matrix; block b covers flat column-major elements [b*bs, (b+1)*bs)
 template <typename T>
@@ -285,6 +323,18 @@ int rb_int4_dequant(int out_dtype, int scale_dtype, const int* packed, const voi
   long long blocks = (total + 255) / 256;
   const long long cap = (long long)rbh::sm_count() * 32;
   if (blocks > cap) blocks = cap;
+  if (out_dtype != rbh::DT_F32 && N % 8 == 0 &&
+      ((reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(dense)) & 15) == 0) {
+    long long b8 = (total / 8 + 255) / 256;
+    if (b8 > cap) b8 = cap;
+    if (b8 < 1) b8 = 1;
+#define RB_DQ8(TO, TS) int4_dequant_vec8_kernel<TO, TS><<<(unsigned)b8, 256, 0, st>>>(packed, (const TS*)scales, (const TS*)zps, (TO*)dense, N, K, group)
+    if (out_dtype == rbh::DT_BF16) { if (scale_dtype == rbh::DT_F16) RB_DQ8(__nv_bfloat16, __half); else RB_DQ8(__nv_bfloat16, float); }
+    else { if (scale_dtype == rbh::DT_F16) RB_DQ8(__half, __half); else RB_DQ8(__half, float); }
+#undef RB_DQ8
+    cudaError_t e8 = cudaGetLastError();
+    return e8 == cudaSuccess ? 0 : 3000 + (int)e8;
+  }
 #define RB_DQ(TO, TS) int4_dequant_kernel<TO, TS><<<(unsigned)blocks, 256, 0, st>>>(packed, (const TS*)scales, (const TS*)zps, (TO*)dense, N, K, group)
   if (out_dtype == rbh::DT_BF16) { if (scale_dtype == rbh::DT_F16) RB_DQ(__nv_bfloat16, __half); else RB_DQ(__nv_bfloat16, float); }
   else if (out_dtype == rbh::DT_F16) { if (scale_dtype == rbh::DT_F16) RB_DQ(__half, __half); else RB_DQ(__half, float); }
