@@ -12,7 +12,7 @@ column's K run is contiguous, then cut into blocks of ``block_size`` values; a b
 header (f16 scale in the low 16 bits) followed by ``block_size`` int8 values;
 ``scale = absmax/127`` (1.0 for an all-zero block), ``q = clamp(round(v*127/absmax), -128, 127)``.
 
-The dequant-GEMM kernels live in ``csrc/kernels/quant_gemm.cu``; CPU tensors use the PyTorch
+The GEMV / dequantise kernels live in ``csrc/kernels/quant.cu``; CPU tensors use the PyTorch
 restatement below, which is also the test oracle.
 """
 from __future__ import annotations

@@ -1,8 +1,8 @@
 """Vision ops: conv2d / conv_transpose2d / max_pool2d / adaptive_avg_pool2d / batch_norm2d.
 
 CPU tensors use PyTorch math (the fp32 reference); CUDA tensors run the kernels in
-``csrc/kernels/conv.cu`` / ``pool_bn.cu`` (implicit-GEMM convolution on the tcgen05 GEMM,
-NCHW activations, reference-layout weights).
+``csrc/kernels/vision.cu`` (channels-last im2col / col2im around the tcgen05 GEMM with split-K
+weight gradients, batch norm, pooling; reference-layout weights).
 
 Reference: rumus-vision/src/ops.rs:56-410 (direct conv fwd / bwd-data / bwd-weight / bias,
 max-pool with local argmax), rumus/src/tensor/ops.rs:1010-1233 (im2col conv, pools),

@@ -10,12 +10,12 @@ vector (``flat.FlatUnit``).  Per step and unit:
 
 * backward writes gradients straight into the unit's flat gradient buffer;
 * when the unit's backward has finished (an autograd boundary node fires), the side stream runs
-  **reduce-scatter + sharded Adam** — in ``fused`` mode ONE kernel (``csrc/comm/rs_adam.cu``)
+  **reduce-scatter + sharded Adam** — in ``fused`` mode ONE kernel (``rs_adam_kernel``, ``csrc/comm/fsdp_comm.cu``)
   that reads this rank's slice of every peer's gradient buffer over NVLink, averages in fp32,
   applies Adam(W) to the fp32 master shard and moments, and writes the bf16 shard in place;
 * the updated shards are **all-gathered** for the next forward — in ``fused`` mode by copy CTAs
   that pull peer shards with plain P2P loads (stand-alone kernel, or folded into the unit's first
-  consuming GEMM, ``csrc/comm/ag_gemm.cu``).
+  consuming GEMM, ``ag_gemm_kernel`` in ``csrc/comm/tp_comm.cu``).
 
 ``nccl`` mode issues ``reduce_scatter_tensor`` / ``all_gather_into_tensor`` plus the fused flat
 Adam kernel: that is the comparison baseline.  With a world size of 1 no communication happens.
