@@ -99,6 +99,8 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--mode", default=None, help="fused | nccl (multi-GPU communication path)")
     ap.add_argument("--phases", action="store_true", help="also report forward/backward/tail device times")
+    ap.add_argument("--kernel-profile", action="store_true",
+                    help="after the timed runs, print a per-kernel breakdown of two extra steps (stderr)")
     ap.add_argument("--layers", type=int, default=None, help="debug only: invalidates the number")
     ap.add_argument("--seqs-per-gpu", type=int, default=8)
     args = ap.parse_args()
@@ -216,6 +218,16 @@ def main():
         if world > 1 and hasattr(engine, "stop_trace"):
             tr = engine.stop_trace(ev[0])
             phases["unit_trace_ms"] = [[n, round(a, 2), round(b_, 2), round(c, 2)] for n, a, b_, c in tr]
+
+    if args.kernel_profile:
+        from rumus_b200.utils.metrics import kernel_breakdown
+        kb = kernel_breakdown(lambda: train_step_device(dev_tokens[args.warmup]), steps=2)
+        if rank == 0:
+            print(f"[kernel profile] {kb['kernel_ms_per_step']:.2f} ms of kernels per step over "
+                  f"{kb['launches_per_step']:.0f} launches; span {kb['span_ms_per_step']:.2f} ms; "
+                  f"busy {kb['busy_fraction']:.3f}", file=sys.stderr)
+            for name, ms, n in kb["kernels"]:
+                print(f"[kernel profile] {ms:9.3f} ms {n:6.0f}x  {name}", file=sys.stderr)
 
     if rank == 0:
         flops = cfg.flops_per_token() * B * S

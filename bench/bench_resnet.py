@@ -20,6 +20,8 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--mode", default=None)
+    ap.add_argument("--kernel-profile", action="store_true",
+                    help="print a per-kernel breakdown of two extra steps to stderr")
     a = ap.parse_args()
     import torch
     import torch.distributed as dist
@@ -82,6 +84,15 @@ def main():
                                      "optimizer": "SGD momentum 0.9"},
                           "loss": float(loss.item()), "gpu_launches": _lib.launch_count(),
                           "device_status": native.read_status()}))
+    if a.kernel_profile:
+        from rumus_b200.utils.metrics import kernel_breakdown
+        kb = kernel_breakdown(step, steps=2)
+        if rank == 0:
+            print(f"[kernel profile] {kb['kernel_ms_per_step']:.2f} ms of kernels per step over "
+                  f"{kb['launches_per_step']:.0f} launches; span {kb['span_ms_per_step']:.2f} ms; "
+                  f"busy {kb['busy_fraction']:.3f}", file=sys.stderr)
+            for name, ms_k, n in kb["kernels"]:
+                print(f"[kernel profile] {ms_k:9.3f} ms {n:6.0f}x  {name}", file=sys.stderr)
     if world > 1:
         dist.destroy_process_group()
 

@@ -75,3 +75,37 @@ def trace_range(name: str):
 
 def peak_memory_gb() -> float:
     return torch.cuda.max_memory_allocated() / 2 ** 30 if torch.cuda.is_available() else 0.0
+
+
+def kernel_breakdown(step_fn, steps: int = 2, top: int = 25):
+    """Per-kernel device time of ``steps`` calls of ``step_fn`` (torch profiler, CUDA activities).
+
+    Returns ``{"kernel_ms_per_step", "launches_per_step", "span_ms_per_step", "busy_fraction",
+    "kernels": [[name, ms_per_step, launches_per_step], ...]}``.  Kernel durations measured under
+    the profiler serve to rank kernels against each other; throughput numbers are always taken
+    without it (CUDA events around unprofiled steps).
+    """
+    import collections
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            step_fn()
+        torch.cuda.synchronize()
+    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+    agg = collections.defaultdict(lambda: [0.0, 0])
+    for e in ev:
+        agg[e.name][0] += e.device_time
+        agg[e.name][1] += 1
+    total = sum(v[0] for v in agg.values())
+    span = (max(e.time_range.end for e in ev) - min(e.time_range.start for e in ev)) if ev else 0.0
+    rows = [[name[:120], t / steps / 1e3, n / steps]
+            for name, (t, n) in sorted(agg.items(), key=lambda kv: -kv[1][0])[:top]]
+    return {"kernel_ms_per_step": total / steps / 1e3,
+            "launches_per_step": sum(v[1] for v in agg.values()) / steps,
+            "span_ms_per_step": span / steps / 1e3,
+            "busy_fraction": (total / span) if span else 0.0,
+            "kernels": rows}
