@@ -223,3 +223,51 @@ def test_topology_groups():
     assert g["tp"] == [[0, 1, 2, 3], [4, 5, 6, 7]] and g["pp"][0] == [0, 4] and g["dp_size"] == 1
     g = groups_for(8, tp=2, pp=2)
     assert g["dp"][0] == [0, 4] and len(g["tp"]) == 4
+
+
+# ------------------------------------------------------------------ context parallel attention
+def _cp_inputs(B=2, S=24, H=4, Hkv=2, D=8):
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(B, S, H, D, generator=g)
+    k = torch.randn(B, S, Hkv, D, generator=g)
+    v = torch.randn(B, S, Hkv, D, generator=g)
+    w = torch.randn(B, S, H, D, generator=g)
+    return q, k, v, w
+
+
+def _cp_worker(rank, world, scheme, causal):
+    from rumus_b200.parallel.cp import ring_attention, ulysses_attention
+    q, k, v, w = _cp_inputs()
+    S = q.shape[1]
+    sl = slice(rank * S // world, (rank + 1) * S // world)
+    ql, kl, vl = (t[:, sl].clone().requires_grad_(True) for t in (q, k, v))
+    fn = ulysses_attention if scheme == "ulysses" else ring_attention
+    o = fn(ql, kl, vl, causal)
+    (o * w[:, sl]).sum().backward()
+    return {"o": o.detach(), "dq": ql.grad, "dk": kl.grad, "dv": vl.grad}
+
+
+def _cp_check(scheme, causal, world):
+    from rumus_b200.ops import functional as F
+    q, k, v, w = _cp_inputs()
+    qr, kr, vr = (t.clone().requires_grad_(True) for t in (q, k, v))
+    o_ref = F.sdpa_reference(qr, kr, vr, causal)
+    (o_ref * w).sum().backward()
+    outs = run_ranks(_cp_worker, world, scheme, causal)
+    S = q.shape[1]
+    for r in range(world):
+        sl = slice(r * S // world, (r + 1) * S // world)
+        assert torch.allclose(outs[r]["o"], o_ref[:, sl].detach(), atol=2e-5), (scheme, causal, r)
+        assert torch.allclose(outs[r]["dq"], qr.grad[:, sl], atol=5e-5)
+        assert torch.allclose(outs[r]["dk"], kr.grad[:, sl], atol=5e-5)
+        assert torch.allclose(outs[r]["dv"], vr.grad[:, sl], atol=5e-5)
+
+
+def test_context_parallel_ulysses_matches_full_attention():
+    _cp_check("ulysses", True, 2)
+    _cp_check("ulysses", False, 2)
+
+
+def test_context_parallel_ring_matches_full_attention():
+    _cp_check("ring", True, 3)
+    _cp_check("ring", False, 2)

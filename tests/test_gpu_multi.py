@@ -26,3 +26,12 @@ def test_fused_collective_kernels_match_nccl():
     r = _run(os.path.join(ROOT, "tests", "multi_gpu", "fused_checks.py"), n)
     assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-4000:]
     assert "ALL FUSED CHECKS PASSED" in r.stdout
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2,
+                    reason="needs >= 2 GPUs")
+def test_context_parallel_attention_matches_full_sequence():
+    n = min(torch.cuda.device_count(), 4)
+    r = _run(os.path.join(ROOT, "tests", "multi_gpu", "cp_checks.py"), n)
+    assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-4000:]
+    assert "ALL CP CHECKS PASSED" in r.stdout
