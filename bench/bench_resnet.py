@@ -49,9 +49,10 @@ def main():
     def step():
         dp.zero_grad()
         loss = F.cross_entropy_loss(model(x), y)
-        scaler.scale(loss).backward()
         scaler._ensure(dev)
-        found = dp.all_reduce_grads(inv_scale=scaler.inv_scale)
+        dp.begin_backward(scaler.inv_scale)      # buckets are reduced as backward fills them
+        scaler.scale(loss).backward()
+        found = dp.all_reduce_grads()
         opt.grad_scale, opt.skip_flag = None, found      # unscale already happened inside the all-reduce
         scaler.found_inf = found
         opt.step()

@@ -56,12 +56,14 @@ class DataParallel:
     """``dp = DataParallel(model); loss.backward(); dp.all_reduce_grads(scaler)`` then step."""
 
     def __init__(self, model: nn.Module, group: Optional[dist.ProcessGroup] = None,
-                 mode: Optional[str] = None, bucket_mb: int = 256, arena=None):
+                 mode: Optional[str] = None, bucket_mb: int = 25, arena=None):
         self.model = model
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        params = [p for p in model.parameters() if p.requires_grad]
+        # reverse registration order: backward produces gradients roughly from the last layer to the
+        # first, so the first bucket to fill is the first one in the list
+        params = [p for p in model.parameters() if p.requires_grad][::-1]
         dev = params[0].device
         mode = mode or os.environ.get("RB_BACKEND", "fused")
         if self.world == 1:
@@ -96,6 +98,19 @@ class DataParallel:
                 self.buckets.append(GradBucket(cur, self.world, alloc))
         self.epoch = 0
         self.found_inf = torch.zeros(1, dtype=torch.int32, device=dev)
+        # overlap with backward: per-parameter hooks count a bucket full and reduce it right away on
+        # a side stream (armed per step by ``begin_backward``)
+        self._armed = False
+        self._inv_scale = None
+        self._launched = [False] * len(self.buckets)
+        self._pending = [0] * len(self.buckets)
+        self._handles = []
+        self._cuda = dev.type == "cuda"
+        self.comm_stream = (torch.cuda.Stream(device=dev, priority=-1)
+                            if self._cuda and self.world > 1 else None)
+        for bi, b in enumerate(self.buckets):
+            for p in b.params:
+                p.register_post_accumulate_grad_hook(self._make_hook(bi))
         if mode == "fused":
             a = self.arena
             self._flags = [(a.alloc_flags(self.world), a.alloc_flags(self.world), a.alloc_flags(self.world))
@@ -117,25 +132,77 @@ class DataParallel:
         for p in self.model.parameters():
             p.grad = None
 
-    def all_reduce_grads(self, inv_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Mean all-reduce of every bucket, fused with the unscale by ``inv_scale`` (device scalar,
-        ``1/loss_scale``).  Returns the job-wide non-finite flag (int32 device tensor)."""
+    # ------------------------------------------------------------------ overlap with backward
+    def begin_backward(self, inv_scale: Optional[torch.Tensor] = None) -> None:
+        """Call right before ``loss.backward()`` of the step whose gradients are to be reduced:
+        from then on a bucket is all-reduced (and unscaled by ``inv_scale``, a device scalar) on
+        the side stream as soon as backward has produced its last gradient."""
         self.epoch += 1
         self.found_inf.zero_()
-        for i, b in enumerate(self.buckets):
-            b.collect()
-            if self.mode == "fused":
-                from . import fused_ops
-                ef, xf, nf = self._flags[i]
+        self._armed = True
+        self._inv_scale = inv_scale
+        self._launched = [False] * len(self.buckets)
+        self._pending = [len(b.params) for b in self.buckets]
+        self._handles = []
+
+    def _make_hook(self, bi: int):
+        def hook(p):
+            if not self._armed or self._launched[bi]:
+                return
+            self._pending[bi] -= 1
+            if self._pending[bi] == 0:
+                self._launch(bi)
+        return hook
+
+    def _launch(self, i: int) -> None:
+        b = self.buckets[i]
+        self._launched[i] = True
+        b.collect()
+        if self.mode == "fused":
+            from . import fused_ops
+            ef, xf, nf = self._flags[i]
+            cur = torch.cuda.current_stream()
+            self.comm_stream.wait_stream(cur)
+            with torch.cuda.stream(self.comm_stream):
                 fused_ops.allreduce_unscale(self.arena, b.flat, enter_flags_off=ef, exit_flags_off=xf,
-                                            inf_flags_off=nf, epoch=self.epoch, inv_scale=inv_scale,
-                                            extra_scale=1.0 / self.world, found_inf=self.found_inf,
-                                            done_counter=self._counters[i])
+                                            inf_flags_off=nf, epoch=self.epoch,
+                                            inv_scale=self._inv_scale, extra_scale=1.0 / self.world,
+                                            found_inf=self.found_inf, done_counter=self._counters[i])
+        elif self.world > 1:
+            if self._cuda:
+                cur = torch.cuda.current_stream()
+                self.comm_stream.wait_stream(cur)
+                with torch.cuda.stream(self.comm_stream):
+                    self._handles.append(dist.all_reduce(b.flat, op=dist.ReduceOp.SUM, group=self.group,
+                                                         async_op=True))
             else:
-                if self.world > 1:
-                    dist.all_reduce(b.flat, op=dist.ReduceOp.SUM, group=self.group)
-                s = (float(inv_scale.item()) if inv_scale is not None else 1.0) / self.world
-                b.flat.mul_(s)
+                self._handles.append(dist.all_reduce(b.flat, op=dist.ReduceOp.SUM, group=self.group,
+                                                     async_op=True))
+
+    def all_reduce_grads(self, inv_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Mean all-reduce of every bucket, fused with the unscale by ``inv_scale`` (device scalar,
+        ``1/loss_scale``).  Returns the job-wide non-finite flag (int32 device tensor).  Buckets
+        that ``begin_backward`` already reduced during backward are only waited for."""
+        if not self._armed:
+            self.epoch += 1
+            self.found_inf.zero_()
+            self._inv_scale = inv_scale
+            self._launched = [False] * len(self.buckets)
+            self._handles = []
+        self._armed = False
+        for i in range(len(self.buckets)):
+            if not self._launched[i]:
+                self._launch(i)
+        for h in self._handles:
+            h.wait()
+        self._handles = []
+        if self.comm_stream is not None:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+        if self.mode != "fused":
+            inv = self._inv_scale
+            for b in self.buckets:
+                s_ = (float(inv.item()) if inv is not None else 1.0) / self.world
+                b.flat.mul_(s_)
                 if not torch.isfinite(b.flat).all():
                     self.found_inf.fill_(1)
         return self.found_inf

@@ -217,6 +217,41 @@ def test_data_parallel_mean_gradients():
         assert torch.allclose(p.grad, gref, atol=1e-6)
 
 
+def _dp_overlap_worker(rank, world):
+    from rumus_b200.parallel.dp import DataParallel
+    torch.manual_seed(30)
+    m = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Tanh(), torch.nn.Linear(5, 4),
+                            torch.nn.Tanh(), torch.nn.Linear(4, 2))
+    dp = DataParallel(m, bucket_mb=0)          # one bucket per parameter
+    assert len(dp.buckets) == 6
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(world * 3, 6, generator=g)
+    launched_during_backward = []
+    for use_overlap in (True, False):
+        dp.zero_grad()
+        if use_overlap:
+            dp.begin_backward()
+        (m(x[rank * 3:(rank + 1) * 3]) ** 2).mean().backward()
+        launched_during_backward.append(sum(dp._launched) if use_overlap else 0)
+        found = dp.all_reduce_grads()
+        assert int(found.item()) == 0
+        if use_overlap:
+            g_overlap = [p.grad.clone() for p in m.parameters()]
+        else:
+            g_plain = [p.grad.clone() for p in m.parameters()]
+    return g_overlap, g_plain, launched_during_backward[0]
+
+
+def test_data_parallel_overlapped_buckets_match_plain():
+    outs = run_ranks(_dp_overlap_worker, 2)
+    for g_overlap, g_plain, n_launched in outs:
+        assert n_launched == 6, "every bucket must have been reduced from its hook during backward"
+        for a, b in zip(g_overlap, g_plain):
+            assert torch.allclose(a, b, atol=1e-6)
+    for a, b in zip(outs[0][0], outs[1][0]):
+        assert torch.allclose(a, b, atol=1e-6)
+
+
 def test_topology_groups():
     from rumus_b200.parallel.topology import groups_for
     g = groups_for(8, tp=4, pp=2)
