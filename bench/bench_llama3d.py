@@ -107,7 +107,8 @@ def main():
                           "config": {"model": f"Llama {a.layers}L d{a.d_model} h{a.heads} ffn{a.ffn} vocab{a.vocab}",
                                      "global_batch": a.global_batch, "seq_len": a.seq,
                                      "parallelism": f"tp{a.tp}xpp{a.pp}xdp{topo.dp}", "micro_batches": a.micro_batches,
-                                     "schedule": "1F1B", "comm_mode": tp.mode},
+                                     "schedule": "1F1B", "comm_mode": tp.mode,
+                                     "bubble_fraction_ideal": (a.pp - 1) / (a.micro_batches + a.pp - 1)},
                           "model_tflops_per_gpu": cfg.flops_per_token() * tokens / (ms / 1e3) / 1e12 / world,
                           "loss": lt.item(), "gpu_launches": _lib.launch_count(), "device_status": int(st.item())}))
     dist.destroy_process_group()

@@ -33,6 +33,12 @@ def one_f_one_b_order(stage: int, num_stages: int, num_micro: int) -> List[tuple
     return ops
 
 
+def bubble_fraction(num_stages: int, num_micro: int) -> float:
+    """Idle share of a 1F1B step when every micro-batch stage takes the same time:
+    ``(P - 1) / (M + P - 1)`` (P - 1 warm-up and P - 1 drain slots out of M + P - 1 per direction)."""
+    return (num_stages - 1) / float(num_micro + num_stages - 1)
+
+
 class PipelineStage:
     """``forward_fn(x_or_microbatch) -> tensor``; the last stage's ``forward_fn`` returns the loss
     of the micro-batch (already divided by the number of micro-batches by ``run``)."""

@@ -128,6 +128,16 @@ def test_pipeline_1f1b_matches_sequential():
     assert all(run_ranks(_pp_worker, 3))
 
 
+def test_bubble_fraction_matches_schedule_length():
+    from rumus_b200.parallel.pp import bubble_fraction, one_f_one_b_order
+    for P, M in ((2, 8), (4, 8), (4, 4)):
+        # stage 0's schedule has M forwards and M backwards; with unit-time slots the step spans
+        # M + P - 1 slots per direction, the rest is the bubble
+        assert len(one_f_one_b_order(0, P, M)) == 2 * M
+        assert abs(bubble_fraction(P, M) - (P - 1) / (M + P - 1)) < 1e-12
+    assert bubble_fraction(2, 8) == 1 / 9
+
+
 def test_1f1b_order_properties():
     from rumus_b200.parallel.pp import one_f_one_b_order
     for P in (2, 4):
