@@ -226,8 +226,8 @@ def main():
             print(f"[kernel profile] {kb['kernel_ms_per_step']:.2f} ms of kernels per step over "
                   f"{kb['launches_per_step']:.0f} launches; span {kb['span_ms_per_step']:.2f} ms; "
                   f"busy {kb['busy_fraction']:.3f}", file=sys.stderr)
-            for name, ms, n in kb["kernels"]:
-                print(f"[kernel profile] {ms:9.3f} ms {n:6.0f}x  {name}", file=sys.stderr)
+            for k_name, k_ms, k_n in kb["kernels"]:
+                print(f"[kernel profile] {k_ms:9.3f} ms {k_n:6.0f}x  {k_name}", file=sys.stderr)
 
     if rank == 0:
         flops = cfg.flops_per_token() * B * S
