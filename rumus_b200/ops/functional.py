@@ -627,3 +627,130 @@ def _sdpa_composed(q, k, v, causal, scale):
     p = softmax(s)
     o = bmm(p, vh)
     return o.view(B, H, S, d).permute(0, 2, 1, 3)
+
+
+# ---------------------------------------------------------------------------------------------
+# Reference op names that are plain tensor-layer operations here
+# ---------------------------------------------------------------------------------------------
+# The reference implements views, pointwise arithmetic, slicing and concatenation itself
+# (rumus/src/tensor/ops.rs); here the tensor layer is PyTorch, so these are its own
+# (differentiable, broadcasting, strided) operations under the reference's names, kept so that code
+# written against the reference's op list finds every entry.
+
+def transpose(x, dim0: int = -2, dim1: int = -1):
+    """rumus/src/tensor/ops.rs:36 / :1612 (tracked): a strided view, no copy."""
+    return x.transpose(dim0, dim1)
+
+
+def batched_transpose(x):
+    """rumus/src/tensor/ops.rs:1644: swap the last two dims of a ``[B, M, N]`` tensor."""
+    return x.transpose(-2, -1)
+
+
+def reshape(x, *shape):
+    """rumus/src/tensor/ops.rs:44 / :1242 (tracked)."""
+    return x.reshape(*shape)
+
+
+def flatten(x, start_dim: int = 1):
+    """rumus/src/tensor/ops.rs:2366: ``[B, ...] -> [B, prod(...)]``."""
+    return x.flatten(start_dim)
+
+
+def contiguous(x):
+    """rumus/src/tensor/ops.rs:61 / :1573 (tracked)."""
+    return x.contiguous()
+
+
+def add(a, b):
+    """rumus/src/tensor/ops.rs:404 (same shape) and :2154 (broadcast)."""
+    return a + b
+
+
+def sub(a, b):
+    """rumus/src/tensor/ops.rs:448 and :2174."""
+    return a - b
+
+
+def mul(a, b):
+    """rumus/src/tensor/ops.rs:469 and :2194."""
+    return a * b
+
+
+broadcast_add, broadcast_sub, broadcast_mul = add, sub, mul
+
+
+def tanh_act(x):
+    """rumus/src/tensor/ops.rs:1422."""
+    return tanh(x)
+
+
+def to_dtype(x, dtype: torch.dtype):
+    """rumus/src/tensor/ops.rs:2205 (F32 <-> F16 there; any floating dtype here, differentiable)."""
+    return x.to(dtype)
+
+
+def slice_batch(x, start: int, end: int):
+    """rumus/src/tensor/ops.rs:944: rows ``[start, end)`` of the leading dim."""
+    return x[start:end]
+
+
+def slice_range(x, dim: int, start: int, end: int):
+    """rumus/src/tensor/ops.rs:2423."""
+    return x.narrow(dim, start, end - start)
+
+
+def cat(tensors, dim: int = 0):
+    """rumus/src/tensor/ops.rs:2498."""
+    return torch.cat(list(tensors), dim=dim)
+
+
+def stack(tensors, dim: int = 0):
+    """rumus/src/tensor/ops.rs:2599."""
+    return torch.stack(list(tensors), dim=dim)
+
+
+def add_channel_bias(x, bias):
+    """rumus/src/tensor/ops.rs:1084: ``x [.., C, H, W] + bias [C]``."""
+    return x + bias.view(-1, 1, 1)
+
+
+def im2col(x, kernel_size: int, stride: int = 1, padding: int = 0):
+    """rumus/src/tensor/ops.rs:1010: ``[C, H, W]`` (or ``[B, C, H, W]``) -> ``[C*k*k, L]`` columns
+    (``[B, C*k*k, L]``).  Convolutions do not go through this op here (they use the channels-last
+    kernels of ``ops/vision.py``); it exists for code that builds its own unfold-based layers."""
+    squeeze = x.dim() == 3
+    cols = torch.nn.functional.unfold(x[None] if squeeze else x, kernel_size, padding=padding,
+                                      stride=stride)
+    return cols[0] if squeeze else cols
+
+
+def batch_norm_2d(x, weight, bias, running_mean, running_var, training: bool,
+                  momentum: float = 0.1, eps: float = 1e-5):
+    """rumus/src/tensor/ops.rs:1840."""
+    from .vision import batch_norm2d
+    return batch_norm2d(x, weight, bias, running_mean, running_var, training, momentum, eps)
+
+
+def max_pool2d(x, kernel_size: int, stride: Optional[int] = None, padding: int = 0):
+    """rumus/src/tensor/ops.rs:1163."""
+    from .vision import max_pool2d as _mp
+    return _mp(x, kernel_size, stride, padding)
+
+
+def adaptive_avg_pool2d(x, output_size):
+    """rumus/src/tensor/ops.rs:2019."""
+    from .vision import adaptive_avg_pool2d as _ap
+    return _ap(x, output_size)
+
+
+def quantize(weight, block_size: int = 32):
+    """rumus/src/tensor/ops.rs:2290: per-block INT8 of a ``[K, N]`` weight (reference byte layout)."""
+    from ..nn.quant import quantize_q8
+    return quantize_q8(weight, block_size)
+
+
+def dequantize(q, dtype: torch.dtype = torch.float32):
+    """rumus/src/tensor/ops.rs:2332."""
+    from ..nn.quant import dequantize_q8
+    return dequantize_q8(q, dtype)

@@ -283,3 +283,29 @@ def test_int4_and_q8_formats():
     assert raw.item() == scale.item()
     assert (dequantize_q8(q8) - w8).abs().max() < 0.02 * w8.abs().max()
     assert matmul_q8(torch.randn(3, 64), q8).shape == torch.Size([3, 6])
+
+
+def test_reference_op_names_are_all_present():
+    """Every public op of the reference's tensor surface (rumus/src/tensor/ops.rs) has a function of
+    the same name; the plain tensor-layer ones behave like their PyTorch counterparts."""
+    import torch
+    from rumus_b200.ops import functional as F
+    names = ("transpose reshape contiguous add sub mul matmul relu mse_loss cross_entropy_loss add_bias "
+             "slice_batch im2col add_channel_bias max_pool2d flatten dropout sigmoid tanh_act gelu leaky_relu "
+             "bmm batched_transpose softmax layer_norm batch_norm_2d adaptive_avg_pool2d embedding "
+             "broadcast_add broadcast_sub broadcast_mul to_dtype quantize dequantize slice_range cat stack "
+             "flash_attention").split()
+    missing = [n for n in names if not callable(getattr(F, n, None))]
+    assert not missing, missing
+    torch.manual_seed(0)
+    x = torch.randn(2, 3, 8, 8, requires_grad=True)
+    assert F.im2col(x, 3, 1, 1).shape == (2, 27, 64) and F.im2col(x[0], 3).shape == (27, 36)
+    assert torch.equal(F.add_channel_bias(x, torch.arange(3.0)), x + torch.arange(3.0).view(3, 1, 1))
+    assert torch.equal(F.slice_range(x, 1, 1, 3), x[:, 1:3]) and torch.equal(F.slice_batch(x, 1, 2), x[1:2])
+    assert F.stack([x, x]).shape == (2, 2, 3, 8, 8) and F.cat([x, x], 1).shape == (2, 6, 8, 8)
+    assert torch.equal(F.broadcast_mul(x, torch.ones(8)), x) and torch.equal(F.sub(x, x), torch.zeros_like(x))
+    assert F.batched_transpose(x).shape == (2, 3, 8, 8) and F.flatten(x).shape == (2, 192)
+    w = torch.randn(64, 16)
+    assert (F.dequantize(F.quantize(w)) - w).abs().max() < 0.05
+    F.to_dtype(F.tanh_act(x), torch.float64).sum().backward()
+    assert x.grad is not None and x.grad.shape == x.shape
