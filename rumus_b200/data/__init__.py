@@ -3,3 +3,5 @@ record format."""
 from .dataset import DataItem, Dataset, TensorDataset, SyntheticTokens, SyntheticImages
 from .dataloader import DataLoader, collate
 from .record import RecordWriter, RecordDataset
+
+RecordReader = RecordDataset   # the reference's name for the mmap reader (rumus/src/data/record.rs)
