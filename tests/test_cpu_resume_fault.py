@@ -138,3 +138,20 @@ def test_peer_loss_is_detected_before_the_next_collective():
     out = run_ranks(_fault_worker, 2, timeout=120)
     assert out[1] == (2, False)          # the leaving rank completed steps 0 and 1
     assert out[0] == (2, True)           # the survivor noticed and launched nothing further
+
+
+def test_flag_protocols_hold_on_every_interleaving():
+    """Model check of the fused kernels' epoch-flag protocols (every interleaving of 2 and 3 ranks
+    over two steps), and proof that the checker sees the hazard once a wait is taken out."""
+    import pytest
+    from rumus_b200.utils.protocol_check import (ProtocolViolation, allreduce_programs, explore,
+                                                 fsdp_unit_programs)
+    assert explore(fsdp_unit_programs(2, 2)) > 100
+    assert explore(fsdp_unit_programs(3, 2)) > 1000
+    assert explore(allreduce_programs(2, 2)) > 100
+    with pytest.raises(ProtocolViolation):
+        explore(fsdp_unit_programs(2, 2, wait_param_flags=False))   # shard read before it is written
+    with pytest.raises(ProtocolViolation):
+        explore(fsdp_unit_programs(2, 2, wait_grad_flags=False))    # gradient read before the write
+    with pytest.raises(ProtocolViolation):
+        explore(allreduce_programs(2, 2, exit_barrier=False))       # reads a half-reduced bucket
