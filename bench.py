@@ -99,6 +99,9 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--mode", default=None, help="fused | nccl (multi-GPU communication path)")
     ap.add_argument("--phases", action="store_true", help="also report forward/backward/tail device times")
+    ap.add_argument("--trace-export", default=None,
+                    help="write a torch.profiler Chrome trace of two extra steps (with the NVTX-named "
+                         "ranges of the fused paths) to this path")
     ap.add_argument("--kernel-profile", action="store_true",
                     help="after the timed runs, print a per-kernel breakdown of two extra steps (stderr)")
     ap.add_argument("--layers", type=int, default=None, help="debug only: invalidates the number")
@@ -219,6 +222,18 @@ def main():
             tr = engine.stop_trace(ev[0])
             phases["unit_trace_ms"] = [[n, round(a, 2), round(b_, 2), round(c, 2)] for n, a, b_, c in tr]
 
+    if args.trace_export:
+        # every rank runs the two extra steps (they contain collectives); rank 0 writes the trace
+        from torch.profiler import ProfilerActivity, profile
+        from rumus_b200.utils.metrics import enable_tracing
+        enable_tracing(True)
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+            for _ in range(2):
+                train_step_device(dev_tokens[args.warmup])
+            torch.cuda.synchronize()
+        if rank == 0:
+            prof.export_chrome_trace(args.trace_export)
+        enable_tracing(False)
     if args.kernel_profile:
         from rumus_b200.utils.metrics import kernel_breakdown
         kb = kernel_breakdown(lambda: train_step_device(dev_tokens[args.warmup]), steps=2)

@@ -17,6 +17,7 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from ..utils.metrics import trace_range
 from .flat import _round_up
 
 
@@ -155,6 +156,10 @@ class DataParallel:
         return hook
 
     def _launch(self, i: int) -> None:
+        with trace_range(f"dp.{self.mode}.bucket{i}"):
+            self._launch_bucket(i)
+
+    def _launch_bucket(self, i: int) -> None:
         b = self.buckets[i]
         self._launched[i] = True
         b.collect()

@@ -30,6 +30,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from ..ops import native
+from ..utils.metrics import trace_range
 from .flat import FlatUnit, build_units, default_units
 
 
@@ -187,7 +188,7 @@ class FSDP:
             ev[0].record(cur)
             trace.append((u.name, ev))
         self.comm_stream.wait_stream(cur)
-        with torch.cuda.stream(self.comm_stream):
+        with torch.cuda.stream(self.comm_stream), trace_range(f"fsdp.{self.mode}.{u.name}"):
             if trace is not None:
                 ev[1].record(self.comm_stream)
             if self.mode == "fused":

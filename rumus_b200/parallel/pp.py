@@ -17,6 +17,8 @@ from __future__ import annotations
 from typing import Callable, List, Optional, Sequence
 
 import torch
+
+from ..utils.metrics import trace_range
 import torch.distributed as dist
 
 
@@ -98,7 +100,8 @@ class PipelineStage:
                 x = x.requires_grad_(True)
             else:
                 x = micro_batches[mb]
-            out = self.forward_fn(x) if not self.is_last else self.forward_fn((x, micro_batches[mb]))
+            with trace_range(f"pp.stage{self.stage}.fwd.mb{mb}"):
+                out = self.forward_fn(x) if not self.is_last else self.forward_fn((x, micro_batches[mb]))
             if self.is_last:
                 out = out / M
                 total_loss = out.detach() if total_loss is None else total_loss + out.detach()
@@ -110,10 +113,11 @@ class PipelineStage:
             if ops_log is not None:
                 ops_log.append(("B", mb))
             x, out = inputs.pop(0), outputs.pop(0)
-            if self.is_last:
-                out.backward()
-            else:
-                torch.autograd.backward(out, grad_out)
+            with trace_range(f"pp.stage{self.stage}.bwd.mb{mb}"):
+                if self.is_last:
+                    out.backward()
+                else:
+                    torch.autograd.backward(out, grad_out)
             return None if self.is_first else x.grad
 
         f = b = 0

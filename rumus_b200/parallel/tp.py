@@ -30,6 +30,7 @@ import torch.nn as nn
 from ..nn.modules import Module, _linear_rng, _uniform
 from ..ops import functional as F
 from ..ops import native
+from ..utils.metrics import trace_range
 
 
 class TPContext:
@@ -96,6 +97,11 @@ def _mm(a, b):
 
 
 def _fused_ag_gemm(ctx: TPContext, x_local, w, bias=None, act=None):
+    with trace_range("tp.fused.ag_gemm"):
+        return _fused_ag_gemm_impl(ctx, x_local, w, bias, act)
+
+
+def _fused_ag_gemm_impl(ctx: TPContext, x_local, w, bias=None, act=None):
     """x_local [M/T, K] (each rank's rows) , w [K, N] logical -> (y [M, N], gathered x [M, K])."""
     from . import fused_ops
     a = ctx.arena
@@ -129,6 +135,11 @@ def _announce(ctx: TPContext, epoch: int) -> None:
 
 
 def _fused_gemm_rs(ctx: TPContext, a_mat, w, bias=None):
+    with trace_range("tp.fused.gemm_rs"):
+        return _fused_gemm_rs_impl(ctx, a_mat, w, bias)
+
+
+def _fused_gemm_rs_impl(ctx: TPContext, a_mat, w, bias=None):
     """a_mat [M, K_local], w [K_local, N] -> y_local [M/T, N] (sum over ranks)."""
     from . import fused_ops
     M, K = a_mat.shape

@@ -28,6 +28,7 @@ import torch
 import torch.distributed as dist
 
 from ..models.llama import LlamaConfig
+from ..utils.metrics import trace_range
 from ..nn.quant import QuantizedTensor, qmatmul_int4
 from ..ops import _lib, functional as F, native
 from ..ops._lib import check, count_launch, ptr, stream_ptr
@@ -385,7 +386,8 @@ class Engine:
     # ------------------------------------------------------------------ one engine step
     def step(self) -> List[int]:
         """Runs one scheduling step; returns the ids of requests that finished."""
-        decode_ids, prefills = self.sched.schedule()
+        with trace_range("serve.schedule"):
+            decode_ids, prefills = self.sched.schedule()
         if not decode_ids and not prefills:
             return []
         dev, scale = self.device, 1.0 / math.sqrt(self.model.hd)
@@ -409,7 +411,8 @@ class Engine:
                 vv = self.cache.v[li][table[idx // bs], idx % bs]
                 return F.flash_attention(q[None], kk[None], vv[None], True, scale)[0]
 
-            hidden = self._forward(toks, pos, slots, attend)
+            with trace_range("serve.prefill_chunk"):
+                hidden = self._forward(toks, pos, slots, attend)
             if start + n >= len(seq):
                 now_tokens[rid] = int(self._logits_argmax(hidden[-1:])[0])
         # ---- decode batch
@@ -436,7 +439,8 @@ class Engine:
                 return paged_decode_attention(q.contiguous(), self.cache.k[li], self.cache.v[li], tables,
                                               ctx_t, scale, max_ctx)
 
-            hidden = self._forward(toks, pos, slots_t, attend_dec)
+            with trace_range("serve.decode_batch"):
+                hidden = self._forward(toks, pos, slots_t, attend_dec)
             ids = self._logits_argmax(hidden)
             for r, t in zip(decode_ids, ids.tolist()):
                 now_tokens[r] = int(t)

@@ -60,10 +60,21 @@ class DeviceTimer:
         return False
 
 
+_NVTX_ON = os.environ.get("RB_NVTX", "0") == "1"
+
+
+def enable_tracing(on: bool = True) -> None:
+    """Turns the NVTX ranges of the fused paths / pipeline / serving phases on or off (default:
+    env ``RB_NVTX=1``)."""
+    global _NVTX_ON
+    _NVTX_ON = on
+
+
 @contextlib.contextmanager
 def trace_range(name: str):
-    """NVTX range (shows up in profiler timelines); no-op without CUDA."""
-    if torch.cuda.is_available():
+    """NVTX range around a fused path or scheduler phase (shows up in profiler timelines).  Off by
+    default so that the hot path pays nothing; no-op without CUDA."""
+    if _NVTX_ON and torch.cuda.is_available():
         torch.cuda.nvtx.range_push(name)
         try:
             yield
