@@ -155,3 +155,65 @@ def test_flag_protocols_hold_on_every_interleaving():
         explore(fsdp_unit_programs(2, 2, wait_grad_flags=False))    # gradient read before the write
     with pytest.raises(ProtocolViolation):
         explore(allreduce_programs(2, 2, exit_barrier=False))       # reads a half-reduced bucket
+
+
+def _elastic_worker(rank, world, generation, root, total_steps):
+    """FSDP training on CPU ranks with a checkpoint every 2 steps.  In generation 0 rank 1 leaves
+    after step 3 (host-side injection) and the survivors stop on ``PeerLost``; every later
+    generation resumes from the newest checkpoint, whatever its world size was."""
+    import sys
+    from rumus_b200.io.checkpoint import load_checkpoint, save_checkpoint
+    from rumus_b200.parallel import FSDP
+    from rumus_b200.utils import FaultInjector, Heartbeat, PeerLost
+    from rumus_b200.utils.elastic import latest_checkpoint
+    os.environ["RB_BACKEND"] = "cpu"
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    store = dist.distributed_c10d._get_default_store()
+    hb = Heartbeat(store, rank, world, interval_s=0.05, timeout_s=0.6).start()
+    inj = FaultInjector(rank, "exit:1:3" if generation == 0 else "")
+    m = _make(); e = FSDP(m, lr=1e-2)
+    ck = latest_checkpoint(root)
+    if ck is not None:
+        load_checkpoint(ck, m, e)
+    data = _data()
+    rc = 0
+    try:
+        while e.step_count < total_steps:
+            step = e.step_count
+            if not inj.before_step(step, hb):
+                rc = 17                                   # leaves between steps, nothing in flight
+                break
+            if generation == 0 and step >= 3:
+                time.sleep(0.9)                           # let the lost peer's heartbeat go stale
+            hb.check_peers()
+            per = 4 // world if 4 % world == 0 else 1
+            _step(m, e, data[step % 6][rank * per:(rank + 1) * per])
+            if e.step_count % 2 == 0:
+                save_checkpoint(os.path.join(root, f"step-{e.step_count}"), m, e)
+    except PeerLost:
+        rc = 18
+    hb.stop()
+    if rc == 0:
+        dist.barrier()
+        if rank == 0:
+            with open(os.path.join(root, f"done-gen{generation}.json"), "w") as f:
+                json.dump({"steps": e.step_count, "world": world, "resumed_from": ck}, f)
+        dist.destroy_process_group()
+    # a rank that lost a peer must not run the process-group destructor's collectives
+    os._exit(rc)
+
+
+def test_elastic_supervisor_restarts_smaller_from_last_checkpoint(tmp_path):
+    from rumus_b200.utils.elastic import ElasticSupervisor, latest_checkpoint
+    root = str(tmp_path)
+    sup = ElasticSupervisor(_elastic_worker, world=2, args=(root, 8), max_restarts=2,
+                            shrink_on_failure=True)
+    hist = sup.run()
+    assert len(hist) == 2
+    assert hist[0].world == 2 and 1 in hist[0].failed_ranks and hist[0].exit_codes[1] == 17
+    assert hist[1].world == 1 and hist[1].exit_codes == [0]
+    done = json.load(open(os.path.join(root, "done-gen1.json")))
+    # generation 0 saved step-2 (step 4 was never reached: rank 1 left after step 3)
+    assert done["steps"] == 8 and done["world"] == 1 and done["resumed_from"].endswith("step-2")
+    assert latest_checkpoint(root).endswith("step-8")
