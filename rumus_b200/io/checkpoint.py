@@ -6,11 +6,15 @@ re-shards the optimizer state for a different world size.
 Layout of a checkpoint directory:
   model.safetensors            fp32, reference tensor names, [in, out] Linear weights (rank 0)
   optim-rank{r}.safetensors    fp32 master / exp_avg / exp_avg_sq shards of every flat unit
-  trainer_state.json           step, lr, betas, world size, per-unit (numel, padded, shard) sizes
-All files are written to a temporary name and renamed (atomic on POSIX).
+  trainer_state.json           step, lr, betas, world size, per-unit (numel, padded, shard) sizes,
+                               SHA-256 of every other file
+All files are written to a temporary name and renamed (atomic on POSIX); ``trainer_state.json`` is
+written last, after every rank's shard is on disk, so its presence marks a complete checkpoint and
+its digests let a loader reject a damaged one.
 """
 from __future__ import annotations
 
+import hashlib
 import json
 import os
 from typing import Optional
@@ -30,30 +34,69 @@ def _atomic_json(obj, path):
     os.replace(tmp, path)
 
 
+class CheckpointCorrupt(IOError):
+    pass
+
+
+def _sha256(path: str) -> str:
+    h = hashlib.sha256()
+    with open(path, "rb") as f:
+        for chunk in iter(lambda: f.read(1 << 22), b""):
+            h.update(chunk)
+    return h.hexdigest()
+
+
+def verify_checkpoint(directory: str) -> bool:
+    """True when ``trainer_state.json`` exists and every file it lists has the recorded digest."""
+    try:
+        with open(os.path.join(directory, "trainer_state.json")) as f:
+            st = json.load(f)
+        for name, digest in st.get("files", {}).items():
+            if _sha256(os.path.join(directory, name)) != digest:
+                return False
+        return True
+    except (OSError, ValueError):
+        return False
+
+
 def save_checkpoint(directory: str, model: torch.nn.Module, engine, extra: Optional[dict] = None) -> None:
     """``engine`` is a ``parallel.FSDP`` (any world size, including 1)."""
     os.makedirs(directory, exist_ok=True)
     rank, world = engine.rank, engine.world
+    mine = {}
     if rank == 0:
         save_safetensors(model.state_dict(), os.path.join(directory, "model.safetensors"))
-    save_safetensors(engine.optimizer_state(), os.path.join(directory, f"optim-rank{rank}.safetensors"))
+        mine["model.safetensors"] = _sha256(os.path.join(directory, "model.safetensors"))
+    shard_name = f"optim-rank{rank}.safetensors"
+    save_safetensors(engine.optimizer_state(), os.path.join(directory, shard_name))
+    mine[shard_name] = _sha256(os.path.join(directory, shard_name))
+    files = dict(mine)
+    if world > 1 and dist.is_initialized():
+        # every shard is on disk (and its digest known to rank 0) before the state file appears
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine, group=engine.group)
+        files = {k: v for d in gathered for k, v in d.items()}
     if rank == 0:
         state = {"step": engine.step_count, "lr": engine.lr, "beta1": engine.beta1, "beta2": engine.beta2,
                  "eps": engine.eps, "weight_decay": engine.weight_decay, "adamw": engine.adamw,
                  "world": world,
                  "units": [{"name": u.name, "numel": u.numel, "padded": u.padded, "shard": u.shard_numel}
                            for u in engine.units],
+                 "files": files,
                  "extra": extra or {}}
         _atomic_json(state, os.path.join(directory, "trainer_state.json"))
     if world > 1 and dist.is_initialized():
         dist.barrier(engine.group)
 
 
-def load_checkpoint(directory: str, model: torch.nn.Module, engine) -> dict:
+def load_checkpoint(directory: str, model: torch.nn.Module, engine, verify: bool = True) -> dict:
     """Restores weights, optimizer shards (re-sharded if the saved world size differs), step and
-    hyper-parameters.  Returns the ``extra`` dict that was saved."""
+    hyper-parameters.  Returns the ``extra`` dict that was saved.  With ``verify`` the files are
+    checked against the digests in ``trainer_state.json`` first (``CheckpointCorrupt``)."""
     with open(os.path.join(directory, "trainer_state.json")) as f:
         st = json.load(f)
+    if verify and not verify_checkpoint(directory):
+        raise CheckpointCorrupt(f"{directory}: a file does not match its recorded SHA-256")
     load_into(model, os.path.join(directory, "model.safetensors"))
     old_world = st["world"]
     if old_world == engine.world:

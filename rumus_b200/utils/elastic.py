@@ -38,9 +38,12 @@ def _free_port() -> int:
     return port
 
 
-def latest_checkpoint(root: str) -> Optional[str]:
+def latest_checkpoint(root: str, verify: bool = False) -> Optional[str]:
     """Newest complete checkpoint directory ``root/step-<n>`` (complete = has ``trainer_state.json``,
-    which ``save_checkpoint`` writes last and atomically), or ``None``."""
+    which ``save_checkpoint`` writes last and atomically), or ``None``.  With ``verify`` a
+    checkpoint whose files do not match their recorded digests is skipped in favour of an older
+    one."""
+    from ..io.checkpoint import verify_checkpoint
     best, best_step = None, -1
     if not os.path.isdir(root):
         return None
@@ -53,6 +56,8 @@ def latest_checkpoint(root: str) -> Optional[str]:
             continue
         d = os.path.join(root, name)
         if step > best_step and os.path.exists(os.path.join(d, "trainer_state.json")):
+            if verify and not verify_checkpoint(d):
+                continue
             best, best_step = d, step
     return best
 

@@ -217,3 +217,27 @@ def test_elastic_supervisor_restarts_smaller_from_last_checkpoint(tmp_path):
     # generation 0 saved step-2 (step 4 was never reached: rank 1 left after step 3)
     assert done["steps"] == 8 and done["world"] == 1 and done["resumed_from"].endswith("step-2")
     assert latest_checkpoint(root).endswith("step-8")
+
+
+def test_corrupted_checkpoint_is_rejected_and_skipped(tmp_path):
+    """Host-side fault injection on storage: a flipped byte in an optimizer shard."""
+    from rumus_b200.io.checkpoint import CheckpointCorrupt, load_checkpoint, save_checkpoint, verify_checkpoint
+    from rumus_b200.parallel import FSDP
+    from rumus_b200.utils.elastic import latest_checkpoint
+    m = _make(); e = FSDP(m, lr=1e-2)
+    data = _data()
+    for s in range(4):
+        _step(m, e, data[s])
+        if e.step_count % 2 == 0:
+            save_checkpoint(str(tmp_path / f"step-{e.step_count}"), m, e)
+    newest = tmp_path / "step-4"
+    assert verify_checkpoint(str(newest)) and latest_checkpoint(str(tmp_path), verify=True).endswith("step-4")
+    shard = newest / "optim-rank0.safetensors"
+    raw = bytearray(shard.read_bytes())
+    raw[len(raw) // 2] ^= 0x40
+    shard.write_bytes(bytes(raw))
+    assert not verify_checkpoint(str(newest))
+    with pytest.raises(CheckpointCorrupt):
+        load_checkpoint(str(newest), _make(), FSDP(_make(), lr=1.0))
+    assert latest_checkpoint(str(tmp_path), verify=True).endswith("step-2")
+    assert latest_checkpoint(str(tmp_path)).endswith("step-4")      # unverified: newest by name
