@@ -155,6 +155,12 @@ def test_flag_protocols_hold_on_every_interleaving():
         explore(fsdp_unit_programs(2, 2, wait_grad_flags=False))    # gradient read before the write
     with pytest.raises(ProtocolViolation):
         explore(allreduce_programs(2, 2, exit_barrier=False))       # reads a half-reduced bucket
+    # a rank that never publishes one of its flags: the model deadlocks (on the device the bounded
+    # wait turns that into a status code instead)
+    progs = fsdp_unit_programs(2, 1)
+    progs[1] = [a for a in progs[1] if not (a[0] == "set" and a[1] == "grad_ready[0][1]")]
+    with pytest.raises(ProtocolViolation, match="deadlock"):
+        explore(progs)
 
 
 def _elastic_worker(rank, world, generation, root, total_steps):
