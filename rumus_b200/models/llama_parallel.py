@@ -147,6 +147,60 @@ class ParallelLlamaStage(Module):
                 v = cfg.vocab_size // T
                 self.head.weight.copy_(dense_state["head.weight"][:, r * v:(r + 1) * v])
 
+    def export_dense(self, gather_stages: bool = True) -> Optional[dict]:
+        """Inverse of ``load_dense``: the reference-layout dense state dict assembled from the
+        shards.  Tensor-parallel shards are all-gathered inside the TP group and concatenated along
+        the dimension they were cut on (columns for q/k/v/gate/up/head, rows for out/down); with
+        ``gather_stages`` the pipeline stages are then merged on global rank 0 (returns the full
+        dict there, ``None`` on the other ranks).  Saving it with ``save_safetensors`` gives a
+        checkpoint any other TP x PP layout — or the dense model — can load."""
+        T, cfg = self.tp.world, self.cfg
+        per = cfg.num_layers // self.num_stages
+        hd = cfg.d_model // cfg.num_heads
+
+        def gather(t: torch.Tensor):
+            t = t.detach().contiguous()
+            if T == 1:
+                return [t]
+            parts = [torch.empty_like(t) for _ in range(T)]
+            dist.all_gather(parts, t, group=self.tp.group)
+            return parts
+
+        out = {}
+        if self.first:
+            out["token_emb.weight"] = self.token_emb.weight.detach().clone()
+        nq, nkv = cfg.num_heads // T * hd, cfg.num_kv_heads // T * hd
+        f = cfg.ffn_dim // T
+        for i, blk in enumerate(self.blocks):
+            p = f"blocks.{self.stage * per + i}."
+            qkv = gather(blk.qkv.weight)
+            out[p + "attn.q_proj.weight"] = torch.cat([w[:, :nq] for w in qkv], dim=1)
+            out[p + "attn.k_proj.weight"] = torch.cat([w[:, nq:nq + nkv] for w in qkv], dim=1)
+            out[p + "attn.v_proj.weight"] = torch.cat([w[:, nq + nkv:] for w in qkv], dim=1)
+            out[p + "attn.out_proj.weight"] = torch.cat(gather(blk.out_proj.weight), dim=0)
+            gu = gather(blk.gate_up.weight)
+            out[p + "mlp.gate_proj.weight"] = torch.cat([w[:, :f] for w in gu], dim=1)
+            out[p + "mlp.up_proj.weight"] = torch.cat([w[:, f:] for w in gu], dim=1)
+            out[p + "mlp.down_proj.weight"] = torch.cat(gather(blk.down.weight), dim=0)
+            out[p + "ln1.weight"] = blk.ln1.weight.detach().clone()
+            out[p + "ln2.weight"] = blk.ln2.weight.detach().clone()
+        if self.last:
+            out["ln_final.weight"] = self.ln_final.weight.detach().clone()
+            out["head.weight"] = torch.cat(gather(self.head.weight), dim=1)
+        if not gather_stages or not dist.is_initialized():
+            return out
+        world = dist.get_world_size()
+        mine = {k: v.cpu() for k, v in out.items()} if self.tp.rank == 0 else None
+        every = [None] * world
+        dist.all_gather_object(every, mine)
+        if dist.get_rank() != 0:
+            return None
+        full = {}
+        for d in every:
+            if d:
+                full.update(d)
+        return full
+
     def embed(self, tokens: torch.Tensor) -> torch.Tensor:
         """tokens [B, S] -> token-sharded residual stream [B*S/T, d]."""
         self.batch, self.seq = tokens.shape

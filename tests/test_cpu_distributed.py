@@ -187,6 +187,15 @@ def _tp_pp_worker(rank, world):
     f = cfg.ffn_dim // 2
     mine = stage.blocks[0].down.weight.grad
     assert torch.allclose(mine, gd[topo.tp_idx * f:(topo.tp_idx + 1) * f], atol=1e-5)
+    # shards -> reference-layout dense state dict (TP shards concatenated, stages merged on rank 0)
+    full = stage.export_dense()
+    if rank == 0:
+        ref_sd = dense.state_dict()
+        assert set(full) == set(ref_sd), set(ref_sd) ^ set(full)
+        for k, v in ref_sd.items():
+            assert torch.equal(full[k], v), k
+    else:
+        assert full is None
     return True
 
 
