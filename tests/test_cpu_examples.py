@@ -34,3 +34,37 @@ def test_fsdp_example_on_two_gloo_ranks():
     first = float(r.stdout.split("step 0: loss ")[1].split()[0])
     last = float(r.stdout.split("step 25: loss ")[1].split()[0])
     assert last < first
+
+
+def test_launcher_trains_checkpoints_and_resumes_with_fewer_ranks(tmp_path):
+    """python -m rumus_b200.launch: 2 gloo ranks write checkpoints, 1 rank resumes from the newest
+    verified one (re-sharded optimizer state) and finishes; metrics land in JSONL files."""
+    import json
+    ck, met = str(tmp_path / "ck"), str(tmp_path / "metrics")
+    r = _run(["-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+              "--master-port", "29633", "-m", "rumus_b200.launch", "--config", "tiny-decoder-cpu",
+              "--steps", "12", "--ckpt-dir", ck, "--ckpt-every", "6", "--metrics-dir", met, "--log-every", "3"])
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    out = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    assert out["steps"] == 12 and out["world"] == 2 and out["mode"] == "cpu"
+    assert sorted(os.listdir(ck)) == ["step-12", "step-6"]
+    assert sorted(os.listdir(met)) == ["metrics-rank0.jsonl", "metrics-rank1.jsonl"]
+    r = _run(["-m", "rumus_b200.launch", "--config", "tiny-decoder-cpu", "--steps", "18", "--ckpt-dir", ck,
+              "--resume", "--log-every", "3"])
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    out2 = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    assert out2["resumed_from"].endswith("step-12") and out2["steps"] == 18 and out2["world"] == 1
+    assert out2["last_loss"] < out["first_logged_loss"]
+
+
+def test_launcher_vision_config_from_yaml(tmp_path):
+    import json
+    cfg = tmp_path / "small_resnet.yaml"
+    cfg.write_text("name: small-resnet\n"
+                   "model: {family: resnet50, kwargs: {num_classes: 10, layers: [1, 1, 1, 1], width: 8}}\n"
+                   "precision: {compute: fp32, master_weights: false, loss_scaling: true, init_scale: 128.0}\n"
+                   "optimizer: sgd\nlr: 0.05\nmomentum: 0.9\nseqs_per_gpu: 2\nsteps: 3\n")
+    r = _run(["-m", "rumus_b200.launch", "--config", str(cfg), "--image-size", "32", "--log-every", "1"])
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    out = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    assert out["family"] == "resnet50" and out["steps"] == 3 and out["last_loss"] == out["last_loss"]
