@@ -6,8 +6,8 @@
 
 ``--config`` is a preset name (``utils/config.PRESETS``) or a YAML file with the same fields.
 The run builds the model family of the config (GPT with the sharded-data-parallel engine, ResNet-50
-with data parallelism and dynamic loss scaling), feeds it synthetic data of the configured shape or
-a ``.rrec`` file (``--data``, read by the native batch loader), writes JSONL metrics per rank
+with data parallelism and dynamic loss scaling, Llama with tensor x pipeline parallelism), feeds it
+synthetic data of the configured shape or a ``.rrec`` file (``--data``, read by the native batch loader), writes JSONL metrics per rank
 (``--metrics-dir``), saves checkpoints (``--ckpt-dir`` / ``--ckpt-every``) and, with ``--resume``,
 continues from the newest checkpoint whose digests verify — also when it was written by a different
 number of ranks.  Under an ``ElasticSupervisor`` this is the worker a restart re-enters.
@@ -154,6 +154,77 @@ def _run_resnet(cfg: TrainConfig, a, rank, world, dev) -> dict:
     return {"family": "resnet50", "steps": steps, "last_loss": last, "mode": dp.mode, "world": world}
 
 
+def _run_llama(cfg: TrainConfig, a, rank, world, dev) -> dict:
+    """Tensor x pipeline parallel Llama: 1F1B over ``parallel.pp`` stages, sequence-parallel
+    tensor-parallel blocks, per-stage fused Adam; ``--export-dense`` writes the reference-layout
+    ``model.safetensors`` assembled from all shards at the end."""
+    from .io.safetensors import save_safetensors
+    from .models.llama import LlamaConfig
+    from .models.llama_parallel import ParallelLlamaStage
+    from .parallel import FSDP
+    from .parallel.pp import PipelineStage, bubble_fraction
+    from .parallel.topology import build_topology
+    from .parallel.tp import TPContext
+    from .utils import MetricsLogger
+    par = cfg.parallel
+    if par.pp < 2:
+        raise SystemExit("the Llama launcher path needs pp >= 2 (use FSDP / DP presets otherwise)")
+    topo = build_topology(tp=par.tp, pp=par.pp)
+    mc = LlamaConfig(**cfg.model.kwargs)
+    dtype = _DTYPES[cfg.precision.compute] if dev.type == "cuda" else torch.float32
+    global_batch = cfg.global_batch or cfg.seqs_per_gpu * topo.dp * par.micro_batches
+    mb_seqs = global_batch // (topo.dp * par.micro_batches)
+    mb_tokens = mb_seqs * mc.seq_len
+    mode = "nccl" if dev.type != "cuda" else (None if par.backend == "fused" else par.backend)
+    tp = TPContext(group=topo.tp_group, mode=mode, max_tokens=mb_tokens, max_features=mc.d_model)
+    stage = ParallelLlamaStage(mc, tp, topo.pp_idx, par.pp, device=dev, dtype=dtype)
+    stage.init_weights(0.02, seed=cfg.seed)
+    stage.set_microbatch_shape(mb_seqs, mc.seq_len)
+    units = [(f"blocks.{i}", [b]) for i, b in enumerate(stage.blocks)]
+    rest = [p for n, p in stage.named_parameters() if not n.startswith("blocks.")]
+    if rest:
+        units.append(("edge", rest))
+    opt = FSDP(stage, lr=cfg.lr, unit_roots=units, local_only=True)
+    ps = PipelineStage(stage, topo.pp_idx, par.pp, topo.prev_stage_rank, topo.next_stage_rank,
+                       (mb_tokens // par.tp, mc.d_model), dtype, dev)
+    first, last = topo.pp_idx == 0, topo.pp_idx == par.pp - 1
+    g = torch.Generator().manual_seed(cfg.seed * 1000 + topo.dp_idx)
+    log = MetricsLogger(a.metrics_dir, rank=rank) if a.metrics_dir else None
+    steps = a.steps if a.steps is not None else cfg.steps
+    first_loss = last_loss = None
+    for step in range(1, steps + 1):
+        toks = []
+        for _ in range(par.micro_batches):
+            start = torch.randint(0, mc.vocab_size, (mb_seqs, 1), generator=g)
+            toks.append((start + torch.arange(mc.seq_len + 1)[None]) % mc.vocab_size)
+        if first:
+            mbs = [t[:, :-1].to(dev) for t in toks]
+        elif last:
+            mbs = [t[:, 1:].to(dev) for t in toks]
+        else:
+            mbs = [None] * par.micro_batches
+        opt.zero_grad()
+        loss = ps.run(mbs)
+        opt.step()
+        if last and (step % a.log_every == 0 or step == steps):
+            last_loss = float(loss)
+            first_loss = last_loss if first_loss is None else first_loss
+            if log and tp.rank == 0:
+                log.log(step=step, loss=last_loss)
+    if a.export_dense:
+        full = stage.export_dense()
+        if rank == 0:
+            os.makedirs(os.path.dirname(os.path.abspath(a.export_dense)), exist_ok=True)
+            save_safetensors(full, a.export_dense)
+    # the loss lives on the last stage: hand it to rank 0 for the summary line
+    summary = [None] * world
+    dist.all_gather_object(summary, (first_loss, last_loss) if last and tp.rank == 0 else None)
+    got = [s for s in summary if s is not None][0]
+    return {"family": "llama", "steps": steps, "first_logged_loss": got[0], "last_loss": got[1],
+            "parallelism": f"tp{par.tp}xpp{par.pp}xdp{topo.dp}", "mode": tp.mode, "world": world,
+            "bubble_fraction_ideal": bubble_fraction(par.pp, par.micro_batches)}
+
+
 def main(argv=None) -> dict:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--config", required=True, help="preset name or YAML path")
@@ -166,6 +237,8 @@ def main(argv=None) -> dict:
     ap.add_argument("--log-every", type=int, default=10)
     ap.add_argument("--batch", type=int, default=None, help="per-rank batch override (vision)")
     ap.add_argument("--image-size", type=int, default=224)
+    ap.add_argument("--export-dense", default=None,
+                    help="(Llama) write the dense reference-layout model.safetensors here at the end")
     a = ap.parse_args(argv)
     cfg = load_config(a.config)
     rank, world, dev = _setup()
@@ -173,10 +246,10 @@ def main(argv=None) -> dict:
         out = _run_gpt(cfg, a, rank, world, dev)
     elif cfg.model.family == "resnet50":
         out = _run_resnet(cfg, a, rank, world, dev)
+    elif cfg.model.family == "llama":
+        out = _run_llama(cfg, a, rank, world, dev)
     else:
-        raise SystemExit(f"family {cfg.model.family!r}: tensor x pipeline parallel Llama training is driven by "
-                         "bench/bench_llama3d.py (models/llama_parallel.py + parallel/pp.py); serving by "
-                         "python -m rumus_b200.serve.server")
+        raise SystemExit(f"unknown model family {cfg.model.family!r}")
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -68,3 +68,26 @@ def test_launcher_vision_config_from_yaml(tmp_path):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     out = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
     assert out["family"] == "resnet50" and out["steps"] == 3 and out["last_loss"] == out["last_loss"]
+
+
+def test_launcher_llama_tp2_pp2_on_four_gloo_ranks(tmp_path):
+    import json
+    cfg = tmp_path / "llama_small.yaml"
+    cfg.write_text("name: llama-small\n"
+                   "model: {family: llama, kwargs: {vocab_size: 64, seq_len: 16, d_model: 32, num_heads: 2, "
+                   "num_kv_heads: 2, num_layers: 2, ffn_dim: 64}}\n"
+                   "parallel: {tp: 2, pp: 2, micro_batches: 2, backend: nccl}\n"
+                   "precision: {compute: fp32, master_weights: false}\n"
+                   "lr: 0.01\nglobal_batch: 4\nsteps: 12\n")
+    dense = str(tmp_path / "out" / "model.safetensors")
+    r = _run(["-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr", "127.0.0.1",
+              "--master-port", "29635", "-m", "rumus_b200.launch", "--config", str(cfg), "--log-every", "4",
+              "--export-dense", dense], timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    out = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    assert out["parallelism"] == "tp2xpp2xdp1" and out["steps"] == 12
+    assert out["last_loss"] < out["first_logged_loss"]
+    assert abs(out["bubble_fraction_ideal"] - 1 / 3) < 1e-9
+    from rumus_b200.io import load_safetensors
+    sd = load_safetensors(dense)
+    assert sd["blocks.1.mlp.down_proj.weight"].shape == (64, 32) and sd["head.weight"].shape == (32, 64)
