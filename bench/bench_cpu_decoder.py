@@ -6,7 +6,9 @@ then a safetensors round trip that must be bit exact.
     python bench/bench_cpu_decoder.py [--steps 50] [--threads N]
 
 Prints one JSON line: seconds per step (wall clock, CPU), first/last loss, round-trip check.
-The same model through plain ``torch.nn`` modules (``--impl torch``) is the comparison arm.
+Comparison arms: the same model through plain ``torch.nn`` modules (``--impl torch``), and the
+same step as a chain of single-threaded scalar C++ kernels (``--impl oracle``) — one kernel per op,
+naive loops, the way the reference's CPU backend executes it (rumus/src/backend/cpu.rs).
 """
 import argparse
 import json
@@ -51,7 +53,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--threads", type=int, default=0)
-    ap.add_argument("--impl", default="ours", choices=["ours", "torch"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "torch", "oracle"])
     a = ap.parse_args()
     if a.threads:
         torch.set_num_threads(a.threads)
@@ -60,6 +62,24 @@ def main():
     torch.manual_seed(0)
     tok = torch.randint(0, cfg.vocab_size, (8, cfg.seq_len + 1))
     x, y = tok[:, :-1], tok[:, 1:]
+    if a.impl == "oracle":
+        from rumus_b200.oracle import OracleDecoder
+        dec = OracleDecoder(cfg, 8)
+        dec.load_state_dict(build_ours(cfg).state_dict())
+        for _ in range(3):
+            dec.forward_backward(x, y); dec.adam_step(1e-3)
+        losses = []
+        t0 = time.perf_counter()
+        for _ in range(a.steps):
+            losses.append(dec.forward_backward(x, y))
+            dec.adam_step(1e-3)
+        dt = time.perf_counter() - t0
+        print(json.dumps({"metric": "CPU seconds per training step", "impl": "oracle",
+                          "value": dt / a.steps, "unit": "s/step", "steps": a.steps, "threads": 1,
+                          "dtype": "f32", "first_loss": losses[0], "last_loss": losses[-1],
+                          "safetensors_round_trip_exact": None,
+                          "config": "2L d128 4h ffn512 relu vocab1024 seq64 batch8, Adam 1e-3"}))
+        return
     if a.impl == "ours":
         from rumus_b200.optim import Adam
         model = build_ours(cfg)

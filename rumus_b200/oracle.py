@@ -120,3 +120,76 @@ def dropout(x, p, seed):
     y = torch.empty_like(x)
     _L().orc_dropout(_p(x), _p(y), c_longlong(x.numel()), c_uint(seed & 0xFFFFFFFF), c_float(p))
     return y
+
+
+class OracleDecoder:
+    """The small pre-LN decoder as one chain of oracle kernels (``csrc/cpu_oracle/decoder_baseline.cpp``):
+    forward, backward and Adam, single-threaded scalar fp32 like the reference's CPU backend
+    (rumus/src/backend/cpu.rs, rumus/src/nn/transformer.rs).  Parameters live in the native object
+    in the order of ``GPT.state_dict()``; ``load_state_dict`` copies them in, ``grads`` / ``params``
+    hand back tensors under the state-dict names."""
+
+    def __init__(self, cfg, batch: int):
+        if getattr(cfg, "activation", "relu") != "relu":
+            raise ValueError("the oracle decoder implements the ReLU feed-forward of the functional configuration")
+        L = _L()
+        L.orc_decoder_create.restype = c_void_p
+        L.orc_decoder_tensor.restype = ctypes.POINTER(c_float)
+        L.orc_decoder_forward_backward.restype = c_float
+        self._L, self.cfg, self.batch = L, cfg, batch
+        self._h = c_void_p(L.orc_decoder_create(c_int(cfg.vocab_size), c_int(cfg.seq_len), c_int(cfg.d_model),
+                                                c_int(cfg.num_heads), c_int(cfg.num_layers), c_int(cfg.ffn_dim),
+                                                c_int(batch)))
+        if not self._h:
+            raise ValueError("invalid decoder configuration")
+        names = ["token_emb.weight", "pos_emb.weight"]
+        for l in range(cfg.num_layers):
+            b = f"blocks.{l}."
+            names += [b + n for n in ("ln1.weight", "ln1.bias", "attn.q_proj.weight", "attn.q_proj.bias",
+                                      "attn.k_proj.weight", "attn.k_proj.bias", "attn.v_proj.weight",
+                                      "attn.v_proj.bias", "attn.out_proj.weight", "attn.out_proj.bias",
+                                      "ln2.weight", "ln2.bias", "mlp_fc1.weight", "mlp_fc1.bias",
+                                      "mlp_fc2.weight", "mlp_fc2.bias")]
+        names += ["ln_final.weight", "ln_final.bias", "head.weight"]
+        assert len(names) == L.orc_decoder_num_tensors(self._h)
+        self.names = names
+
+    def _view(self, i, which):
+        n = c_longlong(0)
+        ptr = self._L.orc_decoder_tensor(self._h, c_int(i), c_int(which), ctypes.byref(n))
+        return torch.from_numpy(np.ctypeslib.as_array(ptr, shape=(n.value,)))      # aliases native memory
+
+    def load_state_dict(self, sd):
+        for i, name in enumerate(self.names):
+            dst = self._view(i, 0)
+            src = _f(sd[name]).reshape(-1)
+            if src.numel() != dst.numel():
+                raise ValueError(f"{name}: {src.numel()} elements, expected {dst.numel()}")
+            dst.copy_(src)
+
+    def params(self):
+        return {n: self._view(i, 0).clone() for i, n in enumerate(self.names)}
+
+    def grads(self):
+        return {n: self._view(i, 1).clone() for i, n in enumerate(self.names)}
+
+    def forward_backward(self, x, y, backward: bool = True) -> float:
+        x = x.to(torch.int64).contiguous().reshape(-1)
+        y = y.to(torch.int64).contiguous().reshape(-1)
+        if x.numel() != self.batch * self.cfg.seq_len or y.numel() != x.numel():
+            raise ValueError("token tensors must be [batch, seq_len]")
+        return float(self._L.orc_decoder_forward_backward(self._h, _p(x), _p(y), c_int(1 if backward else 0)))
+
+    def adam_step(self, lr=1e-3, betas=(0.9, 0.999), eps=1e-8):
+        self._L.orc_decoder_adam(self._h, c_float(lr), c_float(betas[0]), c_float(betas[1]), c_float(eps))
+
+    def close(self):
+        if self._h:
+            self._L.orc_decoder_destroy(self._h)
+            self._h = c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

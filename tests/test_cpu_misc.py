@@ -43,6 +43,45 @@ def test_cpu_oracle_agrees_with_pytorch():
     assert torch.allclose(oracle.qmatmul_int4(xm, qw), xm @ qw.dequantize(), atol=1e-4)
 
 
+def test_oracle_decoder_step_matches_framework_decoder():
+    """End-to-end second opinion: loss, every gradient and two Adam steps of the scalar C++ decoder
+    chain against the framework's GPT on the same weights."""
+    from rumus_b200.models import GPT, GPTConfig
+    from rumus_b200.optim import Adam
+    cfg = GPTConfig(vocab_size=96, seq_len=12, d_model=32, num_heads=4, num_layers=2, ffn_dim=48, activation="relu")
+    m = GPT(cfg, device="cpu", dtype=torch.float32)
+    m.init_weights(0.05, seed=3)
+    torch.manual_seed(4)
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+    tok = torch.randint(0, cfg.vocab_size, (3, cfg.seq_len + 1))
+    x, y = tok[:, :-1], tok[:, 1:]
+    dec = oracle.OracleDecoder(cfg, 3)
+    dec.load_state_dict(m.state_dict())
+    loss = m(x, y)
+    loss.backward()
+    assert abs(dec.forward_backward(x, y) - loss.item()) < 1e-5
+    g, d = dec.grads(), cfg.d_model
+    for n, p in m.named_parameters():
+        if n.endswith("qkv_weight"):
+            ref = torch.cat([g[n.replace("qkv_weight", f"{c}_proj.weight")].view(d, d) for c in "qkv"], 1)
+        elif n.endswith("qkv_bias"):
+            ref = torch.cat([g[n.replace("qkv_bias", f"{c}_proj.bias")] for c in "qkv"])
+        else:
+            ref = g[n]
+        assert torch.allclose(p.grad.reshape(-1), ref.reshape(-1), atol=1e-6, rtol=1e-4), n
+    opt = Adam(m.parameters(), lr=1e-3)
+    for _ in range(2):
+        l = m(x, y); opt.zero_grad(); l.backward(); opt.step()
+        lo = dec.forward_backward(x, y); dec.adam_step(1e-3)
+        assert abs(lo - l.item()) < 1e-4
+    with pytest.raises(ValueError):
+        dec.forward_backward(x[:, :-1], y[:, :-1])
+    dec.close()
+
+
 def test_dropout_matches_reference_hash_on_cpu_oracle():
     x = torch.ones(4096)
     y = oracle.dropout(x, 0.25, 99)
