@@ -98,6 +98,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--mode", default=None, help="fused | nccl (multi-GPU communication path)")
+    ap.add_argument("--reshard", action="store_true",
+                    help="FSDP keeps only parameter shards between a block's forward and backward (needs --mode nccl)")
     ap.add_argument("--phases", action="store_true", help="also report forward/backward/tail device times")
     ap.add_argument("--trace-export", default=None,
                     help="write a torch.profiler Chrome trace of two extra steps (with the NVTX-named "
@@ -136,7 +138,7 @@ def main():
     model.init_weights(0.02, seed=0)
     native.lib().rb_init_device()
     engine = FSDP(model, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0, adamw=False,
-                  mode=args.mode)
+                  mode=args.mode, reshard_after_forward=args.reshard)
 
     gen = torch.Generator(device="cpu").manual_seed(1000 + rank)
     n_batches = args.warmup + args.steps
@@ -255,7 +257,7 @@ def main():
             "config": {"model": "GPT 1.3B (24L d2048 16h FFN8192 GELU vocab50304)" if not args.layers
                        else f"DEBUG {cfg.num_layers} layers",
                        "global_batch": world * B, "seq_len": S,
-                       "parallelism": f"fsdp{world}" if world > 1 else "fsdp1 (single GPU)",
+                       "parallelism": (f"fsdp{world}" + (" reshard-after-forward" if args.reshard else "")) if world > 1 else "fsdp1 (single GPU)",
                        "comm_mode": engine.mode, "optimizer": "Adam fp32 master + moments",
                        "l2": "per-step working set (tens of GB) exceeds the 126 MB L2; no explicit flush"},
             "clocks": clocks,

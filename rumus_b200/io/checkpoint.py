@@ -14,6 +14,7 @@ its digests let a loader reject a damaged one.
 """
 from __future__ import annotations
 
+import contextlib
 import hashlib
 import json
 import os
@@ -64,9 +65,11 @@ def save_checkpoint(directory: str, model: torch.nn.Module, engine, extra: Optio
     os.makedirs(directory, exist_ok=True)
     rank, world = engine.rank, engine.world
     mine = {}
-    if rank == 0:
-        save_safetensors(model.state_dict(), os.path.join(directory, "model.safetensors"))
-        mine["model.safetensors"] = _sha256(os.path.join(directory, "model.safetensors"))
+    # with resharded parameters every rank takes part in gathering them for the writer
+    with getattr(engine, "summon_full_params", contextlib.nullcontext)():
+        if rank == 0:
+            save_safetensors(model.state_dict(), os.path.join(directory, "model.safetensors"))
+            mine["model.safetensors"] = _sha256(os.path.join(directory, "model.safetensors"))
     shard_name = f"optim-rank{rank}.safetensors"
     save_safetensors(engine.optimizer_state(), os.path.join(directory, shard_name))
     mine[shard_name] = _sha256(os.path.join(directory, shard_name))
@@ -97,7 +100,9 @@ def load_checkpoint(directory: str, model: torch.nn.Module, engine, verify: bool
         st = json.load(f)
     if verify and not verify_checkpoint(directory):
         raise CheckpointCorrupt(f"{directory}: a file does not match its recorded SHA-256")
-    load_into(model, os.path.join(directory, "model.safetensors"))
+    summon = getattr(engine, "summon_full_params", None)
+    with (summon(writeback=True) if summon is not None else contextlib.nullcontext()):
+        load_into(model, os.path.join(directory, "model.safetensors"))
     old_world = st["world"]
     if old_world == engine.world:
         sd = load_safetensors(os.path.join(directory, f"optim-rank{engine.rank}.safetensors"))

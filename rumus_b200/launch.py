@@ -77,7 +77,8 @@ def _run_gpt(cfg: TrainConfig, a, rank, world, dev) -> dict:
     model = GPT(GPTConfig(**cfg.model.kwargs), device=dev, dtype=dtype)
     model.init_weights(0.02, seed=cfg.seed)
     mode = None if cfg.parallel.backend == "fused" else cfg.parallel.backend
-    engine = FSDP(model, lr=cfg.lr, adamw=cfg.optimizer == "adamw", mode=mode)
+    engine = FSDP(model, lr=cfg.lr, adamw=cfg.optimizer == "adamw", mode=mode,
+                  reshard_after_forward=cfg.parallel.reshard_after_forward)
     resumed = None
     if a.resume and a.ckpt_dir:
         resumed = latest_checkpoint(a.ckpt_dir, verify=True)

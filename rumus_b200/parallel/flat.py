@@ -45,6 +45,7 @@ class FlatUnit:
         self.padded = _round_up(off, world_size * ALIGN * 4)
         self.shard_numel = self.padded // world_size
         alloc = alloc or (lambda n, dt, dev: torch.zeros(n, dtype=dt, device=dev))
+        self.persist: Optional[torch.Tensor] = None   # set by reshard(): the shard's own buffer
         self.flat_param = alloc(self.padded, self.dtype, self.device)
         self.flat_grad = alloc(self.padded, self.dtype, self.device)
         for p, o in zip(params, offs):
@@ -63,8 +64,25 @@ class FlatUnit:
 
     # views of this rank's shard inside the full buffers
     def param_shard(self) -> torch.Tensor:
+        if self.persist is not None:
+            return self.persist
         lo, hi = self.shard_range
         return self.flat_param[lo:hi]
+
+    def bind_storage(self, buf: torch.Tensor) -> None:
+        """Points the full flat vector, and every parameter view, at ``buf`` (at least ``padded``
+        elements).  The contents are whatever ``buf`` holds."""
+        self.flat_param = buf[: self.padded]
+        for p, o in zip(self.params, self.offsets):
+            p.data = self.flat_param[o:o + p.numel()].view(p.shape)
+
+    def reshard(self, slot: torch.Tensor) -> None:
+        """Gives up the unit's own full parameter buffer: this rank's shard moves to a buffer of
+        its own (``persist``), and the full vector lives in ``slot``, a buffer shared with other
+        units that only holds this unit's parameters while an engine has gathered them there."""
+        lo, hi = self.shard_range
+        self.persist = self.flat_param[lo:hi].clone()
+        self.bind_storage(slot)
 
     def grad_shard(self) -> torch.Tensor:
         lo, hi = self.shard_range

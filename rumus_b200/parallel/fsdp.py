@@ -17,11 +17,19 @@ vector (``flat.FlatUnit``).  Per step and unit:
   that pull peer shards with plain P2P loads (stand-alone kernel, or folded into the unit's first
   consuming GEMM, ``ag_gemm_kernel`` in ``csrc/comm/tp_comm.cu``).
 
+With ``reshard_after_forward`` (the reference's flow, rumus/src/nn/fsdp.rs:117-312: weights are
+gathered for a layer's forward, dropped, and gathered again for its backward) a block keeps only
+its shard between uses: the full vector of a block lives in one of two rotating slots, the next
+block's shards are gathered into the other slot while this block computes, and nothing is gathered
+after the update.  Parameter memory is then shards + two block-sized slots instead of every block
+in full.  Implemented for the ``nccl`` and CPU-rank modes.
+
 ``nccl`` mode issues ``reduce_scatter_tensor`` / ``all_gather_into_tensor`` plus the fused flat
 Adam kernel: that is the comparison baseline.  With a world size of 1 no communication happens.
 """
 from __future__ import annotations
 
+import contextlib
 import os
 from typing import List, Optional
 
@@ -49,11 +57,27 @@ class _Boundary(torch.autograd.Function):
         return g, None, None
 
 
+class _PreBackward(torch.autograd.Function):
+    """Identity on a unit's *output*; its backward runs before the unit's own backward and makes
+    sure the unit's full parameters are back in their slot."""
+
+    @staticmethod
+    def forward(ctx, x, engine, unit_idx):
+        ctx.engine, ctx.unit_idx = engine, unit_idx
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        ctx.engine._materialize(ctx.unit_idx, direction=-1)
+        return g, None, None
+
+
 class FSDP:
     def __init__(self, model: nn.Module, lr: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999,
                  eps: float = 1e-8, weight_decay: float = 0.0, adamw: bool = False,
                  group: Optional[dist.ProcessGroup] = None, mode: Optional[str] = None,
-                 unit_roots: Optional[list] = None, arena=None, local_only: bool = False):
+                 unit_roots: Optional[list] = None, arena=None, local_only: bool = False,
+                 reshard_after_forward: bool = False):
         self.model = model
         self.lr, self.beta1, self.beta2, self.eps = lr, beta1, beta2, eps
         self.weight_decay, self.adamw = weight_decay, adamw
@@ -89,7 +113,14 @@ class FSDP:
                             if self._cuda and self.world > 1 else None)
         self._unit_events = [None] * len(self.units)
         self._trace = None
+        self._reshard = bool(reshard_after_forward) and self.world > 1
+        if self._reshard and mode == "fused":
+            raise NotImplementedError("reshard_after_forward is available with mode='nccl' (and on CPU ranks); "
+                                      "the fused kernels gather into per-unit arena buffers")
         self._install_boundaries()
+        self._resharded: List[int] = []
+        if self._reshard:
+            self._setup_reshard()
         if mode == "fused":
             from .fused_fsdp import FusedFsdpComm
             self.fused = FusedFsdpComm(self)
@@ -112,7 +143,13 @@ class FSDP:
                 def fwd(x, *a, _orig=orig, _idx=idx, **kw):
                     if torch.is_grad_enabled() and x.requires_grad:
                         x = _Boundary.apply(x, engine, _idx)
-                    return _orig(x, *a, **kw)
+                    if not engine._reshard:
+                        return _orig(x, *a, **kw)
+                    engine._materialize(_idx, direction=+1)
+                    out = _orig(x, *a, **kw)
+                    if torch.is_grad_enabled() and isinstance(out, torch.Tensor) and out.requires_grad:
+                        out = _PreBackward.apply(out, engine, _idx)
+                    return out
 
                 b.forward = fwd
         tail_idx = name_to_idx.get("tail")
@@ -128,6 +165,92 @@ class FSDP:
             ln_final.forward = fwd_tail
         self._hooked = {i for n, i in name_to_idx.items() if n.startswith("blocks.") or n == "tail"}
         self._first_hooked = min(self._hooked) if self._hooked else -1
+
+    # ------------------------------------------------------------------ resharding (ZeRO-3 flow)
+    def _setup_reshard(self) -> None:
+        """Blocks give up their full parameter buffers; embeddings and the tail (used at both ends
+        of every step) stay resident."""
+        self._resharded = sorted(i for i, u in enumerate(self.units) if u.name.startswith("blocks."))
+        if not self._resharded:
+            self._reshard = False
+            return
+        u0 = self.units[self._resharded[0]]
+        size = max(self.units[i].padded for i in self._resharded)
+        self._slots = [torch.zeros(size, dtype=u0.dtype, device=u0.device) for _ in range(2)]
+        self._slot_of = {idx: k % 2 for k, idx in enumerate(self._resharded)}
+        self._slot_owner = [None, None]
+        self._slot_event = [None, None]
+        self.gather_stream = torch.cuda.Stream(device=u0.device) if self._cuda else None
+        self.gathers_issued = 0
+        for idx in self._resharded:
+            self.units[idx].reshard(self._slots[self._slot_of[idx]])
+
+    def _gather_into_slot(self, idx: int) -> None:
+        s = self._slot_of[idx]
+        if self._slot_owner[s] == idx:
+            return
+        u = self.units[idx]
+        slot = self._slots[s][: u.padded]
+        if self._cuda:
+            # every kernel that still reads the slot's previous owner was enqueued before this point
+            self.gather_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.gather_stream), trace_range(f"fsdp.gather.{u.name}"):
+                dist.all_gather_into_tensor(slot, u.persist, group=self.group)
+                ev = torch.cuda.Event()
+                ev.record(self.gather_stream)
+            self._slot_event[s] = ev
+        else:
+            dist.all_gather_into_tensor(slot, u.persist, group=self.group)
+        self._slot_owner[s] = idx
+        self.gathers_issued += 1
+
+    def _materialize(self, idx: int, direction: int) -> None:
+        """Full parameters of unit ``idx`` into its slot (no-op if they are still there), then the
+        gather of the unit that runs next in ``direction`` (+1 forward, -1 backward) is started
+        into the other slot so that it overlaps this unit's compute."""
+        if idx not in self._slot_of:
+            return
+        self._gather_into_slot(idx)
+        if self._cuda and self._slot_event[self._slot_of[idx]] is not None:
+            torch.cuda.current_stream().wait_event(self._slot_event[self._slot_of[idx]])
+        k = self._resharded.index(idx) + direction
+        if 0 <= k < len(self._resharded):
+            self._gather_into_slot(self._resharded[k])
+
+    @contextlib.contextmanager
+    def summon_full_params(self, writeback: bool = False):
+        """Inside the block every parameter of the model holds its full, current value (needed to
+        read a state dict, or with ``writeback`` to load one: on exit each rank keeps its shard of
+        what was written).  Collective: every rank must enter.  A no-op unless parameters are
+        resharded."""
+        if not self._reshard:
+            yield
+            return
+        for idx in self._resharded:
+            u = self.units[idx]
+            full = torch.empty(u.padded, dtype=u.dtype, device=u.device)
+            dist.all_gather_into_tensor(full, u.persist, group=self.group)
+            u.bind_storage(full)
+        try:
+            yield
+        finally:
+            for idx in self._resharded:
+                u = self.units[idx]
+                if writeback:
+                    lo, hi = u.shard_range
+                    u.persist.copy_(u.flat_param[lo:hi])
+                u.bind_storage(self._slots[self._slot_of[idx]])
+            self._slot_owner = [None, None]
+
+    def param_bytes(self) -> int:
+        """Bytes of low-precision parameter storage this rank holds between steps."""
+        total = 0
+        for i, u in enumerate(self.units):
+            esz = u.flat_param.element_size()
+            total += (u.shard_numel if u.persist is not None else u.padded) * esz
+        if self._reshard:
+            total += sum(s.numel() * s.element_size() for s in self._slots)
+        return total
 
     # ------------------------------------------------------------------ step protocol
     def zero_grad(self) -> None:
@@ -179,7 +302,10 @@ class FSDP:
             shard = torch.empty(u.shard_numel, dtype=u.dtype)
             dist.reduce_scatter_tensor(shard, u.flat_grad, op=dist.ReduceOp.SUM, group=self.group)
             _adam_reference(shard.float() / self.world, u, **self._adam_args())
-            dist.all_gather_into_tensor(u.flat_param, u.param_shard().clone(), group=self.group)
+            if u.persist is not None:
+                self._invalidate(idx)       # gathered again on next use
+            else:
+                dist.all_gather_into_tensor(u.flat_param, u.param_shard().clone(), group=self.group)
             return
         cur = torch.cuda.current_stream()
         trace = self._trace
@@ -199,9 +325,17 @@ class FSDP:
                 dist.reduce_scatter_tensor(shard, u.flat_grad, op=dist.ReduceOp.AVG, group=self.group)
                 native.adam_flat(shard, u.master, u.exp_avg, u.exp_avg_sq, u.param_shard(),
                                  **self._adam_args())
-                dist.all_gather_into_tensor(u.flat_param, u.param_shard(), group=self.group)
+                if u.persist is not None:
+                    self._invalidate(idx)   # gathered again on next use
+                else:
+                    dist.all_gather_into_tensor(u.flat_param, u.param_shard(), group=self.group)
             if trace is not None:
                 ev[2].record(self.comm_stream)
+
+    def _invalidate(self, idx: int) -> None:
+        s = self._slot_of[idx]
+        if self._slot_owner[s] == idx:
+            self._slot_owner[s] = None
 
     def start_trace(self) -> None:
         """Record, for every unit of the following steps, when its backward finished (compute
@@ -239,8 +373,11 @@ class FSDP:
             u.exp_avg_sq.copy_(sd[f"{u.name}.exp_avg_sq"])
             u.param_shard().copy_(u.master)
         if self.world > 1:
-            for u in self.units:
-                dist.all_gather_into_tensor(u.flat_param, u.param_shard().clone(), group=self.group)
+            for i, u in enumerate(self.units):
+                if u.persist is not None:
+                    self._invalidate(i)
+                else:
+                    dist.all_gather_into_tensor(u.flat_param, u.param_shard().clone(), group=self.group)
 
 
 def _adam_reference(g32, u: FlatUnit, *, lr, beta1, beta2, eps, weight_decay, step, adamw):

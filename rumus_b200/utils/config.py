@@ -18,6 +18,7 @@ class ParallelConfig:
     fsdp: bool = False
     micro_batches: int = 1
     backend: str = "fused"      # fused | nccl | cpu
+    reshard_after_forward: bool = False   # FSDP: keep only shards between a block's forward and backward (nccl / cpu backends)
 
 
 @dataclass

@@ -50,6 +50,60 @@ def test_fsdp_matches_single_process():
         assert torch.allclose(states[0][k], rs[k], atol=2e-5), k
 
 
+def _fsdp_reshard_worker(rank, world, ckpt_dir):
+    """Same job twice: parameters resident (gathered after each update) and resharded (gathered
+    around each block's forward and backward).  Both must produce identical losses and weights."""
+    from rumus_b200.io.checkpoint import load_checkpoint, save_checkpoint
+    from rumus_b200.models import GPT, GPTConfig
+    from rumus_b200.parallel import FSDP
+    cfg = GPTConfig(vocab_size=64, seq_len=16, d_model=32, num_heads=2, num_layers=5, ffn_dim=64)
+    g = torch.Generator().manual_seed(5)
+    data = torch.randint(0, 64, (5, world * 2, 17), generator=g)
+
+    def run(reshard, steps, eng=None, model=None, start=0):
+        if eng is None:
+            torch.manual_seed(0)
+            model = GPT(cfg)
+            eng = FSDP(model, lr=1e-2, reshard_after_forward=reshard)
+        losses = []
+        for step in range(start, start + steps):
+            tok = data[step, rank * 2:(rank + 1) * 2]
+            eng.zero_grad()
+            loss = model(tok[:, :-1], tok[:, 1:])
+            loss.backward()
+            eng.step()
+            losses.append(loss.item())
+        return model, eng, losses
+
+    m0, e0, l0 = run(False, 5)
+    m1, e1, l1 = run(True, 3)
+    assert e1._resharded == [1, 2, 3, 4, 5] and e1.param_bytes() < e0.param_bytes()
+    # per step: 5 gathers forward; backward reuses what the two slots still hold (blocks 5 and 4)
+    assert e1.gathers_issued == 3 * (2 * 5 - 2)
+    save_checkpoint(ckpt_dir, m1, e1)
+    # resume into a fresh resharded engine and finish the run
+    torch.manual_seed(123)
+    m2 = GPT(cfg)
+    e2 = FSDP(m2, lr=1.0, reshard_after_forward=True)
+    load_checkpoint(ckpt_dir, m2, e2)
+    _, _, l2 = run(True, 2, eng=e2, model=m2, start=3)
+    with e2.summon_full_params():
+        sd2 = {k: v.clone() for k, v in m2.state_dict().items()}
+    with torch.no_grad():   # evaluation forward also gathers
+        tok = data[0, :2]
+        ev = (m0(tok[:, :-1], tok[:, 1:]).item(), m2(tok[:, :-1], tok[:, 1:]).item())
+    return l0, l1 + l2, {k: v.clone() for k, v in m0.state_dict().items()}, sd2, ev
+
+
+def test_fsdp_reshard_after_forward_is_identical_and_resumes(tmp_path):
+    out = run_ranks(_fsdp_reshard_worker, 2, str(tmp_path), timeout=240)
+    for l_res, l_shard, sd_res, sd_shard, ev in out:
+        assert l_res == l_shard
+        assert ev[0] == ev[1]
+        for k in sd_res:
+            assert torch.equal(sd_res[k], sd_shard[k]), k
+
+
 # ------------------------------------------------------------------ TP layers
 def _tp_worker(rank, world):
     from rumus_b200.parallel.tp import ColumnParallelLinear, RowParallelLinear, TPContext, scatter_rows, gather_rows
