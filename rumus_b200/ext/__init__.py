@@ -146,3 +146,71 @@ def custom_forward(op: CustomOp, *inputs: torch.Tensor) -> torch.Tensor:
     """Run ``op`` on ``inputs`` (reference: ext/mod.rs:122)."""
     assert len(inputs) == op.num_inputs, f"{op.name}: expected {op.num_inputs} inputs"
     return _CustomFn.apply(op, *inputs)
+
+
+# ------------------------------------------------------------------ dispatcher registration
+_registered = {}
+
+
+def register_torch_op(op: CustomOp, namespace: str = "rumus_b200_ext"):
+    """Registers ``op`` with PyTorch's dispatcher as ``torch.ops.<namespace>.<op.name>`` and returns
+    the callable.
+
+    The reference's plug-in point is the ``CustomOp`` trait + ``BackwardOp::Custom`` tape entry
+    (rumus/src/ext/mod.rs:52-110, rumus/src/autograd/backward_ops.rs:502-528); with PyTorch as the
+    tensor layer the native counterpart is a dispatcher operator, which — unlike a bare
+    ``autograd.Function`` — carries a schema, has separate CPU and CUDA kernels, a shape-only
+    ("fake") kernel so that the op can be traced and exported, and an autograd formula:
+
+    * CPU kernel   = ``op.cpu_fn``;
+    * CUDA kernel  = the NVRTC-compiled source launched on the current stream;
+    * fake kernel  = ``op.output_shape`` (no data);
+    * autograd     = ``op.backward(grad_out, inputs, out)`` when the op has a backward handler.
+
+    Registering the same op name twice returns the first registration.
+    """
+    qual = f"{namespace}::{op.name}"
+    with _lock:
+        if qual in _registered:
+            return _registered[qual]
+    args = ", ".join(f"Tensor in{i}" for i in range(op.num_inputs))
+    torch.library.define(qual, f"({args}) -> Tensor")
+
+    def cuda_impl(*inputs):
+        ins = [i.contiguous() for i in inputs]
+        out = torch.empty(tuple(op.output_shape([i.shape for i in ins])), dtype=ins[0].dtype, device=ins[0].device)
+        fn = compile_cuda(op.cuda_source, op.entry)
+        launch(fn, (op.grid(out.numel()), 1, 1), (op.block_size, 1, 1), ins + [out], op.uniform_data(ins))
+        return out
+
+    def cpu_impl(*inputs):
+        if op.cpu_fn is None:
+            raise CustomOpError(f"custom op {op.name!r} has no cpu_fn")
+        out = op.cpu_fn(*inputs)
+        # a dispatcher kernel must not return one of its inputs
+        return out.clone() if any(out is i for i in inputs) else out
+
+    def fake_impl(*inputs):
+        return inputs[0].new_empty(tuple(op.output_shape([i.shape for i in inputs])))
+
+    torch.library.impl(qual, "CUDA")(cuda_impl)
+    torch.library.impl(qual, "CPU")(cpu_impl)
+    torch.library.register_fake(qual)(fake_impl)
+
+    if op.backward is not None:
+        def setup_context(ctx, inputs, output):
+            if op.save:
+                ctx.save_for_backward(*inputs, output)
+
+        def backward(ctx, grad_out):
+            saved = ctx.saved_tensors
+            grads = op.backward(grad_out, saved[:-1], saved[-1])
+            return grads if isinstance(grads, (tuple, list)) and len(grads) > 1 else (
+                grads[0] if isinstance(grads, (tuple, list)) else grads)
+
+        torch.library.register_autograd(qual, backward, setup_context=setup_context)
+
+    fn = getattr(getattr(torch.ops, namespace), op.name)
+    with _lock:
+        _registered[qual] = fn
+    return fn

@@ -210,3 +210,26 @@ def test_custom_op_cpu_path_and_backward():
     y = custom_forward(op, a, b)
     y.sum().backward()
     assert torch.allclose(y, a * a + b) and torch.allclose(a.grad, 2 * a.detach()) and torch.allclose(b.grad, torch.ones(5))
+
+
+def test_custom_op_registered_with_the_dispatcher():
+    """A CustomOp as torch.ops.<ns>.<name>: schema, CPU kernel, shape-only kernel, autograd formula."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    from rumus_b200.ext import CustomOp, register_torch_op
+    src = ("extern \"C\" __global__ void k(const float* a, const float* b, float* o, int n) {"
+           " int i = blockIdx.x * blockDim.x + threadIdx.x; if (i < n) o[i] = a[i] + 2.f * b[i]; }")
+    op = CustomOp("scaled_add_for_test", src, "k", 2, output_shape=lambda shapes: shapes[0],
+                  backward=lambda g, ins, out: (g, 2 * g), cpu_fn=lambda a, b: a + 2 * b)
+    f = register_torch_op(op)
+    assert register_torch_op(op) is f
+    a = torch.randn(5, requires_grad=True)
+    b = torch.randn(5, requires_grad=True)
+    y = torch.ops.rumus_b200_ext.scaled_add_for_test(a, b)
+    assert torch.allclose(y, a + 2 * b)
+    y.sum().backward()
+    assert torch.equal(a.grad, torch.ones(5)) and torch.equal(b.grad, 2 * torch.ones(5))
+    res = torch.library.opcheck(f, (a.detach().requires_grad_(), b.detach().requires_grad_()),
+                                test_utils=("test_schema", "test_autograd_registration", "test_faketensor"))
+    assert set(res.values()) == {"SUCCESS"}
+    with FakeTensorMode():
+        assert f(torch.empty(3, 4), torch.empty(3, 4)).shape == (3, 4)
