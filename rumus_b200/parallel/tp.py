@@ -306,3 +306,110 @@ class _GatherRowsFn(torch.autograd.Function):
         # every rank computed the same loss contribution pattern downstream: the gradient of a
         # gather is the local slab of the (summed) upstream gradient
         return ctx.tp.reduce_scatter_rows(g.contiguous()), None
+
+
+# ------------------------------------------------------------------ vocabulary-parallel embedding
+class _VocabParallelEmbedFn(torch.autograd.Function):
+    """Rows of the table outside this rank's vocabulary slice contribute zeros; the partial results
+    are summed over the group — as a reduce-scatter over tokens when the output feeds a
+    sequence-parallel region, else as an all-reduce."""
+
+    @staticmethod
+    def forward(ctx, weight, tokens, tp, vocab_start, sequence_parallel):
+        vloc = weight.shape[0]
+        tl = tokens.reshape(-1) - vocab_start
+        mine = (tl >= 0) & (tl < vloc)
+        idx = tl.clamp(0, vloc - 1)
+        out = weight.index_select(0, idx) * mine[:, None].to(weight.dtype)
+        ctx.tp, ctx.sp, ctx.vloc = tp, sequence_parallel, vloc
+        ctx.save_for_backward(idx, mine)
+        if sequence_parallel:
+            return tp.reduce_scatter_rows(out)
+        return tp.all_reduce(out)
+
+    @staticmethod
+    def backward(ctx, g):
+        idx, mine = ctx.saved_tensors
+        if ctx.sp:
+            g = ctx.tp.all_gather_rows(g.contiguous())
+        g = g * mine[:, None].to(g.dtype)
+        dw = torch.zeros(ctx.vloc, g.shape[1], dtype=torch.float32, device=g.device)
+        dw.index_add_(0, idx, g.float())
+        return dw.to(g.dtype), None, None, None, None
+
+
+class VocabParallelEmbedding(Module):
+    """Embedding table split along the vocabulary: rank ``r`` of ``T`` holds rows
+    ``[r*V/T, (r+1)*V/T)``.  The reference has only the replicated ``Embedding``
+    (rumus/src/nn/embedding.rs; no vocabulary-parallel helper in rumus-distributed/src/tensor_parallel.rs);
+    for a 7B model on 8 ranks the split table saves 7/8 of 0.26 GB per rank and, more to the point,
+    leaves the token embedding in the same layout as the vocabulary-parallel head, so tied weights
+    stay possible.
+
+    ``forward(tokens)`` takes the full ``[M]`` token ids (replicated on the group) and returns
+    ``[M, d]``, or this rank's ``[M/T, d]`` token slab with ``sequence_parallel=True``.
+    The full table is drawn from the same random stream as ``Embedding`` (every rank draws all of
+    it) and then sliced, so the values do not depend on the group size."""
+
+    def __init__(self, vocab_size: int, dim: int, tp: TPContext, sequence_parallel: bool = False,
+                 device=None, dtype=None):
+        super().__init__()
+        if vocab_size % tp.world:
+            raise ValueError(f"vocab_size {vocab_size} is not divisible by the group size {tp.world}")
+        from ..nn.modules import Embedding
+        self.tp, self.sp = tp, sequence_parallel
+        self.vocab_size, self.dim = vocab_size, dim
+        self.vloc = vocab_size // tp.world
+        self.vocab_start = tp.rank * self.vloc
+        full = Embedding(vocab_size, dim).weight.data
+        w = full[self.vocab_start:self.vocab_start + self.vloc].clone()
+        self.weight = nn.Parameter(w.to(device=device, dtype=dtype or w.dtype))
+
+    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+        if self.tp.world == 1:
+            return self.weight.index_select(0, tokens.reshape(-1))
+        return _VocabParallelEmbedFn.apply(self.weight, tokens, self.tp, self.vocab_start, self.sp)
+
+
+def vocab_parallel_cross_entropy(logits_local: torch.Tensor, targets: torch.Tensor, tp: TPContext) -> torch.Tensor:
+    """Mean cross entropy of ``[M, V/T]`` logit slices against full-vocabulary ``targets`` without
+    gathering the logits (three small all-reduces: row max, sum of exponentials, target logit)."""
+    from ..models.llama_parallel import _VocabParallelCE
+    return _VocabParallelCE.apply(logits_local, targets.reshape(-1), tp, tp.rank * logits_local.shape[1])
+
+
+# ------------------------------------------------------------------ replicated-activation regions
+class _CopyToRegionFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.tp.all_reduce(g.contiguous().clone()), None
+
+
+class _ReduceFromRegionFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, tp):
+        return tp.all_reduce(x.contiguous().clone())
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+def copy_to_region(x: torch.Tensor, tp: TPContext) -> torch.Tensor:
+    """Entry of a tensor-parallel region whose input is replicated: identity in forward, SUM
+    all-reduce of the gradient in backward (every rank only sees the contribution of its own
+    weight columns).  The reference leaves this to the user as an explicit
+    ``ColumnParallelLinear::allreduce_grad_x`` call (rumus-distributed/src/tensor_parallel.rs:39-48)."""
+    return x if tp.world == 1 else _CopyToRegionFn.apply(x, tp)
+
+
+def reduce_from_region(x: torch.Tensor, tp: TPContext) -> torch.Tensor:
+    """Exit of a tensor-parallel region with replicated output: SUM all-reduce of the partial
+    results in forward (the reference averages, rumus-distributed/src/collective.rs:56-60, which is
+    wrong for partial sums), identity in backward."""
+    return x if tp.world == 1 else _ReduceFromRegionFn.apply(x, tp)

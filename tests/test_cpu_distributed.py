@@ -104,6 +104,53 @@ def test_fsdp_reshard_after_forward_is_identical_and_resumes(tmp_path):
             assert torch.equal(sd_res[k], sd_shard[k]), k
 
 
+def _vocab_parallel_worker(rank, world):
+    """Vocabulary-parallel embedding (replicated and sequence-parallel output) and cross entropy
+    against the dense computation, values and gradients."""
+    from rumus_b200.nn import Embedding
+    from rumus_b200.parallel.tp import (TPContext, VocabParallelEmbedding, copy_to_region, gather_rows,
+                                        vocab_parallel_cross_entropy)
+    tp = TPContext(mode="nccl")
+    V, d, M = 24, 8, 12
+    torch.manual_seed(7)
+    dense = Embedding(V, d)
+    torch.manual_seed(7)
+    emb = VocabParallelEmbedding(V, d, tp)
+    torch.manual_seed(7)
+    emb_sp = VocabParallelEmbedding(V, d, tp, sequence_parallel=True)
+    vloc = V // world
+    assert torch.equal(emb.weight, dense.weight[rank * vloc:(rank + 1) * vloc])
+    g = torch.Generator().manual_seed(3)
+    tok = torch.randint(0, V, (M,), generator=g)
+    tgt = torch.randint(0, V, (M,), generator=g)
+    head = torch.randn(d, V, generator=g) * 0.3
+    # dense reference
+    h = dense(tok)
+    loss_ref = torch.nn.functional.cross_entropy(h @ head, tgt)
+    loss_ref.backward()
+    out = {}
+    for name, e in (("ar", emb), ("sp", emb_sp)):
+        x = e(tok)
+        if name == "sp":
+            assert x.shape == (M // world, d)
+            x = gather_rows(x, tp)
+        else:
+            x = copy_to_region(x, tp)     # replicated input of a column-parallel product
+        assert torch.allclose(x, h.detach(), atol=1e-6)
+        hl = head[:, rank * vloc:(rank + 1) * vloc].clone().requires_grad_()
+        loss = vocab_parallel_cross_entropy(x @ hl, tgt, tp)
+        loss.backward()
+        out[name] = (abs(loss.item() - loss_ref.item()),
+                     (e.weight.grad - dense.weight.grad[rank * vloc:(rank + 1) * vloc]).abs().max().item())
+    return out
+
+
+def test_vocab_parallel_embedding_and_cross_entropy():
+    for res in run_ranks(_vocab_parallel_worker, 2):
+        for name, (dl, dg) in res.items():
+            assert dl < 1e-5 and dg < 1e-5, (name, dl, dg)
+
+
 # ------------------------------------------------------------------ TP layers
 def _tp_worker(rank, world):
     from rumus_b200.parallel.tp import ColumnParallelLinear, RowParallelLinear, TPContext, scatter_rows, gather_rows
