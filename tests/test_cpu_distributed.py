@@ -151,6 +151,24 @@ def test_vocab_parallel_embedding_and_cross_entropy():
             assert dl < 1e-5 and dg < 1e-5, (name, dl, dg)
 
 
+def _async_allreduce_worker(rank, world):
+    from rumus_b200.parallel import all_reduce, async_all_reduce
+    a = torch.full((1000,), float(rank + 1))
+    b = torch.arange(4.0) * (rank + 1)
+    ha = async_all_reduce(a)                    # mean, like the reference's barrier
+    hb = async_all_reduce(b, average=False)
+    c = torch.ones(3) * rank                    # independent work while the collectives run
+    c = c * 2
+    ra, rb = ha.wait(), hb.wait()
+    assert ra is a and ha.is_completed() and ha.wait() is a    # waiting twice is harmless
+    return ra[0].item(), rb.tolist(), all_reduce(c.clone()).tolist()
+
+
+def test_async_all_reduce_handles():
+    for ra, rb, rc in run_ranks(_async_allreduce_worker, 3):
+        assert ra == 2.0 and rb == [0.0, 6.0, 12.0, 18.0] and rc == [2.0, 2.0, 2.0]
+
+
 # ------------------------------------------------------------------ TP layers
 def _tp_worker(rank, world):
     from rumus_b200.parallel.tp import ColumnParallelLinear, RowParallelLinear, TPContext, scatter_rows, gather_rows
