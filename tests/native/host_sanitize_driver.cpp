@@ -1,7 +1,7 @@
 // Stress driver for the host-side native code, built by tests/test_cpu_native_sanitizers.py with
 // -fsanitize=address,undefined and with -fsanitize=thread: the serving scheduler / KV block
 // allocator under concurrent submitters, the .rrec reader and the multi-threaded batch loader over
-// several epochs (including one abandoned half way).  Exits 0 when every invariant held; the
+// several epochs (including one abandoned half way), and the file-descriptor exchange between ranks.  Exits 0 when every invariant held; the
 // sanitizers abort the process on a report.
 #include <atomic>
 #include <cstdint>
@@ -10,6 +10,7 @@
 #include <string>
 #include <thread>
 #include <vector>
+#include <unistd.h>
 
 extern "C" {
 void* rbs_create(int num_blocks, int block_size, int max_batch, int token_budget);
@@ -156,10 +157,55 @@ static int loader_stress(const char* path) {
   return 0;
 }
 
+extern "C" int rb_fd_exchange(const char* dir, int rank, int world, int my_fd, int* out_fds, int timeout_ms);
+
+// Four "ranks" (threads; descriptors pass through real Unix sockets all the same) exchange the read
+// ends of pipes; every rank then finds every other rank's byte in the pipe it received.
+static int fd_exchange_stress(const std::string& dir) {
+  const int world = 4;
+  for (int round = 0; round < 3; ++round) {
+    int pipes[world][2];
+    for (int r = 0; r < world; ++r) {
+      CHECK(pipe(pipes[r]) == 0);
+      const char b = (char)('a' + r);
+      CHECK(write(pipes[r][1], &b, 1) == 1);
+    }
+    std::vector<std::vector<int>> got(world, std::vector<int>(world, -1));
+    std::vector<int> rc(world, -1);
+    std::vector<std::thread> th;
+    for (int r = 0; r < world; ++r)
+      th.emplace_back([&, r] { rc[r] = rb_fd_exchange(dir.c_str(), r, world, pipes[r][0], got[r].data(), 10000); });
+    for (auto& t : th) t.join();
+    for (int r = 0; r < world; ++r) {
+      CHECK(rc[r] == 0);
+      for (int p = 0; p < world; ++p) CHECK(got[r][p] >= 0);
+      CHECK(got[r][r] == pipes[r][0]);
+    }
+    // one reader per pipe: rank (p+1)%world reads rank p's byte through the descriptor it received
+    for (int p = 0; p < world; ++p) {
+      char b = 0;
+      CHECK(read(got[(p + 1) % world][p], &b, 1) == 1);
+      CHECK(b == (char)('a' + p));
+    }
+    for (int r = 0; r < world; ++r) {
+      for (int p = 0; p < world; ++p) if (p != r) close(got[r][p]);
+      close(pipes[r][0]);
+      close(pipes[r][1]);
+    }
+  }
+  std::printf("fd exchange: ok\n");
+  return 0;
+}
+
 int main(int argc, char** argv) {
   if (argc < 2) { std::fprintf(stderr, "usage: driver <scratch .rrec path>\n"); return 2; }
   if (scheduler_stress()) return 1;
   if (loader_stress(argv[1])) return 1;
+  {
+    std::string dir(argv[1]);
+    const size_t slash = dir.find_last_of('/');
+    if (fd_exchange_stress(slash == std::string::npos ? std::string(".") : dir.substr(0, slash))) return 1;
+  }
   std::printf("HOST SANITIZE DRIVER OK\n");
   return 0;
 }

@@ -233,3 +233,48 @@ def test_custom_op_registered_with_the_dispatcher():
     assert set(res.values()) == {"SUCCESS"}
     with FakeTensorMode():
         assert f(torch.empty(3, 4), torch.empty(3, 4)).shape == (3, 4)
+
+
+def _fd_exchange_child(rank, world, d, q, late):
+    import ctypes
+    import time
+    from rumus_b200.ops import _lib
+    if late and rank == 0:
+        time.sleep(0.3)                       # peers must retry until this rank listens
+    fd = os.memfd_create(f"rank{rank}")
+    os.write(fd, f"payload-of-rank-{rank}".encode())
+    fds = (ctypes.c_int * world)()
+    rc = _lib.host_lib().rb_fd_exchange(d.encode(), ctypes.c_int(rank), ctypes.c_int(world), ctypes.c_int(fd),
+                                        fds, ctypes.c_int(10000))
+    seen = []
+    if rc == 0:
+        for r in range(world):
+            seen.append(os.pread(fds[r], 64, 0).decode())
+    q.put((rank, rc, seen))
+
+
+def test_fd_exchange_between_processes(tmp_path):
+    """Every rank hands one descriptor (here: a memfd with a rank-specific payload) to every other
+    process over Unix sockets, including a rank that starts listening late; a missing rank makes
+    the others time out with a status code instead of blocking."""
+    import ctypes
+    import multiprocessing as mp
+    from rumus_b200.ops import _lib
+    ctx = mp.get_context("spawn")
+    world = 3
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_fd_exchange_child, args=(r, world, str(tmp_path), q, True)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = sorted(q.get(timeout=60) for _ in range(world))
+    for p in procs:
+        p.join(timeout=30)
+    for rank, rc, seen in got:
+        assert rc == 0 and seen == [f"payload-of-rank-{r}" for r in range(world)]
+    # a peer that never shows up: bounded wait, status 3
+    fds = (ctypes.c_int * 2)()
+    fd = os.memfd_create("alone")
+    rc = _lib.host_lib().rb_fd_exchange(str(tmp_path).encode(), ctypes.c_int(0), ctypes.c_int(2), ctypes.c_int(fd),
+                                        fds, ctypes.c_int(300))
+    os.close(fd)
+    assert rc == 3 and fds[1] == -1

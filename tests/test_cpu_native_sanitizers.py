@@ -10,6 +10,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SOURCES = [os.path.join(ROOT, "csrc", "serve", "kv_scheduler.cpp"),
            os.path.join(ROOT, "csrc", "runtime", "rrec_reader.cpp"),
            os.path.join(ROOT, "csrc", "runtime", "batch_loader.cpp"),
+           os.path.join(ROOT, "csrc", "runtime", "fd_exchange.cpp"),
            os.path.join(ROOT, "tests", "native", "host_sanitize_driver.cpp")]
 
 
