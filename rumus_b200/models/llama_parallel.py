@@ -60,7 +60,7 @@ class _VocabParallelCE(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, logits_local, targets, tp: TPContext, vocab_start: int):
-        lf = logits_local.float()
+        lf = logits_local if logits_local.dtype == torch.float64 else logits_local.float()
         m = lf.max(dim=-1).values
         tp.all_reduce(m, op=dist.ReduceOp.MAX)
         e = torch.exp(lf - m[:, None])

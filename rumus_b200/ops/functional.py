@@ -29,6 +29,12 @@ _ACT_TORCH = {
 }
 
 
+def _acc(t: torch.Tensor) -> torch.Tensor:
+    """Accumulation dtype of the plain-math paths: fp32, except that fp64 inputs stay fp64 (so the
+    formulas can be checked by finite differences)."""
+    return t if t.dtype == torch.float64 else t.float()
+
+
 def _is_native(t: torch.Tensor) -> bool:
     return t.is_cuda
 
@@ -343,7 +349,7 @@ def layer_norm(x, weight, bias, eps: float = 1e-5, residual=None):
 def rms_norm(x, weight, eps: float = 1e-6, residual=None):
     if not _is_native(x):
         h = x + residual if residual is not None else x
-        hf = h.float()
+        hf = _acc(h)
         y = (hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + eps)).to(h.dtype) * weight
         return (y, h) if residual is not None else y
     y, h = _NormFn.apply(x, weight, None, residual, eps, True)
@@ -396,7 +402,7 @@ def cross_entropy_loss(logits: torch.Tensor, targets: torch.Tensor) -> torch.Ten
         logits = logits.reshape(-1, logits.shape[-1])
         targets = targets.reshape(-1)
     if not _is_native(logits):
-        return TF.cross_entropy(logits.float(), targets.long())
+        return TF.cross_entropy(_acc(logits), targets.long())
     if logits.stride(-1) != 1:
         logits = logits.contiguous()
     return _CrossEntropyFn.apply(logits, targets)
@@ -440,7 +446,7 @@ def lm_head_loss(x, weight_io, targets):
     their gradient as two tensors."""
     if not _is_native(x):
         logits = x.reshape(-1, x.shape[-1]) @ weight_io
-        return TF.cross_entropy(logits.float(), targets.reshape(-1).long())
+        return TF.cross_entropy(_acc(logits), targets.reshape(-1).long())
     return _LmHeadLossFn.apply(x, weight_io, targets)
 
 
@@ -526,7 +532,7 @@ def _rope_torch(x, seq_len, theta, inverse=False):
     cs, sn = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
     if inverse:
         sn = -sn
-    a, b = x[..., :half].float(), x[..., half:].float()
+    a, b = _acc(x[..., :half]), _acc(x[..., half:])
     return torch.cat([a * cs - b * sn, b * cs + a * sn], dim=-1).to(x.dtype)
 
 
@@ -573,10 +579,11 @@ def rope_qkv(qkv: torch.Tensor, seq_len: int, heads: int, kv_heads: int, head_di
 # attention
 # ----------------------------------------------------------------------------
 def sdpa_reference(q, k, v, causal: bool, scale: Optional[float] = None):
-    """Plain-math attention on [B, S, H, d] tensors (fp32 softmax)."""
+    """Plain-math attention on [B, S, H, d] tensors (softmax in fp32; fp64 inputs stay fp64)."""
     B, S, H, d = q.shape
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
-    qf, kf, vf = (t.permute(0, 2, 1, 3).float() for t in (q, k, v))
+    acc = torch.float64 if q.dtype == torch.float64 else torch.float32
+    qf, kf, vf = (t.permute(0, 2, 1, 3).to(acc) for t in (q, k, v))
     if kf.shape[1] != H:
         rep = H // kf.shape[1]
         kf = kf.repeat_interleave(rep, dim=1)

@@ -57,7 +57,8 @@ def batch_norm2d(x, weight, bias, running_mean, running_var, training: bool, mom
     (``y = relu(bn(x) + residual)``).  Running variance uses the biased batch variance like the
     reference (rumus/src/backend/cpu.rs:320-324)."""
     if not x.is_cuda:
-        xf = x.float()
+        acc = torch.float64 if x.dtype == torch.float64 else torch.float32   # fp64 stays fp64 for finite-difference checks
+        xf = x.to(acc)
         if training:
             mean = xf.mean(dim=(0, 2, 3))
             var = xf.var(dim=(0, 2, 3), unbiased=False)
@@ -67,9 +68,9 @@ def batch_norm2d(x, weight, bias, running_mean, running_var, training: bool, mom
         else:
             mean, var = running_mean, running_var
         y = (xf - mean[None, :, None, None]) * torch.rsqrt(var[None, :, None, None] + eps)
-        y = y * weight.float()[None, :, None, None] + bias.float()[None, :, None, None]
+        y = y * weight.to(acc)[None, :, None, None] + bias.to(acc)[None, :, None, None]
         if residual is not None:
-            y = y + residual.float()
+            y = y + residual.to(acc)
         if relu:
             y = torch.relu(y)
         return y.to(x.dtype)

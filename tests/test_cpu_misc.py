@@ -278,3 +278,25 @@ def test_fd_exchange_between_processes(tmp_path):
                                         fds, ctypes.c_int(300))
     os.close(fd)
     assert rc == 3 and fds[1] == -1
+
+
+def test_canary_guard_detects_out_of_bounds_writes():
+    """Bounds-guard mode on CPU tensors: clean runs pass, an overrun on either side is reported with
+    the allocation site; tensors allocated without an explicit device are left alone."""
+    from rumus_b200.utils.canary import CanaryError, canary_guard
+    with canary_guard(devices=("cpu",)) as g:
+        a = torch.empty((3, 5), dtype=torch.float32, device="cpu")
+        b = torch.zeros(7, dtype=torch.int64, device="cpu")
+        c = torch.empty_like(a)
+        d = torch.empty_strided((2, 3), (3, 1), dtype=torch.float16, device="cpu")
+        torch.empty(4)
+        a.fill_(1); c.copy_(a); d.fill_(2)
+        assert b.sum().item() == 0 and a.is_contiguous() and g.check() == 4
+    with pytest.raises(CanaryError, match=r"\(3, 5\).*after the tensor.*\+0 from its end"):
+        with canary_guard(devices=("cpu",)):
+            a = torch.empty((3, 5), dtype=torch.float32, device="cpu")
+            torch.as_strided(a, (17,), (1,)).fill_(3.0)
+    with pytest.raises(CanaryError, match="before the tensor"):
+        with canary_guard(devices=("cpu",)):
+            a = torch.empty((8,), dtype=torch.float32, device="cpu")
+            torch.as_strided(a, (1,), (1,), storage_offset=a.storage_offset() - 1).fill_(3.0)
