@@ -18,6 +18,7 @@ The reference has no launcher: jobs are Rust programs that wire modules by hand
 from __future__ import annotations
 
 import argparse
+import contextlib
 import json
 import os
 import sys
@@ -71,7 +72,7 @@ def _run_gpt(cfg: TrainConfig, a, rank, world, dev) -> dict:
     from .io.checkpoint import load_checkpoint, save_checkpoint
     from .models import GPT, GPTConfig
     from .parallel import FSDP
-    from .utils import MetricsLogger
+    from .utils import DeviceTimer, MetricsLogger
     from .utils.elastic import latest_checkpoint
     dtype = _DTYPES[cfg.precision.compute] if dev.type == "cuda" else torch.float32
     model = GPT(GPTConfig(**cfg.model.kwargs), device=dev, dtype=dtype)
@@ -89,19 +90,26 @@ def _run_gpt(cfg: TrainConfig, a, rank, world, dev) -> dict:
     steps = a.steps if a.steps is not None else cfg.steps
     tokens_per_step = world * cfg.seqs_per_gpu * cfg.model.kwargs["seq_len"]
     first = last = None
-    t0 = time.time()
+    t0, step0 = time.time(), engine.step_count
     while engine.step_count < steps:
         x, y = next(batches)
-        engine.zero_grad()
-        loss = model(x, y)
-        loss.backward()
-        engine.step()
-        if engine.step_count % a.log_every == 0 or engine.step_count == steps:
+        will_log = (engine.step_count + 1) % a.log_every == 0 or engine.step_count + 1 == steps
+        timer = DeviceTimer() if will_log else contextlib.nullcontext()
+        with timer:      # device-timed (CUDA events) on the steps that are logged; no sync otherwise
+            engine.zero_grad()
+            loss = model(x, y)
+            loss.backward()
+            engine.step()
+        if will_log:
             last = float(loss.item())
             first = last if first is None else first
             if log:
-                log.log(step=engine.step_count, loss=last, lr=engine.lr,
-                        tokens_per_s=tokens_per_step * engine.step_count / max(1e-9, time.time() - t0))
+                rec = dict(step=engine.step_count, loss=last, lr=engine.lr, step_ms=timer.ms,
+                           tokens_per_s_device=tokens_per_step / max(1e-9, timer.ms / 1e3),
+                           tokens_per_s=tokens_per_step * (engine.step_count - step0) / max(1e-9, time.time() - t0))
+                if dev.type == "cuda":
+                    rec["hbm_peak_gb"] = torch.cuda.max_memory_allocated(dev) / 2 ** 30
+                log.log(**rec)
         if a.ckpt_dir and a.ckpt_every and engine.step_count % a.ckpt_every == 0:
             save_checkpoint(os.path.join(a.ckpt_dir, f"step-{engine.step_count}"), model, engine,
                             extra={"config": cfg.name})

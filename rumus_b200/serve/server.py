@@ -36,6 +36,7 @@ class EngineWorker:
         self.thread = threading.Thread(target=self._run, daemon=True)
         self.completed = 0
         self.ttft_ms = []
+        self.itl_ms = []          # per request: mean time between output tokens after the first
 
     def start(self):
         self.thread.start()
@@ -70,8 +71,11 @@ class EngineWorker:
                 req = eng.requests.pop(rid)
                 loop, fut, t0 = self.waiters.pop(rid)
                 self.completed += 1
+                now = time.time()
                 if req.first_token_time:
                     self.ttft_ms.append((req.first_token_time - t0) * 1e3)
+                    if len(req.output) > 1:
+                        self.itl_ms.append((now - req.first_token_time) * 1e3 / (len(req.output) - 1))
                 res = {"generated_ids": req.output, "latency_ms": (time.time() - t0) * 1e3}
                 loop.call_soon_threadsafe(fut.set_result, res)
 
@@ -101,14 +105,19 @@ def build_app(worker: EngineWorker):
         e = worker.engine
         tt = sorted(worker.ttft_ms)
         p50 = tt[len(tt) // 2] if tt else 0.0
+        it = sorted(worker.itl_ms)
+        itl50 = it[len(it) // 2] if it else 0.0
+        total_blocks = e.cfg.num_blocks
         txt = (f"rumus_requests_completed {worker.completed}\n"
                f"rumus_tokens_generated {e.tokens_out}\n"
                f"rumus_engine_steps {e.steps}\n"
                f"rumus_kv_free_blocks {e.sched.free_blocks()}\n"
+               f"rumus_kv_block_utilisation {1.0 - e.sched.free_blocks() / max(1, total_blocks):.4f}\n"
                f"rumus_queue_waiting {e.sched.num_waiting()}\n"
                f"rumus_running {e.sched.num_running()}\n"
                f"rumus_preemptions {e.sched.preemptions()}\n"
-               f"rumus_ttft_p50_ms {p50:.3f}\n")
+               f"rumus_ttft_p50_ms {p50:.3f}\n"
+               f"rumus_inter_token_latency_p50_ms {itl50:.3f}\n")
         return web.Response(text=txt)
 
     app = web.Application()

@@ -91,7 +91,11 @@ def test_http_api_shape():
             bad = await client.post("/v1/generate", json={"token_ids": []})
             assert bad.status == 400
             m = await client.get("/metrics")
-            assert "rumus_requests_completed 1" in await m.text()
+            text = await m.text()
+            assert "rumus_requests_completed 1" in text
+            vals = dict(line.split() for line in text.strip().splitlines())
+            assert float(vals["rumus_inter_token_latency_p50_ms"]) > 0 and float(vals["rumus_ttft_p50_ms"]) > 0
+            assert 0.0 <= float(vals["rumus_kv_block_utilisation"]) <= 1.0
         finally:
             await client.close()
             worker.stop()
