@@ -1,12 +1,14 @@
 """CUDA paths of the quantised matmuls (kernels: ``csrc/kernels/quant.cu``).
 
-INT4: ``M <= 32`` rows (decode) run the split-K GEMV that streams the packed weights once;
-larger ``M`` (prefill) expand the weight to a dense 16-bit matrix and run the tcgen05 GEMM.
+INT4: small batches (decode) run the split-K GEMV that streams the packed weights once; larger
+``M`` expand the weight to a dense 16-bit matrix and run the tcgen05 GEMM; batches up to 128 rows
+can instead take the fused W4A16 tcgen05 kernel (opt-in, see ``w4a16_enabled``).
 INT8 blocks: quantise / dequantise kernels; the matmul dequantises then uses the GEMM.
 """
 from __future__ import annotations
 
-from ctypes import c_int, c_void_p
+import os
+from ctypes import c_int, c_longlong, c_void_p
 
 import torch
 
@@ -17,6 +19,8 @@ P, I = c_void_p, c_int
 native.register_signature("rb_int4_gemv_splits", [I, I])
 native.register_signature("rb_int4_gemv", [I, I, P, P, P, P, P, P, P, I, I, I, I, I, P])
 native.register_signature("rb_int4_dequant", [I, I, P, P, P, P, I, I, I, P])
+native.register_signature("rb_w4a16_slices", [I, I])
+native.register_signature("rb_w4a16_gemm", [I, I, P, c_longlong, P, P, P, P, P, P, I, I, I, I, I, P])
 native.register_signature("rb_q8_quantize", [I, P, P, I, I, I, P])
 native.register_signature("rb_q8_dequantize", [I, P, P, I, I, I, P])
 
@@ -35,12 +39,48 @@ def int4_dequant(qw, dtype: torch.dtype) -> torch.Tensor:
     return dense
 
 
+# Batches of GEMV_CHUNKED_MAX_M+1 .. 128 rows can take the fused W4A16 tcgen05 kernel
+# (csrc/kernels/w4a16_gemm.cu), which expands the packed weight inside shared memory instead of
+# writing a dense 16-bit copy.  Opt-in (RB_W4A16=1) until it has been measured against the
+# dequantise + GEMM path.
+W4A16_MAX_M = 128
+
+
+def w4a16_enabled() -> bool:
+    return os.environ.get("RB_W4A16", "0") == "1"
+
+
+def int4_matmul_fused(x: torch.Tensor, qw, bias=None):
+    """The fused W4A16 kernel; returns ``None`` when the shape / alignment is outside what it covers."""
+    L = native.lib()
+    M, K = x.shape
+    if M > W4A16_MAX_M or x.dtype not in (torch.bfloat16, torch.float16):
+        return None
+    x = x.contiguous()
+    y = torch.empty((M, qw.n), dtype=x.dtype, device=x.device)
+    ws = None
+    if L.rb_w4a16_slices(qw.n, qw.padded_k) > 1:
+        ws = torch.empty((M, qw.n), dtype=torch.float32, device=x.device)
+    rc = L.rb_w4a16_gemm(native.dtype_code(x.dtype), native.dtype_code(qw.scales.dtype), ptr(x),
+                         c_longlong(x.stride(0)), ptr(qw.packed), ptr(qw.scales), ptr(qw.zero_points),
+                         ptr(bias), ptr(y), ptr(ws), M, qw.n, K, qw.padded_k, qw.group_size, stream_ptr())
+    if rc == 51:
+        return None
+    check(rc, "rb_w4a16_gemm")
+    count_launch(3 if ws is not None else 1)
+    return y
+
+
 def int4_matmul(x: torch.Tensor, qw, bias=None) -> torch.Tensor:
     """x [M, K] @ dequant(qw) [K, N]."""
     L = native.lib()
     M, K = x.shape
     assert K == qw.k
     x = x.contiguous()
+    if GEMV_CHUNKED_MAX_M < M <= W4A16_MAX_M and w4a16_enabled():
+        y = int4_matmul_fused(x, qw, bias)
+        if y is not None:
+            return y
     if M <= GEMV_CHUNKED_MAX_M:
         # decode batches: the packed weights are streamed once per 32 rows
         splits = L.rb_int4_gemv_splits(qw.padded_k, qw.n)

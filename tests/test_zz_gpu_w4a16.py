@@ -1,0 +1,45 @@
+"""Fused W4A16 tcgen05 GEMM (``csrc/kernels/w4a16_gemm.cu``) against the dequantised fp32 product.
+
+The kernel is opt-in (``RB_W4A16=1``): these tests run only when that switch is set, which is also
+what routes ``int4_matmul`` to the kernel."""
+import os
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(os.environ.get("RB_W4A16", "0") != "1", reason="fused W4A16 kernel is opt-in")]
+
+
+def _rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("scale_dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("M,K,N", [(9, 256, 128),        # one tile, one K slice of 4 blocks
+                                   (16, 4096, 512),      # K split across CTAs, fp32 workspace
+                                   (33, 1160, 520),      # K padded to the group, N not a multiple of 128
+                                   (128, 1024, 256)])    # the largest batch (UMMA N = 128)
+def test_w4a16_matches_dequantised_product(dtype, scale_dtype, M, K, N):
+    from rumus_b200.nn.quant import QuantizedTensor
+    from rumus_b200.ops import native
+    from rumus_b200.ops import quant_cuda as Q
+    torch.manual_seed(M + K + N)
+    w = torch.randn(K, N) * 0.05
+    q = QuantizedTensor.from_f32(w, 128, scale_dtype).to("cuda")
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dtype)
+    bias = torch.randn(N, device="cuda").to(dtype)
+    y = Q.int4_matmul_fused(x, q, bias)
+    assert y is not None
+    ref = x.float() @ q.dequantize(torch.float32) + bias.float()
+    assert native.read_status() == 0
+    assert _rel(y, ref) < 1.5e-2, _rel(y, ref)
+    # rows are independent: a one-row change only moves that row
+    x2 = x.clone()
+    x2[M // 2] += 1.0
+    y2 = Q.int4_matmul_fused(x2, q, bias)
+    same = torch.ones(M, dtype=torch.bool, device="cuda")
+    same[M // 2] = False
+    assert torch.equal(y2[same], y[same]) or _rel(y2[same], y[same]) < 1e-3   # split-K atomics reorder sums
