@@ -12,16 +12,20 @@ import os
 import re
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-SKIP_DIRS = {".git", "_work", "gpurun_out", "baseline", "__pycache__", ".pytest_cache", "build"}
+SOURCE_ROOTS = ("csrc", "rumus_b200", "tests", "bench", "examples")
 EXTS = (".cu", ".cuh", ".cpp", ".h", ".hpp", ".py", ".cc")
 
 
 def _sources():
-    for d, dirs, files in os.walk(ROOT):
-        dirs[:] = [x for x in dirs if x not in SKIP_DIRS]
-        for f in files:
-            if f.endswith(EXTS):
-                yield os.path.join(d, f)
+    for f in sorted(os.listdir(ROOT)):
+        if f.endswith(EXTS) and os.path.isfile(os.path.join(ROOT, f)):
+            yield os.path.join(ROOT, f)
+    for root in SOURCE_ROOTS:
+        for d, dirs, files in os.walk(os.path.join(ROOT, root)):
+            dirs[:] = [x for x in dirs if x != "__pycache__"]
+            for f in files:
+                if f.endswith(EXTS):
+                    yield os.path.join(d, f)
 
 
 def _scan(patterns):
