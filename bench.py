@@ -99,7 +99,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--mode", default=None, help="fused | nccl (multi-GPU communication path)")
     ap.add_argument("--reshard", action="store_true",
-                    help="FSDP keeps only parameter shards between a block's forward and backward (needs --mode nccl)")
+                    help="FSDP keeps only parameter shards between a block's forward and backward")
     ap.add_argument("--phases", action="store_true", help="also report forward/backward/tail device times")
     ap.add_argument("--trace-export", default=None,
                     help="write a torch.profiler Chrome trace of two extra steps (with the NVTX-named "

@@ -379,6 +379,49 @@ __global__ void flag_gate_kernel(PeerTable pt, long long flags_off, int epoch, i
       return;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Gather of persistent shards into a LOCAL full-size buffer (parameters resharded between uses):
+// every rank keeps its shard of a unit in a small arena buffer at the same offset; the full vector
+// is assembled in memory that no peer ever reads (a slot shared by several units), so reusing the
+// slot needs no cross-rank handshake.  Shard `r` lands at dst + r * shard_bytes; the local shard is
+// copied too.
+struct SgParams {
+  PeerTable peers;
+  long long src_off;          // bytes: the shard buffer (same offset on every rank)
+  char* dst;                  // local, world * shard_bytes
+  long long shard_bytes;      // multiple of 16
+  long long src_flags_off;    // int[world] "shard of rank r has been updated" (epoch), or -1
+  long long chunk_bytes;
+  int chunks_per_shard;
+  int epoch;
+  int* status;
+};
+
+__global__ void __launch_bounds__(512) shard_gather_kernel(const SgParams p) {
+  __shared__ int s_ok;
+  const PeerTable& pt = p.peers;
+  for (int k = 0; k < pt.world; ++k) {
+    const int src = (pt.rank + k) % pt.world;
+    if (threadIdx.x == 0) {
+      bool ok = true;
+      if (k > 0 && p.src_flags_off >= 0)
+        ok = wait_flag_sys(peer_ptr<int>(pt, pt.rank, p.src_flags_off) + src, p.epoch, p.status,
+                           RB_ERR_TIMEOUT_FLAG);
+      s_ok = ok ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const char* remote = peer_ptr<char>(pt, src, p.src_off);
+    char* dst = p.dst + (long long)src * p.shard_bytes;
+    for (int c = blockIdx.x; c < p.chunks_per_shard; c += gridDim.x) {
+      const long long lo = (long long)c * p.chunk_bytes;
+      const long long hi = min(p.shard_bytes, lo + p.chunk_bytes);
+      copy_range_16(dst, remote, lo, hi);
+    }
+    __syncthreads();
+  }
+}
+
 static PeerTable make_table(void* const* bases, void* mc_base, int world, int rank) {
   PeerTable t;
   for (int i = 0; i < kMaxRanks; ++i) t.base[i] = i < world ? bases[i] : nullptr;
@@ -461,6 +504,29 @@ int rb_all_gather(void* const* bases, int world, int rank, long long buf_off, lo
   if (src_flags_off >= 0)
     flag_gate_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(p.peers, src_flags_off, epoch, 0, p.status);
   all_gather_kernel<<<ctas, comm_threads(), 0, (cudaStream_t)stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
+}
+
+// Assemble a unit's full parameter vector in local memory `dst` from every rank's shard buffer at
+// arena offset `src_off` (see shard_gather_kernel).  With `src_flags_off >= 0` a peer's shard is
+// read only once its flag has reached `epoch`.
+int rb_shard_gather(void* const* bases, int world, int rank, long long src_off, void* dst,
+                    long long shard_bytes, long long src_flags_off, int epoch, int ctas, void* stream) {
+  using namespace rb;
+  if (world > kMaxRanks || shard_bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(dst) & 15)) return 30;
+  SgParams p;
+  p.peers = make_table(bases, nullptr, world, rank);
+  p.src_off = src_off; p.dst = static_cast<char*>(dst); p.shard_bytes = shard_bytes;
+  p.src_flags_off = src_flags_off; p.epoch = epoch;
+  if (ctas <= 0) ctas = 16;
+  p.chunk_bytes = (shard_bytes / ((long long)ctas * 4) + 4095) / 4096 * 4096;
+  if (p.chunk_bytes < 65536) p.chunk_bytes = 65536;
+  p.chunks_per_shard = (int)((shard_bytes + p.chunk_bytes - 1) / p.chunk_bytes);
+  p.status = rbh::device_status_word();
+  if (src_flags_off >= 0)
+    flag_gate_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(p.peers, src_flags_off, epoch, 0, p.status);
+  shard_gather_kernel<<<ctas, comm_threads(), 0, (cudaStream_t)stream>>>(p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 3000 + (int)e;
 }

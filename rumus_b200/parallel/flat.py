@@ -30,7 +30,8 @@ def _round_up(x: int, m: int) -> int:
 
 class FlatUnit:
     def __init__(self, name: str, params: List[nn.Parameter], world_size: int = 1, rank: int = 0,
-                 alloc: Optional[Callable[[int, torch.dtype, torch.device], torch.Tensor]] = None):
+                 alloc: Optional[Callable[[int, torch.dtype, torch.device], torch.Tensor]] = None,
+                 param_alloc: Optional[Callable[[int, torch.dtype, torch.device], torch.Tensor]] = None):
         assert params, name
         self.name, self.params = name, params
         self.world_size, self.rank = world_size, rank
@@ -46,7 +47,9 @@ class FlatUnit:
         self.shard_numel = self.padded // world_size
         alloc = alloc or (lambda n, dt, dev: torch.zeros(n, dtype=dt, device=dev))
         self.persist: Optional[torch.Tensor] = None   # set by reshard(): the shard's own buffer
-        self.flat_param = alloc(self.padded, self.dtype, self.device)
+        # ``param_alloc``: a different home for the full parameter vector than for the gradients
+        # (a unit that is about to be resharded must not take peer-visible memory for it)
+        self.flat_param = (param_alloc or alloc)(self.padded, self.dtype, self.device)
         self.flat_grad = alloc(self.padded, self.dtype, self.device)
         for p, o in zip(params, offs):
             view = self.flat_param[o:o + p.numel()].view(p.shape)
@@ -76,12 +79,17 @@ class FlatUnit:
         for p, o in zip(self.params, self.offsets):
             p.data = self.flat_param[o:o + p.numel()].view(p.shape)
 
-    def reshard(self, slot: torch.Tensor) -> None:
+    def reshard(self, slot: torch.Tensor, shard_alloc=None) -> None:
         """Gives up the unit's own full parameter buffer: this rank's shard moves to a buffer of
-        its own (``persist``), and the full vector lives in ``slot``, a buffer shared with other
-        units that only holds this unit's parameters while an engine has gathered them there."""
+        its own (``persist``; from ``shard_alloc`` when the shard has to be peer-visible), and the
+        full vector lives in ``slot``, a buffer shared with other units that only holds this
+        unit's parameters while an engine has gathered them there."""
         lo, hi = self.shard_range
-        self.persist = self.flat_param[lo:hi].clone()
+        if shard_alloc is None:
+            self.persist = self.flat_param[lo:hi].clone()
+        else:
+            self.persist = shard_alloc(self.shard_numel, self.dtype, self.device)
+            self.persist.copy_(self.flat_param[lo:hi])
         self.bind_storage(slot)
 
     def grad_shard(self) -> torch.Tensor:
@@ -110,7 +118,7 @@ class FlatUnit:
 
 
 def build_units(model: nn.Module, unit_roots: List[tuple], world_size: int = 1, rank: int = 0,
-                alloc=None) -> List[FlatUnit]:
+                alloc=None, param_alloc_for: Optional[Callable[[str], Optional[Callable]]] = None) -> List[FlatUnit]:
     """``unit_roots`` is a list of ``(name, [modules or parameters])``; every model parameter
     must be covered exactly once."""
     seen = set()
@@ -123,7 +131,8 @@ def build_units(model: nn.Module, unit_roots: List[tuple], world_size: int = 1, 
                 if id(p) not in seen:
                     seen.add(id(p))
                     ps.append(p)
-        units.append(FlatUnit(name, ps, world_size, rank, alloc))
+        units.append(FlatUnit(name, ps, world_size, rank, alloc,
+                              param_alloc_for(name) if param_alloc_for is not None else None))
     missing = [n for n, p in model.named_parameters() if id(p) not in seen]
     if missing:
         raise ValueError(f"parameters not assigned to a flat unit: {missing[:5]}")

@@ -22,7 +22,8 @@ gathered for a layer's forward, dropped, and gathered again for its backward) a 
 its shard between uses: the full vector of a block lives in one of two rotating slots, the next
 block's shards are gathered into the other slot while this block computes, and nothing is gathered
 after the update.  Parameter memory is then shards + two block-sized slots instead of every block
-in full.  Implemented for the ``nccl`` and CPU-rank modes.
+in full.  In ``fused`` mode the shards live in the arena and ``shard_gather_kernel`` pulls them into
+the local slot with plain peer loads; ``nccl`` and CPU ranks use ``all_gather_into_tensor``.
 
 ``nccl`` mode issues ``reduce_scatter_tensor`` / ``all_gather_into_tensor`` plus the fused flat
 Adam kernel: that is the comparison baseline.  With a world size of 1 no communication happens.
@@ -95,14 +96,25 @@ class FSDP:
         self.mode = mode
         self.arena = arena
         alloc = None
+        self._reshard = bool(reshard_after_forward) and self.world > 1
+        param_alloc_for = None
         if mode == "fused":
             from .symm import SymmArena
+            total = sum(p.numel() for p in model.parameters())
+            blocks = getattr(model, "blocks", None)
+            in_blocks = sum(p.numel() for b in blocks for p in b.parameters()) if blocks is not None else 0
+            if self._reshard:
+                # peer-visible: all gradients, the resident units' parameters, the blocks' shards
+                elems = total + (total - in_blocks) + in_blocks // self.world
+                plain = lambda n, dt, dev: torch.zeros(n, dtype=dt, device=dev)   # noqa: E731
+                param_alloc_for = lambda name: plain if name.startswith("blocks.") else None   # noqa: E731
+            else:
+                elems = 2 * total
             if self.arena is None:
-                need = sum(p.numel() for p in model.parameters()) * 2 * 2 * 1.05 + (64 << 20)
-                self.arena = SymmArena(int(need), group)
+                self.arena = SymmArena(int(elems * 2 * 1.05) + (64 << 20), group)
             alloc = self.arena.alloc_flat
         self.units: List[FlatUnit] = build_units(model, unit_roots or default_units(model),
-                                                 self.world, self.rank, alloc)
+                                                 self.world, self.rank, alloc, param_alloc_for)
         self.step_count = 0
         self._pending: List[int] = []
         self._cuda = dev.type == "cuda"
@@ -113,10 +125,6 @@ class FSDP:
                             if self._cuda and self.world > 1 else None)
         self._unit_events = [None] * len(self.units)
         self._trace = None
-        self._reshard = bool(reshard_after_forward) and self.world > 1
-        if self._reshard and mode == "fused":
-            raise NotImplementedError("reshard_after_forward is available with mode='nccl' (and on CPU ranks); "
-                                      "the fused kernels gather into per-unit arena buffers")
         self._install_boundaries()
         self._resharded: List[int] = []
         if self._reshard:
@@ -182,8 +190,10 @@ class FSDP:
         self._slot_event = [None, None]
         self.gather_stream = torch.cuda.Stream(device=u0.device) if self._cuda else None
         self.gathers_issued = 0
+        # fused mode: peers read the shards, so they live in the arena; the slots stay local
+        shard_alloc = self.arena.alloc_flat if self.mode == "fused" else None
         for idx in self._resharded:
-            self.units[idx].reshard(self._slots[self._slot_of[idx]])
+            self.units[idx].reshard(self._slots[self._slot_of[idx]], shard_alloc)
 
     def _gather_into_slot(self, idx: int) -> None:
         s = self._slot_of[idx]
@@ -195,7 +205,10 @@ class FSDP:
             # every kernel that still reads the slot's previous owner was enqueued before this point
             self.gather_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.gather_stream), trace_range(f"fsdp.gather.{u.name}"):
-                dist.all_gather_into_tensor(slot, u.persist, group=self.group)
+                if self.mode == "fused":
+                    self.fused.gather_shards(idx, slot)
+                else:
+                    dist.all_gather_into_tensor(slot, u.persist, group=self.group)
                 ev = torch.cuda.Event()
                 ev.record(self.gather_stream)
             self._slot_event[s] = ev
@@ -319,7 +332,10 @@ class FSDP:
                 ev[1].record(self.comm_stream)
             if self.mode == "fused":
                 self.fused.reduce_scatter_adam(idx, tail)
-                self.fused.all_gather(idx, tail)
+                if u.persist is not None:
+                    self._invalidate(idx)   # gathered again on next use
+                else:
+                    self.fused.all_gather(idx, tail)
             else:  # nccl baseline
                 shard = u.grad_shard()
                 dist.reduce_scatter_tensor(shard, u.flat_grad, op=dist.ReduceOp.AVG, group=self.group)

@@ -38,12 +38,19 @@ class FusedFsdpComm:
         self.param_flags = [a.alloc_flags(a.world) for _ in engine.units]
         self.counters = [a.alloc_local_ints(1) for _ in engine.units]
         for u in engine.units:
-            assert hasattr(u.flat_param, "arena_offset") and hasattr(u.flat_grad, "arena_offset")
+            home = u.persist if u.persist is not None else u.flat_param
+            assert hasattr(home, "arena_offset") and hasattr(u.flat_grad, "arena_offset")
         a.barrier()
 
     def reduce_scatter_adam(self, idx: int, tail: bool = False) -> None:
         e, u = self.e, self.e.units[idx]
-        fused_ops.rs_adam(self.arena, u.dtype, u.flat_grad.arena_offset, u.flat_param.arena_offset,
+        if u.persist is not None:
+            # the kernel writes the updated shard at param_off + shard_lo elements: aim that at the
+            # shard's own buffer
+            param_off = u.persist.arena_offset - u.shard_range[0] * u.persist.element_size()
+        else:
+            param_off = u.flat_param.arena_offset
+        fused_ops.rs_adam(self.arena, u.dtype, u.flat_grad.arena_offset, param_off,
                           u.shard_range[0], u.shard_numel, u.master, u.exp_avg, u.exp_avg_sq,
                           lr=e.lr, beta1=e.beta1, beta2=e.beta2, eps=e.eps,
                           weight_decay=e.weight_decay, step=e.step_count + 1, adamw=e.adamw,
@@ -57,6 +64,15 @@ class FusedFsdpComm:
         fused_ops.all_gather(self.arena, u.flat_param.arena_offset, u.shard_numel * esz,
                              src_flags_off=self.param_flags[idx], epoch=e.step_count + 1,
                              ctas=_TAIL_AG_CTAS if tail else _AG_CTAS)
+
+    def gather_shards(self, idx: int, dst, tail: bool = False) -> None:
+        """Resharded unit: every rank's persistent shard -> the local slot ``dst``.  A peer's shard
+        is read once its ``param_ready`` flag shows the update of the last completed step."""
+        e, u = self.e, self.e.units[idx]
+        esz = u.persist.element_size()
+        fused_ops.shard_gather(self.arena, u.persist.arena_offset, dst, u.shard_numel * esz,
+                               src_flags_off=self.param_flags[idx], epoch=e.step_count,
+                               ctas=_TAIL_AG_CTAS if tail else _AG_CTAS)
 
     def end_step(self) -> None:
         pass

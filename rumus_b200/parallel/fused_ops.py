@@ -15,6 +15,7 @@ native.register_signature("rb_rs_adam", [I, P, P, I, I, LL, LL, LL, LL, P, P, P,
                                          I, P, P, LL, LL, I, P, I, I, P])
 native.register_signature("rb_signal_peers", [P, I, I, LL, I, P])
 native.register_signature("rb_all_gather", [P, I, I, LL, LL, LL, P, LL, I, I, P])
+native.register_signature("rb_shard_gather", [P, I, I, LL, P, LL, LL, I, I, P])
 native.register_signature("rb_allreduce_unscale", [I, P, P, I, I, LL, LL, LL, LL, LL, I, P, F, P, P,
                                                    I, I, P])
 native.register_signature("rb_ag_gemm", [I, P, I, I, LL, LL, LL, P, LL, I, I, LL, P, LL, I, I, I, I,
@@ -51,6 +52,16 @@ def all_gather(arena: SymmArena, buf_off: int, shard_bytes: int, *, src_flags_of
     rc = L.rb_all_gather(arena.bases(), arena.world, arena.rank, buf_off, shard_bytes, src_flags_off,
                          ptr(chunk_flags), chunk_bytes, epoch, ctas, stream_ptr())
     check(rc, "rb_all_gather")
+    count_launch(2 if src_flags_off >= 0 else 1)
+
+
+def shard_gather(arena: SymmArena, src_off: int, dst: torch.Tensor, shard_bytes: int, *,
+                 src_flags_off: int = -1, epoch: int = 0, ctas: int = 16):
+    """Every rank's shard buffer (arena offset ``src_off``) -> local ``dst`` (world * shard_bytes)."""
+    assert dst.is_contiguous() and dst.numel() * dst.element_size() >= arena.world * shard_bytes
+    rc = native.lib().rb_shard_gather(arena.bases(), arena.world, arena.rank, src_off, ptr(dst), shard_bytes,
+                                      src_flags_off, epoch, ctas, stream_ptr())
+    check(rc, "rb_shard_gather")
     count_launch(2 if src_flags_off >= 0 else 1)
 
 

@@ -35,3 +35,14 @@ def test_context_parallel_attention_matches_full_sequence():
     r = _run(os.path.join(ROOT, "tests", "multi_gpu", "cp_checks.py"), n)
     assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-4000:]
     assert "ALL CP CHECKS PASSED" in r.stdout
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2,
+                    reason="needs >= 2 GPUs")
+@pytest.mark.skipif(os.environ.get("RB_TEST_RESHARD", "0") != "1",
+                    reason="resharded FSDP on GPUs is opt-in until it has been seen passing once")
+def test_fsdp_reshard_after_forward_matches_resident_flow():
+    n = min(torch.cuda.device_count(), 4)
+    r = _run(os.path.join(ROOT, "tests", "multi_gpu", "reshard_checks.py"), n)
+    assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-4000:]
+    assert "ALL RESHARD CHECKS PASSED" in r.stdout
