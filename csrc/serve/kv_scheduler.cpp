@@ -228,6 +228,28 @@ int rbs_block_table(void* h, long long id, int* out, int max_blocks) {
   return (int)it->second.blocks.size();
 }
 
+// Block tables of `n` sequences at once, into a row-major int32 [n, max_blocks] array (unused
+// entries zero); `counts[i]` receives the number of blocks of sequence i (-1 if unknown).  One call
+// per decode step instead of one per sequence.
+int rbs_block_tables(void* h, const long long* ids, int n, int* out, int max_blocks, int* counts) {
+  Engine* e = static_cast<Engine*>(h);
+  std::lock_guard<std::mutex> lk(e->mu);
+  std::memset(out, 0, sizeof(int) * (size_t)n * (size_t)max_blocks);
+  int missing = 0;
+  for (int i = 0; i < n; ++i) {
+    auto it = e->seqs.find(ids[i]);
+    if (it == e->seqs.end()) {
+      counts[i] = -1;
+      ++missing;
+      continue;
+    }
+    const int nb = std::min((int)it->second.blocks.size(), max_blocks);
+    std::memcpy(out + (size_t)i * max_blocks, it->second.blocks.data(), sizeof(int) * nb);
+    counts[i] = (int)it->second.blocks.size();
+  }
+  return missing;
+}
+
 // Context length (tokens whose KV is cached, counting generated ones) of a sequence.
 int rbs_context_len(void* h, long long id) {
   Engine* e = static_cast<Engine*>(h);

@@ -54,6 +54,7 @@ class Scheduler:
         L.rbs_commit.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                  c_void_p, c_int]
         L.rbs_block_table.argtypes = [c_void_p, c_longlong, c_void_p, c_int]
+        L.rbs_block_tables.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]
         L.rbs_context_len.argtypes = [c_void_p, c_longlong]
         L.rbs_abort.argtypes = [c_void_p, c_longlong]
         for n in ("rbs_num_free_blocks", "rbs_num_waiting", "rbs_num_running"):
@@ -98,6 +99,18 @@ class Scheduler:
         out = (c_int * max_blocks)()
         n = self.L.rbs_block_table(self.h, rid, out, max_blocks)
         return [out[i] for i in range(max(0, min(n, max_blocks)))]
+
+    def block_tables(self, rids: List[int], max_blocks: int, pin: bool = False) -> torch.Tensor:
+        """Block tables of several sequences as one int32 ``[len(rids), max_blocks]`` tensor (unused
+        entries zero), filled by a single native call."""
+        n = len(rids)
+        out = torch.empty((n, max_blocks), dtype=torch.int32, pin_memory=pin)
+        counts = (c_int * n)()
+        ids = (c_longlong * n)(*rids)
+        missing = self.L.rbs_block_tables(self.h, ids, n, c_void_p(out.data_ptr()), max_blocks, counts)
+        if missing:
+            raise KeyError(f"{missing} unknown sequence id(s) in {rids}")
+        return out
 
     def context_len(self, rid: int) -> int:
         return self.L.rbs_context_len(self.h, rid)
@@ -423,15 +436,15 @@ class Engine:
             ctx = [len(self.requests[r].prompt) + len(self.requests[r].output) for r in decode_ids]
             toks = torch.tensor(last, dtype=torch.int64, device=dev)
             pos = torch.tensor([c - 1 for c in ctx], dtype=torch.int64, device=dev)
-            tables = torch.zeros((B, self.max_blocks), dtype=torch.int32)
-            slots = []
             bs = self.cfg.block_size
-            for i, r in enumerate(decode_ids):
-                t = self.sched.block_table(r, self.max_blocks)
-                tables[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
-                slots.append(t[(ctx[i] - 1) // bs] * bs + (ctx[i] - 1) % bs)
-            tables = tables.to(dev)
-            slots_t = torch.tensor(slots, dtype=torch.int64, device=dev)
+            pin = dev.type == "cuda"
+            tables_h = self.sched.block_tables(decode_ids, self.max_blocks, pin=pin)
+            last_pos = torch.tensor(ctx, dtype=torch.int64) - 1
+            # cache slot of each sequence's newest token: its block's id * block size + offset
+            slots_h = (tables_h.gather(1, (last_pos // bs)[:, None]).squeeze(1).to(torch.int64) * bs
+                       + last_pos % bs)
+            tables = tables_h.to(dev, non_blocking=pin)
+            slots_t = slots_h.to(dev)
             ctx_t = torch.tensor(ctx, dtype=torch.int32, device=dev)
             max_ctx = max(ctx)
 

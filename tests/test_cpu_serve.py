@@ -101,3 +101,21 @@ def test_http_api_shape():
             worker.stop()
 
     asyncio.run(go())
+
+
+def test_batched_block_tables_match_per_sequence_tables():
+    from rumus_b200.serve.engine import Scheduler
+    s = Scheduler(256, 16, 8, 512)
+    for r, plen in enumerate((40, 17, 130, 64), start=1):
+        assert s.add(r, plen, 32) == 0
+    for _ in range(6):
+        dec, pre = s.schedule()
+        s.commit(dec, pre)
+    ids = [4, 1, 3, 2]
+    t = s.block_tables(ids, 24)
+    assert t.shape == (4, 24) and t.dtype == torch.int32
+    for i, r in enumerate(ids):
+        bt = s.block_table(r, 24)
+        assert len(bt) > 0 and t[i, :len(bt)].tolist() == bt and int(t[i, len(bt):].sum()) == 0
+    with pytest.raises(KeyError):
+        s.block_tables([1, 99], 24)
