@@ -95,18 +95,20 @@ class SGD(Optimizer):
         if self.skip_flag is not None and int(self.skip_flag.item()) != 0:
             return
         gs = float(self.grad_scale.item()) if self.grad_scale is not None else 1.0
-        for p in act:
-            g = p.grad.float() * gs
-            m = self._master_of(p)
-            if self.weight_decay:
-                g = g + self.weight_decay * m
-            if self.momentum != 0.0:
-                v = self.velocity[p]
-                v.mul_(self.momentum).add_(g)
-                g = v
-            m.sub_(self.lr * g)
+        # CPU tensors: multi-tensor form of the same update
+        gr = [p.grad if (p.grad.dtype == torch.float32 and gs == 1.0) else p.grad.float() * gs for p in act]
+        ws = [self._master_of(p) for p in act]
+        if self.weight_decay:
+            gr = torch._foreach_add(gr, ws, alpha=self.weight_decay)
+        if self.momentum != 0.0:
+            vs = [self.velocity[p] for p in act]
+            torch._foreach_mul_(vs, self.momentum)
+            torch._foreach_add_(vs, gr)
+            gr = vs
+        torch._foreach_add_(ws, gr, alpha=-self.lr)
+        for p, w in zip(act, ws):
             if p.dtype != torch.float32:
-                p.data.copy_(m)
+                p.data.copy_(w)
 
     def state_dict(self):
         sd = super().state_dict()
@@ -158,14 +160,23 @@ class Adam(Optimizer):
             return
         gs = float(self.grad_scale.item()) if self.grad_scale is not None else 1.0
         bc1, bc2 = 1.0 - self.beta1 ** t, 1.0 - self.beta2 ** t
-        for p in act:
-            g = p.grad.float() * gs
-            m, v, w = self.first_moment[p], self.second_moment[p], self._master_of(p)
-            m.mul_(self.beta1).add_(g, alpha=1 - self.beta1)
-            v.mul_(self.beta2).addcmul_(g, g, value=1 - self.beta2)
-            if self._decoupled:
-                w.mul_(1 - self.lr * self.weight_decay)
-            w.sub_(self.lr * (m / bc1) / ((v / bc2).sqrt() + self.epsilon))
+        # CPU tensors: the same update over all parameters at once (multi-tensor ops; one Python
+        # call per operation instead of one per operation and parameter)
+        gr = [p.grad if (p.grad.dtype == torch.float32 and gs == 1.0) else p.grad.float() * gs for p in act]
+        ms = [self.first_moment[p] for p in act]
+        vs = [self.second_moment[p] for p in act]
+        ws = [self._master_of(p) for p in act]
+        torch._foreach_mul_(ms, self.beta1)
+        torch._foreach_add_(ms, gr, alpha=1 - self.beta1)
+        torch._foreach_mul_(vs, self.beta2)
+        torch._foreach_addcmul_(vs, gr, gr, value=1 - self.beta2)
+        if self._decoupled:
+            torch._foreach_mul_(ws, 1 - self.lr * self.weight_decay)
+        den = torch._foreach_div(vs, bc2)
+        torch._foreach_sqrt_(den)
+        torch._foreach_add_(den, self.epsilon)
+        torch._foreach_addcdiv_(ws, ms, den, value=-self.lr / bc1)     # w -= lr * (m / bc1) / den
+        for p, w in zip(act, ws):
             if p.dtype != torch.float32:
                 p.data.copy_(w)
 
