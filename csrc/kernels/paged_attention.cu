@@ -5,8 +5,9 @@
 // (rumus-serve/src/model.rs:14-142) and scans the vocabulary on the CPU for the argmax
 // (rumus-serve/src/scheduler.rs:101-135); none of these kernels has a counterpart there.
 //
-// Cache layout: k_cache / v_cache [num_blocks, block_size, Hkv, D]; a sequence's logical token t
-// lives in physical block block_table[b][t / block_size] at offset t % block_size.
+// Cache layout: k_cache / v_cache [num_blocks, block_size, Hkv, D] (token-major) or, in the `_hm`
+// entry points, [num_blocks, Hkv, block_size, D] (head-major); a sequence's logical token t lives in
+// physical block block_table[b][t / block_size] at offset t % block_size.
 #include "sm100_common.cuh"
 
 namespace rb {
@@ -31,7 +32,10 @@ __device__ __forceinline__ void pa_load16(const T* p, float* f) {
   }
 }
 
-template <typename T>
+// HM = head-major cache [num_blocks, Hkv, block_size, D]: one head's tokens of a block are
+// contiguous (block_size * 256 B), so the four tokens a warp reads per trip are one 1 KiB run
+// instead of four 256-byte pieces a whole token row (Hkv * 256 B) apart.
+template <typename T, bool HM = false>
 __global__ void __launch_bounds__(kPaWarps * 32)
     paged_decode_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
                              const T* __restrict__ v_cache, const int* __restrict__ block_tables,
@@ -58,7 +62,10 @@ __global__ void __launch_bounds__(kPaWarps * 32)
   const int* table = block_tables + (long long)b * max_blocks;
   auto row_base = [&](int t) -> long long {
     const int blk = table[t / block_size];
-    return (((long long)blk * block_size + (t % block_size)) * Hkv + hkv) * D + sub * 16;
+    if constexpr (HM)
+      return (((long long)blk * Hkv + hkv) * block_size + (t % block_size)) * D + sub * 16;
+    else
+      return (((long long)blk * block_size + (t % block_size)) * Hkv + hkv) * D + sub * 16;
   };
   // every lane runs every trip (the shuffles are warp wide); out-of-range tokens are skipped
   for (int tb = t0; tb < t1; tb += 2 * G) {
@@ -168,6 +175,31 @@ __global__ void kv_append_kernel(const T* __restrict__ k_src, const T* __restric
   }
 }
 
+// Head-major cache: cache[slot / bs, hkv, slot % bs, :] = src[t, hkv, :]
+template <typename T>
+__global__ void kv_append_hm_kernel(const T* __restrict__ k_src, const T* __restrict__ v_src,
+                                    long long src_stride, const long long* __restrict__ slots,
+                                    T* __restrict__ k_cache, T* __restrict__ v_cache, int tokens, int Hkv,
+                                    int D, int block_size) {
+  const int vecs_per_head = D / 8;
+  const int vecs = Hkv * vecs_per_head;
+  const long long total = (long long)tokens * vecs;
+  const long long gs = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gs) {
+    const int t = (int)(i / vecs);
+    const int r = (int)(i - (long long)t * vecs);
+    const int hkv = r / vecs_per_head;
+    const int c = (r - hkv * vecs_per_head) * 8;
+    const long long slot = slots[t];
+    if (slot < 0) continue;
+    const long long blk = slot / block_size, off = slot % block_size;
+    const long long dst = ((blk * Hkv + hkv) * block_size + off) * D + c;
+    const long long src = t * src_stride + (long long)hkv * D + c;
+    *reinterpret_cast<uint4*>(k_cache + dst) = *reinterpret_cast<const uint4*>(k_src + src);
+    *reinterpret_cast<uint4*>(v_cache + dst) = *reinterpret_cast<const uint4*>(v_src + src);
+  }
+}
+
 // out_idx[r] = argmax_c x[r, c] (first maximum), out_val[r] = the maximum
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -250,6 +282,53 @@ int rb_kv_append(int dtype, const void* k_src, const void* v_src, long long src_
     kv_append_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)k_src, (const __nv_bfloat16*)v_src, src_stride, slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tokens, row_elems);
   else if (dtype == rbh::DT_F16)
     kv_append_kernel<__half><<<blocks, 256, 0, st>>>((const __half*)k_src, (const __half*)v_src, src_stride, slots, (__half*)k_cache, (__half*)v_cache, tokens, row_elems);
+  else
+    return 20;
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
+}
+
+// Head-major variants (cache [num_blocks, Hkv, block_size, 128]); same arguments otherwise.
+int rb_paged_decode_attn_hm(int dtype, const void* q, const void* k_cache, const void* v_cache,
+                            const int* block_tables, const int* ctx_lens, void* out, float* scratch_o,
+                            float* scratch_ml, int B, int H, int Hkv, int head_dim, int block_size,
+                            int max_blocks, int splits, float scale, void* stream) {
+  using namespace rb;
+  if (head_dim != 128) return 20;
+  if (B <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid(H, B, splits);
+  const float sl2 = scale * 1.4426950408889634f;
+  if (dtype == rbh::DT_BF16) {
+    paged_decode_attn_kernel<__nv_bfloat16, true><<<grid, kPaWarps * 32, 0, st>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+        block_tables, ctx_lens, scratch_o, scratch_ml, H, Hkv, block_size, max_blocks, splits, sl2);
+    paged_decode_reduce_kernel<__nv_bfloat16><<<B * H, 128, 0, st>>>(scratch_o, scratch_ml, (__nv_bfloat16*)out, splits);
+  } else if (dtype == rbh::DT_F16) {
+    paged_decode_attn_kernel<__half, true><<<grid, kPaWarps * 32, 0, st>>>(
+        (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, block_tables, ctx_lens,
+        scratch_o, scratch_ml, H, Hkv, block_size, max_blocks, splits, sl2);
+    paged_decode_reduce_kernel<__half><<<B * H, 128, 0, st>>>(scratch_o, scratch_ml, (__half*)out, splits);
+  } else {
+    return 20;
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
+}
+
+int rb_kv_append_hm(int dtype, const void* k_src, const void* v_src, long long src_stride,
+                    const long long* slots, void* k_cache, void* v_cache, int tokens, int Hkv, int D,
+                    int block_size, void* stream) {
+  using namespace rb;
+  if (tokens <= 0) return 0;
+  if (D % 8 != 0 || src_stride % 8 != 0) return 21;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long total = (long long)tokens * Hkv * (D / 8);
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == rbh::DT_BF16)
+    kv_append_hm_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)k_src, (const __nv_bfloat16*)v_src, src_stride, slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tokens, Hkv, D, block_size);
+  else if (dtype == rbh::DT_F16)
+    kv_append_hm_kernel<__half><<<blocks, 256, 0, st>>>((const __half*)k_src, (const __half*)v_src, src_stride, slots, (__half*)k_cache, (__half*)v_cache, tokens, Hkv, D, block_size);
   else
     return 20;
   cudaError_t e = cudaGetLastError();

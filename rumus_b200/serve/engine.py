@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 import time
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from dataclasses import dataclass, field
@@ -37,6 +38,8 @@ P, LL, I, Fl = c_void_p, c_longlong, c_int, c_float
 native.register_signature("rb_paged_decode_splits", [I])
 native.register_signature("rb_paged_decode_attn", [I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, Fl, P])
 native.register_signature("rb_kv_append", [I, P, P, LL, P, P, P, I, I, P])
+native.register_signature("rb_paged_decode_attn_hm", [I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, Fl, P])
+native.register_signature("rb_kv_append_hm", [I, P, P, LL, P, P, P, I, I, I, I, P])
 native.register_signature("rb_argmax", [I, P, LL, I, I, P, P, P])
 
 
@@ -140,6 +143,10 @@ class ServeConfig:
     dtype: torch.dtype = torch.bfloat16
     scale_dtype: torch.dtype = torch.float16
     comm_mode: str = "nccl"
+    # KV cache layout: False = [blocks, block_size, Hkv, D] (a token's heads together), True =
+    # [blocks, Hkv, block_size, D] (a head's tokens together: long contiguous reads in decode
+    # attention).  Opt-in until measured on hardware.
+    kv_head_major: bool = field(default_factory=lambda: os.environ.get("RB_KV_HEAD_MAJOR", "0") == "1")
 
 
 class _Layer:
@@ -199,49 +206,73 @@ class PagedKVCache:
     def __init__(self, cfg: ServeConfig, hkv_local: int, hd: int, device):
         n, bs = cfg.num_blocks, cfg.block_size
         self.block_size = bs
-        self.k = [torch.zeros((n, bs, hkv_local, hd), dtype=cfg.dtype, device=device)
-                  for _ in range(cfg.model.num_layers)]
-        self.v = [torch.zeros((n, bs, hkv_local, hd), dtype=cfg.dtype, device=device)
-                  for _ in range(cfg.model.num_layers)]
+        self.head_major = bool(cfg.kv_head_major)
+        self.hkv, self.hd = hkv_local, hd
+        shape = (n, hkv_local, bs, hd) if self.head_major else (n, bs, hkv_local, hd)
+        self.k = [torch.zeros(shape, dtype=cfg.dtype, device=device) for _ in range(cfg.model.num_layers)]
+        self.v = [torch.zeros(shape, dtype=cfg.dtype, device=device) for _ in range(cfg.model.num_layers)]
 
     def append(self, layer: int, k_src, v_src, slots):
         """k_src/v_src: [T, Hkv*D] row views (possibly strided); slots: int64 [T]."""
         kc, vc = self.k[layer], self.v[layer]
-        row = kc.shape[2] * kc.shape[3]
+        row = self.hkv * self.hd
         if k_src.is_cuda:
-            check(native.lib().rb_kv_append(native.dtype_code(kc.dtype), ptr(k_src), ptr(v_src),
-                                            k_src.stride(0), ptr(slots), ptr(kc), ptr(vc),
-                                            k_src.shape[0], row, stream_ptr()), "rb_kv_append")
+            if self.head_major:
+                check(native.lib().rb_kv_append_hm(native.dtype_code(kc.dtype), ptr(k_src), ptr(v_src),
+                                                   k_src.stride(0), ptr(slots), ptr(kc), ptr(vc),
+                                                   k_src.shape[0], self.hkv, self.hd, self.block_size,
+                                                   stream_ptr()), "rb_kv_append_hm")
+            else:
+                check(native.lib().rb_kv_append(native.dtype_code(kc.dtype), ptr(k_src), ptr(v_src),
+                                                k_src.stride(0), ptr(slots), ptr(kc), ptr(vc),
+                                                k_src.shape[0], row, stream_ptr()), "rb_kv_append")
             count_launch()
+        elif self.head_major:
+            blk, off = slots // self.block_size, slots % self.block_size
+            T = k_src.shape[0]
+            kc[blk, :, off] = k_src.reshape(T, self.hkv, self.hd)
+            vc[blk, :, off] = v_src.reshape(T, self.hkv, self.hd)
         else:
             kc.view(-1, row)[slots] = k_src
             vc.view(-1, row)[slots] = v_src
 
+    def gather(self, layer: int, table: torch.Tensor, positions: torch.Tensor):
+        """K and V ``[len(positions), Hkv, D]`` of logical token ``positions`` of the sequence whose
+        block table is ``table``."""
+        blk, off = table[positions // self.block_size], positions % self.block_size
+        if self.head_major:
+            return self.k[layer][blk, :, off], self.v[layer][blk, :, off]
+        return self.k[layer][blk, off], self.v[layer][blk, off]
 
-def paged_decode_attention(q, k_cache, v_cache, block_tables, ctx_lens, scale: float, max_ctx: int):
-    """q [B, H, D]; returns [B, H, D]."""
+
+def paged_decode_attention(q, k_cache, v_cache, block_tables, ctx_lens, scale: float, max_ctx: int,
+                           head_major: bool = False):
+    """q [B, H, D]; returns [B, H, D].  ``head_major``: cache is [blocks, Hkv, block_size, D]."""
     B, H, D = q.shape
-    Hkv = k_cache.shape[2]
+    Hkv = k_cache.shape[1] if head_major else k_cache.shape[2]
+    bs = k_cache.shape[2] if head_major else k_cache.shape[1]
     if q.is_cuda:
         L = native.lib()
         splits = L.rb_paged_decode_splits(int(max_ctx))
         so = torch.empty((B, H, splits, D), dtype=torch.float32, device=q.device)
         sml = torch.empty((B, H, splits, 2), dtype=torch.float32, device=q.device)
         out = torch.empty_like(q)
-        check(L.rb_paged_decode_attn(native.dtype_code(q.dtype), ptr(q), ptr(k_cache), ptr(v_cache),
-                                     ptr(block_tables), ptr(ctx_lens), ptr(out), ptr(so), ptr(sml), B, H,
-                                     Hkv, D, k_cache.shape[1], block_tables.shape[1], splits,
-                                     float(scale), stream_ptr()), "rb_paged_decode_attn")
+        fn = L.rb_paged_decode_attn_hm if head_major else L.rb_paged_decode_attn
+        check(fn(native.dtype_code(q.dtype), ptr(q), ptr(k_cache), ptr(v_cache),
+                 ptr(block_tables), ptr(ctx_lens), ptr(out), ptr(so), ptr(sml), B, H,
+                 Hkv, D, bs, block_tables.shape[1], splits,
+                 float(scale), stream_ptr()), "rb_paged_decode_attn")
         count_launch(2)
         return out
     outs = []
-    bs = k_cache.shape[1]
     for b in range(B):
         n = int(ctx_lens[b])
         idx = torch.arange(n)
         blk = block_tables[b, idx // bs].long()
-        kk = k_cache[blk, idx % bs].float()   # [n, Hkv, D]
-        vv = v_cache[blk, idx % bs].float()
+        if head_major:
+            kk, vv = k_cache[blk, :, idx % bs].float(), v_cache[blk, :, idx % bs].float()
+        else:
+            kk, vv = k_cache[blk, idx % bs].float(), v_cache[blk, idx % bs].float()   # [n, Hkv, D]
         rep = H // Hkv
         kk, vv = kk.repeat_interleave(rep, 1), vv.repeat_interleave(rep, 1)
         s = torch.einsum("hd,nhd->hn", q[b].float(), kk) * scale
@@ -420,8 +451,7 @@ class Engine:
                 # continuation chunk: keys/values of the prefix come from the paged cache
                 idx = torch.arange(0, start + n, device=dev)
                 bs = self.cfg.block_size
-                kk = self.cache.k[li][table[idx // bs], idx % bs]
-                vv = self.cache.v[li][table[idx // bs], idx % bs]
+                kk, vv = self.cache.gather(li, table, idx)
                 return F.flash_attention(q[None], kk[None], vv[None], True, scale)[0]
 
             with trace_range("serve.prefill_chunk"):
@@ -450,7 +480,7 @@ class Engine:
 
             def attend_dec(li, q, k, v):
                 return paged_decode_attention(q.contiguous(), self.cache.k[li], self.cache.v[li], tables,
-                                              ctx_t, scale, max_ctx)
+                                              ctx_t, scale, max_ctx, head_major=self.cache.head_major)
 
             with trace_range("serve.decode_batch"):
                 hidden = self._forward(toks, pos, slots_t, attend_dec)

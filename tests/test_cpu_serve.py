@@ -47,10 +47,14 @@ def test_scheduler_blocks_are_conserved():
     assert s.free_blocks() == 8 and s.num_running() == 0 and s.num_waiting() == 0
 
 
-def test_continuous_batching_matches_sequential_and_chunked_prefill():
+@pytest.mark.parametrize("head_major", [False, True])
+def test_continuous_batching_matches_sequential_and_chunked_prefill(head_major):
     r = random.Random(0)
     reqs = {i + 1: ([r.randrange(256) for _ in range(r.randint(5, 150))], r.randint(3, 10)) for i in range(6)}
-    e = Engine(_cfg())          # token budget 64 < some prompts -> chunked prefill is exercised
+    # token budget 64 < some prompts -> chunked prefill is exercised; the batched engine runs with
+    # either KV-cache layout, the sequential one always with the token-major layout
+    e = Engine(_cfg(kv_head_major=head_major))
+    assert e.cache.head_major == head_major and e.cache.k[0].shape == ((64, 1, 16, 128) if head_major else (64, 16, 1, 128))
     for rid, (p, n) in reqs.items():
         assert e.add_request(rid, p, n)
     batched = _drain(e)
@@ -119,3 +123,29 @@ def test_batched_block_tables_match_per_sequence_tables():
         assert len(bt) > 0 and t[i, :len(bt)].tolist() == bt and int(t[i, len(bt):].sum()) == 0
     with pytest.raises(KeyError):
         s.block_tables([1, 99], 24)
+
+
+def test_head_major_kv_cache_gives_the_same_attention():
+    """The two cache layouts hold the same data: append, gather and decode attention agree
+    (two KV heads, grouped queries, tokens spread over non-adjacent blocks)."""
+    from rumus_b200.serve.engine import PagedKVCache, paged_decode_attention
+    mc = LlamaConfig(vocab_size=64, seq_len=64, d_model=512, num_heads=4, num_kv_heads=2, num_layers=1, ffn_dim=64)
+    torch.manual_seed(0)
+    T, Hkv, D, bs = 37, 2, 128, 8
+    k_src, v_src = torch.randn(T, Hkv * D), torch.randn(T, Hkv * D)
+    table = torch.tensor([5, 2, 9, 0, 7], dtype=torch.int64)
+    pos = torch.arange(T)
+    slots = table[pos // bs] * bs + pos % bs
+    outs = []
+    for hm in (False, True):
+        cfg = ServeConfig(model=mc, num_blocks=12, block_size=bs, max_batch=2, token_budget=64,
+                          dtype=torch.float32, scale_dtype=torch.float32, kv_head_major=hm)
+        cache = PagedKVCache(cfg, Hkv, D, torch.device("cpu"))
+        cache.append(0, k_src, v_src, slots)
+        kk, vv = cache.gather(0, table, pos)
+        assert torch.equal(kk.reshape(T, -1), k_src) and torch.equal(vv.reshape(T, -1), v_src)
+        q = torch.randn(2, 4, D, generator=torch.Generator().manual_seed(1))
+        tables = torch.stack([table, table]).to(torch.int32)
+        ctx = torch.tensor([T, 20], dtype=torch.int32)
+        outs.append(paged_decode_attention(q, cache.k[0], cache.v[0], tables, ctx, 0.1, T, head_major=hm))
+    assert torch.allclose(outs[0], outs[1], atol=1e-6)
