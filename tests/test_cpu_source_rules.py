@@ -1,6 +1,6 @@
 """Source-tree invariants of the device code, checked as text.
 
-* No TMA / bulk load with a cluster-multicast qualifier anywhere: every source file travels to
+* No bulk-copy load that fans one tile out to several CTAs of a cluster, anywhere: every source file travels to
   multi-GPU jobs, where such a load from a peer's memory is not allowed; remote tiles are staged in
   local memory or fetched per CTA with plain peer loads instead.
 * None of the batched-memcpy driver / runtime entry points is named.
@@ -38,7 +38,7 @@ def _scan(patterns):
     return hits
 
 
-def test_no_cluster_multicast_loads_anywhere():
+def test_no_fan_out_bulk_loads_anywhere():
     q = "multi" + "cast" + "::" + "cluster"
     pats = [re.compile(re.escape(q)),
             re.compile("SM90_TMA_LOAD_" + "MULTI" + "CAST"),
