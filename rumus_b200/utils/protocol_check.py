@@ -143,3 +143,41 @@ def allreduce_programs(world: int, steps: int, exit_barrier: bool = True) -> Lis
                 p.append(("end_read", f"bucket{r}.slice{s}"))
         progs.append(p)
     return progs
+
+
+def fsdp_reshard_programs(world: int, steps: int, wait_param_flags: bool = True,
+                          wait_grad_flags: bool = True) -> List[List[Action]]:
+    """One unit of the FSDP step with parameters resharded between uses (``shard_gather_kernel`` in
+    ``csrc/comm/fsdp_comm.cu``): at step ``t`` a rank pulls every peer's persistent shard twice
+    (for the forward and again for the backward) once the peer's ``param_ready`` flag shows the
+    update of step ``t-1``, then announces its gradients, waits for every announcement, reduces its
+    slice, overwrites its own shard and announces ``param_ready = t``.  The gathered copies live in
+    local memory and are not modelled.  What keeps a rank from overwriting its shard while a slow
+    peer is still gathering it is the gradient announcement: a peer only announces after its
+    backward, which comes after its second gather."""
+    progs: List[List[Action]] = []
+    for r in range(world):
+        p: List[Action] = []
+        for t in range(1, steps + 1):
+            for _use in ("forward", "backward"):
+                for q in range(world):
+                    if q == r:
+                        continue
+                    if wait_param_flags:
+                        p.append(("wait", f"param_ready[{r}][{q}]", t - 1))
+                    p.append(("begin_read", f"shard{q}", t - 1))
+                    p.append(("end_read", f"shard{q}"))
+            p.append(("write", f"grad{r}", t))
+            for q in range(world):
+                p.append(("set", f"grad_ready[{q}][{r}]", t))
+            if wait_grad_flags:
+                for q in range(world):
+                    p.append(("wait", f"grad_ready[{r}][{q}]", t))
+            for q in range(world):
+                p.append(("begin_read", f"grad{q}", t))
+                p.append(("end_read", f"grad{q}"))
+            p.append(("write", f"shard{r}", t))
+            for q in range(world):
+                p.append(("set", f"param_ready[{q}][{r}]", t))
+        progs.append(p)
+    return progs

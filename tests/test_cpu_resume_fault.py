@@ -145,7 +145,7 @@ def test_flag_protocols_hold_on_every_interleaving():
     over two steps), and proof that the checker sees the hazard once a wait is taken out."""
     import pytest
     from rumus_b200.utils.protocol_check import (ProtocolViolation, allreduce_programs, explore,
-                                                 fsdp_unit_programs)
+                                                 fsdp_reshard_programs, fsdp_unit_programs)
     assert explore(fsdp_unit_programs(2, 2)) > 100
     assert explore(fsdp_unit_programs(3, 2)) > 1000
     assert explore(allreduce_programs(2, 2)) > 100
@@ -155,6 +155,14 @@ def test_flag_protocols_hold_on_every_interleaving():
         explore(fsdp_unit_programs(2, 2, wait_grad_flags=False))    # gradient read before the write
     with pytest.raises(ProtocolViolation):
         explore(allreduce_programs(2, 2, exit_barrier=False))       # reads a half-reduced bucket
+    # parameters resharded between uses: shards are gathered twice per step and overwritten after
+    # the gradient exchange; no extra barrier is needed, and each wait is necessary
+    assert explore(fsdp_reshard_programs(2, 3)) > 500
+    assert explore(fsdp_reshard_programs(3, 2)) > 10000
+    with pytest.raises(ProtocolViolation):
+        explore(fsdp_reshard_programs(2, 2, wait_param_flags=False))  # gathers a shard before its update
+    with pytest.raises(ProtocolViolation):
+        explore(fsdp_reshard_programs(2, 2, wait_grad_flags=False))
     # a rank that never publishes one of its flags: the model deadlocks (on the device the bounded
     # wait turns that into a status code instead)
     progs = fsdp_unit_programs(2, 1)
