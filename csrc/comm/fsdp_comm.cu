@@ -480,6 +480,18 @@ int rb_signal_peers(void* const* bases, int world, int rank, long long flags_off
   return e == cudaSuccess ? 0 : 3000 + (int)e;
 }
 
+// Group barrier on the stream: publish `epoch` in slot [rank] of every rank's flag array at
+// `flags_off`, then wait (bounded) until every rank's slot in the local array has reached it.  One warp.
+int rb_group_barrier(void* const* bases, int world, int rank, long long flags_off, int epoch,
+                     void* stream) {
+  using namespace rb;
+  if (world > kMaxRanks) return 30;
+  flag_gate_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(make_table(bases, nullptr, world, rank), flags_off,
+                                                      epoch, 1, rbh::device_status_word());
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
+}
+
 int rb_all_gather(void* const* bases, int world, int rank, long long buf_off, long long shard_bytes,
                   long long src_flags_off, int* chunk_flags, long long chunk_bytes, int epoch,
                   int ctas, void* stream) {

@@ -14,6 +14,7 @@ P, LL, I, F = c_void_p, c_longlong, c_int, c_float
 native.register_signature("rb_rs_adam", [I, P, P, I, I, LL, LL, LL, LL, P, P, P, F, F, F, F, F, F, F,
                                          I, P, P, LL, LL, I, P, I, I, P])
 native.register_signature("rb_signal_peers", [P, I, I, LL, I, P])
+native.register_signature("rb_group_barrier", [P, I, I, LL, I, P])
 native.register_signature("rb_all_gather", [P, I, I, LL, LL, LL, P, LL, I, I, P])
 native.register_signature("rb_shard_gather", [P, I, I, LL, P, LL, LL, I, I, P])
 native.register_signature("rb_allreduce_unscale", [I, P, P, I, I, LL, LL, LL, LL, LL, I, P, F, P, P,
@@ -42,6 +43,13 @@ def signal_peers(arena: SymmArena, flags_off: int, epoch: int):
     """Stream-ordered: write ``epoch`` into slot ``[rank]`` of every peer's flag array."""
     check(native.lib().rb_signal_peers(arena.bases(), arena.world, arena.rank, flags_off, epoch,
                                        stream_ptr()), "rb_signal_peers")
+    count_launch()
+
+
+def group_barrier(arena: SymmArena, flags_off: int, epoch: int):
+    """Stream-ordered barrier over the arena's ranks (one-warp kernel: signal, then bounded wait)."""
+    check(native.lib().rb_group_barrier(arena.bases(), arena.world, arena.rank, flags_off, epoch,
+                                        stream_ptr()), "rb_group_barrier")
     count_launch()
 
 

@@ -62,12 +62,28 @@ class TPContext:
             self.tile_flags_off = a.alloc_flags(n_tiles * self.world)
             self.tile_counters = a.alloc_local_ints(n_tiles)
             self.enter_flags = a.alloc_flags(self.world)
+            self.bar_flags = a.alloc_flags(self.world)
+            self.bar_epoch = 0
             self.stage_bytes = stage_bytes
             a.barrier()
+        self._last_fused = None
 
     def next_epoch(self) -> int:
         self.epoch += 1
         return self.epoch
+
+    def order_fused(self, kind: str) -> None:
+        """Called before a fused operation of ``kind`` ('A' all-gather→GEMM, 'R' GEMM→reduce-scatter).
+        Neither kernel ends with a barrier: reuse of the staging buffers is safe because finishing
+        one kind needs signals that every peer sends only after its preceding operation of the
+        other kind.  Two operations of the same kind in a row do not have that property (checked on
+        the model in ``utils/protocol_check.tp_sequence_programs``), so a group barrier goes between
+        them."""
+        if self._last_fused == kind:
+            from . import fused_ops
+            self.bar_epoch += 1
+            fused_ops.group_barrier(self.arena, self.bar_flags, self.bar_epoch)
+        self._last_fused = kind
 
     # ------------------------------------------------------------ collectives (baseline paths)
     def all_gather_rows(self, x_local: torch.Tensor) -> torch.Tensor:
@@ -111,10 +127,11 @@ def _fused_ag_gemm_impl(ctx: TPContext, x_local, w, bias=None, act=None):
     esz = x_local.element_size()
     shard_bytes = Ml * K * esz
     assert shard_bytes * ctx.world <= ctx.stage_bytes and shard_bytes % 16 == 0
-    # entry barrier on the staging buffer is implied by the epoch protocol: a peer may only read
-    # my shard after I announced it (src flag) and I only overwrite it after everybody consumed the
-    # previous contents, which the reduce/gather pairing of the layer sequence guarantees;
-    # a host-side group barrier guards the first use.
+    # a peer may only read my shard after I announced it (src flag); I only overwrite it after
+    # everybody consumed the previous contents, which the alternation of gather and reduce
+    # operations guarantees and ``order_fused`` enforces otherwise; a host-side group barrier
+    # guards the first use.
+    ctx.order_fused("A")
     stage = ctx.gather_buf[: shard_bytes * ctx.world].view(x_local.dtype).view(M, K)
     stage[ctx.rank * Ml:(ctx.rank + 1) * Ml].copy_(x_local)
     epoch = ctx.next_epoch()
@@ -145,6 +162,7 @@ def _fused_gemm_rs_impl(ctx: TPContext, a_mat, w, bias=None):
     M, K = a_mat.shape
     N = w.shape[1]
     out = torch.empty((M // ctx.world, N), dtype=a_mat.dtype, device=a_mat.device)
+    ctx.order_fused("R")
     epoch = ctx.next_epoch()
     fused_ops.gemm_rs(ctx.arena, a_mat, w, partial_off=ctx.partial_off,
                       tile_flags_off=ctx.tile_flags_off, tile_counters=ctx.tile_counters, epoch=epoch,

@@ -181,3 +181,50 @@ def fsdp_reshard_programs(world: int, steps: int, wait_param_flags: bool = True,
                 p.append(("set", f"param_ready[{q}][{r}]", t))
         progs.append(p)
     return progs
+
+
+def tp_sequence_programs(world: int, ops: str) -> List[List[Action]]:
+    """A sequence of fused tensor-parallel operations on one ``TPContext`` (``parallel/tp.py``,
+    ``csrc/comm/tp_comm.cu``).  ``ops`` is a string over
+
+    * ``A`` — all-gather → GEMM: a rank writes its shard of the staging buffer, announces it, and
+      pulls every peer's shard after that peer's announcement;
+    * ``R`` — GEMM → reduce-scatter: a rank writes partial tiles for every owner into its partial
+      buffer, signals the owners, and as an owner reads its tiles from every peer after their signals;
+    * ``b`` — a group barrier.
+
+    Neither operation ends with a barrier.  Reusing the staging buffer is safe when ``A`` and ``R``
+    alternate (finishing ``R`` needs every peer's tile signal, which a peer sends after its
+    preceding ``A`` has completed, and vice versa); two operations of the same kind in a row need
+    the barrier between them, which ``TPContext`` inserts."""
+    progs: List[List[Action]] = []
+    for r in range(world):
+        p: List[Action] = []
+        for e, op in enumerate(ops, start=1):
+            if op == "A":
+                p.append(("write", f"stage{r}", e))
+                for q in range(world):
+                    p.append(("set", f"enter[{q}][{r}]", e))
+                for q in range(world):
+                    if q == r:
+                        continue
+                    p.append(("wait", f"enter[{r}][{q}]", e))
+                    p.append(("begin_read", f"stage{q}", e))
+                    p.append(("end_read", f"stage{q}"))
+            elif op == "R":
+                for q in range(world):
+                    p.append(("write", f"partial{r}.for{q}", e))
+                    p.append(("set", f"tile[{q}][{r}]", e))
+                for q in range(world):
+                    p.append(("wait", f"tile[{r}][{q}]", e))
+                    p.append(("begin_read", f"partial{q}.for{r}", e))
+                    p.append(("end_read", f"partial{q}.for{r}"))
+            elif op == "b":
+                for q in range(world):
+                    p.append(("set", f"bar[{q}][{r}]", e))
+                for q in range(world):
+                    p.append(("wait", f"bar[{r}][{q}]", e))
+            else:
+                raise ValueError(op)
+        progs.append(p)
+    return progs

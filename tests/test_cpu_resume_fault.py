@@ -145,7 +145,8 @@ def test_flag_protocols_hold_on_every_interleaving():
     over two steps), and proof that the checker sees the hazard once a wait is taken out."""
     import pytest
     from rumus_b200.utils.protocol_check import (ProtocolViolation, allreduce_programs, explore,
-                                                 fsdp_reshard_programs, fsdp_unit_programs)
+                                                 fsdp_reshard_programs, fsdp_unit_programs,
+                                                 tp_sequence_programs)
     assert explore(fsdp_unit_programs(2, 2)) > 100
     assert explore(fsdp_unit_programs(3, 2)) > 1000
     assert explore(allreduce_programs(2, 2)) > 100
@@ -163,6 +164,14 @@ def test_flag_protocols_hold_on_every_interleaving():
         explore(fsdp_reshard_programs(2, 2, wait_param_flags=False))  # gathers a shard before its update
     with pytest.raises(ProtocolViolation):
         explore(fsdp_reshard_programs(2, 2, wait_grad_flags=False))
+    # fused tensor-parallel operations on one context: gather (A) and reduce (R) operations may follow
+    # each other without a barrier only when they alternate; the context inserts one (b) otherwise
+    assert explore(tp_sequence_programs(2, "ARARAR")) > 100
+    assert explore(tp_sequence_programs(3, "RARA")) > 1000
+    assert explore(tp_sequence_programs(3, "AbARbR")) > 1000
+    for bad in ("AA", "RR", "ARRA"):
+        with pytest.raises(ProtocolViolation):
+            explore(tp_sequence_programs(2, bad))
     # a rank that never publishes one of its flags: the model deadlocks (on the device the bounded
     # wait turns that into a status code instead)
     progs = fsdp_unit_programs(2, 1)
