@@ -1,0 +1,44 @@
+"""Host model of the W4A16 kernel's mbarrier pipeline (``rumus_b200/utils/pipeline_model.py``): the
+roles' stage / parity arithmetic under random interleavings, for short and long K ranges and for
+other ring depths; planted defects must be caught."""
+import pytest
+
+from rumus_b200.utils.pipeline_model import Mbar, PipelineError, run, w4a16_roles
+
+
+def test_mbarrier_phase_parity_semantics():
+    b = Mbar(2)
+    assert b.passed(1) and not b.passed(0)        # fresh barrier: "previous" phase counts as complete
+    b.arrive()
+    assert not b.passed(0)
+    b.arrive()
+    assert b.passed(0) and not b.passed(1)        # phase 0 complete, phase 1 running
+    b.arrive(); b.arrive()
+    assert b.passed(1) and not b.passed(0)
+
+
+@pytest.mark.parametrize("nkb", [1, 2, 3, 7, 8, 9, 16, 24, 25, 64, 172])
+def test_w4a16_pipeline_runs_to_completion_under_any_schedule(nkb):
+    for seed in range(25 if nkb < 64 else 4):
+        assert run(w4a16_roles(nkb), seed) > 0
+
+
+def test_w4a16_pipeline_other_ring_depths():
+    for raw_stages, ab_stages in ((2, 1), (3, 2), (8, 3), (4, 6)):
+        for seed in range(10):
+            run(w4a16_roles(20, raw_stages=raw_stages, ab_stages=ab_stages), seed)
+
+
+@pytest.mark.parametrize("bug,what", [("no_stage_wait", "overwritten while the MMA reads it|holds weights"),
+                                      ("raw_count", "deadlock|holds k-block"),
+                                      ("parity", "deadlock")])
+def test_planted_defects_are_caught(bug, what):
+    caught = 0
+    for seed in range(20):
+        try:
+            run(w4a16_roles(24, bug=bug), seed)
+        except PipelineError as e:
+            import re
+            assert re.search(what, str(e)), str(e)
+            caught += 1
+    assert caught >= 15
