@@ -7,6 +7,7 @@ stream and returns tensors.  No autograd here — see ``functional.py``.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p, c_uint
 from typing import Optional
 
@@ -48,6 +49,8 @@ def _declare(lib) -> None:
     P, LL, I, F = c_void_p, c_longlong, c_int, c_float
     lib.rb_gemm.argtypes = [I, I, I, P, LL, P, LL, I, I, I, P, LL, I, P, P, LL, P, LL, P, LL, I, I,
                             F, I, I, I, I, P, P]
+    lib.rb_gemm_2cta.argtypes = [I, I, I, P, LL, P, LL, I, I, I, P, LL, I, P, P, LL, P, LL, P, LL, I, I,
+                                 F, I, P]
     lib.rb_bmm_simt.argtypes = [I, I, I, P, LL, LL, P, LL, LL, I, I, I, I, P, LL, LL, I, F, P]
     lib.rb_norm_fwd.argtypes = [I, I, P, P, P, P, P, P, P, LL, I, F, P]
     lib.rb_norm_bwd_partials.argtypes = [LL]
@@ -138,6 +141,10 @@ def sm_count() -> int:
     return _SM_COUNT
 
 
+def _use_2cta() -> bool:
+    return os.environ.get("RB_GEMM_2CTA", "0") == "1"
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
          act: Optional[str] = None, residual: Optional[torch.Tensor] = None,
          aux_out: bool = False, aux_in: Optional[torch.Tensor] = None, dact: Optional[str] = None,
@@ -150,6 +157,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
     (``x.t()``) — the storage order is passed to the kernel as the operand's
     "major", nothing is copied.  Returns ``out`` or ``(out, pre_activation)``
     when ``aux_out``.
+
+    ``path``: 0 automatic, 1 force the one-CTA tcgen05 kernel, 2 force the SIMT kernel, 3 force the
+    two-CTA tcgen05 kernel (also taken automatically for large 16-bit problems when
+    ``RB_GEMM_2CTA=1``).
 
     ``split_k`` (0 = automatic): when the output has far fewer tiles than the GPU has SMs and K
     is long (weight gradients of convolutions: M, N a few hundred, K = batch x pixels), K is cut
@@ -213,6 +224,20 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
             ws.add_(residual)
         out.copy_(ws)
         return out
+    if path in (0, 3) and (path == 3 or _use_2cta()) and a.dtype != torch.float32 and M >= 256 and N >= 256:
+        # two-CTA kernel (256 x 256 tiles, each SM stages half of B); opt-in, see gemm_2cta.cu
+        rc = L.rb_gemm_2cta(dt, a_mn, b_mn, ptr(a), lda, ptr(b), ldb, M, N, K, ptr(out), out.stride(0),
+                            out_f32, ptr(bias), ptr(residual),
+                            residual.stride(0) if residual is not None else 0, ptr(pre), N, ptr(aux_in),
+                            aux_in.stride(0) if aux_in is not None else 0, ACT_CODES[act], ACT_CODES[dact],
+                            float(alpha), max_ctas, stream_ptr())
+        if rc != 13:
+            check(rc, "rb_gemm_2cta")
+            count_launch()
+            gemm.last_path = 3
+            return (out, pre) if aux_out else out
+        if path == 3:
+            raise ValueError("operands are outside what the two-CTA GEMM covers")
     used = c_int(0)
     rc = L.rb_gemm(dt, a_mn, b_mn, ptr(a), lda, ptr(b), ldb, M, N, K, ptr(out), out.stride(0) if M > 1 else N,
                    out_f32, ptr(bias), ptr(residual),

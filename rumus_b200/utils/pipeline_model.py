@@ -179,3 +179,107 @@ def _final_check(state, consumed, nkb, warps) -> Role:
     yield (lambda: state["epilogues"] == warps)
     if consumed != list(range(nkb)):
         raise PipelineError(f"k-blocks consumed out of order: {consumed}")
+
+
+def gemm_2cta_roles(num_tiles: int, num_kb: int, stages: int = 6, epi_warps: int = 2, bug: str = "") -> Dict[str, Role]:
+    """The CTA pair of ``gemm_2cta_kernel`` (``csrc/kernels/gemm_2cta.cu``) walking ``num_tiles`` tiles
+    of ``num_kb`` K blocks: a copy producer per CTA (both complete on the leader's ``full`` barrier,
+    whose expected byte count the leader alone arms), the leader's MMA issuer (its commits release
+    the stage in both CTAs and hand the accumulator to both CTAs' epilogue warps), ``epi_warps``
+    epilogue warps per CTA (they release the accumulator on the leader's barrier and finally arrive
+    on both CTAs' ``done`` barriers).  Transaction bytes are modelled as a count that may run ahead
+    of the arming (a copy of the peer may land first).  ``bug``: ``"peer_not_released"`` (the leader
+    forgets the commit into the peer's ``empty`` barrier), ``"half_tx"`` (the leader arms the barrier
+    for its own bytes only)."""
+    full = [{"bar": Mbar(1), "tx": 0} for _ in range(stages)]          # leader's
+    empty = [[Mbar(1) for _ in range(stages)] for _ in range(2)]        # per CTA
+    tmem_full = [[Mbar(1) for _ in range(2)] for _ in range(2)]         # per CTA, per accumulator
+    tmem_empty = [Mbar(2 * epi_warps) for _ in range(2)]                # leader's
+    done = [Mbar(2 * epi_warps) for _ in range(2)]
+    stage_tag = [[None] * stages for _ in range(2)]                     # (tile, kb) held by each CTA's stage
+    acc_tag = [None, None]                                              # tile held by each accumulator
+    state = {"reading": None, "finished": 0}
+    PER_CTA_TX = 2                                                      # A box + B box
+
+    def full_complete(s, parity):
+        # the phase can only complete after the leader's arrival; bytes must have netted to zero
+        return full[s]["bar"].passed(parity)
+
+    def tx_done(s):
+        f = full[s]
+        if f.get("armed") and f["tx"] == 0:
+            f["armed"] = False
+            f["bar"].arrive()
+
+    def producer(cta: int):
+        stage, phase = 0, 0
+        for tile in range(num_tiles):
+            for kb in range(num_kb):
+                yield (lambda s=stage, ph=phase: empty[cta][s].passed(ph ^ 1))
+                if state["reading"] == stage:
+                    raise PipelineError(f"CTA {cta}: stage {stage} overwritten while the MMA reads it")
+                if cta == 0:
+                    full[stage]["tx"] += PER_CTA_TX if bug == "half_tx" else 2 * PER_CTA_TX
+                    full[stage]["armed"] = True
+                for _ in range(PER_CTA_TX):
+                    yield (lambda: True)                    # the copy lands later
+                    full[stage]["tx"] -= 1
+                    stage_tag[cta][stage] = (tile, kb)
+                    tx_done(stage)
+                if cta == 0:
+                    tx_done(stage)
+                stage += 1
+                if stage == stages:
+                    stage, phase = 0, phase ^ 1
+
+    def mma():
+        stage, phase, acc, acc_phase = 0, 0, 0, 0
+        for tile in range(num_tiles):
+            yield (lambda a=acc, ph=acc_phase: tmem_empty[a].passed(ph ^ 1))
+            for kb in range(num_kb):
+                yield (lambda s=stage, ph=phase: full_complete(s, ph))
+                if stage_tag[0][stage] != (tile, kb) or stage_tag[1][stage] != (tile, kb):
+                    raise PipelineError(f"MMA tile {tile} kb {kb}: stage {stage} holds {stage_tag[0][stage]} / "
+                                        f"{stage_tag[1][stage]}")
+                state["reading"] = stage
+                yield (lambda: True)
+                state["reading"] = None
+                empty[0][stage].arrive()
+                if bug != "peer_not_released":
+                    empty[1][stage].arrive()
+                stage += 1
+                if stage == stages:
+                    stage, phase = 0, phase ^ 1
+            acc_tag[acc] = tile
+            tmem_full[0][acc].arrive()
+            tmem_full[1][acc].arrive()
+            acc += 1
+            if acc == 2:
+                acc, acc_phase = 0, acc_phase ^ 1
+
+    def epilogue(cta: int, w: int):
+        acc, acc_phase = 0, 0
+        for tile in range(num_tiles):
+            yield (lambda a=acc, ph=acc_phase: tmem_full[cta][a].passed(ph))
+            if acc_tag[acc] != tile:
+                raise PipelineError(f"CTA {cta} epilogue {w}: accumulator {acc} holds tile {acc_tag[acc]}, expected {tile}")
+            yield (lambda: True)                            # tcgen05.ld + stores
+            if acc_tag[acc] != tile:
+                raise PipelineError(f"CTA {cta} epilogue {w}: accumulator {acc} overwritten while it was read")
+            tmem_empty[acc].arrive()
+            acc += 1
+            if acc == 2:
+                acc, acc_phase = 0, acc_phase ^ 1
+        done[0].arrive()
+        done[1].arrive()
+
+    def teardown(cta: int):
+        yield (lambda: done[cta].passed(0))
+        state["finished"] += 1
+
+    roles: Dict[str, Role] = {"producer0": producer(0), "producer1": producer(1), "mma": mma(),
+                              "teardown0": teardown(0), "teardown1": teardown(1)}
+    for cta in range(2):
+        for w in range(epi_warps):
+            roles[f"epi{cta}.{w}"] = epilogue(cta, w)
+    return roles

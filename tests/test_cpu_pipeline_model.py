@@ -42,3 +42,24 @@ def test_planted_defects_are_caught(bug, what):
             assert re.search(what, str(e)), str(e)
             caught += 1
     assert caught >= 15
+
+
+@pytest.mark.parametrize("tiles,nkb", [(1, 1), (1, 7), (2, 6), (3, 13), (5, 2)])
+def test_two_cta_gemm_pair_protocol(tiles, nkb):
+    from rumus_b200.utils.pipeline_model import gemm_2cta_roles
+    for seed in range(12):
+        assert run(gemm_2cta_roles(tiles, nkb), seed) > 0
+    for stages in (2, 3):
+        run(gemm_2cta_roles(tiles, nkb, stages=stages), 0)
+
+
+@pytest.mark.parametrize("bug", ["peer_not_released", "half_tx"])
+def test_two_cta_gemm_planted_defects_are_caught(bug):
+    from rumus_b200.utils.pipeline_model import gemm_2cta_roles
+    caught = 0
+    for seed in range(12):
+        try:
+            run(gemm_2cta_roles(3, 9, bug=bug), seed)
+        except PipelineError:
+            caught += 1
+    assert caught == 12
