@@ -20,7 +20,7 @@ from __future__ import annotations
 
 import math
 import traceback
-from typing import List, Optional
+from typing import List
 
 import torch
 from torch.overrides import TorchFunctionMode

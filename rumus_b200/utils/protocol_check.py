@@ -16,7 +16,7 @@ Actions: ``("write", buf, version)``, ``("set", flag, value)``, ``("wait", flag,
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Sequence, Tuple
 
 Action = Tuple
 
