@@ -264,3 +264,20 @@ def test_corrupted_checkpoint_is_rejected_and_skipped(tmp_path):
         load_checkpoint(str(newest), _make(), FSDP(_make(), lr=1.0))
     assert latest_checkpoint(str(tmp_path), verify=True).endswith("step-2")
     assert latest_checkpoint(str(tmp_path)).endswith("step-4")      # unverified: newest by name
+
+
+def test_llama_stage_never_issues_two_same_kind_fused_ops_in_a_row():
+    """The staging buffers of the fused tensor-parallel kernels are reused without a barrier as long as
+    gather (A) and reduce (R) operations alternate.  Under every 1F1B schedule the parallel Llama
+    stage issues: forward = ARAR per block (+ A for the head on the last stage), backward = (R for the
+    head) + ARAR per block — so the sequence alternates and ``TPContext.order_fused`` never has to
+    insert its barrier there."""
+    from rumus_b200.parallel.pp import one_f_one_b_order
+    for stages in (1, 2, 4):
+        for micro in (1, 2, 4, 8):
+            for st in range(stages):
+                last = st == stages - 1
+                seq = ""
+                for kind, _mb in one_f_one_b_order(st, stages, micro):
+                    seq += ("ARAR" * 2 + ("A" if last else "")) if kind == "F" else (("R" if last else "") + "ARAR" * 2)
+                assert all(seq[i] != seq[i - 1] for i in range(1, len(seq))), (stages, micro, st)
