@@ -36,6 +36,8 @@ for (M,N,K,bt) in [(16384,2048,2048,False),(16384,6144,2048,False),(16384,8192,2
     for bn in (128,256):
         t=timeit(lambda: native.gemm(a,b,path=1,bn=bn)); 
         print(f"M{M} N{N} K{K} bt={bt} bn={bn}: {t:.3f} ms {2*M*N*K/t/1e9:.0f} TF", flush=True)
+    if os.environ.get("RB_GEMM_2CTA", "0") == "1":   # the two-CTA kernel, once it is switched on
+        t=timeit(lambda: native.gemm(a,b,path=3)); print(f"   two-CTA 256x256: {t:.3f} ms {2*M*N*K/t/1e9:.0f} TF", flush=True)
     t=timeit(lambda: torch.matmul(a,b)); print(f"   torch: {t:.3f} ms {2*M*N*K/t/1e9:.0f} TF", flush=True)
     st=native.read_status(); assert st==0, st
 # wgrad-like: A^T B
