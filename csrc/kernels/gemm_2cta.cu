@@ -26,6 +26,8 @@
 // pre-activation side output); static tile schedule over clusters; bf16 / fp16 operands in any of
 // the four storage-major combinations.  Reference counterpart: the naive one-thread-per-output
 // matmul of rumus/src/backend/gpu/shaders/matmul.wgsl:22.
+#include <cstdlib>
+
 #include "gemm_launch.cuh"
 
 namespace rb {
@@ -169,6 +171,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      long long issued = 0;     // K blocks loaded so far (the first G2_STAGES find their stage free)
       bool ok = true;
       for (int tile = cluster_id; tile < total_tiles && ok; tile += num_clusters) {
         int m_idx, n_idx;
@@ -178,6 +181,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
         for (int kb = 0; kb < num_kb && ok; ++kb) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, RB_ERR_TIMEOUT_EMPTY);
           if (!ok) break;
+          // forwarding mode: the leader's commit only reached the leader's barrier; pass the release
+          // of this stage on to the peer (not on the first round, when every stage starts out free)
+          if (p.pair_release == 1 && leader && issued >= G2_STAGES)
+            mbar_arrive_cluster(map_to_cta(smem_u32(&empty_bar[stage]), 1));
           const uint32_t leader_full = map_to_cta(smem_u32(&full_bar[stage]), 0);
           if (leader) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * G2_STAGE_BYTES);
           const uint32_t a_dst = smem_u32(sA + stage * G2_A_BYTES);
@@ -196,6 +203,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
             for (int j = 0; j < 128 / CH; ++j)
               tma_load_2d_pair(b_dst + j * G2_BK * 128, &tma_b, leader_full, n0 + j * CH, kb * G2_BK);
           }
+          ++issued;
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -229,12 +237,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
           }
           // the stage is free again in both CTAs once these MMAs have read it
           umma_commit_pair_w(smem_u32(&empty_bar[stage]));
-          umma_commit_pair_w(map_to_cta(smem_u32(&empty_bar[stage]), 1));
+          if (p.pair_release == 0) umma_commit_pair_w(map_to_cta(smem_u32(&empty_bar[stage]), 1));
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         umma_commit_pair_w(smem_u32(&tmem_full_bar[acc]));
-        umma_commit_pair_w(map_to_cta(smem_u32(&tmem_full_bar[acc]), 1));
+        if (p.pair_release == 0) umma_commit_pair_w(map_to_cta(smem_u32(&tmem_full_bar[acc]), 1));
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
@@ -253,6 +261,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
       ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      // forwarding mode: one warp of the leader hands the accumulator to the peer's epilogue
+      if (p.pair_release == 1 && leader && warp_idx == 2 && lane == 0)
+        mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_full_bar[acc]), 1));
       tc_fence_after();
       const long long row = static_cast<long long>(m_idx) * G2_BM + cta_rank * 128 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * G2_BN;
@@ -367,6 +378,10 @@ int rb_gemm_2cta(int dtype, int a_mn, int b_mn, const void* A, long long lda, co
   p.group_m = 4;      // 4 x 256 rows share a B column panel in L2, like 8 x 128 in the one-CTA kernel
   p.split_k = 1;
   p.sched = nullptr;
+  {
+    const char* e = getenv("RB_G2_RELEASE");     // "forward": see GemmParams::pair_release
+    p.pair_release = (e && e[0] == 'f') ? 1 : 0;
+  }
   const int osz = out_f32 ? 4 : 2;
   p.vec_ok = al(out) && (ldc * osz) % 16 == 0 && (!residual || (al(residual) && (ldr * osz) % 16 == 0)) &&
              (!aux_out || (al(aux_out) && (ldaux_out * osz) % 16 == 0)) &&

@@ -48,6 +48,8 @@ struct GemmParams {
   int* sched;            // device int[2] {next tile, finished CTAs} for dynamic tile scheduling, or null
   int split_k;           // > 1: K is cut into this many slices, every (tile, slice) is a work item and
                          // the epilogue adds into a zero-initialised fp32 output (no bias/act/residual)
+  int pair_release;      // two-CTA kernel only: 0 = the leader's commits arrive on both CTAs' barriers,
+                         // 1 = they arrive on the leader's own barriers and are forwarded to the peer
 };
 
 struct NoHooks {
