@@ -41,6 +41,10 @@ struct W4Params {
   const void* bias;          // [N] of T or null (applied only when the K range is not split)
   void* out;                 // [M,N] of T (unsplit)
   float* ws;                 // [M,N] fp32, zero-initialised (split K)
+  int* tile_counters;        // split K: one int per column tile (zero before the launch), or null.
+                             // With counters the CTA that adds the last K slice of a tile also converts
+                             // it (ws + bias -> out) and puts ws and the counter back to zero, so neither
+                             // a clearing pass before nor a conversion kernel after the launch is needed.
   int* status;
 };
 
@@ -107,8 +111,11 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
   uint64_t* x_full = a_full + W4_AB_STAGES;                 // TMA -> MMA
   uint64_t* ab_empty = x_full + W4_AB_STAGES;               // MMA commit -> dequant, X producer
   uint64_t* acc_full = ab_empty + W4_AB_STAGES;             // MMA commit -> epilogue
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* fin_bar = acc_full + 1;                         // epilogue warps: "my additions are out" (4 arrivals)
+  uint64_t* fin2_bar = fin_bar + 1;                         // one thread: "last_flag is written"
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(fin2_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+  volatile int* last_flag = abort_flag + 1;
 
   const int warp_idx = uniform_warp_idx();
   const int lane = threadIdx.x & 31;
@@ -127,7 +134,10 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
       mbar_init(smem_u32(&ab_empty[s]), 1);
     }
     mbar_init(smem_u32(acc_full), 1);
+    mbar_init(smem_u32(fin_bar), 4);
+    mbar_init(smem_u32(fin2_bar), 1);
     *abort_flag = 0;
+    *last_flag = 0;
     fence_barrier_init();
   }
   if (warp_idx == 1) {
@@ -289,6 +299,34 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
           }
         }
       }
+      if (split && p.tile_counters) {
+        // the K slice that arrives last at this column tile finishes it
+        // (bounded mbarrier waits rather than a named barrier: a warp that gave up must not leave
+        // the other three waiting for ever)
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(fin_bar));
+        if (nl == 0) {
+          if (mbar_wait(smem_u32(fin_bar), 0, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL))
+            *last_flag = atomicAdd(p.tile_counters + blockIdx.x, 1) == (int)gridDim.y - 1 ? 1 : 0;
+          mbar_arrive(smem_u32(fin2_bar));
+        }
+        bool fin_ok = mbar_wait(smem_u32(fin2_bar), 0, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL);
+        fin_ok = __all_sync(0xffffffffu, fin_ok);
+        if (fin_ok && *last_flag) {
+          __threadfence();
+          if (n_ok) {
+            const float bs = p.bias ? to_f32<T>(static_cast<const T*>(p.bias)[n]) : 0.f;
+            for (int m = 0; m < p.M; ++m) {
+              float* w = p.ws + (long long)m * p.N + n;
+              const float v = __ldcg(w);
+              *w = 0.f;                                          // ready for the next launch
+              static_cast<T*>(p.out)[(long long)m * p.N + n] = from_f32<T>(v + bs);
+            }
+          }
+          if (nl == 0) p.tile_counters[blockIdx.x] = 0;
+        }
+      }
     }
   }
 
@@ -363,10 +401,13 @@ int rb_w4a16_slices(int N, int Kp) {
 }
 
 // Y[M,N] = X[M,K] . dequant(packed)[K,N] + bias.  Error 51 = shape / alignment outside what this
-// kernel covers (the caller uses another path).  `ws` is only touched when the K range is split.
+// kernel covers (the caller uses another path).  `ws` is only touched when the K range is split:
+// with `tile_counters` (one zeroed int per 128 columns) it must be zero on entry and is zero again
+// on return — one launch in total; without counters it is cleared here and converted by a second
+// kernel.
 int rb_w4a16_gemm(int x_dtype, int scale_dtype, const void* x, long long ldx, const int* packed,
-                  const void* scales, const void* zps, const void* bias, void* y, float* ws, int M,
-                  int N, int K, int Kp, int group, void* stream) {
+                  const void* scales, const void* zps, const void* bias, void* y, float* ws,
+                  int* tile_counters, int M, int N, int K, int Kp, int group, void* stream) {
   using namespace rb;
   if (M <= 0 || N <= 0) return 0;
   if (M > 128 || (x_dtype != rbh::DT_BF16 && x_dtype != rbh::DT_F16)) return 51;
@@ -380,10 +421,11 @@ int rb_w4a16_gemm(int x_dtype, int scale_dtype, const void* x, long long ldx, co
   const int k_slices = rb_w4a16_slices(N, Kp);
   p.kb_per_slice = (Kp / W4_BK + k_slices - 1) / k_slices;
   p.scales = scales; p.zps = zps; p.bias = bias; p.out = y; p.ws = ws;
+  p.tile_counters = k_slices > 1 ? tile_counters : nullptr;
   p.status = rbh::device_status_word();
   if (k_slices > 1) {
     if (!ws) return 52;
-    cudaMemsetAsync(ws, 0, (size_t)M * N * sizeof(float), st);
+    if (!tile_counters) cudaMemsetAsync(ws, 0, (size_t)M * N * sizeof(float), st);
   }
   int rc;
   if (x_dtype == rbh::DT_BF16)
@@ -393,7 +435,7 @@ int rb_w4a16_gemm(int x_dtype, int scale_dtype, const void* x, long long ldx, co
     rc = scale_dtype == rbh::DT_F16 ? launch_w4a16<__half, __half>(x_dtype, x, ldx, packed, p, k_slices, st)
                                     : launch_w4a16<__half, float>(x_dtype, x, ldx, packed, p, k_slices, st);
   if (rc) return rc;
-  if (k_slices > 1) {
+  if (k_slices > 1 && !tile_counters) {
     const long long total = (long long)M * N;
     long long blocks = (total + 255) / 256;
     const long long cap = (long long)rbh::sm_count() * 8;

@@ -20,7 +20,7 @@ native.register_signature("rb_int4_gemv_splits", [I, I])
 native.register_signature("rb_int4_gemv", [I, I, P, P, P, P, P, P, P, I, I, I, I, I, P])
 native.register_signature("rb_int4_dequant", [I, I, P, P, P, P, I, I, I, P])
 native.register_signature("rb_w4a16_slices", [I, I])
-native.register_signature("rb_w4a16_gemm", [I, I, P, c_longlong, P, P, P, P, P, P, I, I, I, I, I, P])
+native.register_signature("rb_w4a16_gemm", [I, I, P, c_longlong, P, P, P, P, P, P, P, I, I, I, I, I, P])
 native.register_signature("rb_q8_quantize", [I, P, P, I, I, I, P])
 native.register_signature("rb_q8_dequantize", [I, P, P, I, I, I, P])
 
@@ -58,17 +58,39 @@ def int4_matmul_fused(x: torch.Tensor, qw, bias=None):
         return None
     x = x.contiguous()
     y = torch.empty((M, qw.n), dtype=x.dtype, device=x.device)
-    ws = None
-    if L.rb_w4a16_slices(qw.n, qw.padded_k) > 1:
-        ws = torch.empty((M, qw.n), dtype=torch.float32, device=x.device)
+    ws = counters = None
+    split = L.rb_w4a16_slices(qw.n, qw.padded_k) > 1
+    if split:
+        if os.environ.get("RB_W4A16_TWO_PASS", "0") == "1":
+            ws = torch.empty((M, qw.n), dtype=torch.float32, device=x.device)     # cleared / converted by extra launches
+        else:
+            ws, counters = _w4_workspace(x.device, M * qw.n, (qw.n + 127) // 128)
     rc = L.rb_w4a16_gemm(native.dtype_code(x.dtype), native.dtype_code(qw.scales.dtype), ptr(x),
                          c_longlong(x.stride(0)), ptr(qw.packed), ptr(qw.scales), ptr(qw.zero_points),
-                         ptr(bias), ptr(y), ptr(ws), M, qw.n, K, qw.padded_k, qw.group_size, stream_ptr())
+                         ptr(bias), ptr(y), ptr(ws), ptr(counters), M, qw.n, K, qw.padded_k, qw.group_size,
+                         stream_ptr())
     if rc == 51:
         return None
     check(rc, "rb_w4a16_gemm")
-    count_launch(3 if ws is not None else 1)
+    count_launch(1 if (not split or counters is not None) else 3)
     return y
+
+
+_W4_WS = {}
+
+
+def _w4_workspace(device, numel: int, tiles: int):
+    """Per-device fp32 accumulation buffer and per-tile counters for split-K launches.  Both are zero
+    between launches (the kernel that finishes a tile puts them back), so consecutive launches on one
+    stream share them; they only grow."""
+    key = (device.type, device.index)
+    ws, cnt = _W4_WS.get(key, (None, None))
+    if ws is None or ws.numel() < numel:
+        ws = torch.zeros(max(numel, 1 << 22), dtype=torch.float32, device=device)
+    if cnt is None or cnt.numel() < tiles:
+        cnt = torch.zeros(max(tiles, 1024), dtype=torch.int32, device=device)
+    _W4_WS[key] = (ws, cnt)
+    return ws, cnt
 
 
 def int4_matmul(x: torch.Tensor, qw, bias=None) -> torch.Tensor:

@@ -22,7 +22,11 @@ def _rel(a, b):
                                    (16, 4096, 512),      # K split across CTAs, fp32 workspace
                                    (33, 1160, 520),      # K padded to the group, N not a multiple of 128
                                    (128, 1024, 256)])    # the largest batch (UMMA N = 128)
-def test_w4a16_matches_dequantised_product(dtype, scale_dtype, M, K, N):
+@pytest.mark.parametrize("two_pass", [False, True])
+def test_w4a16_matches_dequantised_product(dtype, scale_dtype, M, K, N, two_pass, monkeypatch):
+    # two_pass: workspace cleared before and converted after the launch by separate kernels; default:
+    # the CTA that adds a tile's last K slice converts it and restores the zeroed workspace
+    monkeypatch.setenv("RB_W4A16_TWO_PASS", "1" if two_pass else "0")
     from rumus_b200.nn.quant import QuantizedTensor
     from rumus_b200.ops import native
     from rumus_b200.ops import quant_cuda as Q
@@ -36,6 +40,9 @@ def test_w4a16_matches_dequantised_product(dtype, scale_dtype, M, K, N):
     ref = x.float() @ q.dequantize(torch.float32) + bias.float()
     assert native.read_status() == 0
     assert _rel(y, ref) < 1.5e-2, _rel(y, ref)
+    # the shared workspace is zero again after a launch: the same call gives the same answer
+    y_again = Q.int4_matmul_fused(x, q, bias)
+    assert _rel(y_again, y) < 1e-3
     # rows are independent: a one-row change only moves that row
     x2 = x.clone()
     x2[M // 2] += 1.0
