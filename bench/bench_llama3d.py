@@ -59,7 +59,7 @@ def main():
     rest = [p for n, p in stage.named_parameters() if not n.startswith("blocks.")]
     if rest:
         units.append(("edge", rest))
-    opt = FSDP(stage, lr=1e-4, beta2=0.95, unit_roots=units, local_only=True)
+    opt = FSDP(stage, lr=1e-4, beta2=0.95, unit_roots=units, local_only=True, defer_update=True)
     ps = PipelineStage(stage, topo.pp_idx, a.pp, topo.prev_stage_rank, topo.next_stage_rank,
                        (mb_tokens // a.tp, a.d_model), torch.bfloat16, dev)
     g = torch.Generator(device="cpu").manual_seed(1234 + topo.dp_idx)
@@ -78,6 +78,7 @@ def main():
     def step():
         opt.zero_grad()
         loss = ps.run(make_batch())
+        opt.reduce_grads(replicated_group=topo.tp_group, dp_group=topo.dp_group)
         opt.step()
         return loss
 

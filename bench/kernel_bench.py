@@ -18,6 +18,21 @@ def timeit(fn, n=10, warm=3):
         s=torch.cuda.Event(enable_timing=True); e=torch.cuda.Event(enable_timing=True)
         s.record(); fn(); e.record(); torch.cuda.synchronize(); ts.append(s.elapsed_time(e))
     ts.sort(); return ts[len(ts)//2]
+if "--gemm-compare" in sys.argv:
+    # one GEMM shape through the one-CTA kernel, the two-CTA kernel and torch.matmul, a few launches
+    # each (sized for a counter capture: python bench/kernel_bench.py --gemm-compare M N K)
+    i = sys.argv.index("--gemm-compare")
+    M, N, K = (int(v) for v in sys.argv[i + 1:i + 4])
+    a = torch.randn(M, K, device='cuda').bfloat16(); b = torch.randn(K, N, device='cuda').bfloat16()
+    for _ in range(3):
+        native.gemm(a, b, path=1, bn=256)
+    for _ in range(3):
+        native.gemm(a, b, path=3)
+    for _ in range(3):
+        torch.matmul(a, b)
+    torch.cuda.synchronize()
+    print("gemm compare done, status", native.read_status())
+    sys.exit(0)
 if "--small" in sys.argv:
     a = torch.randn(8192, 4096, device='cuda').bfloat16(); b = torch.randn(4096, 8192, device='cuda').bfloat16()
     for _ in range(3):

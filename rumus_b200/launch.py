@@ -193,7 +193,7 @@ def _run_llama(cfg: TrainConfig, a, rank, world, dev) -> dict:
     rest = [p for n, p in stage.named_parameters() if not n.startswith("blocks.")]
     if rest:
         units.append(("edge", rest))
-    opt = FSDP(stage, lr=cfg.lr, unit_roots=units, local_only=True)
+    opt = FSDP(stage, lr=cfg.lr, unit_roots=units, local_only=True, defer_update=True)
     ps = PipelineStage(stage, topo.pp_idx, par.pp, topo.prev_stage_rank, topo.next_stage_rank,
                        (mb_tokens // par.tp, mc.d_model), dtype, dev)
     first, last = topo.pp_idx == 0, topo.pp_idx == par.pp - 1
@@ -214,6 +214,9 @@ def _run_llama(cfg: TrainConfig, a, rank, world, dev) -> dict:
             mbs = [None] * par.micro_batches
         opt.zero_grad()
         loss = ps.run(mbs)
+        # norm weights are replicated over the tensor-parallel group, the whole stage over the
+        # data-parallel replicas: sum resp. average those gradients before the update
+        opt.reduce_grads(replicated_group=topo.tp_group, dp_group=topo.dp_group)
         opt.step()
         if last and (step % a.log_every == 0 or step == steps):
             last_loss = float(loss)

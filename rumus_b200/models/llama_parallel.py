@@ -19,7 +19,7 @@ import torch.nn as nn
 from ..nn import Embedding, Module, RMSNorm
 from ..ops import functional as F
 from ..parallel.tp import (ColumnParallelLinear, RowParallelLinear, TPContext, gather_rows,
-                           scatter_rows)
+                           mark_tp_replicated, scatter_rows)
 from .llama import LlamaConfig
 
 
@@ -41,6 +41,9 @@ class ParallelLlamaBlock(Module):
         self.gate_up = ColumnParallelLinear(cfg.d_model, 2 * cfg.ffn_dim, tp, bias=False, device=device,
                                             dtype=dtype)
         self.down = RowParallelLinear(cfg.ffn_dim, cfg.d_model, tp, bias=False, device=device, dtype=dtype)
+        # the norms run on this rank's token slab only: their weight gradients are partial sums
+        mark_tp_replicated(self.ln1.weight)
+        mark_tp_replicated(self.ln2.weight)
 
     def forward(self, x_local, batch: int, seq: int):
         H, Hkv, hd = self.h_local, self.hkv_local, self.hd
@@ -97,6 +100,7 @@ class ParallelLlamaStage(Module):
         self.blocks = nn.ModuleList([ParallelLlamaBlock(cfg, tp, device, dtype) for _ in range(per)])
         if self.last:
             self.ln_final = RMSNorm(cfg.d_model, cfg.rms_eps, device, dtype)
+            mark_tp_replicated(self.ln_final.weight)
             self.head = ColumnParallelLinear(cfg.d_model, cfg.vocab_size, tp, bias=False, device=device,
                                              dtype=dtype)
         self.batch = self.seq = None

@@ -113,6 +113,7 @@ class SGD(Optimizer):
     def state_dict(self):
         sd = super().state_dict()
         sd["velocity"] = [self.velocity.get(p) for p in self.params]
+        sd["master"] = [self.master.get(p) for p in self.params]
         return sd
 
     def load_state_dict(self, sd):
@@ -120,6 +121,9 @@ class SGD(Optimizer):
         for p, v in zip(self.params, sd.get("velocity", [])):
             if v is not None:
                 self.velocity[p] = v.to(p.device)
+        for p, w in zip(self.params, sd.get("master", [])):
+            if w is not None:
+                self.master[p] = w.to(p.device)
 
 
 class Adam(Optimizer):
@@ -131,8 +135,15 @@ class Adam(Optimizer):
     def __init__(self, params, lr: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999,
                  epsilon: float = 1e-8, weight_decay: float = 0.0):
         super().__init__(params, lr)
+        if weight_decay and not self._decoupled:
+            # the reference's Adam has no weight decay (rumus/src/optim/adam.rs:14-40); an L2 term
+            # silently dropped would be worse than an error
+            raise ValueError("Adam takes no weight_decay; use AdamW for decoupled weight decay")
         self.beta1, self.beta2, self.epsilon, self.weight_decay = beta1, beta2, epsilon, weight_decay
         self.first_moment, self.second_moment = {}, {}
+        # set when the last step ran on the device under a skip flag whose value the host has not
+        # seen: GradScaler.update() takes the step count back if that step turned out to be skipped
+        self._device_skip_pending = False
 
     def step(self) -> None:
         act = self._active()
@@ -154,6 +165,7 @@ class Adam(Optimizer):
                     lr=self.lr, beta1=self.beta1, beta2=self.beta2, eps=self.epsilon,
                     weight_decay=self.weight_decay, step=t, adamw=self._decoupled,
                     grad_scale=self.grad_scale, skip=self.skip_flag)
+            self._device_skip_pending = self.skip_flag is not None
             return
         if self.skip_flag is not None and int(self.skip_flag.item()) != 0:
             self.step_count -= 1
@@ -214,13 +226,17 @@ def clip_grad_norm_(params: Iterable[torch.nn.Parameter], max_norm: float) -> to
     also produces the clip coefficient on the device, one in-place scale per tensor — no host
     round-trip."""
     assert max_norm > 0
-    grads = [p.grad for p in params if p.grad is not None]
+    params = [p for p in params if p.grad is not None]
+    for p in params:
+        if not p.grad.is_contiguous():
+            p.grad = p.grad.contiguous()       # scaled in place below: must be the tensor the optimizer reads
+    grads = [p.grad for p in params]
     if not grads:
         return torch.zeros(())
     if grads[0].is_cuda:
         norm, coef = native.global_norm(grads, max_norm=max_norm)
         for g in grads:
-            native.scale_check_(g if g.is_contiguous() else g.contiguous(), scale_tensor=coef)
+            native.scale_check_(g, scale_tensor=coef)
         return norm
     total = math.sqrt(sum(float(g.float().pow(2).sum()) for g in grads))
     if total > max_norm:
@@ -332,10 +348,18 @@ class GradScaler:
             self.found_inf.fill_(1 if bad else 0)
         optimizer.grad_scale = self.inv_scale
         optimizer.skip_flag = self.found_inf
+        self._optimizer = optimizer
 
     def update(self) -> bool:
         """Returns True when the last step overflowed (and was skipped)."""
         overflow = bool(int(self.found_inf.item())) if self.found_inf is not None else False
+        opt = getattr(self, "_optimizer", None)
+        if opt is not None and getattr(opt, "_device_skip_pending", False):
+            # the device-side step counted itself before the flag was known: a skipped step must not
+            # advance the bias-correction exponent (the CPU path never counts it)
+            if overflow:
+                opt.step_count -= 1
+            opt._device_skip_pending = False
         if overflow:
             self.scale_value *= self.backoff_factor
             self._good_steps = 0

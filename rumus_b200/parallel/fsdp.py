@@ -78,11 +78,15 @@ class FSDP:
                  eps: float = 1e-8, weight_decay: float = 0.0, adamw: bool = False,
                  group: Optional[dist.ProcessGroup] = None, mode: Optional[str] = None,
                  unit_roots: Optional[list] = None, arena=None, local_only: bool = False,
-                 reshard_after_forward: bool = False):
+                 reshard_after_forward: bool = False, defer_update: bool = False):
         self.model = model
         self.lr, self.beta1, self.beta2, self.eps = lr, beta1, beta2, eps
         self.weight_decay, self.adamw = weight_decay, adamw
         self.group = group
+        # ``defer_update``: several backward passes feed one optimizer step (pipeline micro-batches,
+        # gradient accumulation), so a unit is only reduced and updated from ``step()``, never from
+        # the boundary node that fires at the end of each backward pass
+        self._defer = bool(defer_update)
         # ``local_only``: no sharding (the parameters of a tensor/pipeline-parallel stage are
         # already this rank's own); the engine is then just the flat-arena fused optimizer
         self.world = dist.get_world_size(group) if dist.is_initialized() and not local_only else 1
@@ -274,7 +278,7 @@ class FSDP:
         self._done = [False] * len(self.units)
 
     def _unit_backward_done(self, idx: int) -> None:
-        if self._done[idx] or not self._cuda:
+        if self._done[idx] or not self._cuda or self._defer:
             # CPU ranks get parameter gradients through plain autograd accumulation, which may
             # run after this node: they finish every unit in step() instead.
             return
@@ -282,6 +286,39 @@ class FSDP:
         # after the first block's backward only the embedding gradient is left to compute: from
         # here on the communication kernels have the GPU to themselves
         self._reduce_and_update(idx, tail=(idx == self._first_hooked))
+
+    def reduce_grads(self, replicated_group: Optional[dist.ProcessGroup] = None,
+                     dp_group: Optional[dist.ProcessGroup] = None) -> None:
+        """For an engine built with ``local_only`` (a tensor x pipeline parallel stage), between the
+        last backward pass and ``step()``:
+
+        * parameters tagged ``_tp_replicated`` (norm weights and row-parallel biases, which every
+          tensor-parallel rank holds in full but which only see that rank's token slab) get the SUM
+          of their gradients over ``replicated_group``;
+        * every gradient is then averaged over ``dp_group`` (replicas that saw different data).
+
+        Both are collectives: every rank of the group has to call this."""
+        for u in self.units:
+            u.collect_stray_grads()
+        if replicated_group is not None and dist.get_world_size(replicated_group) > 1:
+            views = [p.main_grad for u in self.units for p in u.params
+                     if getattr(p, "_tp_replicated", False)]
+            if views:
+                flat = torch.cat([v.reshape(-1).float() for v in views])
+                dist.all_reduce(flat, group=replicated_group)
+                o = 0
+                for v in views:
+                    v.copy_(flat[o:o + v.numel()].view(v.shape))
+                    o += v.numel()
+        if dp_group is not None and dist.get_world_size(dp_group) > 1:
+            n = dist.get_world_size(dp_group)
+            for u in self.units:
+                g = u.flat_grad
+                if g.is_cuda and g.dtype != torch.float16:
+                    dist.all_reduce(g, op=dist.ReduceOp.AVG, group=dp_group)
+                else:
+                    dist.all_reduce(g, group=dp_group)
+                    g.div_(n)
 
     def step(self) -> None:
         """Call after ``loss.backward()``: finishes the units whose backward did not fire a

@@ -235,8 +235,44 @@ class _RowParallelFn(torch.autograd.Function):
         return dx, dw, db, None
 
 
+_fallback_logged = set()
+
+
 def _fusable(tp: TPContext, M: int) -> bool:
-    return M % (128 * tp.world) == 0
+    ok = M % (128 * tp.world) == 0
+    if not ok and (M, tp.world) not in _fallback_logged:
+        _fallback_logged.add((M, tp.world))
+        import warnings
+        warnings.warn(f"tensor-parallel layer with {M} tokens on {tp.world} ranks: the fused "
+                      f"gather/GEMM/reduce-scatter kernels need a multiple of {128 * tp.world} tokens; "
+                      "using NCCL collectives + separate GEMMs for this shape", stacklevel=3)
+    return ok
+
+
+def mark_tp_replicated(p: nn.Parameter) -> nn.Parameter:
+    """Tags a parameter that every tensor-parallel rank holds in full while its gradient only
+    covers that rank's token slab (norm weights in a sequence-parallel region, the bias of a
+    row-parallel layer).  ``sync_replicated_grads`` / ``FSDP.reduce_grads`` sum those gradients
+    over the group so that the copies stay identical."""
+    p._tp_replicated = True
+    return p
+
+
+def sync_replicated_grads(module: nn.Module, tp: TPContext) -> None:
+    """SUM all-reduce, over the tensor-parallel group, of ``.grad`` of every parameter tagged by
+    ``mark_tp_replicated`` (for models driven by a plain optimizer; flat-arena engines use
+    ``FSDP.reduce_grads``).  Collective."""
+    if tp.world == 1:
+        return
+    grads = [p.grad for p in module.parameters() if getattr(p, "_tp_replicated", False) and p.grad is not None]
+    if not grads:
+        return
+    flat = torch.cat([g.reshape(-1).float() for g in grads])
+    dist.all_reduce(flat, group=tp.group)
+    o = 0
+    for g in grads:
+        g.copy_(flat[o:o + g.numel()].view(g.shape))
+        o += g.numel()
 
 
 class ColumnParallelLinear(Module):
@@ -279,6 +315,8 @@ class RowParallelLinear(Module):
         k = in_features // tp.world
         self.weight = nn.Parameter(full[tp.rank * k:(tp.rank + 1) * k].contiguous())
         self.bias = nn.Parameter(_uniform((out_features,), bound, _linear_rng, device, dtype)) if bias else None
+        if self.bias is not None:
+            mark_tp_replicated(self.bias)
 
     def forward(self, x):
         if self.tp.world == 1:

@@ -62,11 +62,28 @@ def latest_checkpoint(root: str, verify: bool = False) -> Optional[str]:
     return best
 
 
-def _entry(fn, rank, world, generation, port, backend_env, args):
+_stop_event = None
+
+
+def stop_requested() -> bool:
+    """True once the supervisor has asked this generation to stop (a peer was lost).  Workers poll
+    it between steps, next to ``Heartbeat.check_peers``, and return: a rank that leaves between
+    steps has no kernel or collective in flight.  Ranks that do not return within the grace period
+    are terminated by process handle."""
+    return _stop_event is not None and _stop_event.is_set()
+
+
+def _entry(fn, rank, world, generation, port, backend_env, args, stop_event=None):
+    global _stop_event
+    _stop_event = stop_event
     os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "RANK": str(rank),
                        "LOCAL_RANK": str(rank), "WORLD_SIZE": str(world),
                        "RB_ELASTIC_GENERATION": str(generation)})
     os.environ.update(backend_env)
+    # a supervised rank may be stopped while its peers still run: its memory must never be bound to
+    # an NVLink multicast object (neither the arena's nor NCCL's), whatever the caller's environment says
+    os.environ["RB_MULTIMEM"] = "0"
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
     fn(rank, world, generation, *args)
 
 
@@ -92,7 +109,8 @@ class ElasticSupervisor:
     def _run_generation(self, generation: int, world: int) -> GenerationRecord:
         ctx = mp.get_context("spawn")
         port = _free_port()
-        procs = [ctx.Process(target=_entry, args=(self.fn, r, world, generation, port, self.env, self.args))
+        stop = ctx.Event()
+        procs = [ctx.Process(target=_entry, args=(self.fn, r, world, generation, port, self.env, self.args, stop))
                  for r in range(world)]
         t0 = time.time()
         for p in procs:
@@ -109,7 +127,12 @@ class ElasticSupervisor:
                 break
             time.sleep(self.poll_s)
         if failed:
-            # coordinated stop of this generation: only the processes started above, by handle
+            # coordinated stop of this generation: first ask (workers that poll ``stop_requested``
+            # leave between steps), then end what is left — only the processes started above, by handle
+            stop.set()
+            deadline = time.time() + self.stop_grace_s
+            for p in procs:
+                p.join(timeout=max(0.0, deadline - time.time()))
             for p in procs:
                 if p.is_alive():
                     p.terminate()

@@ -306,6 +306,15 @@ def _tp_pp_worker(rank, world):
     f = cfg.ffn_dim // 2
     mine = stage.blocks[0].down.weight.grad
     assert torch.allclose(mine, gd[topo.tp_idx * f:(topo.tp_idx + 1) * f], atol=1e-5)
+    # norm weights are replicated over the tensor-parallel ranks but only see this rank's token
+    # slab: after the group sum every copy carries the dense gradient
+    from rumus_b200.parallel.tp import sync_replicated_grads
+    sync_replicated_grads(stage, tp)
+    db = dense.blocks[topo.pp_idx * per]
+    assert torch.allclose(stage.blocks[0].ln1.weight.grad, db.ln1.weight.grad, atol=1e-5)
+    assert torch.allclose(stage.blocks[0].ln2.weight.grad, db.ln2.weight.grad, atol=1e-5)
+    if last:
+        assert torch.allclose(stage.ln_final.weight.grad, dense.ln_final.weight.grad, atol=1e-5)
     # shards -> reference-layout dense state dict (TP shards concatenated, stages merged on rank 0)
     full = stage.export_dense()
     if rank == 0:
@@ -320,6 +329,65 @@ def _tp_pp_worker(rank, world):
 
 def test_llama_tp2_pp2_matches_dense():
     assert all(run_ranks(_tp_pp_worker, 4))
+
+
+def _tp_pp_dp_train_worker(rank, world, tp_size, pp_size):
+    """Two optimizer steps of the stage engine (flat arenas, deferred update over the micro-batches,
+    gradient sums over the tensor-parallel group and averages over the replicas)."""
+    from rumus_b200.models import LlamaConfig
+    from rumus_b200.models.llama_parallel import ParallelLlamaStage
+    from rumus_b200.parallel import FSDP
+    from rumus_b200.parallel.pp import PipelineStage
+    from rumus_b200.parallel.topology import build_topology
+    from rumus_b200.parallel.tp import TPContext
+    topo = build_topology(tp=tp_size, pp=pp_size)
+    cfg = LlamaConfig(vocab_size=64, seq_len=8, d_model=32, num_heads=2, num_kv_heads=2, num_layers=2,
+                      ffn_dim=64)
+    tp = TPContext(group=topo.tp_group, mode="nccl")
+    stage = ParallelLlamaStage(cfg, tp, topo.pp_idx, pp_size)
+    stage.init_weights(0.05, seed=3)
+    B, S, M = 2, 8, 2
+    stage.set_microbatch_shape(B, S)
+    units = [(f"blocks.{i}", [b]) for i, b in enumerate(stage.blocks)]
+    rest = [p for n, p in stage.named_parameters() if not n.startswith("blocks.")]
+    if rest:
+        units.append(("edge", rest))
+    opt = FSDP(stage, lr=1e-2, unit_roots=units, local_only=True, defer_update=True)
+    ps = PipelineStage(stage, topo.pp_idx, pp_size, topo.prev_stage_rank, topo.next_stage_rank,
+                       (B * S // tp_size, cfg.d_model), torch.float32, torch.device("cpu"))
+    g = torch.Generator().manual_seed(40 + topo.dp_idx)       # every replica sees its own data
+    first = topo.pp_idx == 0
+    for _ in range(2):
+        toks = [torch.randint(0, 64, (B, S + 1), generator=g) for _ in range(M)]
+        mbs = [t[:, :-1] for t in toks] if first else [t[:, 1:] for t in toks]
+        opt.zero_grad()
+        ps.run(mbs)
+        opt.reduce_grads(replicated_group=topo.tp_group, dp_group=topo.dp_group)
+        opt.step()
+    norms = {n: p.detach().clone() for n, p in stage.named_parameters() if "ln" in n}
+    sharded = {n: p.detach().clone() for n, p in stage.named_parameters() if "ln" not in n}
+    return {"dp": topo.dp_idx, "pp": topo.pp_idx, "tp": topo.tp_idx, "norms": norms, "sharded": sharded}
+
+
+def test_llama_stage_engine_keeps_replicated_weights_in_sync():
+    # tp2 x pp2: the norm weights of the two tensor-parallel ranks of a stage stay identical and move
+    out = run_ranks(_tp_pp_dp_train_worker, 4, 2, 2)
+    for pp in (0, 1):
+        a, b = [o for o in out if o["pp"] == pp]
+        assert a["norms"] and all(torch.equal(a["norms"][k], b["norms"][k]) for k in a["norms"])
+        assert any((v - 1.0).abs().max() > 1e-4 for v in a["norms"].values())
+
+
+def test_llama_tp2_pp2_dp2_replicas_stay_identical():
+    out = run_ranks(_tp_pp_dp_train_worker, 8, 2, 2, timeout=400)
+    for pp in (0, 1):
+        for tp in (0, 1):
+            a, b = [o for o in out if o["pp"] == pp and o["tp"] == tp]
+            assert a["dp"] != b["dp"]
+            for k in a["sharded"]:
+                assert torch.equal(a["sharded"][k], b["sharded"][k]), k
+            for k in a["norms"]:
+                assert torch.equal(a["norms"][k], b["norms"][k]), k
 
 
 # ------------------------------------------------------------------ DP
