@@ -48,8 +48,12 @@ struct GemmParams {
   int* sched;            // device int[2] {next tile, finished CTAs} for dynamic tile scheduling, or null
   int split_k;           // > 1: K is cut into this many slices, every (tile, slice) is a work item and
                          // the epilogue adds into a zero-initialised fp32 output (no bias/act/residual)
-  int pair_release;      // two-CTA kernel only: 0 = the leader's commits arrive on both CTAs' barriers,
-                         // 1 = they arrive on the leader's own barriers and are forwarded to the peer
+  int tma_store;         // two-CTA kernel only: the output goes through shared memory and TMA stores
+                         // (needs a 16-byte aligned base and row pitch); 0 = per-row stores
+  int pair_commit;       // two-CTA kernel only: 1 = one commit arrives on both CTAs' barriers, 0 = one
+                         // commit per CTA
+  long long* dbg;        // two-CTA kernel only: when set, every pair's MMA warp leaves {cycles in the
+                         // kernel, cycles waiting for operands, cycles waiting for an accumulator, tiles}
 };
 
 struct NoHooks {
@@ -68,6 +72,9 @@ struct NoHooks {
   __device__ __forceinline__ int map_kb(int kb, int num_kb) const { return kb; }
   // Called by one lane of each epilogue warp after its 32 rows of a tile are stored.
   __device__ __forceinline__ void after_tile_store(int m_idx, int n_idx, int quarter) const {}
+  // Whether after_tile_store needs the tile's global writes to be complete (it publishes them to
+  // other GPUs); the two-CTA body then drains its TMA stores first.
+  static constexpr bool kNeedsStoreComplete = false;
   // Maps a linear tile id of this CTA to (m_idx, n_idx); default = grouped raster.
   static constexpr bool kCustomRaster = false;
   __device__ __forceinline__ void raster(int tile, int num_m, int num_n, int& m_idx,

@@ -21,6 +21,9 @@
  *    RB_NOALLOC_ERR_TOO_LARGE and a message on stderr (nothing is launched);
  *  - the first call on each device looks up the device address of the built-in array (with that
  *    device current) and caches it; make that first call before starting any stream capture;
+ *  - the grid is limited to RB_NORM_BWD_NOALLOC_MAX_PARTIALS (64) blocks, one partial row each, so
+ *    on a 148-SM GPU this variant runs slower than rb_norm_bwd (which uses two blocks per SM): it
+ *    trades speed for a fixed footprint;
  *  - all calls on a device share the one array and it keeps the previous call's contents.
  *    Nothing in it has to start at zero — every partial row that is read was written earlier in
  *    the same call — but two calls that overlap on the GPU (different streams, no ordering

@@ -95,8 +95,10 @@ class LlamaBlock(Module):
         self.mlp = LlamaMLP(cfg.d_model, cfg.ffn_dim, device, dtype)
 
     def forward(self, x):
-        h = self.attn(self.ln1(x), residual=x)
-        return self.mlp(self.ln2(h), residual=h)
+        y, skip = F.norm_skip(x, self.ln1.weight, None, self.ln1.eps, rms=True)
+        h = self.attn(y, residual=skip)
+        y2, skip2 = F.norm_skip(h, self.ln2.weight, None, self.ln2.eps, rms=True)
+        return self.mlp(y2, residual=skip2)
 
 
 class Llama(Module):

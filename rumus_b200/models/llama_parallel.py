@@ -47,14 +47,17 @@ class ParallelLlamaBlock(Module):
 
     def forward(self, x_local, batch: int, seq: int):
         H, Hkv, hd = self.h_local, self.hkv_local, self.hd
-        qkv = self.qkv(self.ln1(x_local))                       # [M, (H + 2Hkv) * hd] local heads
+        # the skip stream comes out of the norm op and goes into the row-parallel layer's reduction:
+        # no stand-alone residual add in forward, none for the two gradients in backward
+        y1, skip = F.norm_skip(x_local, self.ln1.weight, None, self.ln1.eps, rms=True)
+        qkv = self.qkv(y1)                                      # [M, (H + 2Hkv) * hd] local heads
         qkv = F.rope_qkv(qkv.view(batch, seq, -1), seq, H, Hkv, hd, self.cfg.rope_theta)
         q, k, v = qkv.split([H * hd, Hkv * hd, Hkv * hd], dim=-1)
         o = F.flash_attention(q.view(batch, seq, H, hd), k.view(batch, seq, Hkv, hd),
                               v.view(batch, seq, Hkv, hd), True)
-        h = x_local + self.out_proj(o.reshape(batch * seq, H * hd))
-        gu = self.gate_up(self.ln2(h))
-        return h + self.down(F.swiglu(gu))
+        h = self.out_proj(o.reshape(batch * seq, H * hd), residual=skip)
+        y2, skip2 = F.norm_skip(h, self.ln2.weight, None, self.ln2.eps, rms=True)
+        return self.down(F.swiglu(self.gate_up(y2)), residual=skip2)
 
 
 class _VocabParallelCE(torch.autograd.Function):

@@ -270,9 +270,13 @@ class TransformerBlock(Module):
         self.mlp_fc2 = Linear(mlp_dim, d_model, True, device, dtype)
 
     def forward(self, x, mask=None):
-        h = self.attn(self.ln1(x), mask, residual=x)
-        return F.mlp(self.ln2(h), self.mlp_fc1.weight, self.mlp_fc1.bias, self.mlp_fc2.weight,
-                     self.mlp_fc2.bias, act=self.activation, residual=h)
+        # the skip stream is taken from the norm op (see F.norm_skip): the gradient that comes back
+        # along it is added inside the norm's backward kernel
+        y, skip = F.norm_skip(x, self.ln1.weight, self.ln1.bias, self.ln1.eps)
+        h = self.attn(y, mask, residual=skip)
+        y2, skip2 = F.norm_skip(h, self.ln2.weight, self.ln2.bias, self.ln2.eps)
+        return F.mlp(y2, self.mlp_fc1.weight, self.mlp_fc1.bias, self.mlp_fc2.weight,
+                     self.mlp_fc2.bias, act=self.activation, residual=skip2)
 
 
 # activation / loss free functions (rumus/src/nn/mod.rs exports)

@@ -46,10 +46,13 @@ class QuantizedTensor:
                  scale_dtype: torch.dtype = torch.float32) -> "QuantizedTensor":
         assert group_size % 8 == 0 and weight.dim() == 2
         k, n = weight.shape
-        w = weight.detach().float().cpu()
+        # the packer is plain tensor math and runs where the weight lives (a 7B model quantised on
+        # the GPU at load time takes seconds; the same code on CPU tensors is the test oracle)
+        w = weight.detach().float()
+        dev0 = w.device
         padded_k = ((k + group_size - 1) // group_size) * group_size
         groups = padded_k // group_size
-        wp = torch.zeros(padded_k, n)
+        wp = torch.zeros(padded_k, n, device=dev0)
         wp[:k] = w
         g = wp.view(groups, group_size, n)
         mn, mx = g.min(dim=1).values, g.max(dim=1).values
@@ -63,7 +66,7 @@ class QuantizedTensor:
             zp = zp.to(scale_dtype).float()
         q = torch.clamp(torch.round(g / scale[:, None, :] + zp[:, None, :]), 0, 15).to(torch.int64)
         q = q.view(padded_k // 8, 8, n)
-        shifts = (torch.arange(8, dtype=torch.int64) * 4).view(1, 8, 1)
+        shifts = (torch.arange(8, dtype=torch.int64, device=dev0) * 4).view(1, 8, 1)
         words = (q << shifts).sum(dim=1)                      # [padded_k/8, N] as int64 in [0, 2^32)
         words = torch.where(words >= 2 ** 31, words - 2 ** 32, words).to(torch.int32)
         dev = weight.device

@@ -335,6 +335,40 @@ class _NormFn(torch.autograd.Function):
         return dx, dg, db, (dx if ctx.has_res else None), None, None
 
 
+class _NormSkipFn(torch.autograd.Function):
+    """``(norm(x), x)``: the second output is ``x`` itself, handed on as the residual stream.  Taking
+    the skip connection from here instead of from ``x`` directly means ``x`` has ONE consumer in the
+    autograd graph, so the two gradients that meet at a pre-norm block's input (through the norm and
+    through the skip) are added inside the norm-backward kernel instead of by a separate add."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps, rms):
+        y, _, stats = native.norm_fwd(x, gamma, beta, eps, rms, None)
+        ctx.rms = rms
+        ctx.has_beta = beta is not None
+        ctx.mg = (_main_grad(gamma), _main_grad(beta))
+        ctx.save_for_backward(x, gamma, stats)
+        return y, x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy, dskip):
+        x, gamma, stats = ctx.saved_tensors
+        dx, dg, db = native.norm_bwd(x, dy, gamma, stats, ctx.rms, dres=dskip, want_beta=ctx.has_beta)
+        dg = _small_grad(dg, ctx.mg[0])
+        db = _small_grad(db, ctx.mg[1]) if ctx.has_beta else None
+        return dx, dg, db, None, None
+
+
+def norm_skip(x, weight, bias=None, eps: float = 1e-5, rms: bool = False):
+    """``(norm(x), skip)`` for pre-norm blocks: use ``skip`` (same values as ``x``) as the residual of
+    the branch that consumes the norm output.  LayerNorm, or RMSNorm with ``rms=True``."""
+    if not _is_native(x):
+        if rms:
+            return rms_norm(x, weight, eps), x
+        return layer_norm(x, weight, bias, eps), x
+    return _NormSkipFn.apply(x, weight, None if rms else bias, eps, rms)
+
+
 def layer_norm(x, weight, bias, eps: float = 1e-5, residual=None):
     """LayerNorm over the last dim (reference: tensor/ops.rs:1727).  With ``residual`` the kernel
     first forms ``h = x + residual`` and returns ``(norm(h), h)``."""

@@ -50,7 +50,9 @@ def _declare(lib) -> None:
     lib.rb_gemm.argtypes = [I, I, I, P, LL, P, LL, I, I, I, P, LL, I, P, P, LL, P, LL, P, LL, I, I,
                             F, I, I, I, I, P, P]
     lib.rb_gemm_2cta.argtypes = [I, I, I, P, LL, P, LL, I, I, I, P, LL, I, P, P, LL, P, LL, P, LL, I, I,
-                                 F, I, P]
+                                 F, I, I, P]
+    lib.rb_gemm_2cta_set_debug.argtypes = [P]
+    lib.rb_gemm_2cta_set_debug.restype = None
     lib.rb_bmm_simt.argtypes = [I, I, I, P, LL, LL, P, LL, LL, I, I, I, I, P, LL, LL, I, F, P]
     lib.rb_norm_fwd.argtypes = [I, I, P, P, P, P, P, P, P, LL, I, F, P]
     lib.rb_norm_bwd_partials.argtypes = [LL]
@@ -141,8 +143,14 @@ def sm_count() -> int:
     return _SM_COUNT
 
 
-def _use_2cta() -> bool:
-    return os.environ.get("RB_GEMM_2CTA", "0") == "1"
+def _use_2cta(M: int, N: int) -> bool:
+    """Large 16-bit GEMMs run on CTA pairs (256- or 512-row tiles, 256 columns): less operand traffic
+    per FLOP, which is what the power-capped sustained rate follows.  Problems with fewer than half a
+    wave of such tiles, or fewer than 256 columns, keep the one-CTA kernel's smaller tiles.
+    ``RB_GEMM_2CTA=0`` switches the pair kernel off."""
+    if os.environ.get("RB_GEMM_2CTA", "1") != "1" or N < 256 or M < 256:
+        return False
+    return ((M + 255) // 256) * ((N + 255) // 256) * 4 >= sm_count()
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
@@ -150,7 +158,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
          aux_out: bool = False, aux_in: Optional[torch.Tensor] = None, dact: Optional[str] = None,
          out_dtype: Optional[torch.dtype] = None, alpha: float = 1.0,
          out: Optional[torch.Tensor] = None, path: int = 0, bn: int = 0, max_ctas: int = 0,
-         split_k: int = 0):
+         split_k: int = 0, mt: int = 0):
     """``out = dact'(aux_in) * act(alpha * a @ b + bias) + residual``.
 
     ``a`` is logical [M,K], ``b`` logical [K,N]; either may be a transposed view
@@ -159,8 +167,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
     when ``aux_out``.
 
     ``path``: 0 automatic, 1 force the one-CTA tcgen05 kernel, 2 force the SIMT kernel, 3 force the
-    two-CTA tcgen05 kernel (also taken automatically for large 16-bit problems when
-    ``RB_GEMM_2CTA=1``).
+    two-CTA tcgen05 kernel (taken automatically for large 16-bit problems); ``mt`` picks its tile:
+    0 automatic, 1 = 256 x 256, 2 = 512 x 256.
 
     ``split_k`` (0 = automatic): when the output has far fewer tiles than the GPU has SMs and K
     is long (weight gradients of convolutions: M, N a few hundred, K = batch x pixels), K is cut
@@ -224,13 +232,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
             ws.add_(residual)
         out.copy_(ws)
         return out
-    if path in (0, 3) and (path == 3 or _use_2cta()) and a.dtype != torch.float32 and M >= 256 and N >= 256:
-        # two-CTA kernel (256 x 256 tiles, each SM stages half of B); opt-in, see gemm_2cta.cu
+    if path in (0, 3) and a.dtype != torch.float32 and M >= 256 and N >= 256 and (path == 3 or _use_2cta(M, N)):
+        # two-CTA kernel (each SM stages half of the B tile), see gemm_pair.cuh
         rc = L.rb_gemm_2cta(dt, a_mn, b_mn, ptr(a), lda, ptr(b), ldb, M, N, K, ptr(out), out.stride(0),
                             out_f32, ptr(bias), ptr(residual),
                             residual.stride(0) if residual is not None else 0, ptr(pre), N, ptr(aux_in),
                             aux_in.stride(0) if aux_in is not None else 0, ACT_CODES[act], ACT_CODES[dact],
-                            float(alpha), max_ctas, stream_ptr())
+                            float(alpha), max_ctas, mt, stream_ptr())
         if rc != 13:
             check(rc, "rb_gemm_2cta")
             count_launch()

@@ -21,6 +21,8 @@ native.register_signature("rb_int4_gemv", [I, I, P, P, P, P, P, P, P, I, I, I, I
 native.register_signature("rb_int4_dequant", [I, I, P, P, P, P, I, I, I, P])
 native.register_signature("rb_w4a16_slices", [I, I])
 native.register_signature("rb_w4a16_gemm", [I, I, P, c_longlong, P, P, P, P, P, P, P, I, I, I, I, I, P])
+native.register_signature("rb_w8a16_slices", [I, I])
+native.register_signature("rb_w8a16_gemm", [I, P, c_longlong, P, I, P, P, P, P, I, I, I, P])
 native.register_signature("rb_q8_quantize", [I, P, P, I, I, I, P])
 native.register_signature("rb_q8_dequantize", [I, P, P, I, I, I, P])
 
@@ -39,25 +41,26 @@ def int4_dequant(qw, dtype: torch.dtype) -> torch.Tensor:
     return dense
 
 
-# Batches of GEMV_CHUNKED_MAX_M+1 .. 128 rows can take the fused W4A16 tcgen05 kernel
+# Batches of GEMV_CHUNKED_MAX_M+1 .. W4A16_MAX_M rows take the fused W4A16 tcgen05 kernel
 # (csrc/kernels/w4a16_gemm.cu), which expands the packed weight inside shared memory instead of
-# writing a dense 16-bit copy.  Opt-in (RB_W4A16=1) until it has been measured against the
-# dequantise + GEMM path.
+# writing a dense 16-bit copy (RB_W4A16=0 switches back to dequantise + GEMM).
 W4A16_MAX_M = 128
+W4A16_ROUTE_MAX_M = 48     # above this the split-K additions of the fused kernel cost more than a dense copy
 
 
 def w4a16_enabled() -> bool:
-    return os.environ.get("RB_W4A16", "0") == "1"
+    return os.environ.get("RB_W4A16", "1") == "1"
 
 
-def int4_matmul_fused(x: torch.Tensor, qw, bias=None):
-    """The fused W4A16 kernel; returns ``None`` when the shape / alignment is outside what it covers."""
+def int4_matmul_fused(x: torch.Tensor, qw, bias=None, out=None):
+    """The fused W4A16 kernel; returns ``None`` when the shape / alignment is outside what it covers.
+    ``out``: contiguous ``[M, N]`` tensor to write into (for instance a peer-visible buffer)."""
     L = native.lib()
     M, K = x.shape
     if M > W4A16_MAX_M or x.dtype not in (torch.bfloat16, torch.float16):
         return None
     x = x.contiguous()
-    y = torch.empty((M, qw.n), dtype=x.dtype, device=x.device)
+    y = out if out is not None else torch.empty((M, qw.n), dtype=x.dtype, device=x.device)
     ws = counters = None
     split = L.rb_w4a16_slices(qw.n, qw.padded_k) > 1
     if split:
@@ -93,21 +96,38 @@ def _w4_workspace(device, numel: int, tiles: int):
     return ws, cnt
 
 
-def int4_matmul(x: torch.Tensor, qw, bias=None) -> torch.Tensor:
-    """x [M, K] @ dequant(qw) [K, N]."""
+_GEMV_SCRATCH = {}
+
+
+def _gemv_scratch(device, numel: int) -> torch.Tensor:
+    """Per-device split-K partial-sum buffer of the GEMV, reused by every call on the decode loop
+    (the launches of one stream run in order; the buffer is fully rewritten by each launch before
+    its reduction pass reads it).  It only grows."""
+    key = (device.type, device.index)
+    buf = _GEMV_SCRATCH.get(key)
+    if buf is None or buf.numel() < numel:
+        buf = torch.empty(max(numel, 1 << 20), dtype=torch.float32, device=device)
+        _GEMV_SCRATCH[key] = buf
+    return buf
+
+
+def int4_matmul(x: torch.Tensor, qw, bias=None, out=None) -> torch.Tensor:
+    """x [M, K] @ dequant(qw) [K, N]; ``out`` (optional): contiguous ``[M, N]`` destination."""
     L = native.lib()
     M, K = x.shape
     assert K == qw.k
     x = x.contiguous()
-    if GEMV_CHUNKED_MAX_M < M <= W4A16_MAX_M and w4a16_enabled():
-        y = int4_matmul_fused(x, qw, bias)
+    if out is not None:
+        assert out.shape == (M, qw.n) and out.dtype == x.dtype and out.is_contiguous()
+    if GEMV_CHUNKED_MAX_M < M <= W4A16_ROUTE_MAX_M and w4a16_enabled():
+        y = int4_matmul_fused(x, qw, bias, out)
         if y is not None:
             return y
     if M <= GEMV_CHUNKED_MAX_M:
         # decode batches: the packed weights are streamed once per 32 rows
         splits = L.rb_int4_gemv_splits(qw.padded_k, qw.n)
-        y = torch.empty((M, qw.n), dtype=x.dtype, device=x.device)
-        scratch = torch.empty((splits, min(M, GEMV_MAX_M), qw.n), dtype=torch.float32, device=x.device)
+        y = out if out is not None else torch.empty((M, qw.n), dtype=x.dtype, device=x.device)
+        scratch = _gemv_scratch(x.device, splits * min(M, GEMV_MAX_M) * qw.n)
         for r0 in range(0, M, GEMV_MAX_M):
             rows = min(GEMV_MAX_M, M - r0)
             check(L.rb_int4_gemv(native.dtype_code(x.dtype), native.dtype_code(qw.scales.dtype),
@@ -118,7 +138,7 @@ def int4_matmul(x: torch.Tensor, qw, bias=None) -> torch.Tensor:
             count_launch(2)
         return y
     dense = int4_dequant(qw, x.dtype)
-    return native.gemm(x, dense, bias=bias)
+    return native.gemm(x, dense, bias=bias, out=out)
 
 
 class QMatmulInt4Fn(torch.autograd.Function):
@@ -156,5 +176,41 @@ def dequantize_q8_cuda(q, dtype: torch.dtype) -> torch.Tensor:
     return out
 
 
-def matmul_q8_cuda(x: torch.Tensor, q) -> torch.Tensor:
-    return native.gemm(x.contiguous(), dequantize_q8_cuda(q, x.dtype))
+W8A16_MAX_M = 128          # rows one fused launch covers (the batch is the MMA's N dimension)
+W8A16_MAX_CHUNKS = 4       # larger batches would re-read the weight more often than dequantising it once
+
+
+def q8_matmul_fused(x: torch.Tensor, q, bias=None):
+    """The fused W8A16 kernel (``csrc/kernels/w8a16_gemm.cu``): the quantised blocks are expanded in
+    shared memory inside the GEMM.  Returns ``None`` when the shape / dtype is outside what it covers."""
+    L = native.lib()
+    M, K = x.shape
+    if x.dtype not in (torch.bfloat16, torch.float16) or M > W8A16_MAX_M * W8A16_MAX_CHUNKS:
+        return None
+    if K % 8 or q.block_size % 8 or K != q.k:
+        return None
+    x = x.contiguous()
+    y = torch.empty((M, q.n), dtype=x.dtype, device=x.device)
+    ws = counters = None
+    if L.rb_w8a16_slices(q.n, K) > 1:
+        ws, counters = _w4_workspace(x.device, min(M, W8A16_MAX_M) * q.n, (q.n + 127) // 128)
+    for r0 in range(0, M, W8A16_MAX_M):
+        rows = min(W8A16_MAX_M, M - r0)
+        rc = L.rb_w8a16_gemm(native.dtype_code(x.dtype), ptr(x[r0:r0 + rows]), c_longlong(x.stride(0)),
+                             ptr(q.data), q.block_size, ptr(bias), ptr(y[r0:r0 + rows]), ptr(ws), ptr(counters),
+                             rows, q.n, K, stream_ptr())
+        if rc == 53:
+            return None
+        check(rc, "rb_w8a16_gemm")
+        count_launch()
+    return y
+
+
+def matmul_q8_cuda(x: torch.Tensor, q, bias=None) -> torch.Tensor:
+    """``x [M, K] @ dequant(q) [K, N]`` (+ bias): 16-bit batches of up to 512 rows run the fused
+    dequantise-in-shared-memory kernel; fp32 activations and larger batches expand the weight once
+    and use the dense GEMM."""
+    y = q8_matmul_fused(x, q, bias)
+    if y is not None:
+        return y
+    return native.gemm(x.contiguous(), dequantize_q8_cuda(q, x.dtype), bias=bias)

@@ -204,10 +204,14 @@ class DataParallel:
         if self.comm_stream is not None:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
         if self.mode != "fused":
+            # unscale and non-finite check stay on the device (no host round trip per bucket): the
+            # scale is a device scalar, the flag is accumulated with a device-side maximum
             inv = self._inv_scale
             for b in self.buckets:
-                s_ = (float(inv.item()) if inv is not None else 1.0) / self.world
-                b.flat.mul_(s_)
-                if not torch.isfinite(b.flat).all():
-                    self.found_inf.fill_(1)
+                if inv is not None:
+                    b.flat.mul_((inv / self.world).to(b.flat.dtype))
+                elif self.world > 1:
+                    b.flat.mul_(1.0 / self.world)
+                bad = torch.logical_not(torch.isfinite(b.flat).all()).to(self.found_inf.dtype)
+                torch.maximum(self.found_inf, bad.reshape(self.found_inf.shape), out=self.found_inf)
         return self.found_inf

@@ -151,13 +151,14 @@ def _announce(ctx: TPContext, epoch: int) -> None:
     fused_ops.signal_peers(ctx.arena, ctx.enter_flags, epoch)
 
 
-def _fused_gemm_rs(ctx: TPContext, a_mat, w, bias=None):
+def _fused_gemm_rs(ctx: TPContext, a_mat, w, bias=None, residual=None):
     with trace_range("tp.fused.gemm_rs"):
-        return _fused_gemm_rs_impl(ctx, a_mat, w, bias)
+        return _fused_gemm_rs_impl(ctx, a_mat, w, bias, residual)
 
 
-def _fused_gemm_rs_impl(ctx: TPContext, a_mat, w, bias=None):
-    """a_mat [M, K_local], w [K_local, N] -> y_local [M/T, N] (sum over ranks)."""
+def _fused_gemm_rs_impl(ctx: TPContext, a_mat, w, bias=None, residual=None):
+    """a_mat [M, K_local], w [K_local, N] -> y_local [M/T, N] (sum over ranks, + bias, + residual:
+    both are added by the reducing owner of each output tile)."""
     from . import fused_ops
     M, K = a_mat.shape
     N = w.shape[1]
@@ -166,7 +167,7 @@ def _fused_gemm_rs_impl(ctx: TPContext, a_mat, w, bias=None):
     epoch = ctx.next_epoch()
     fused_ops.gemm_rs(ctx.arena, a_mat, w, partial_off=ctx.partial_off,
                       tile_flags_off=ctx.tile_flags_off, tile_counters=ctx.tile_counters, epoch=epoch,
-                      out=out, bias=bias)
+                      out=out, bias=bias, residual=residual)
     return out
 
 
@@ -205,14 +206,17 @@ class _ColumnParallelFn(torch.autograd.Function):
 
 class _RowParallelFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, bias, tp: TPContext):
+    def forward(ctx, x, w, bias, tp: TPContext, residual=None):
         if tp.mode == "fused" and x.is_cuda and _fusable(tp, x.shape[0]):
-            y_local = _fused_gemm_rs(tp, x, w, bias)
+            y_local = _fused_gemm_rs(tp, x, w, bias, residual.contiguous() if residual is not None else None)
         else:
             y_local = tp.reduce_scatter_rows(_mm(x, w))
             if bias is not None:
                 y_local = y_local + bias
+            if residual is not None:
+                y_local = y_local + residual
         ctx.tp = tp
+        ctx.has_res = residual is not None
         ctx.has_bias = bias is not None
         ctx.w_mg = F._main_grad(w)
         ctx.save_for_backward(x, w)
@@ -232,7 +236,7 @@ class _RowParallelFn(torch.autograd.Function):
         db = None
         if ctx.has_bias:
             db = native.colsum(dy_local) if dy_local.is_cuda else dy_local.sum(0)
-        return dx, dw, db, None
+        return dx, dw, db, None, (dy_local if ctx.has_res else None)
 
 
 _fallback_logged = set()
@@ -318,10 +322,12 @@ class RowParallelLinear(Module):
         if self.bias is not None:
             mark_tp_replicated(self.bias)
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
+        """``residual``: token-sharded ``[M/T, out]`` tensor added to the reduced output (inside the
+        fused kernel's reduction)."""
         if self.tp.world == 1:
-            return F.linear(x, self.weight, self.bias)
-        return _RowParallelFn.apply(x, self.weight, self.bias, self.tp)
+            return F.linear(x, self.weight, self.bias, residual=residual)
+        return _RowParallelFn.apply(x, self.weight, self.bias, self.tp, residual)
 
 
 def scatter_rows(x: torch.Tensor, tp: TPContext) -> torch.Tensor:

@@ -167,14 +167,17 @@ class Int4LlamaShard:
         ffn_local = m.ffn_dim // world
         # row-parallel K splits must fall on quantisation-group boundaries
         assert (self.h_local * hd) % cfg.group_size == 0 and ffn_local % cfg.group_size == 0 or world == 1
-        g = torch.Generator(device="cpu").manual_seed(seed)
+        # full matrices are drawn (same seed on every rank, so the slices fit together) and
+        # quantised on the device the shard lives on
+        gdev = device if torch.device(device).type == "cuda" else "cpu"
+        g = torch.Generator(device=gdev).manual_seed(seed)
         std = 0.02
 
         def rnd(*shape):
-            return torch.randn(*shape, generator=g) * std
+            return torch.randn(*shape, generator=g, device=gdev) * std
 
         def q(w):
-            return QuantizedTensor.from_f32(w, cfg.group_size, cfg.scale_dtype).to(device)
+            return QuantizedTensor.from_f32(w.contiguous(), cfg.group_size, cfg.scale_dtype).to(device)
 
         self.emb = rnd(m.vocab_size, m.d_model).to(cfg.dtype).to(device)
         self.layers: List[_Layer] = []
@@ -322,6 +325,11 @@ class Request:
 
 
 class Engine:
+    # partial sums up to this size take the one-shot all-reduce (every rank reads all partials:
+    # one flag round, latency bound); larger ones (long prompt chunks) are bandwidth bound and go
+    # through NCCL's reduce-scatter / all-gather schedule
+    ONESHOT_MAX_BYTES = 2 << 20
+
     def __init__(self, cfg: ServeConfig, device=None, group: Optional[dist.ProcessGroup] = None, seed: int = 0):
         self.cfg = cfg
         self.group = group
@@ -338,13 +346,12 @@ class Engine:
         self._ar = None
         if self.world > 1 and cfg.comm_mode == "fused" and self.device.type == "cuda":
             from ..parallel.symm import SymmArena
-            self.arena = SymmArena(64 << 20, group)
             n = cfg.token_budget * cfg.model.d_model
-            self._ar_buf, _ = self.arena.alloc(n, cfg.dtype)
-            self._ar_flags = (self.arena.alloc_flags(self.world), self.arena.alloc_flags(self.world),
-                              self.arena.alloc_flags(self.world))
-            self._ar_cnt = self.arena.alloc_local_ints(1)
-            self._ar_found = torch.zeros(1, dtype=torch.int32, device=self.device)
+            esz = torch.empty((), dtype=cfg.dtype).element_size()
+            self.arena = SymmArena(2 * n * esz + (1 << 20), group)
+            # two partial-sum buffers used in turn (see csrc/comm/oneshot_allreduce.cu)
+            self._ar_bufs = [self.arena.alloc(n, cfg.dtype)[0] for _ in range(2)]
+            self._ar_flags = self.arena.alloc_flags(self.world)
             self._ar_epoch = 0
             self.arena.barrier()
             self._ar = True
@@ -359,26 +366,28 @@ class Engine:
     def has_work(self) -> bool:
         return self.sched.num_waiting() + self.sched.num_running() > 0
 
-    # ------------------------------------------------------------------ TP all-reduce
-    def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+    # ------------------------------------------------------------------ row-parallel layer + all-reduce
+    def _row_parallel(self, h: torch.Tensor, qw, residual: torch.Tensor) -> torch.Tensor:
+        """``residual + sum over ranks of (h @ dequant(qw))``.  Fused mode: the matmul writes its
+        partial result straight into a peer-visible buffer and ONE kernel does the flag round, the
+        reduction over all ranks' partials and the residual add; NCCL mode: matmul, all-reduce, add."""
         if self.world == 1:
-            return x
-        if self._ar:
+            return residual + qmatmul_int4(h, qw)
+        if self._ar and h.shape[0] * qw.n * h.element_size() <= self.ONESHOT_MAX_BYTES:
+            from ..ops.quant_cuda import int4_matmul
             from ..parallel import fused_ops
-            n = x.numel()
-            pad = (-n) % (8 * self.world)
-            buf = self._ar_buf[: n + pad]
-            buf[:n].copy_(x.reshape(-1))
-            if pad:
-                buf[n:].zero_()
+            T = h.shape[0]
             self._ar_epoch += 1
-            ef, xf, nf = self._ar_flags
-            fused_ops.allreduce_unscale(self.arena, buf, enter_flags_off=ef, exit_flags_off=xf,
-                                        inf_flags_off=nf, epoch=self._ar_epoch, found_inf=self._ar_found,
-                                        done_counter=self._ar_cnt, ctas=8)
-            return buf[:n].view(x.shape).clone()
-        dist.all_reduce(x, group=self.group)
-        return x
+            part = self._ar_bufs[self._ar_epoch & 1][: T * qw.n].view(T, qw.n)
+            int4_matmul(h, qw, out=part)
+            out = torch.empty_like(residual)
+            with trace_range("serve.oneshot_allreduce"):
+                fused_ops.oneshot_allreduce(self.arena, part, out, flags_off=self._ar_flags,
+                                            epoch=self._ar_epoch, residual=residual.contiguous())
+            return out
+        part = qmatmul_int4(h, qw)
+        dist.all_reduce(part, group=self.group)
+        return residual + part
 
     # ------------------------------------------------------------------ forward
     def _forward(self, tokens: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, attend):
@@ -398,12 +407,10 @@ class Engine:
             _rope(k, positions, Hkv, hd, m.rope_theta)
             self.cache.append(li, k, v, slots)
             o = attend(li, q.reshape(T, H, hd), k.reshape(T, Hkv, hd), v.reshape(T, Hkv, hd))
-            a = self._all_reduce(qmatmul_int4(o.reshape(T, H * hd).contiguous(), L.out))
-            x = x + a
+            x = self._row_parallel(o.reshape(T, H * hd).contiguous(), L.out, x)
             h2 = F.rms_norm(x, L.ln2, m.rms_eps)
             gu = qmatmul_int4(h2, L.gate_up)
-            d = self._all_reduce(qmatmul_int4(F.swiglu(gu), L.down))
-            x = x + d
+            x = self._row_parallel(F.swiglu(gu), L.down, x)
         return F.rms_norm(x, md.ln_f, m.rms_eps)
 
     def _logits_argmax(self, hidden: torch.Tensor) -> torch.Tensor:

@@ -26,8 +26,14 @@ from .engine import Engine, ServeConfig
 
 
 class EngineWorker:
-    def __init__(self, engine: Engine, max_queue: int = 1024, idle_sleep_s: float = 0.0005):
+    """Owns the engine thread.  With tensor parallelism this is rank 0's worker: before every engine
+    step it tells the other ranks which requests joined (one host-side broadcast over ``cpu_group``),
+    so every rank adds the same requests before the same step; ``follower_loop`` is what the other
+    ranks run."""
+
+    def __init__(self, engine: Engine, max_queue: int = 1024, idle_sleep_s: float = 0.0005, cpu_group=None):
         self.engine = engine
+        self.cpu_group = cpu_group
         self.inbox: "queue.Queue" = queue.Queue(maxsize=max_queue)
         self.waiters: Dict[int, tuple] = {}
         self.ids = itertools.count(1)
@@ -45,6 +51,11 @@ class EngineWorker:
         self.stop_flag = True
         self.thread.join(timeout=5)
 
+    def _announce(self, new_requests, stop: bool = False) -> None:
+        if self.cpu_group is not None:
+            import torch.distributed as dist
+            dist.broadcast_object_list([("stop",) if stop else ("step", new_requests)], src=0, group=self.cpu_group)
+
     def submit(self, token_ids, max_new, loop, fut) -> bool:
         try:
             self.inbox.put_nowait((next(self.ids), list(token_ids), int(max_new), loop, fut, time.time()))
@@ -55,6 +66,7 @@ class EngineWorker:
     def _run(self):
         eng = self.engine
         while not self.stop_flag:
+            joined = []
             while True:
                 try:
                     rid, toks, max_new, loop, fut, t0 = self.inbox.get_nowait()
@@ -62,11 +74,13 @@ class EngineWorker:
                     break
                 if eng.add_request(rid, toks, max_new, arrival=t0):
                     self.waiters[rid] = (loop, fut, t0)
+                    joined.append((rid, toks, max_new))
                 else:
                     loop.call_soon_threadsafe(fut.set_exception, ValueError("request does not fit the KV pool"))
             if not eng.has_work():
-                time.sleep(self.idle_sleep_s)
+                time.sleep(self.idle_sleep_s)     # the other ranks stay parked in their broadcast
                 continue
+            self._announce(joined)
             for rid in eng.step():
                 req = eng.requests.pop(rid)
                 loop, fut, t0 = self.waiters.pop(rid)
@@ -78,6 +92,22 @@ class EngineWorker:
                         self.itl_ms.append((now - req.first_token_time) * 1e3 / (len(req.output) - 1))
                 res = {"generated_ids": req.output, "latency_ms": (time.time() - t0) * 1e3}
                 loop.call_soon_threadsafe(fut.set_result, res)
+
+
+def follower_loop(engine: Engine, cpu_group) -> None:
+    """Ranks other than 0 of a tensor-parallel server: take rank 0's word for which requests join,
+    then run the same engine step (its collectives pair up with rank 0's)."""
+    import torch.distributed as dist
+    while True:
+        box = [None]
+        dist.broadcast_object_list(box, src=0, group=cpu_group)
+        msg = box[0]
+        if msg[0] == "stop":
+            return
+        for rid, toks, max_new in msg[1]:
+            engine.add_request(rid, toks, max_new)
+        for rid in engine.step():
+            engine.requests.pop(rid, None)
 
 
 def build_app(worker: EngineWorker):
@@ -137,18 +167,50 @@ def main(argv=None):
     ap.add_argument("--num-heads", type=int, default=4)
     ap.add_argument("--num-layers", type=int, default=2)
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    ap.add_argument("--tp", type=int, default=1,
+                    help="tensor-parallel degree: start that many ranks with python -m torch.distributed.run; "
+                         "rank 0 serves HTTP, the others follow its schedule")
+    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     a = ap.parse_args(argv)
-    from aiohttp import web
+    import os
+    from datetime import timedelta
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if a.tp != world:
+        raise SystemExit(f"--tp {a.tp} but {world} rank(s) were started")
+    dev = torch.device(a.device)
+    cpu_group = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if dev.type == "cuda":
+            dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+            torch.cuda.set_device(dev)
+            dist.init_process_group("nccl", device_id=dev)
+        else:
+            dist.init_process_group("gloo")
+        # followers park in a broadcast until rank 0 has a step for them: no timeout to speak of
+        cpu_group = dist.new_group(backend="gloo", timeout=timedelta(days=7))
     mc = LlamaConfig(vocab_size=a.vocab_size, d_model=a.hidden_dim, num_heads=a.num_heads,
                      num_kv_heads=a.num_heads, num_layers=a.num_layers, ffn_dim=4 * a.hidden_dim,
                      seq_len=2048)
-    dev = torch.device(a.device)
-    cfg = ServeConfig(model=mc, max_batch=a.max_batch, num_blocks=1024,
+    cfg = ServeConfig(model=mc, max_batch=a.max_batch, num_blocks=1024, comm_mode=a.comm,
                       dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32,
                       scale_dtype=torch.float16 if dev.type == "cuda" else torch.float32)
-    worker = EngineWorker(Engine(cfg, dev))
+    engine = Engine(cfg, dev)
+    if world > 1 and dist.get_rank() != 0:
+        follower_loop(engine, cpu_group)
+        dist.destroy_process_group()
+        return
+    from aiohttp import web
+    worker = EngineWorker(engine, cpu_group=cpu_group)
     worker.start()
-    web.run_app(build_app(worker), port=a.port)
+    try:
+        web.run_app(build_app(worker), port=a.port)
+    finally:
+        worker.stop()
+        if world > 1:
+            worker._announce([], stop=True)
+            dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -181,9 +181,8 @@ def _final_check(state, consumed, nkb, warps) -> Role:
         raise PipelineError(f"k-blocks consumed out of order: {consumed}")
 
 
-def gemm_2cta_roles(num_tiles: int, num_kb: int, stages: int = 6, epi_warps: int = 2, bug: str = "",
-                    forward_release: bool = False) -> Dict[str, Role]:
-    """The CTA pair of ``gemm_2cta_kernel`` (``csrc/kernels/gemm_2cta.cu``) walking ``num_tiles`` tiles
+def gemm_2cta_roles(num_tiles: int, num_kb: int, stages: int = 6, epi_warps: int = 2, bug: str = "") -> Dict[str, Role]:
+    """The CTA pair of ``gemm_pair_body`` (``csrc/kernels/gemm_pair.cuh``, 256 x 256 tiles) walking ``num_tiles`` tiles
     of ``num_kb`` K blocks: a copy producer per CTA (both complete on the leader's ``full`` barrier,
     whose expected byte count the leader alone arms), the leader's MMA issuer (its commits release
     the stage in both CTAs and hand the accumulator to both CTAs' epilogue warps), ``epi_warps``
@@ -191,10 +190,7 @@ def gemm_2cta_roles(num_tiles: int, num_kb: int, stages: int = 6, epi_warps: int
     on both CTAs' ``done`` barriers).  Transaction bytes are modelled as a count that may run ahead
     of the arming (a copy of the peer may land first).  ``bug``: ``"peer_not_released"`` (the leader
     forgets the commit into the peer's ``empty`` barrier), ``"half_tx"`` (the leader arms the barrier
-    for its own bytes only).  ``forward_release`` models ``GemmParams::pair_release = 1``: the commits
-    arrive on the leader's barriers only, the leader's producer passes each stage release on to the
-    peer when it reuses the stage itself, and one epilogue warp of the leader hands each accumulator
-    to the peer."""
+    for its own bytes only)."""
     full = [{"bar": Mbar(1), "tx": 0} for _ in range(stages)]          # leader's
     empty = [[Mbar(1) for _ in range(stages)] for _ in range(2)]        # per CTA
     tmem_full = [[Mbar(1) for _ in range(2)] for _ in range(2)]         # per CTA, per accumulator
@@ -220,8 +216,6 @@ def gemm_2cta_roles(num_tiles: int, num_kb: int, stages: int = 6, epi_warps: int
         for tile in range(num_tiles):
             for kb in range(num_kb):
                 yield (lambda s=stage, ph=phase: empty[cta][s].passed(ph ^ 1))
-                if forward_release and cta == 0 and issued >= stages:
-                    empty[1][stage].arrive()
                 issued += 1
                 if state["reading"] == stage:
                     raise PipelineError(f"CTA {cta}: stage {stage} overwritten while the MMA reads it")
@@ -252,15 +246,14 @@ def gemm_2cta_roles(num_tiles: int, num_kb: int, stages: int = 6, epi_warps: int
                 yield (lambda: True)
                 state["reading"] = None
                 empty[0][stage].arrive()
-                if bug != "peer_not_released" and not forward_release:
+                if bug != "peer_not_released":
                     empty[1][stage].arrive()
                 stage += 1
                 if stage == stages:
                     stage, phase = 0, phase ^ 1
             acc_tag[acc] = tile
             tmem_full[0][acc].arrive()
-            if not forward_release:
-                tmem_full[1][acc].arrive()
+            tmem_full[1][acc].arrive()
             acc += 1
             if acc == 2:
                 acc, acc_phase = 0, acc_phase ^ 1
@@ -269,8 +262,6 @@ def gemm_2cta_roles(num_tiles: int, num_kb: int, stages: int = 6, epi_warps: int
         acc, acc_phase = 0, 0
         for tile in range(num_tiles):
             yield (lambda a=acc, ph=acc_phase: tmem_full[cta][a].passed(ph))
-            if forward_release and cta == 0 and w == 0:
-                tmem_full[1][acc].arrive()
             if acc_tag[acc] != tile:
                 raise PipelineError(f"CTA {cta} epilogue {w}: accumulator {acc} holds tile {acc_tag[acc]}, expected {tile}")
             yield (lambda: True)                            # tcgen05.ld + stores

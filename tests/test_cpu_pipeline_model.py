@@ -51,8 +51,6 @@ def test_two_cta_gemm_pair_protocol(tiles, nkb):
         assert run(gemm_2cta_roles(tiles, nkb), seed) > 0
     for stages in (2, 3):
         run(gemm_2cta_roles(tiles, nkb, stages=stages), 0)
-    for seed in range(12):      # releases forwarded by the leader instead of committed into the peer
-        assert run(gemm_2cta_roles(tiles, nkb, forward_release=True), seed) > 0
 
 
 @pytest.mark.parametrize("bug", ["peer_not_released", "half_tx"])

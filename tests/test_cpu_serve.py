@@ -149,3 +149,83 @@ def test_head_major_kv_cache_gives_the_same_attention():
         ctx = torch.tensor([T, 20], dtype=torch.int32)
         outs.append(paged_decode_attention(q, cache.k[0], cache.v[0], tables, ctx, 0.1, T, head_major=hm))
     assert torch.allclose(outs[0], outs[1], atol=1e-6)
+
+
+# ------------------------------------------------------------------ tensor-parallel serving (gloo ranks)
+def _tp_cfg():
+    mc = LlamaConfig(vocab_size=256, seq_len=256, d_model=256, num_heads=2, num_kv_heads=2,
+                     num_layers=2, ffn_dim=256)
+    return ServeConfig(model=mc, num_blocks=64, block_size=16, max_batch=4, token_budget=64,
+                       dtype=torch.float32, scale_dtype=torch.float32, comm_mode="nccl")
+
+
+def _tp_requests():
+    r = random.Random(5)
+    return [(i + 1, [r.randrange(256) for _ in range(r.randint(5, 90))], r.randint(3, 8)) for i in range(4)]
+
+
+def _tp_server_worker(rank, world):
+    """Rank 0 runs the engine worker the HTTP server uses (requests go straight into its inbox), the
+    other rank follows its schedule; returns rank 0's outputs."""
+    import time
+    from datetime import timedelta
+    import torch.distributed as dist
+    from rumus_b200.serve.server import EngineWorker, follower_loop
+    cpu_group = dist.new_group(backend="gloo", timeout=timedelta(seconds=120))
+    engine = Engine(_tp_cfg())
+    assert engine.world == 2
+    if rank != 0:
+        follower_loop(engine, cpu_group)
+        return None
+    worker = EngineWorker(engine, cpu_group=cpu_group)
+    done = {}
+
+    class _Loop:                      # the worker only ever calls call_soon_threadsafe(callback, value)
+        def call_soon_threadsafe(self, fn, val):
+            fn(val)
+
+    class _Fut:
+        def __init__(self, rid):
+            self.rid = rid
+
+        def set_result(self, res):
+            done[self.rid] = res["generated_ids"]
+
+        def set_exception(self, e):
+            done[self.rid] = e
+
+    worker.start()
+    for rid, toks, n in _tp_requests():
+        worker.inbox.put((rid, toks, n, _Loop(), _Fut(rid), time.time()))
+        time.sleep(0.01)
+    t0 = time.time()
+    while len(done) < 4 and time.time() - t0 < 100:
+        time.sleep(0.01)
+    worker.stop()
+    worker._announce([], stop=True)
+    return {k: torch.tensor(v) for k, v in done.items()}
+
+
+def test_tensor_parallel_server_matches_single_rank_engine():
+    from dist_utils import run_ranks
+    out = run_ranks(_tp_server_worker, 2)[0]
+    e = Engine(_tp_cfg())
+    for rid, toks, n in _tp_requests():
+        e.add_request(rid, toks, n)
+    ref = _drain(e)
+    assert sorted(out) == sorted(ref)
+    for rid in ref:
+        assert out[rid].tolist() == ref[rid], rid
+
+
+def _tp_loadgen_worker(rank, world):
+    from rumus_b200.serve.loadgen import run
+    engine = Engine(_tp_cfg())
+    res = run(engine, n_requests=5, rate=200.0, prompt_rng=(5, 40), out_rng=(3, 6), seed=2, vocab=256)
+    return {"tokens": res["generated_tokens"], "steps": res["steps"]}
+
+
+def test_tensor_parallel_load_generator_keeps_ranks_in_step():
+    from dist_utils import run_ranks
+    a, b = run_ranks(_tp_loadgen_worker, 2)
+    assert a == b and a["tokens"] > 0

@@ -1,14 +1,8 @@
-"""Fused W4A16 tcgen05 GEMM (``csrc/kernels/w4a16_gemm.cu``) against the dequantised fp32 product.
-
-The kernel is opt-in (``RB_W4A16=1``): these tests run only when that switch is set, which is also
-what routes ``int4_matmul`` to the kernel."""
-import os
-
+"""Fused W4A16 tcgen05 GEMM (``csrc/kernels/w4a16_gemm.cu``) against the dequantised fp32 product."""
 import pytest
 import torch
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("RB_W4A16", "0") != "1", reason="fused W4A16 kernel is opt-in")]
+pytestmark = pytest.mark.gpu
 
 
 def _rel(a, b):

@@ -4,8 +4,9 @@ Some users of the library cannot allocate device memory when they need this kern
 budgets, code running inside someone else's pool or under a lock where cudaMalloc is off limits),
 so ``rb_norm_bwd_noalloc`` keeps its scratch in an array built into the library.  The test drives
 the raw symbol with ctypes — no helper from the package in between — and checks it against the
-regular entry point on two back-to-back calls (the second reuses the array with different sizes,
-so leftovers of the first call must not matter) plus the size refusal.
+regular entry point and against a plain fp32 PyTorch backward on two back-to-back calls (the second
+reuses the array with different sizes, so leftovers of the first call must not matter; one of them
+passes a gradient to add to dx), plus the size refusal.
 
 Collected last on purpose: a ``-x`` run has already exercised everything else when it gets here.
 """
@@ -23,7 +24,7 @@ def _rel(a, b):
     return ((a - b).norm() / (b.norm() + 1e-12)).item()
 
 
-def _call_noalloc(lib, x, dy, gamma, stats, rms):
+def _call_noalloc(lib, x, dy, gamma, stats, rms, dres=None):
     rows, D = x.shape
     dx = torch.empty_like(x)
     dgamma = torch.empty_like(gamma)
@@ -31,7 +32,8 @@ def _call_noalloc(lib, x, dy, gamma, stats, rms):
     code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[x.dtype]
     rc = lib.rb_norm_bwd_noalloc(code, 1 if rms else 0, c_void_p(x.data_ptr()),
                                  c_void_p(dy.data_ptr()), c_void_p(gamma.data_ptr()),
-                                 c_void_p(stats.data_ptr()), c_void_p(0), c_void_p(dx.data_ptr()),
+                                 c_void_p(stats.data_ptr()),
+                                 c_void_p(dres.data_ptr() if dres is not None else 0), c_void_p(dx.data_ptr()),
                                  c_void_p(dgamma.data_ptr()), c_void_p(dbeta.data_ptr()),
                                  c_longlong(rows), c_int(D),
                                  c_void_p(torch.cuda.current_stream().cuda_stream))
@@ -49,15 +51,16 @@ def test_norm_bwd_noalloc_matches_regular_entry_point_twice():
     max_dim = lib.rb_norm_bwd_noalloc_max_dim()
     assert max_dim == 4096
     torch.manual_seed(7)
-    cases = [(torch.bfloat16, 3000, 2048, False), (torch.float32, 517, 264, True)]
-    for dtype, rows, D, rms in cases:      # two calls in a row on the shared array
+    cases = [(torch.bfloat16, 3000, 2048, False, True), (torch.float32, 517, 264, True, False)]
+    for dtype, rows, D, rms, with_dres in cases:      # two calls in a row on the shared array
         x = torch.randn(rows, D, device="cuda").to(dtype)
         dy = torch.randn(rows, D, device="cuda").to(dtype)
         gamma = (1 + 0.1 * torch.randn(D, device="cuda")).to(dtype)
         beta = torch.zeros(D, device="cuda").to(dtype)
+        dres = torch.randn(rows, D, device="cuda").to(dtype) if with_dres else None
         _, _, stats = native.norm_fwd(x, gamma, None if rms else beta, 1e-5, rms)
-        ref_dx, ref_dg, ref_db = native.norm_bwd(x, dy, gamma, stats, rms)
-        rc, dx, dg, db = _call_noalloc(lib, x, dy, gamma, stats, rms)
+        ref_dx, ref_dg, ref_db = native.norm_bwd(x, dy, gamma, stats, rms, dres=dres)
+        rc, dx, dg, db = _call_noalloc(lib, x, dy, gamma, stats, rms, dres)
         assert rc == 0
         torch.cuda.synchronize()
         tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
@@ -65,6 +68,20 @@ def test_norm_bwd_noalloc_matches_regular_entry_point_twice():
         assert _rel(dg, ref_dg) < tol
         if not rms:
             assert _rel(db, ref_db) < tol
+        # the same gradients from plain fp32 PyTorch math
+        xf = x.float().requires_grad_(True)
+        gf = gamma.float().requires_grad_(True)
+        bf = beta.float().requires_grad_(True)
+        if rms:
+            yf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * gf
+        else:
+            yf = torch.nn.functional.layer_norm(xf, (D,), gf, bf, 1e-5)
+        yf.backward(dy.float())
+        want_dx = xf.grad + (dres.float() if dres is not None else 0)
+        assert _rel(dx, want_dx) < tol
+        assert _rel(dg, gf.grad) < tol
+        if not rms:
+            assert _rel(db, bf.grad) < tol
     # a row longer than the built-in array is refused, nothing runs
     D = max_dim + 8
     x = torch.randn(4, D, device="cuda")
