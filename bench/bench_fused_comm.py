@@ -39,6 +39,10 @@ def timed(fn, iters=8, warm=3):
 
 
 def main():
+    # started directly (no launcher) this is a group of one rank: the kernels then run their full
+    # code path against this GPU's own buffers, which is the case to capture under a profiler
+    os.environ.setdefault("RANK", "0"); os.environ.setdefault("WORLD_SIZE", "1")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", "29517")
     rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)

@@ -121,6 +121,8 @@ struct GatherHooks {
     return k >= num_kb ? k - num_kb : k;
   }
   __device__ __forceinline__ void after_tile_store(int, int, int) const {}
+  static constexpr bool kCustomLoadA = false, kCustomLoadB = false, kCustomRows = false;
+  static constexpr bool kNeedsStoreComplete = false;
   static constexpr bool kCustomRaster = true;
   __device__ __forceinline__ void raster(int tile, int num_m, int num_n, int& m_idx,
                                          int& n_idx) const {
@@ -185,6 +187,8 @@ struct RsHooks {
                      epoch);
     }
   }
+  static constexpr bool kCustomLoadA = false, kCustomLoadB = false, kCustomRows = false;
+  static constexpr bool kNeedsStoreComplete = true;
   static constexpr bool kCustomRaster = true;
   __device__ __forceinline__ void raster(int tile, int num_m, int num_n_, int& m_idx,
                                          int& n_idx) const {

@@ -10,13 +10,13 @@
 
 namespace rb {
 
-template <typename T, int MT, bool TMA_EPI, bool A_MN, bool B_MN>
+template <typename T, int MT, bool LEAN, bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
     gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                      const __grid_constant__ CUtensorMap tma_c, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   NoHooks hooks;
-  gemm_pair_body<T, MT, TMA_EPI, A_MN, B_MN, NoHooks>(&tma_a, &tma_b, &tma_c, p, hooks, smem_raw, blockIdx.x / 2,
+  gemm_pair_body<T, MT, LEAN, A_MN, B_MN, NoHooks>(&tma_a, &tma_b, &tma_c, p, hooks, smem_raw, blockIdx.x / 2,
                                              gridDim.x / 2);
 }
 
@@ -74,9 +74,9 @@ int max_resident_clusters(K kern, int smem_bytes) {
   return n;
 }
 
-template <typename T, int MT, bool TMA_EPI, bool A_MN, bool B_MN>
+template <typename T, int MT, bool LEAN, bool A_MN, bool B_MN>
 int launch_gemm_2cta(GemmArgs& a) {
-  using C = PairCfg<MT, TMA_EPI>;
+  using C = PairCfg<MT>;
   CUtensorMap ta, tb, tc;
   int rc = make_pair_operand_maps<T, A_MN, B_MN>(a, &ta, &tb);
   if (rc) return 1000 + rc;
@@ -86,7 +86,7 @@ int launch_gemm_2cta(GemmArgs& a) {
   } else {
     tc = ta;
   }
-  auto kern = gemm_2cta_kernel<T, MT, TMA_EPI, A_MN, B_MN>;
+  auto kern = gemm_2cta_kernel<T, MT, LEAN, A_MN, B_MN>;
   static int resident = 0;
   if (resident == 0) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
@@ -103,20 +103,26 @@ int launch_gemm_2cta(GemmArgs& a) {
   return e == cudaSuccess ? 0 : 3000 + (int)e;
 }
 
-template <typename T, int MT, bool TMA_EPI>
+template <typename T, int MT, bool LEAN>
 int launch_gemm_2cta_major(GemmArgs& a) {
-  if (!a.a_mn && !a.b_mn) return launch_gemm_2cta<T, MT, TMA_EPI, false, false>(a);
-  if (!a.a_mn && a.b_mn) return launch_gemm_2cta<T, MT, TMA_EPI, false, true>(a);
-  if (a.a_mn && !a.b_mn) return launch_gemm_2cta<T, MT, TMA_EPI, true, false>(a);
-  return launch_gemm_2cta<T, MT, TMA_EPI, true, true>(a);
+  if (!a.a_mn && !a.b_mn) return launch_gemm_2cta<T, MT, LEAN, false, false>(a);
+  if (!a.a_mn && a.b_mn) return launch_gemm_2cta<T, MT, LEAN, false, true>(a);
+  if (a.a_mn && !a.b_mn) return launch_gemm_2cta<T, MT, LEAN, true, false>(a);
+  return launch_gemm_2cta<T, MT, LEAN, true, true>(a);
 }
 
-template <typename T, int MT>
-int launch_gemm_2cta_mt(GemmArgs& a) {
-  // an output that is not TMA-legal takes per-row stores; 256 x 256 tiles then get a 7th stage
-  if (a.p.tma_store) return launch_gemm_2cta_major<T, MT, true>(a);
-  if (MT == 1) return launch_gemm_2cta_major<T, 1, false>(a);
-  return launch_gemm_2cta_major<T, MT, true>(a);
+// Two flavours of the kernel.  LEAN: 16-bit output through the TMA-store epilogue with only the
+// common epilogue terms (alpha, bias, residual) compiled in; its epilogue code is a few KB, which is
+// what keeps the drain of 512-row tiles short (the epilogue of the full flavour — every activation,
+// derivative, side output, fp32 output, per-row stores — is so much code that fetching it costs more
+// than executing it).  FULL: everything, 256-row tiles only, where the epilogue of one tile runs
+// under the main loop of the next.
+template <typename T>
+int launch_gemm_2cta_flavour(GemmArgs& a, int mt) {
+  const GemmParams& p = a.p;
+  const bool lean = p.tma_store && !p.out_f32 && !p.aux_out && !p.aux_in && p.act == ACT_NONE;
+  if (!lean) return launch_gemm_2cta_major<T, 1, false>(a);
+  return mt == 2 ? launch_gemm_2cta_major<T, 2, true>(a) : launch_gemm_2cta_major<T, 1, true>(a);
 }
 
 // Rows of A per CTA and tile.  512 x 256 tiles move a quarter less operand data per FLOP than
@@ -128,14 +134,14 @@ int pick_pair_mt(int M, int N, int clusters) {
     const long long w = (t + clusters - 1) / clusters;
     return (double)t / (double)(w * clusters);
   };
-  return waves(512) * 1.10 >= waves(256) ? 2 : 1;
+  return waves(512) * 1.15 >= waves(256) ? 2 : 1;
 }
 
 }  // namespace rb
 
 extern "C" {
 
-// Debug hook: when set (device pointer to 4 * clusters long longs), every launch makes each pair's
+// Debug hook: when set (device pointer to 8 * clusters long longs), every launch makes each pair's
 // MMA warp record {cycles in the kernel, cycles waiting for operands, cycles waiting for an
 // accumulator, tiles done}.  Null switches it off.
 void rb_gemm_2cta_set_debug(long long* buf) { rb::g_pair_dbg = buf; }
@@ -164,10 +170,6 @@ int rb_gemm_2cta(int dtype, int a_mn, int b_mn, const void* A, long long lda, co
   p.split_k = 1;
   p.sched = rbh::dynamic_tiles() ? rbh::next_sched_slot() : nullptr;
   p.dbg = g_pair_dbg;
-  {
-    const char* e = getenv("RB_G2_COMMIT");      // "2": one commit per CTA instead of one for the pair
-    p.pair_commit = (e && e[0] == '2') ? 0 : 1;
-  }
   const int osz = out_f32 ? 4 : 2;
   p.vec_ok = al(out) && (ldc * osz) % 16 == 0 && (!residual || (al(residual) && (ldr * osz) % 16 == 0)) &&
              (!aux_out || (al(aux_out) && (ldaux_out * osz) % 16 == 0)) &&
@@ -188,8 +190,6 @@ int rb_gemm_2cta(int dtype, int a_mn, int b_mn, const void* A, long long lda, co
     const char* e = getenv("RB_G2_GROUP_M");
     if (e && atoi(e) > 0) p.group_m = atoi(e);
   }
-  if (dtype == rbh::DT_BF16)
-    return mt == 2 ? launch_gemm_2cta_mt<__nv_bfloat16, 2>(a) : launch_gemm_2cta_mt<__nv_bfloat16, 1>(a);
-  return mt == 2 ? launch_gemm_2cta_mt<__half, 2>(a) : launch_gemm_2cta_mt<__half, 1>(a);
+  return dtype == rbh::DT_BF16 ? launch_gemm_2cta_flavour<__nv_bfloat16>(a, mt) : launch_gemm_2cta_flavour<__half>(a, mt);
 }
 }

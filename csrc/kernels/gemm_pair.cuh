@@ -49,14 +49,13 @@ constexpr int G2_SCHED_CONSUMERS = 2 * G2_EPI_WARPS + 2;   // leader MMA warp, p
 // (a quarter less operand traffic per FLOP again), the two accumulators hold the tile's two row
 // blocks; the epilogue hands each back as soon as it is drained, so the next tile's first MMAs only
 // wait for the first of them.
-template <int MT, bool TMA_EPI = true>
+template <int MT>
 struct PairCfg {
   static constexpr int BM = 256 * MT;
   static constexpr int A_BYTES = MT * 128 * 128;
   static constexpr int STAGE_BYTES = A_BYTES + G2_B_BYTES;
-  // without the staging tiles of the TMA-store epilogue one more 32 KB stage fits
-  static constexpr int STAGES = MT == 1 ? (TMA_EPI ? 6 : 7) : 4;
-  static constexpr int STAGING = TMA_EPI ? 2 * G2_STAGING_BYTES : 0;
+  static constexpr int STAGES = MT == 1 ? 6 : 4;
+  static constexpr int STAGING = 2 * G2_STAGING_BYTES;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING + 1024 + 512;
   static constexpr int ACC_RELEASERS = 2 * G2_EPI_WARPS;   // epilogue warps of both CTAs drain every accumulator
 };
@@ -138,13 +137,6 @@ __device__ __forceinline__ void umma_f16_pair_w(uint32_t tmem_d, uint64_t adesc,
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
-// one commit that arrives on the barrier at this offset in BOTH CTAs of the pair
-__device__ __forceinline__ void umma_commit_pair_both_w(uint32_t bar) {
-  asm volatile(
-      "{\n\t.reg .pred e;\n\t.reg .b16 m;\n\tmov.b16 m, 3;\n\telect.sync _|e, 0xffffffff;\n\t"
-      "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}\n" ::"r"(bar)
-      : "memory");
-}
 // the barrier (anywhere in the cluster) receives one arrival once every MMA issued so far is complete
 __device__ __forceinline__ void umma_commit_pair_w(uint32_t bar_cluster_addr) {
   asm volatile(
@@ -180,7 +172,7 @@ __device__ __forceinline__ bool bar_vote_and(int id, int threads, bool pred) {
 
 // Everything of the fused epilogue except the final store: v = dact(aux_in) * act(alpha*acc + bias) + residual
 // for 32 consecutive columns of one row; the pre-activation side output is stored here.
-template <typename T, typename OT>
+template <typename T, typename OT, bool LEAN = false>
 __device__ __forceinline__ void epilogue_math32(const GemmParams& p, const uint32_t* acc_bits, long long row,
                                                 int col, int ncols_valid, bool row_ok, float* v) {
 #pragma unroll
@@ -204,16 +196,35 @@ __device__ __forceinline__ void epilogue_math32(const GemmParams& p, const uint3
   }
   const bool vec = p.vec_ok != 0;
   if (!row_ok || ncols_valid <= 0) return;
-  if (p.aux_out) store_row32<OT>(reinterpret_cast<OT*>(p.aux_out), p.ldaux_out, row, col, ncols_valid, vec, v);
-  if (p.act != ACT_NONE) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = apply_act(v[i], p.act);
+  if constexpr (!LEAN) {     // LEAN: the caller has checked that there is no side output / derivative input
+    if (p.aux_out) store_row32<OT>(reinterpret_cast<OT*>(p.aux_out), p.ldaux_out, row, col, ncols_valid, vec, v);
   }
-  if (p.aux_in) {
-    float a[32];
-    load_row32<OT>(reinterpret_cast<const OT*>(p.aux_in), p.ldaux_in, row, col, ncols_valid, vec, a);
+  if constexpr (!LEAN) {
+    // one loop per activation kind (a switch inside the unrolled loop would lay down every kind 32 times)
+    if (p.act == ACT_RELU) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] *= apply_dact(a[i], p.dact);
+      for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
+    } else if (p.act == ACT_GELU) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+    } else if (p.act == ACT_SILU) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = silu_f(v[i]);
+    }
+    if (p.aux_in) {
+      float a[32];
+      load_row32<OT>(reinterpret_cast<const OT*>(p.aux_in), p.ldaux_in, row, col, ncols_valid, vec, a);
+      if (p.dact == ACT_RELU) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = a[i] > 0.0f ? v[i] : 0.0f;
+      } else if (p.dact == ACT_GELU) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] *= gelu_tanh_grad(a[i]);
+      } else if (p.dact == ACT_SILU) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] *= silu_grad(a[i]);
+      }
+    }
   }
   if (p.residual) {
     float r[32];
@@ -244,6 +255,53 @@ __device__ __forceinline__ void stage_row32(uint8_t* staging, int r, int piece, 
   }
 }
 
+// Lean epilogue of 32 consecutive columns of one row straight into 16 packed words:
+// out = alpha * acc + bias + residual, eight columns at a time so that no 32-float temporary is live.
+template <typename T>
+__device__ __forceinline__ void lean_pack32(const GemmParams& p, const uint32_t* acc_bits, long long row, int col,
+                                            int ncols_valid, bool row_ok, uint32_t* pk) {
+  const T* b = p.bias ? reinterpret_cast<const T*>(p.bias) + col : nullptr;
+  const T* rs = (p.residual && row_ok) ? reinterpret_cast<const T*>(p.residual) + row * p.ldr + col : nullptr;
+  const bool full = ncols_valid == 32 && p.vec_ok && (!b || (reinterpret_cast<uintptr_t>(b) & 15) == 0);
+  if (full) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      float f[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(acc_bits[g * 8 + i]) * p.alpha;
+      if (b) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(b) + g);
+        const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] += to_f32<T>(e[i]);
+      }
+      if (rs) {
+        const uint4 q = *(reinterpret_cast<const uint4*>(rs) + g);
+        const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] += to_f32<T>(e[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pk[g * 4 + i] = pack2<T>(f[2 * i], f[2 * i + 1]);
+    }
+  } else {
+    // ragged edge or unaligned operands: element by element
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float f0 = __uint_as_float(acc_bits[2 * i]) * p.alpha, f1 = __uint_as_float(acc_bits[2 * i + 1]) * p.alpha;
+      if (2 * i < ncols_valid) {
+        if (b) f0 += to_f32<T>(b[2 * i]);
+        if (rs) f0 += to_f32<T>(rs[2 * i]);
+      }
+      if (2 * i + 1 < ncols_valid) {
+        if (b) f1 += to_f32<T>(b[2 * i + 1]);
+        if (rs) f1 += to_f32<T>(rs[2 * i + 1]);
+      }
+      pk[i] = pack2<T>(f0, f1);
+    }
+  }
+}
+
 // 32 values of row `r`, already packed to 16-bit pairs, -> the staging tile (piece 0 or 1 of the row's chunk)
 __device__ __forceinline__ void stage_packed32(uint8_t* staging, int r, int piece, const uint32_t* pk) {
   uint8_t* rowp = staging + r * 128;
@@ -255,11 +313,11 @@ __device__ __forceinline__ void stage_packed32(uint8_t* staging, int r, int piec
   }
 }
 
-template <typename T, int MT, bool TMA_EPI, bool A_MN, bool B_MN, typename Hooks>
+template <typename T, int MT, bool LEAN, bool A_MN, bool B_MN, typename Hooks>
 __device__ __forceinline__ void gemm_pair_body(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
                                                const CUtensorMap* tma_c, const GemmParams& p, const Hooks& hooks,
                                                uint8_t* smem_raw, int cluster_id, int num_clusters) {
-  using C = PairCfg<MT, TMA_EPI>;
+  using C = PairCfg<MT>;
   constexpr int STAGES = C::STAGES;
   // both CTAs of a pair must use the same shared-memory offsets (the MMA addresses the peer's
   // operands by offset, remote arrivals address barriers by offset); the dynamic segment starts at
@@ -288,7 +346,7 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap* tma_a, const C
   if (threadIdx.x == 0) {
     prefetch_tensormap(tma_a);
     prefetch_tensormap(tma_b);
-    if (TMA_EPI && p.tma_store) prefetch_tensormap(tma_c);
+    if (p.tma_store) prefetch_tensormap(tma_c);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
@@ -465,28 +523,20 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap* tma_a, const C
             }
             if (kb == num_kb - 1) {
               // this accumulator is complete: hand it to both CTAs' epilogue warps
-              if (p.pair_commit == 1) {
-                umma_commit_pair_both_w(smem_u32(&tmem_full_bar[acc]));
-              } else {
-                umma_commit_pair_w(smem_u32(&tmem_full_bar[acc]));
-                umma_commit_pair_w(map_to_cta(smem_u32(&tmem_full_bar[acc]), 1));
-              }
+              umma_commit_pair_w(smem_u32(&tmem_full_bar[acc]));
+              umma_commit_pair_w(map_to_cta(smem_u32(&tmem_full_bar[acc]), 1));
             }
           }
           if (!ok) break;
           // the stage is free again in both CTAs once these MMAs have read it
-          if (p.pair_commit == 1) {
-            umma_commit_pair_both_w(smem_u32(&empty_bar[stage]));
-          } else {
-            umma_commit_pair_w(smem_u32(&empty_bar[stage]));
-            umma_commit_pair_w(map_to_cta(smem_u32(&empty_bar[stage]), 1));
-          }
+          umma_commit_pair_w(smem_u32(&empty_bar[stage]));
+          umma_commit_pair_w(map_to_cta(smem_u32(&empty_bar[stage]), 1));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         item += MT;
       }
       if (p.dbg && lane == 0) {
-        long long* d = p.dbg + 4 * cluster_id;
+        long long* d = p.dbg + 8 * cluster_id;
         d[0] = clock64() - t_begin;
         d[1] = t_full;
         d[2] = t_tmem;
@@ -510,10 +560,11 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap* tma_a, const C
     bool ok = true;
     const uint32_t leader_empty0 = map_to_cta(smem_u32(&tmem_empty_bar[0]), 0);
     const uint32_t leader_empty1 = map_to_cta(smem_u32(&tmem_empty_bar[1]), 0);
-    const int osz = p.out_f32 ? 4 : (int)sizeof(T);
+    const int osz = (!LEAN && p.out_f32) ? 4 : (int)sizeof(T);
     const int cw = 128 / osz;                           // columns per staged chunk (64 or 32)
     const int pieces = cw / 32;                         // 32-column pieces per chunk
-    const bool use_tma = TMA_EPI && p.tma_store;
+    const bool use_tma = LEAN || p.tma_store;
+    long long edbg[4] = {0, 0, 0, 0};   // cycles: full -> release (acc 0 / 1), full -> tile done; tiles
     while (ok) {
       ok = mbar_wait_cluster(smem_u32(&sched_full[slot]), slot_phase, abort_flag, p.status, RB_ERR_TIMEOUT_FULL);
       ok = __all_sync(0xffffffffu, ok);
@@ -524,11 +575,13 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap* tma_a, const C
       int m_idx = 0, n_idx = 0;
       if (tile >= 0) tile_coords(tile, m_idx, n_idx);
       const int col_g0 = n_idx * G2_BN + group * 128;
-      if (MT == 2 && use_tma && !p.out_f32) {
+      if constexpr (LEAN && MT == 2) {
         // 512 x 256 tiles own all of TMEM, so the next tile's MMAs wait for this drain: both
         // accumulators are first emptied into registers (as packed 16-bit results) and handed back,
         // and only then written out
         uint32_t pk[2][4][16];
+        long long t_a = 0;
+        if (p.dbg) t_a = clock64();
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const int acc = (item + j) & 1;
@@ -539,26 +592,29 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap* tma_a, const C
           }
           ok = bar_vote_and(group_bar, 128, ok);        // the group goes on, or gives up, together
           const bool go = ok && tile >= 0;
+          if (p.dbg && j == 0) t_a = clock64();
           tc_fence_after();
-          const int m_blk = row_block(m_idx, j);
-          const long long row = static_cast<long long>(m_blk) * 128 + r_in_cta;
+          const long long row = static_cast<long long>(row_block(m_idx, j)) * 128 + r_in_cta;
           const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * G2_BN + group * 128;
+          // one 32-column piece at a time (load, epilogue arithmetic, pack); the accumulator goes back
+          // to the MMA warp as soon as the last piece has landed in registers
+          const bool rok = go && row < p.M;
 #pragma unroll
           for (int pc = 0; pc < 4; ++pc) {
             uint32_t r[32];
-            float v[32];
             if (go) {
               tmem_ld_32x32b_x32(taddr + pc * 32, r);
               tmem_ld_wait();
             }
-            const int col = col_g0 + pc * 32;
-            epilogue_math32<T, T>(p, r, row, col, min(32, p.N - col), go && row < p.M, v);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) pk[j][pc][i] = pack2<T>(v[2 * i], v[2 * i + 1]);
+            if (pc == 3) {
+              tc_fence_before();
+              __syncwarp();
+              if (go && lane == 0) mbar_arrive_cluster(acc == 0 ? leader_empty0 : leader_empty1);
+              if (p.dbg && leader && warp_idx == G2_EPI_WARP0 && lane == 0) edbg[j] += clock64() - t_a;
+            }
+            const int c0 = col_g0 + pc * 32;
+            lean_pack32<T>(p, r, row, c0, min(32, p.N - c0), rok, pk[j][pc]);
           }
-          tc_fence_before();
-          __syncwarp();
-          if (go && lane == 0) mbar_arrive_cluster(acc == 0 ? leader_empty0 : leader_empty1);
         }
         if (!ok || tile < 0) break;
 #pragma unroll
@@ -586,9 +642,13 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap* tma_a, const C
           }
           if (lane == 0 && m_blk * 128 < p.M) hooks.after_tile_store(m_blk, n_idx, quarter);
         }
+        if (p.dbg && leader && warp_idx == G2_EPI_WARP0 && lane == 0) { edbg[2] += clock64() - t_a; edbg[3] += 1; }
         item += MT;
         continue;
       }
+      constexpr int gcols = 128;                        // columns of an accumulator this group handles
+      const int gcol0 = group * 128;
+      long long t_b = 0;
 #pragma unroll 1
       for (int j = 0; j < MT; ++j) {
         const int acc = (item + j) & 1;
@@ -605,36 +665,44 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap* tma_a, const C
         const int m_blk = row_block(m_idx, j);
         const long long row = static_cast<long long>(m_blk) * 128 + r_in_cta;
         const bool row_ok = row < p.M;
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * G2_BN + group * 128;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * G2_BN + gcol0;
         const uint32_t leader_empty = acc == 0 ? leader_empty0 : leader_empty1;
+        if (p.dbg) t_b = clock64();
         if (use_tma) {
-          const int nchunks = 128 / cw;
+          const int nchunks = gcols / cw;
 #pragma unroll 1
           for (int ch = 0; ch < nchunks; ++ch) {
-            const int col0 = col_g0 + ch * cw;
+            const int col0 = n_idx * G2_BN + gcol0 + ch * cw;
             const bool live = col0 < p.N && m_blk * 128 < p.M;    // uniform over the group's 4 warps
             float v[2][32];
+            uint32_t r[2][32];
             if (live) {
-              uint32_t r[32];
 #pragma unroll
-              for (int pc = 0; pc < 2; ++pc) {
-                if (pc < pieces) {
-                  tmem_ld_32x32b_x32(taddr + ch * cw + pc * 32, r);
-                  tmem_ld_wait();
-                  const int col = col0 + pc * 32;
-                  const int ncols_valid = min(32, p.N - col);
-                  if (p.out_f32)
-                    epilogue_math32<T, float>(p, r, row, col, ncols_valid, row_ok, v[pc]);
-                  else
-                    epilogue_math32<T, T>(p, r, row, col, ncols_valid, row_ok, v[pc]);
-                }
-              }
+              for (int pc = 0; pc < 2; ++pc)
+                if (pc < pieces) tmem_ld_32x32b_x32(taddr + ch * cw + pc * 32, r[pc]);
+              tmem_ld_wait();
             }
             if (ch == nchunks - 1) {
-              // the accumulator has been read completely: hand it back before the stores
+              // the accumulator has been read completely: hand it back before the arithmetic and the stores
               tc_fence_before();
               __syncwarp();
               if (lane == 0) mbar_arrive_cluster(leader_empty);
+              if (p.dbg && leader && warp_idx == G2_EPI_WARP0 && lane == 0) edbg[0] += clock64() - t_b;
+            }
+            if (live) {
+#pragma unroll
+              for (int pc = 0; pc < 2; ++pc) {
+                if (pc < pieces) {
+                  const int col = col0 + pc * 32;
+                  const int ncols_valid = min(32, p.N - col);
+                  if constexpr (LEAN)
+                    epilogue_math32<T, T, true>(p, r[pc], row, col, ncols_valid, row_ok, v[pc]);
+                  else if (p.out_f32)
+                    epilogue_math32<T, float>(p, r[pc], row, col, ncols_valid, row_ok, v[pc]);
+                  else
+                    epilogue_math32<T, T>(p, r[pc], row, col, ncols_valid, row_ok, v[pc]);
+                }
+              }
             }
             if (!live) continue;
             // the previous chunk's TMA store must have finished reading the staging tile
@@ -643,7 +711,9 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap* tma_a, const C
 #pragma unroll
             for (int pc = 0; pc < 2; ++pc) {
               if (pc < pieces) {
-                if (p.out_f32)
+                if constexpr (LEAN)
+                  stage_row32<T>(staging, r_in_cta, pc, v[pc]);
+                else if (p.out_f32)
                   stage_row32<float>(staging, r_in_cta, pc, v[pc]);
                 else
                   stage_row32<T>(staging, r_in_cta, pc, v[pc]);
@@ -660,13 +730,13 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap* tma_a, const C
             if (issuer) tma_store_wait<0>();
             bar_sync_named(group_bar, 128);
           }
-        } else {
+        } else if constexpr (!LEAN) {
 #pragma unroll 1
-          for (int ci = 0; ci < 4; ++ci) {
+          for (int ci = 0; ci < gcols / 32; ++ci) {
             uint32_t r[32];
             tmem_ld_32x32b_x32(taddr + ci * 32, r);
             tmem_ld_wait();
-            const int col = col_g0 + ci * 32;
+            const int col = n_idx * G2_BN + gcol0 + ci * 32;
             const int ncols_valid = min(32, p.N - col);
             if (row_ok && ncols_valid > 0) {
               if (p.out_f32)
@@ -680,13 +750,18 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap* tma_a, const C
           if (lane == 0) mbar_arrive_cluster(leader_empty);
         }
         if (lane == 0 && m_blk * 128 < p.M) hooks.after_tile_store(m_blk, n_idx, quarter);
+        if (p.dbg && leader && warp_idx == G2_EPI_WARP0 && lane == 0) { edbg[2] += clock64() - t_b; edbg[3] += 1; }
       }
       if (!ok || tile < 0) break;
       item += MT;
     }
+    if (p.dbg && leader && warp_idx == G2_EPI_WARP0 && lane == 0) {
+      long long* d = p.dbg + 8 * cluster_id + 4;
+      d[0] = edbg[0]; d[1] = edbg[1]; d[2] = edbg[2]; d[3] = edbg[3];
+    }
     // the staging tile must outlive the last store's read; then this warp will not touch TMEM or
     // signal any barrier again: tell both CTAs
-    if (TMA_EPI && issuer) tma_store_wait_read<0>();
+    if (issuer) tma_store_wait_read<0>();
     __syncwarp();
     if (lane == 0) {
       mbar_arrive_cluster(map_to_cta(smem_u32(done_bar), 0));

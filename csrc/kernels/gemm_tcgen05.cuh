@@ -50,8 +50,6 @@ struct GemmParams {
                          // the epilogue adds into a zero-initialised fp32 output (no bias/act/residual)
   int tma_store;         // two-CTA kernel only: the output goes through shared memory and TMA stores
                          // (needs a 16-byte aligned base and row pitch); 0 = per-row stores
-  int pair_commit;       // two-CTA kernel only: 1 = one commit arrives on both CTAs' barriers, 0 = one
-                         // commit per CTA
   long long* dbg;        // two-CTA kernel only: when set, every pair's MMA warp leaves {cycles in the
                          // kernel, cycles waiting for operands, cycles waiting for an accumulator, tiles}
 };
@@ -72,6 +70,13 @@ struct NoHooks {
   __device__ __forceinline__ int map_kb(int kb, int num_kb) const { return kb; }
   // Called by one lane of each epilogue warp after its 32 rows of a tile are stored.
   __device__ __forceinline__ void after_tile_store(int m_idx, int n_idx, int quarter) const {}
+  // Operand loads / output rows other than "tile (m_idx, kb) of a row-major matrix" (implicit-GEMM
+  // convolution: operand tiles are patches of an NHWC tensor, output rows are pixels of a patch).
+  // When set, the hook provides load_a / load_b (issue the copies of one K block, which must add up to
+  // the stage's byte count) and out_row (tile row -> output row index, negative = no such row).
+  static constexpr bool kCustomLoadA = false;
+  static constexpr bool kCustomLoadB = false;
+  static constexpr bool kCustomRows = false;
   // Whether after_tile_store needs the tile's global writes to be complete (it publishes them to
   // other GPUs); the two-CTA body then drains its TMA stores first.
   static constexpr bool kNeedsStoreComplete = false;
@@ -195,15 +200,31 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
   }
   const bool vec = p.vec_ok != 0;
   if (p.aux_out) store_row32<OT>(reinterpret_cast<OT*>(p.aux_out), p.ldaux_out, row, col, ncols_valid, vec, v);
-  if (p.act != ACT_NONE) {
+  // one loop per activation kind: a switch inside the unrolled loop would lay down every kind 32
+  // times, and an epilogue that is mostly code the call never runs costs more to fetch than to execute
+  if (p.act == ACT_RELU) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = apply_act(v[i], p.act);
+    for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
+  } else if (p.act == ACT_GELU) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+  } else if (p.act == ACT_SILU) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = silu_f(v[i]);
   }
   if (p.aux_in) {
     float a[32];
     load_row32<OT>(reinterpret_cast<const OT*>(p.aux_in), p.ldaux_in, row, col, ncols_valid, vec, a);
+    if (p.dact == ACT_RELU) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] *= apply_dact(a[i], p.dact);
+      for (int i = 0; i < 32; ++i) v[i] = a[i] > 0.0f ? v[i] : 0.0f;
+    } else if (p.dact == ACT_GELU) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] *= gelu_tanh_grad(a[i]);
+    } else if (p.dact == ACT_SILU) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] *= silu_grad(a[i]);
+    }
   }
   if (p.residual) {
     float r[32];
@@ -356,14 +377,18 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
           mbar_arrive_expect_tx(bar, C::A_BYTES + C::B_BYTES);
           const uint32_t a_dst = smem_u32(sA + stage * C::A_BYTES);
           const uint32_t b_dst = smem_u32(sB + stage * C::B_BYTES);
-          if constexpr (!A_MN) {
+          if constexpr (Hooks::kCustomLoadA) {
+            hooks.load_a(a_dst, tma_a, bar, m_idx, kb);
+          } else if constexpr (!A_MN) {
             tma_load_2d(a_dst, tma_a, bar, kb * BK, m_idx * BM);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / CH; ++j)
               tma_load_2d(a_dst + j * BK * 128, tma_a, bar, m_idx * BM + j * CH, kb * BK);
           }
-          if constexpr (!B_MN) {
+          if constexpr (Hooks::kCustomLoadB) {
+            hooks.load_b(b_dst, tma_b, bar, n_idx, kb);
+          } else if constexpr (!B_MN) {
             tma_load_2d(b_dst, tma_b, bar, kb * BK, n_idx * BN);
           } else {
 #pragma unroll
@@ -472,7 +497,12 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const long long row = static_cast<long long>(m_idx) * BM + quarter * 32 + lane;
+      long long row = static_cast<long long>(m_idx) * BM + quarter * 32 + lane;
+      bool row_ok = row < p.M;
+      if constexpr (Hooks::kCustomRows) {
+        row = hooks.out_row(m_idx, quarter * 32 + lane);
+        row_ok = row >= 0;
+      }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
       for (int ci = 0; ci < CHUNKS_PER_HALF; ++ci) {
@@ -482,7 +512,7 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
         tmem_ld_wait();
         const int col = n_idx * BN + c * 32;
         const int ncols_valid = min(32, p.N - col);
-        if (row < p.M && ncols_valid > 0) {
+        if (row_ok && ncols_valid > 0) {
           if (split_k > 1)
             epilogue_chunk_atomic(p, r, row, col, ncols_valid);
           else if (p.out_f32)

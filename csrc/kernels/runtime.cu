@@ -34,6 +34,12 @@ void load_encode() {
 
 int encode_tensor_map(CUtensorMap* out, int dtype, int rank, void* base, const uint64_t* dims,
                       const uint64_t* strides_bytes, const uint32_t* box, int swizzle_128b) {
+  return encode_tensor_map_strided(out, dtype, rank, base, dims, strides_bytes, box, nullptr, swizzle_128b);
+}
+
+int encode_tensor_map_strided(CUtensorMap* out, int dtype, int rank, void* base, const uint64_t* dims,
+                              const uint64_t* strides_bytes, const uint32_t* box, const uint32_t* elem_strides,
+                              int swizzle_128b) {
   std::call_once(g_encode_once, load_encode);
   if (!g_encode) return -1;
   // The driver entry point needs a current context on the calling thread.  Threads that have
@@ -54,7 +60,7 @@ int encode_tensor_map(CUtensorMap* out, int dtype, int rank, void* base, const u
   for (int i = 0; i < rank; ++i) {
     gdims[i] = dims[i];
     gbox[i] = box[i];
-    estr[i] = 1;
+    estr[i] = elem_strides ? elem_strides[i] : 1;
     if (i > 0) gstrides[i - 1] = strides_bytes[i];
   }
   CUresult r = g_encode(out, dt, (cuuint32_t)rank, base, gdims, gstrides, gbox, estr,

@@ -486,6 +486,12 @@ enum : int { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2 };
 int encode_tensor_map(CUtensorMap* out, int dtype, int rank, void* base, const uint64_t* dims,
                       const uint64_t* strides_bytes, const uint32_t* box, int swizzle_128b);
 
+// The same with a traversal stride per dimension: along dimension i the copy takes every
+// elem_strides[i]-th element of a box of box[i] elements, i.e. ceil(box[i] / elem_strides[i]) of them.
+int encode_tensor_map_strided(CUtensorMap* out, int dtype, int rank, void* base, const uint64_t* dims,
+                              const uint64_t* strides_bytes, const uint32_t* box, const uint32_t* elem_strides,
+                              int swizzle_128b);
+
 // Device status word (one per device, lives in mapped pinned host memory so the
 // host can poll it without a stream sync).  Returned pointer is device-usable.
 int* device_status_word();

@@ -1,5 +1,7 @@
-"""CUDA paths of the vision ops: implicit-GEMM convolution (im2col/col2im kernels around the
-tcgen05 GEMM), BatchNorm2d, max-pool, adaptive average pool.  Activations are kept channels-last
+"""CUDA paths of the vision ops: convolution (implicit GEMM: operand tiles gathered from the NHWC
+tensor by TMA inside the tcgen05 GEMM, ``csrc/kernels/conv_igemm.cu``; im2col / col2im kernels around
+the GEMM remain for the 3-channel stem, fp32 and strided data gradients), BatchNorm2d, max-pool,
+adaptive average pool.  Activations are kept channels-last
 (NHWC in memory, NCHW in shape) so 1x1 convolutions are plain GEMMs on the activation tensor and
 BatchNorm reduces over contiguous channel vectors.  Kernels: ``csrc/kernels/vision.cu``."""
 from __future__ import annotations
@@ -14,6 +16,8 @@ from ._lib import check, count_launch, ptr, stream_ptr
 P, LL, I, F = c_void_p, c_longlong, c_int, c_float
 native.register_signature("rb_im2col_nhwc", [I, P, P] + [I] * 12 + [P])
 native.register_signature("rb_col2im_nhwc", [I, P, P] + [I] * 12 + [P])
+native.register_signature("rb_conv_igemm", [I, I, P, P, P, P, I] + [I] * 15 + [P])
+native.register_signature("rb_conv_igemm_wgrad", [I, P, P, P] + [I] * 12 + [P])
 native.register_signature("rb_bn_slabs", [LL])
 native.register_signature("rb_bn_fwd", [I, P, P, P, P, P, P, P, P, P, P, LL, I, F, F, I, I, P])
 native.register_signature("rb_bn_bwd", [I, P, P, P, P, P, P, P, P, P, P, P, P, LL, I, I, I, P])
@@ -66,6 +70,54 @@ def _weight_matrix(weight, Kpad):
     return wm.contiguous()
 
 
+def _igemm_ok(x: torch.Tensor, cin: int, cout: int) -> bool:
+    """The implicit-GEMM kernels (``csrc/kernels/conv_igemm.cu``) gather 64-channel blocks of a 16-bit
+    NHWC tensor; other convolutions (the 3-channel stem, fp32) keep the im2col path."""
+    import os
+    return (x.dtype in (torch.bfloat16, torch.float16) and cin % 64 == 0 and cout % 8 == 0
+            and os.environ.get("RB_CONV_IGEMM", "1") == "1")
+
+
+def _pixel_tile(B: int, Ho: int, Wo: int):
+    """(tw, th, tn): the patch of 128 output pixels (tw x th pixels of tn images, powers of two) that
+    wastes the fewest rows on the edges of the ``B x Ho x Wo`` grid; ties go to the larger patch."""
+    best = None
+    for lw in range(8):
+        for lh in range(8 - lw):
+            tw, th, tn = 1 << lw, 1 << lh, 1 << (7 - lw - lh)
+            cover = (-(-Wo // tw) * tw) * (-(-Ho // th) * th) * (-(-B // tn) * tn)
+            key = (cover, -(tw * th), abs(lw - lh))
+            if best is None or key < best[0]:
+                best = (key, (tw, th, tn))
+    return best[1]
+
+
+def conv_igemm(mode: int, act: torch.Tensor, wmat: torch.Tensor, Ho: int, Wo: int, KH: int, KW: int,
+               stride: int, pad: int, dil: int, bias=None, relu: bool = False) -> torch.Tensor:
+    """``act`` NHWC ``[B, H, W, C]``, ``wmat [N, KH*KW*C]`` -> NHWC ``[B, Ho, Wo, N]``; mode 0 forward,
+    mode 1 data gradient of a stride-1 convolution (``act`` = dY, taps mirrored)."""
+    B, H, W, C = act.shape
+    N = wmat.shape[0]
+    out = torch.empty((B, Ho, Wo, N), dtype=act.dtype, device=act.device)
+    tw, th, tn = _pixel_tile(B, Ho, Wo)
+    check(native.lib().rb_conv_igemm(mode, native.dtype_code(act.dtype), ptr(act), ptr(wmat), ptr(out), ptr(bias),
+                                     1 if relu else 0, B, H, W, C, Ho, Wo, N, KH, KW, stride, pad, dil, tw, th, tn,
+                                     stream_ptr()), "rb_conv_igemm")
+    count_launch()
+    return out
+
+
+def conv_igemm_wgrad(dyh: torch.Tensor, xh: torch.Tensor, KH: int, KW: int, stride: int, pad: int, dil: int) -> torch.Tensor:
+    """dY NHWC ``[B, Ho, Wo, Cout]``, x NHWC ``[B, H, W, C]`` -> fp32 ``[Cout, KH*KW*C]`` (K ordered kh, kw, c)."""
+    B, Ho, Wo, Cout = dyh.shape
+    _, H, W, C = xh.shape
+    dwm = torch.zeros((Cout, KH * KW * C), dtype=torch.float32, device=xh.device)
+    check(native.lib().rb_conv_igemm_wgrad(native.dtype_code(xh.dtype), ptr(dyh), ptr(xh), ptr(dwm), B, H, W, C, Ho, Wo,
+                                           Cout, KH, KW, stride, pad, dil, stream_ptr()), "rb_conv_igemm_wgrad")
+    count_launch()
+    return dwm
+
+
 class Conv2dFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, stride, padding, dilation):
@@ -75,11 +127,17 @@ class Conv2dFn(torch.autograd.Function):
         xh = _nhwc(x)
         esz = x.element_size()
         pointwise = KH == 1 and KW == 1 and stride == 1 and padding == 0 and Cin % (16 // esz) == 0
-        Kpad = Cin if pointwise else _pad8(KH * KW * Cin, esz)
-        cols = xh.view(B * H * W, Cin) if pointwise else _im2col(xh, KH, KW, Ho, Wo, stride, padding,
-                                                                 dilation, Kpad)
+        igemm = not pointwise and _igemm_ok(x, Cin, Cout)
+        Kpad = Cin if pointwise else (KH * KW * Cin if igemm else _pad8(KH * KW * Cin, esz))
         wm = _weight_matrix(weight, Kpad)
-        y = native.gemm(cols, wm.t(), bias=bias)          # [M, Cout] == NHWC output
+        if igemm:
+            # operand tiles come straight out of the NHWC tensor: no patch matrix is written
+            y = conv_igemm(0, xh, wm, Ho, Wo, KH, KW, stride, padding, dilation, bias=bias)
+        else:
+            cols = xh.view(B * H * W, Cin) if pointwise else _im2col(xh, KH, KW, Ho, Wo, stride, padding,
+                                                                     dilation, Kpad)
+            y = native.gemm(cols, wm.t(), bias=bias)      # [M, Cout] == NHWC output
+        ctx.igemm = igemm
         ctx.geom = (B, H, W, Cin, Cout, KH, KW, Ho, Wo, stride, padding, dilation, Kpad, pointwise)
         ctx.save_for_backward(xh, wm)
         ctx.has_bias = bias is not None
@@ -92,6 +150,22 @@ class Conv2dFn(torch.autograd.Function):
         B, H, W, Cin, Cout, KH, KW, Ho, Wo, stride, padding, dilation, Kpad, pointwise = ctx.geom
         dyh = _nhwc(dy).view(B * Ho * Wo, Cout)
         dx = dw = db = None
+        if ctx.igemm:
+            dy4 = dyh.view(B, Ho, Wo, Cout)
+            if ctx.needs_input_grad[1]:
+                dwm = conv_igemm_wgrad(dy4, xh, KH, KW, stride, padding, dilation)
+                dw = dwm.view(Cout, KH, KW, Cin).permute(0, 3, 1, 2).to(ctx.w_dtype).contiguous()
+            if ctx.needs_input_grad[0]:
+                if stride == 1 and Cout % 64 == 0:
+                    # data gradient = the same gather on dY with mirrored taps; weight as [Cin, (kh, kw, co)]
+                    wd = wm.view(Cout, KH, KW, Cin).permute(3, 1, 2, 0).reshape(Cin, KH * KW * Cout).contiguous()
+                    dx = _as_nchw(conv_igemm(1, dy4, wd, H, W, KH, KW, 1, padding, dilation))
+                else:
+                    dcols = native.gemm(dyh, wm)           # [M, K]: strided data gradients scatter through col2im
+                    dx = _as_nchw(_col2im(dcols, B, H, W, Cin, KH, KW, Ho, Wo, stride, padding, dilation, Kpad))
+            if ctx.has_bias and ctx.needs_input_grad[2]:
+                db = native.colsum(dyh)
+            return dx, dw, db, None, None, None
         cols = xh.view(B * H * W, Cin) if pointwise else _im2col(xh, KH, KW, Ho, Wo, stride, padding,
                                                                  dilation, Kpad)
         if ctx.needs_input_grad[1]:

@@ -54,6 +54,14 @@ class SymmArena:
 
     def _map(self) -> None:
         """Allocate this rank's arena and map every peer's: sets ``buf``, ``base_ptrs``, ``mc_ptr``."""
+        if self.world == 1:
+            # a group of one has no peer to map: plain device memory serves (this is how the fused
+            # collective kernels run on a single GPU, e.g. under a profiler)
+            self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=self.device)
+            self.hdl = None
+            self.base_ptrs = [self.buf.data_ptr()]
+            self.mc_ptr = 0
+            return
         import torch.distributed._symmetric_memory as symm
         self.buf = symm.empty(self.nbytes, dtype=torch.uint8, device=self.device)
         self.hdl = symm.rendezvous(self.buf, self.group)

@@ -182,6 +182,36 @@ def main():
         check(f"gemm_rs epoch {epoch}", rel(outr, ref_local), 1.5e-2)
         arena.barrier()
 
+    # residual added by the reducing owner
+    resr = torch.randn(Mr // world, Nr, device=dev).bfloat16()
+    outr = torch.empty(Mr // world, Nr, device=dev, dtype=torch.bfloat16)
+    fused_ops.gemm_rs(arena, ar, br, partial_off=part_off, tile_flags_off=tflags,
+                      tile_counters=tcount, epoch=3, out=outr, bias=biasr, residual=resr)
+    torch.cuda.synchronize()
+    check("gemm_rs + residual", rel(outr, ref_local + resr.float()), 1.5e-2)
+    arena.barrier()
+
+    # ---------------- one-shot all-reduce of decode-sized partial sums (+ residual), two buffers in turn
+    T, d = 48, 4096
+    bufs = [arena.alloc(128 * d, torch.bfloat16)[0] for _ in range(2)]
+    oflags = arena.alloc_flags(world)
+    arena.barrier()
+    for epoch in range(1, 6):
+        rows = T if epoch % 2 else 7
+        torch.manual_seed(500 * epoch + rank)
+        mine = (torch.randn(rows, d, device=dev) * 0.5).bfloat16()
+        torch.manual_seed(77 + epoch)
+        res = torch.randn(rows, d, device=dev).bfloat16()
+        part_buf = bufs[epoch & 1][: rows * d].view(rows, d)
+        part_buf.copy_(mine)
+        want = mine.float().clone()
+        dist.all_reduce(want)
+        want = want + res.float()
+        got = torch.empty_like(mine)
+        fused_ops.oneshot_allreduce(arena, part_buf, got, flags_off=oflags, epoch=epoch, residual=res)
+        torch.cuda.synchronize()
+        check(f"oneshot_allreduce epoch {epoch}", rel(got, want), 1e-2)
+
     dist.barrier()
     if rank == 0:
         print("ALL FUSED CHECKS PASSED", flush=True)

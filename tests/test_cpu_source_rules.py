@@ -40,9 +40,7 @@ def _scan(patterns):
 
 def test_no_fan_out_bulk_loads_anywhere():
     q = "multi" + "cast" + "::" + "cluster"
-    # the qualifier is allowed on tcgen05.commit only (an mbarrier arrival in both CTAs of a pair: a
-    # signal, not a copy); any other line that carries it is a fan-out copy
-    pats = [re.compile(r"^(?!.*tcgen05\.commit).*" + re.escape(q)),
+    pats = [re.compile(re.escape(q)),
             re.compile("SM90_TMA_LOAD_" + "MULTI" + "CAST"),
             re.compile("SM100_TMA_2SM_LOAD_" + "MULTI" + "CAST")]
     assert _scan(pats) == []

@@ -150,3 +150,45 @@ def test_resnet_bottleneck_stack_trains_fp16():
         scaler.update()
         losses.append(loss.item())
     assert losses[-1] < losses[0], losses
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("cfg", [
+    dict(B=4, Cin=64, Cout=64, H=28, W=28, k=3, s=1, p=1, d=1),      # 3x3, tiles of 4 x 4 pixels x 8 images
+    dict(B=3, Cin=128, Cout=256, H=15, W=13, k=3, s=2, p=1, d=1),    # strided gather, ragged image, col2im data grad
+    dict(B=2, Cin=256, Cout=128, H=14, W=14, k=1, s=2, p=0, d=1),    # strided 1x1 shortcut
+    dict(B=5, Cin=64, Cout=192, H=9, W=20, k=3, s=1, p=2, d=2),      # dilation, Cout not a multiple of 128
+    dict(B=2, Cin=192, Cout=64, H=7, W=7, k=5, s=1, p=2, d=1),       # 5x5 taps, three channel blocks
+])
+def test_conv2d_implicit_gemm(dtype, cfg):
+    """Convolutions with 64-channel blocks take the implicit-GEMM kernels (no patch matrix): forward,
+    data gradient (stride 1: mirrored gather; strided: GEMM + col2im) and weight gradient against fp32."""
+    from rumus_b200.ops import native
+    from rumus_b200.ops import vision as V
+    from rumus_b200.ops import vision_cuda as VC
+    torch.manual_seed(1)
+    assert VC._igemm_ok(torch.empty(1, device="cuda", dtype=dtype), cfg["Cin"], cfg["Cout"])
+    x = torch.randn(cfg["B"], cfg["Cin"], cfg["H"], cfg["W"], device="cuda").to(dtype).requires_grad_(True)
+    w = (torch.randn(cfg["Cout"], cfg["Cin"], cfg["k"], cfg["k"], device="cuda") * 0.05).to(dtype).requires_grad_(True)
+    b = torch.randn(cfg["Cout"], device="cuda").to(dtype).requires_grad_(True)
+    y = V.conv2d(x, w, b, cfg["s"], cfg["p"], cfg["d"])
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    yr = TF.conv2d(xr, wr, br, cfg["s"], cfg["p"], cfg["d"])
+    yr.backward(g.float())
+    assert native.read_status() == 0
+    assert y.shape == yr.shape
+    assert _rel(y, yr) < 1e-2
+    assert _rel(x.grad, xr.grad) < 1e-2
+    assert _rel(w.grad, wr.grad) < 1e-2
+    assert _rel(b.grad, br.grad) < 1e-2
+
+
+def test_pixel_tile_choice_covers_the_grid_with_128_pixels():
+    from rumus_b200.ops.vision_cuda import _pixel_tile
+    for B, Ho, Wo in ((256, 56, 56), (256, 28, 28), (256, 14, 14), (256, 7, 7), (3, 8, 7), (1, 1, 1)):
+        tw, th, tn = _pixel_tile(B, Ho, Wo)
+        assert tw * th * tn == 128
+    assert _pixel_tile(256, 7, 7) == (1, 1, 128)        # no wasted rows on 7 x 7 images
+    assert _pixel_tile(256, 56, 56)[2] <= 2
