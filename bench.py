@@ -267,6 +267,7 @@ def main():
             "model_tflops_per_gpu": flops / (ms / args.steps / 1e3) / 1e12,
             "final_loss": float(last_loss.item()) if last_loss is not None else None,
             "device_status": status,
+            "param_bytes_per_rank": engine.param_bytes(),
         }
         if phases:
             out["phases"] = phases

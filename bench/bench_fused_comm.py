@@ -51,7 +51,7 @@ def main():
     native.lib().rb_init_device()
     P = int(os.environ.get("UNIT_NUMEL", str(100 * 1024 * 1024))) // (8 * world) * (8 * world)
     S = P // world
-    arena = SymmArena(4 * P + (64 << 20))
+    arena = SymmArena(4 * P + (128 << 20))
     g = arena.alloc_flat(P, torch.bfloat16); w = arena.alloc_flat(P, torch.bfloat16)
     g.normal_(); w.normal_()
     master = w[rank * S:(rank + 1) * S].float(); m = torch.zeros_like(master); v = torch.zeros_like(master)
@@ -76,6 +76,52 @@ def main():
 
         res[f"fused rs_adam ctas={rs_ctas}"] = timed(rs)
         res[f"fused all_gather ctas={ag_ctas}"] = timed(ag)
+    # ---- all-reduce + unscale + non-finite flag (one data-parallel gradient bucket of 25 MB)
+    nb = (25 << 20) // 2 // (8 * world) * (8 * world)
+    bucket, _ = arena.alloc(nb, torch.float16)
+    bucket.normal_()
+    ef, xf, nf = arena.alloc_flags(world), arena.alloc_flags(world), arena.alloc_flags(world)
+    cnt_ar = arena.alloc_local_ints(1)
+    found = torch.zeros(1, dtype=torch.int32, device=dev)
+    inv = torch.full((), 1.0 / 1024.0, device=dev)
+    ar_epoch = [0]
+    arena.barrier()
+
+    def fused_ar():
+        ar_epoch[0] += 1
+        fused_ops.allreduce_unscale(arena, bucket, enter_flags_off=ef, exit_flags_off=xf, inf_flags_off=nf,
+                                    epoch=ar_epoch[0], inv_scale=inv, extra_scale=1.0 / world, found_inf=found,
+                                    done_counter=cnt_ar, ctas=32)
+
+    def nccl_ar():
+        dist.all_reduce(bucket)
+        bucket.mul_(inv / world)
+        torch.isfinite(bucket).all()
+
+    res["fused allreduce+unscale 25MB"] = timed(fused_ar)
+    res["nccl all_reduce + unscale + isfinite 25MB"] = timed(nccl_ar)
+    # ---- decode-sized all-reduce (one-shot kernel, partial sums already in the arena) against NCCL
+    os_bufs = [arena.alloc(64 * 4096, torch.bfloat16)[0] for _ in range(2)]
+    os_flags = arena.alloc_flags(world)
+    os_epoch = [0]
+    arena.barrier()
+    small = {}
+    for kb in (8, 16, 32, 64, 256, 512):
+        n = kb * 1024 // 2
+        outp = torch.empty(n, dtype=torch.bfloat16, device=dev)
+        resd = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+        tmp = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+
+        def oneshot():
+            os_epoch[0] += 1
+            fused_ops.oneshot_allreduce(arena, os_bufs[os_epoch[0] & 1][:n], outp, flags_off=os_flags,
+                                        epoch=os_epoch[0], residual=resd)
+
+        def nccl_small():
+            dist.all_reduce(tmp)
+            torch.add(resd, tmp, out=outp)
+
+        small[kb] = (timed(oneshot, iters=20), timed(nccl_small, iters=20))
     shard = torch.empty(S, dtype=torch.bfloat16, device=dev)
     res["nccl reduce_scatter"] = timed(lambda: dist.reduce_scatter_tensor(shard, g, op=dist.ReduceOp.AVG))
     res["adam_flat (shard)"] = timed(lambda: native.adam_flat(shard, master, m, v, w[rank * S:(rank + 1) * S],
@@ -86,7 +132,10 @@ def main():
         print(f"unit {P / 1e6:.0f}M bf16 params, world {world}, status {native.read_status()}")
         peer_bytes = (world - 1) * S * 2
         for k, t in res.items():
-            print(f"  {k:34s} {t * 1e3:9.1f} us   ({peer_bytes / t / 1e6:7.1f} GB/s of peer traffic per GPU)")
+            print(f"  {k:44s} {t * 1e3:9.1f} us   ({peer_bytes / t / 1e6:7.1f} GB/s of peer traffic per GPU)")
+        print("  decode all-reduce + residual add, latency in us (one-shot kernel | NCCL all_reduce + add):")
+        for kb, (a_us, b_us) in small.items():
+            print(f"    {kb:4d} KB   {a_us * 1e3:7.1f} | {b_us * 1e3:7.1f}")
     dist.barrier()
     dist.destroy_process_group()
 

@@ -95,6 +95,33 @@ def main():
     dist.barrier(); torch.cuda.synchronize()
     t = torch.tensor([e0.elapsed_time(e1)], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    # Pipeline bubble as measured: one micro-batch's forward + backward on every stage without its
+    # neighbours (every stage at once, so the tensor-parallel collectives inside still pair up);
+    # a step of M micro-batches that never waited would take M times the slowest stage.
+    act_shape = (mb_tokens // a.tp, a.d_model)
+    tok = torch.randint(0, a.vocab, (mb_seqs, a.seq + 1), generator=g)
+    mb_ms = []
+    for it in range(3):
+        opt.zero_grad()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier(); torch.cuda.synchronize()
+        s0.record()
+        if first:
+            out = stage(tok[:, :-1].to(dev))
+            out.backward(torch.ones_like(out))
+        else:
+            xin = torch.randn(act_shape, device=dev, dtype=torch.bfloat16).mul_(0.02).requires_grad_(True)
+            if last:
+                stage((xin, tok[:, 1:].to(dev))).backward()
+            else:
+                out = stage(xin)
+                out.backward(torch.ones_like(out))
+        s1.record()
+        torch.cuda.synchronize()
+        if it > 0:
+            mb_ms.append(s0.elapsed_time(s1))
+    mb = torch.tensor([sum(mb_ms) / len(mb_ms)], device=dev)
+    dist.all_reduce(mb, op=dist.ReduceOp.MAX)
     st = torch.tensor([native.read_status()], device=dev)
     dist.all_reduce(st, op=dist.ReduceOp.MAX)
     lt = torch.tensor([float(loss) if loss is not None else 0.0], device=dev)
@@ -109,7 +136,9 @@ def main():
                                      "global_batch": a.global_batch, "seq_len": a.seq,
                                      "parallelism": f"tp{a.tp}xpp{a.pp}xdp{topo.dp}", "micro_batches": a.micro_batches,
                                      "schedule": "1F1B", "comm_mode": tp.mode,
-                                     "bubble_fraction_ideal": (a.pp - 1) / (a.micro_batches + a.pp - 1)},
+                                     "bubble_fraction_ideal": (a.pp - 1) / (a.micro_batches + a.pp - 1),
+                                     "bubble_fraction_measured": 1.0 - a.micro_batches * mb.item() / ms,
+                                     "micro_batch_fwd_bwd_ms_slowest_stage": mb.item()},
                           "model_tflops_per_gpu": cfg.flops_per_token() * tokens / (ms / 1e3) / 1e12 / world,
                           "loss": lt.item(), "gpu_launches": _lib.launch_count(), "device_status": int(st.item())}))
     dist.destroy_process_group()

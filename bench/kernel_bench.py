@@ -26,8 +26,9 @@ if "--gemm-compare" in sys.argv:
     a = torch.randn(M, K, device='cuda').bfloat16(); b = torch.randn(K, N, device='cuda').bfloat16()
     for _ in range(3):
         native.gemm(a, b, path=1, bn=256)
-    for _ in range(3):
-        native.gemm(a, b, path=3)
+    for mt in (1, 2):
+        for _ in range(3):
+            native.gemm(a, b, path=3, mt=mt)
     for _ in range(3):
         torch.matmul(a, b)
     torch.cuda.synchronize()

@@ -1,15 +1,17 @@
 // FlashAttention forward for sm_100a (tcgen05 + TMEM + TMA).
 //
-// One CTA owns a 128-row query tile of one (batch, head).  K/V tiles of 128 rows
-// stream through a 2-stage TMA ring.  S = Q K^T and O += P V run on tcgen05 with
-// S (double buffered) and O living in TMEM; eight softmax warps, two per 32-row
-// quarter: each thread owns one query row (TMEM lane == row) and half of the tile's
-// 128 key columns, the two halves agree on the row maximum through shared memory,
-// keep the running max / partial sum in registers, write
-// P as bf16/fp16 into a 128B-swizzled shared tile that the second MMA consumes,
-// and rescale O in TMEM only when the running max moved by more than 2^8 (lazy
-// rescale).  exp is exp2 with the softmax scale folded in.  LSE is saved for the
-// backward pass.
+// One CTA owns a 128-row query tile of one (batch, head).  K/V tiles of 128 rows stream through a
+// 2-stage TMA ring.  S = Q K^T and O += P V run on tcgen05 with S (double buffered) and O in TMEM.
+//
+// Two softmax warpgroups take the K/V tiles in turn (even tiles: warps 0-3, odd tiles: warps 4-7).
+// Inside a warpgroup a thread owns one whole query row (TMEM lane == row, all 128 key columns), so
+// the row maximum and sum never leave the thread: no exchange between threads, no barrier inside the
+// softmax.  Each warpgroup keeps its own running maximum / sum and its own O accumulator in TMEM
+// (even tiles -> columns [256, 256+D), odd tiles -> [384, 384+D)), rescaled in place only when the
+// maximum moved by more than 2^8 (lazy rescale); the two partial results are merged once at the end,
+// the way split-KV decoding merges its partitions.  P goes to a 128B-swizzled shared tile (one per
+// warpgroup) that the second MMA consumes.  exp is exp2 with the softmax scale folded in.  LSE is
+// saved for the backward pass.
 //
 // Layout: q/k/v/o are [B, S, H, D] views with arbitrary batch/seq/head strides
 // (so the fused qkv projection output is consumed in place); D in {64, 128}.
@@ -43,7 +45,7 @@ struct FaFwdCfg {
   static constexpr int SMEM_BYTES = Q_BYTES + STAGES * 2 * KV_BYTES + P_BUFS * P_BYTES + 1024 + 256;
   static constexpr int TMEM_COLS = 512;
   static constexpr int S_COL0 = 0;       // S buffers at columns [0,128) and [128,256)
-  static constexpr int O_COL = 256;      // O at [256, 256+HD)
+  static constexpr int O_COL = 256;      // O of the even tiles at [256, 256+HD), of the odd tiles at [384, 384+HD)
 };
 
 template <typename T, int HD>
@@ -65,8 +67,7 @@ __global__ void __launch_bounds__(320, 1)
   uint64_t* s_full = bars + 5;     // [2]
   uint64_t* p_ready = bars + 7;    // [2]
   uint64_t* pv_done = bars + 9;    // [2]
-  uint64_t* max_bar = bars + 11;   // [2] both column halves have published their row maxima
-  uint64_t* sum_bar = bars + 13;   // the two partial row sums are published (once, at the end)
+  // bars 11..13 unused
   uint64_t* v_full = bars + 14;    // [2] V tile landed
   uint64_t* v_empty = bars + 16;   // [2] V slot free again (its P.V GEMM retired)
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + 18);
@@ -98,11 +99,9 @@ __global__ void __launch_bounds__(320, 1)
       mbar_init(smem_u32(&s_full[s]), 1);
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(smem_u32(&p_ready[s]), 256);
+      mbar_init(smem_u32(&p_ready[s]), 128);     // the 128 threads of the warpgroup that owns the tile
       mbar_init(smem_u32(&pv_done[s]), 1);
-      mbar_init(smem_u32(&max_bar[s]), 256);
     }
-    mbar_init(smem_u32(sum_bar), 256);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -192,13 +191,13 @@ __global__ void __launch_bounds__(320, 1)
         tc_fence_after();
         const uint32_t p_base = smem_u32(sP + (j & 1) * C::P_BYTES);
         const uint32_t v_base = smem_u32(sV + st * C::KV_BYTES);
-        const uint32_t d = tmem_base + C::O_COL;
+        const uint32_t d = tmem_base + C::O_COL + (j & 1) * 128;   // even / odd tiles accumulate apart
 #pragma unroll
         for (int k = 0; k < C::BN / 16; ++k) {
           const uint32_t po = (k >> 2) * C::TILE_BYTES + (k & 3) * 32;
           umma_f16_w(d, make_smem_desc_sw128(p_base + po, 16, 1024),
                    make_smem_desc_sw128(v_base + k * 2048, C::TILE_BYTES, 1024), idesc_o,
-                   (j | k) != 0);
+                   (j >= 2 || k != 0) ? 1u : 0u);
         }
         umma_commit_w(smem_u32(&v_empty[st]));
         umma_commit_w(smem_u32(&pv_done[j & 1]));
@@ -206,154 +205,146 @@ __global__ void __launch_bounds__(320, 1)
     }
   } else if (n_tiles > 0) {
     // ------------------------------ softmax warps -----------------------------
-    const int h = warp_idx >> 2;                 // which half of the tile's key columns
-    const int t = (warp_idx & 3) * 32 + lane;    // row within the tile == TMEM lane
-    const int row = q0 + t;                      // global query row
+    const int wg = warp_idx >> 2;                 // 0: even K/V tiles, 1: odd K/V tiles
+    const int t = (warp_idx & 3) * 32 + lane;     // row within the tile == TMEM lane
+    const int row = q0 + t;                       // global query row
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp_idx & 3) * 32) << 16);
-    constexpr int COL_X = C::O_COL + 128;        // spare TMEM columns: per-row scalars of the two halves
-    constexpr int O_CHUNKS = HD / 64;            // 32-column chunks of O per half
-    float m_used = -INFINITY, l = 0.f;           // l: this half's partial row sum
+    const uint32_t o_mine = lane_addr + C::O_COL + wg * 128;     // this warpgroup's O accumulator
+    float m_used = -INFINITY, l = 0.f;            // running maximum (log2 domain) and sum of this warpgroup's tiles
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int jb = j & 1;
+    for (int j = wg; j < n_tiles; j += 2) {
       const uint32_t jph = (j >> 1) & 1;
-      ok = mbar_wait(smem_u32(&s_full[jb]), jph, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL);
+      ok = mbar_wait(smem_u32(&s_full[wg]), jph, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t s_addr = lane_addr + C::S_COL0 + jb * 128 + h * 64;
+      const uint32_t s_addr = lane_addr + C::S_COL0 + wg * 128;
       const int kv0 = j * C::BN;
-      const int kvh0 = kv0 + h * 64;               // first key column of this half
       const bool need_mask = (kv0 + C::BN > p.Sk) || (p.causal && kv0 + C::BN - 1 > q0 + off);
       const int kv_limit = p.causal ? min(p.Sk - 1, row + off) : p.Sk - 1;  // last valid kv index
-      // This half's 64 columns of the S row are loaded once.  Exponentials are first taken against
-      // the running maximum already in use; only when the tile raises the row maximum by more
-      // than 2^8 (always on the first tile, rarely afterwards) O and l are rescaled.
-      uint32_t sreg[2][32];
-      tmem_ld_32x32b_x32(s_addr, sreg[0]);
-      tmem_ld_32x32b_x32(s_addr + 32, sreg[1]);
-      tmem_ld_wait();
+      // pass 1: row maximum over the 128 columns, 64 at a time
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      if (need_mask) {
+#pragma unroll 1
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t sreg[2][32];
+        tmem_ld_32x32b_x32(s_addr + hh * 64, sreg[0]);
+        tmem_ld_32x32b_x32(s_addr + hh * 64 + 32, sreg[1]);
+        tmem_ld_wait();
+        if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
+          for (int c = 0; c < 2; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (kvh0 + c * 32 + i <= kv_limit)
-              mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sreg[c][i]));
-      } else {
+            for (int i = 0; i < 32; ++i)
+              if (kv0 + hh * 64 + c * 32 + i <= kv_limit)
+                mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sreg[c][i]));
+        } else {
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
+          for (int c = 0; c < 2; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sreg[c][i]));
+            for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sreg[c][i]));
+        }
       }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // the other half's maximum of the same row (through a spare TMEM column of this lane)
-      tmem_st_32x32b_x1(lane_addr + COL_X + jb * 2 + h, __float_as_uint(mx));
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(smem_u32(&max_bar[jb]));
-      ok = mbar_wait(smem_u32(&max_bar[jb]), jph, abort_flag, p.status, RB_ERR_TIMEOUT_FLAG);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      mx = fmaxf(mx, __uint_as_float(tmem_ld_32x32b_x1(lane_addr + COL_X + jb * 2 + (h ^ 1))));
-      tmem_ld_wait();
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
-      const bool need = m_new > m_used + 8.0f;  // also true on the first tile (m_used = -inf)
+      const bool need = m_new > m_used + 8.0f;  // also true on this warpgroup's first tile (m_used = -inf)
       if (j >= 2) {
-        // the P buffer of tile j-2 must have been consumed
-        ok = mbar_wait(smem_u32(&pv_done[jb]), ((j - 2) >> 1) & 1, abort_flag, p.status,
+        // the previous tile of this warpgroup (j - 2) used the same P buffer and the same O accumulator:
+        // its P.V must have retired before P is overwritten or O is rescaled
+        ok = mbar_wait(smem_u32(&pv_done[wg]), ((j - 2) >> 1) & 1, abort_flag, p.status,
                        RB_ERR_TIMEOUT_TMEM_EMPTY);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        tc_fence_after();
       }
-      if (__any_sync(0xffffffffu, need)) {
-        if (j > 0) {
-          // O is rescaled in place: the previous P.V must have retired
-          ok = mbar_wait(smem_u32(&pv_done[(j - 1) & 1]), ((j - 1) >> 1) & 1, abort_flag, p.status,
-                         RB_ERR_TIMEOUT_TMEM_EMPTY);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-        }
+      if (__any_sync(0xffffffffu, need)) {       // the TMEM accesses below are warp-wide: uniform branch
         float alpha = 1.0f;
         if (need) {
           alpha = (m_used == -INFINITY) ? 0.0f : fast_exp2(m_used - m_new);
           m_used = m_new;
           l *= alpha;
         }
-        if (j > 0) {
-          // each half rescales its own half of the O columns
+        if (j >= 2) {
 #pragma unroll 1
-          for (int c = 0; c < O_CHUNKS; ++c) {
+          for (int c = 0; c < HD / 32; ++c) {
             uint32_t r[32];
-            const uint32_t o_addr = lane_addr + C::O_COL + h * (HD / 2) + c * 32;
-            tmem_ld_32x32b_x32(o_addr, r);
+            tmem_ld_32x32b_x32(o_mine + c * 32, r);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32b_x32(o_addr, r);
+            tmem_st_32x32b_x32(o_mine + c * 32, r);
           }
           tmem_st_wait();
         }
       }
-      // P = exp2(S*scale - m), partial row sum, store to swizzled smem (sub-tile h of buffer jb)
+      // pass 2: P = exp2(S*scale - m), row sum, store to this warpgroup's swizzled P tile
       const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint8_t* rowp = sP + jb * C::P_BYTES + h * C::TILE_BYTES + t * 128;
+      uint8_t* prow = sP + wg * C::P_BYTES + t * 128;
+#pragma unroll 1
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t sreg[2][32];
+        tmem_ld_32x32b_x32(s_addr + hh * 64, sreg[0]);
+        tmem_ld_32x32b_x32(s_addr + hh * 64 + 32, sreg[1]);
+        tmem_ld_wait();
+        uint8_t* rowp = prow + hh * C::TILE_BYTES;       // sub-tile hh holds key columns [64 hh, 64 hh + 64)
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t packed[16];
+        for (int c = 0; c < 2; ++c) {
+          uint32_t packed[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(sreg[c][i]), p.scale_log2, neg_m));
-          float p1 = fast_exp2(fmaf(__uint_as_float(sreg[c][i + 1]), p.scale_log2, neg_m));
-          if (need_mask) {
-            if (kvh0 + c * 32 + i > kv_limit) p0 = 0.f;
-            if (kvh0 + c * 32 + i + 1 > kv_limit) p1 = 0.f;
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = fast_exp2(fmaf(__uint_as_float(sreg[c][i]), p.scale_log2, neg_m));
+            float p1 = fast_exp2(fmaf(__uint_as_float(sreg[c][i + 1]), p.scale_log2, neg_m));
+            if (need_mask) {
+              if (kv0 + hh * 64 + c * 32 + i > kv_limit) p0 = 0.f;
+              if (kv0 + hh * 64 + c * 32 + i + 1 > kv_limit) p1 = 0.f;
+            }
+            l4[(i >> 1) & 3] += p0 + p1;
+            packed[i >> 1] = pack2<T>(p0, p1);
           }
-          l4[(i >> 1) & 3] += p0 + p1;
-          packed[i >> 1] = pack2<T>(p0, p1);
-        }
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int cc = c * 4 + q;
-          *reinterpret_cast<uint4*>(rowp + ((cc ^ (t & 7)) << 4)) =
-              make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
+          for (int q = 0; q < 4; ++q) {
+            const int cc = c * 4 + q;
+            *reinterpret_cast<uint4*>(rowp + ((cc ^ (t & 7)) << 4)) =
+                make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
+          }
         }
       }
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(smem_u32(&p_ready[jb]));
+      mbar_arrive(smem_u32(&p_ready[wg]));
     }
+    // ---- merge the two warpgroups' partial results and write the output ----
+    // every P.V of both accumulators must have retired
+    const int last0 = ((n_tiles - 1) & 1) == 0 ? n_tiles - 1 : n_tiles - 2;   // last even tile (always exists)
+    const int last1 = ((n_tiles - 1) & 1) == 1 ? n_tiles - 1 : n_tiles - 2;   // last odd tile, or -1
     if (ok) {
-      ok = mbar_wait(smem_u32(&pv_done[(n_tiles - 1) & 1]), ((n_tiles - 1) >> 1) & 1, abort_flag,
-                     p.status, RB_ERR_TIMEOUT_TMEM_EMPTY);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = mbar_wait(smem_u32(&pv_done[0]), (last0 >> 1) & 1, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_EMPTY);
+      if (ok && last1 >= 0)
+        ok = mbar_wait(smem_u32(&pv_done[1]), (last1 >> 1) & 1, abort_flag, p.status, RB_ERR_TIMEOUT_TMEM_EMPTY);
     }
-    if (ok) {
-      tc_fence_after();
-      // total row sum = the two halves' partial sums
-      tmem_st_32x32b_x1(lane_addr + COL_X + 4 + h, __float_as_uint(l));
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(smem_u32(sum_bar));
-      ok = mbar_wait(smem_u32(sum_bar), 0, abort_flag, p.status, RB_ERR_TIMEOUT_FLAG);
-      ok = __all_sync(0xffffffffu, ok);
-    }
+    // (m, l) of the two warpgroups meet in shared memory (the Q tile is no longer needed: reuse it)
+    float2* fin = reinterpret_cast<float2*>(sQ);            // [2][128]
+    fin[wg * 128 + t] = make_float2(m_used, l);
+    asm volatile("bar.sync 1, 256;" ::: "memory");          // the 8 softmax warps; reached on every path
     if (ok) {
       tc_fence_after();
-      l += __uint_as_float(tmem_ld_32x32b_x1(lane_addr + COL_X + 4 + (h ^ 1)));
-      tmem_ld_wait();
-      const float inv_l = l > 0.f ? 1.0f / l : 0.f;
+      const float2 other = fin[(wg ^ 1) * 128 + t];
+      const float m_all = fmaxf(m_used, other.x);
+      const float f_me = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_all);
+      const float f_ot = (other.x == -INFINITY) ? 0.f : fast_exp2(other.x - m_all);
+      const float l_all = l * f_me + other.y * f_ot;
+      const float inv_l = l_all > 0.f ? 1.0f / l_all : 0.f;
+      const float w_even = (wg == 0 ? f_me : f_ot) * inv_l, w_odd = (wg == 0 ? f_ot : f_me) * inv_l;
+      const bool has_odd = last1 >= 0;
+      // warpgroup w writes output columns [w * HD/2, (w+1) * HD/2)
       T* orow = reinterpret_cast<T*>(p.o) + ((static_cast<long long>(b) * p.Sq + row) * p.H + h_idx) * HD +
-                h * (HD / 2);
+                wg * (HD / 2);
 #pragma unroll 1
-      for (int c = 0; c < O_CHUNKS; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(lane_addr + C::O_COL + h * (HD / 2) + c * 32, r);
+      for (int c = 0; c < HD / 64; ++c) {
+        uint32_t re[32], ro[32];
+        tmem_ld_32x32b_x32(lane_addr + C::O_COL + wg * (HD / 2) + c * 32, re);
+        if (has_odd) tmem_ld_32x32b_x32(lane_addr + C::O_COL + 128 + wg * (HD / 2) + c * 32, ro);
         tmem_ld_wait();
         if (row < p.Sq) {
 #pragma unroll
@@ -361,14 +352,18 @@ __global__ void __launch_bounds__(320, 1)
             uint4 v;
             T* e = reinterpret_cast<T*>(&v);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(__uint_as_float(r[q * 8 + i]) * inv_l);
+            for (int i = 0; i < 8; ++i) {
+              float val = __uint_as_float(re[q * 8 + i]) * w_even;
+              if (has_odd) val += __uint_as_float(ro[q * 8 + i]) * w_odd;
+              e[i] = from_f32<T>(val);
+            }
             *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = v;
           }
         }
       }
-      if (h == 0 && row < p.Sq)
+      if (wg == 0 && row < p.Sq)
         p.lse[(static_cast<long long>(b) * p.H + h_idx) * p.Sq + row] =
-            (m_used + log2f(l)) * 0.6931471805599453f;
+            (m_all + log2f(l_all)) * 0.6931471805599453f;
     }
   }
 

@@ -126,15 +126,18 @@ int launch_gemm_2cta_flavour(GemmArgs& a, int mt) {
 }
 
 // Rows of A per CTA and tile.  512 x 256 tiles move a quarter less operand data per FLOP than
-// 256 x 256 ones; they win unless they leave the last wave of clusters too empty.
+// 256 x 256 ones but hold all of TMEM, so their epilogue is exposed once per tile.  Measured back to
+// back under the power cap (bf16, M 16384): wide outputs (N 8192: 1241 vs 1220 TFLOP/s, N 50304: 1218
+// vs 1181) gain from the larger tile, narrow ones (N 2048: 1273 vs 1300 at K 8192, 1078 vs 1143 at
+// K 2048) do not; neither does a problem whose 512-row tiles leave the last wave of clusters emptier.
 int pick_pair_mt(int M, int N, int clusters) {
-  if (M <= 256) return 1;
+  if (M <= 256 || N < 4096) return 1;
   auto waves = [&](int bm) {
     const long long t = (long long)((M + bm - 1) / bm) * ((N + G2_BN - 1) / G2_BN);
     const long long w = (t + clusters - 1) / clusters;
     return (double)t / (double)(w * clusters);
   };
-  return waves(512) * 1.15 >= waves(256) ? 2 : 1;
+  return waves(512) * 1.05 >= waves(256) ? 2 : 1;
 }
 
 }  // namespace rb

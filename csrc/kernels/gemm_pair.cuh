@@ -206,7 +206,7 @@ __device__ __forceinline__ void epilogue_math32(const GemmParams& p, const uint3
       for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
     } else if (p.act == ACT_GELU) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+      for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_fast(v[i]);
     } else if (p.act == ACT_SILU) {
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = silu_f(v[i]);
@@ -219,7 +219,7 @@ __device__ __forceinline__ void epilogue_math32(const GemmParams& p, const uint3
         for (int i = 0; i < 32; ++i) v[i] = a[i] > 0.0f ? v[i] : 0.0f;
       } else if (p.dact == ACT_GELU) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] *= gelu_tanh_grad(a[i]);
+        for (int i = 0; i < 32; ++i) v[i] *= gelu_tanh_grad_fast(a[i]);
       } else if (p.dact == ACT_SILU) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] *= silu_grad(a[i]);

@@ -392,6 +392,26 @@ __device__ __forceinline__ float gelu_tanh_grad(float x) {
   float du = k0 * (1.0f + 3.0f * k1 * x * x);
   return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
 }
+// The same two with the hardware tanh (one special-function instruction, relative error about 2^-11:
+// below what a 16-bit result can hold).  For GEMM epilogues, which run 128 of these per thread and
+// tile and round the result to 16 bits; the stand-alone activation kernels keep tanhf.
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  return 0.5f * x * (1.0f + fast_tanh(u));
+}
+__device__ __forceinline__ float gelu_tanh_grad_fast(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  float t = fast_tanh(u);
+  float du = k0 * (1.0f + 3.0f * k1 * x * x);
+  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
+}
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 __device__ __forceinline__ float silu_grad(float x) {
   float s = 1.0f / (1.0f + __expf(-x));

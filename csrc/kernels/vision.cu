@@ -568,6 +568,52 @@ __global__ void maxpool_nhwc_bwd_kernel(const T* __restrict__ dy, const signed c
     dx[i] = from_f32<T>(acc);
   }
 }
+// the same gather, eight channels (16 bytes of dy, 8 bytes of argmax codes) per thread
+template <typename T>
+__global__ void maxpool_nhwc_bwd_vec8_kernel(const T* __restrict__ dy, const signed char* __restrict__ idx,
+                                             T* __restrict__ dx, int B, int H, int W, int C, int K,
+                                             int stride, int pad, int Ho, int Wo) {
+  const int C8 = C / 8;
+  const long long total = (long long)B * H * W * C8;
+  const long long gs = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gs) {
+    const int c8 = (int)(i % C8);
+    long long t = i / C8;
+    const int iw = (int)(t % W);
+    t /= W;
+    const int ih = (int)(t % H);
+    const int b = (int)(t / H);
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int kh = 0; kh < K; ++kh) {
+      const int nh = ih + pad - kh;
+      if (nh < 0 || nh % stride) continue;
+      const int oh = nh / stride;
+      if (oh >= Ho) continue;
+      for (int kw = 0; kw < K; ++kw) {
+        const int nw = iw + pad - kw;
+        if (nw < 0 || nw % stride) continue;
+        const int ow = nw / stride;
+        if (ow >= Wo) continue;
+        const long long o = (((long long)b * Ho + oh) * Wo + ow) * C + c8 * 8;
+        const uint2 codes = *reinterpret_cast<const uint2*>(idx + o);
+        const uint4 g = *reinterpret_cast<const uint4*>(dy + o);
+        const signed char* cd = reinterpret_cast<const signed char*>(&codes);
+        const T* ge = reinterpret_cast<const T*>(&g);
+        const int want = kh * K + kw;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (cd[j] == want) acc[j] += to_f32<T>(ge[j]);
+      }
+    }
+    uint4 out;
+    T* oe = reinterpret_cast<T*>(&out);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) oe[j] = from_f32<T>(acc[j]);
+    *reinterpret_cast<uint4*>(dx + i * 8) = out;
+  }
+}
 // adaptive average pool, bins [floor(o*H/Ho), ceil((o+1)*H/Ho))
 template <typename T, bool BWD>
 __global__ void adaptive_avgpool_nhwc_kernel(const T* __restrict__ src, T* __restrict__ dst, int B,
@@ -751,6 +797,16 @@ int rb_maxpool_bwd(int dtype, const void* dy, const signed char* idx, void* dx, 
   cudaStream_t st = (cudaStream_t)stream;
   const long long n = (long long)B * H * W * C;
   if (n <= 0) return 0;
+  const bool vec8 = dtype != rbh::DT_F32 && C % 8 == 0 &&
+                    ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx)) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(idx) & 7) == 0;
+  if (vec8) {
+    if (dtype == rbh::DT_BF16)
+      maxpool_nhwc_bwd_vec8_kernel<__nv_bfloat16><<<vgrid(n / 8), 256, 0, st>>>((const __nv_bfloat16*)dy, idx, (__nv_bfloat16*)dx, B, H, W, C, K, stride, pad, Ho, Wo);
+    else
+      maxpool_nhwc_bwd_vec8_kernel<__half><<<vgrid(n / 8), 256, 0, st>>>((const __half*)dy, idx, (__half*)dx, B, H, W, C, K, stride, pad, Ho, Wo);
+    RB_RET_LAST();
+  }
   RB_DISPATCH_T(dtype, (maxpool_nhwc_bwd_kernel<T><<<vgrid(n), 256, 0, st>>>((const T*)dy, idx, (T*)dx, B, H, W, C, K, stride, pad, Ho, Wo)));
   RB_RET_LAST();
 }

@@ -39,8 +39,6 @@ def test_context_parallel_attention_matches_full_sequence():
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2,
                     reason="needs >= 2 GPUs")
-@pytest.mark.skipif(os.environ.get("RB_TEST_RESHARD", "0") != "1",
-                    reason="resharded FSDP on GPUs is opt-in until it has been seen passing once")
 def test_fsdp_reshard_after_forward_matches_resident_flow():
     n = min(torch.cuda.device_count(), 4)
     r = _run(os.path.join(ROOT, "tests", "multi_gpu", "reshard_checks.py"), n)
