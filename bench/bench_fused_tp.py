@@ -1,5 +1,7 @@
 """Times the fused tensor-parallel kernels (all-gather -> GEMM, GEMM -> reduce-scatter) against
-NCCL collectives + the plain GEMM on Llama-7B layer shapes (run under torchrun):
+NCCL collectives + the plain GEMM on Llama-7B layer shapes, and the FSDP form of the first (a whole
+flat parameter unit gathered by the kernel that multiplies by the unit's first weight) on a
+GPT-1.3B block (run under torchrun):
 
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 bench/bench_fused_tp.py
 
@@ -105,10 +107,43 @@ def main():
         dist.reduce_scatter_tensor(out2, full2)
     res.append(("gemm + reduce_scatter (nccl)", timed(nccl2), flops2))
     res.append(("gemm alone", timed(lambda: native.gemm(a2, w2, out=full2)), flops2))
+    # ---- FSDP unit: the flat parameter vector of one GPT-1.3B block (d 2048: 12 d^2 + 13 d values), sharded
+    # evenly; the kernel gathers all of it and multiplies 8 x 2048 tokens by the qkv weight that sits in it
+    dg, tok = 2048, 16384
+    pad = 2 * dg                                                   # ln1 weight and bias come first
+    unit = 12 * dg * dg + 13 * dg
+    flat_n = (unit + world * 1024 - 1) // (world * 1024) * world * 1024
+    Sb = flat_n // world
+    flat, flat_off = arena.alloc(flat_n, torch.bfloat16)
+    shard = (torch.randn(Sb, device=dev) * 0.02).bfloat16()
+    flat_full = torch.empty(flat_n, device=dev, dtype=torch.bfloat16)
+    xa = (torch.randn(tok, dg, device=dev) * 0.5).bfloat16()
+    outq = torch.empty(tok, 3 * dg, device=dev, dtype=torch.bfloat16)
+    bflags = arena.alloc_flags(world)
+    arena.barrier()
+    ep3 = [0]
+    flops3 = 2.0 * tok * dg * 3 * dg
+    for chunk_kb, ncopy in [(1024, 16), (1024, 32), (2048, 24)]:
+        def fused3():
+            ep3[0] += 1
+            flat[rank * Sb:(rank + 1) * Sb].copy_(shard)
+            fused_ops.signal_peers(arena, bflags, ep3[0])
+            fused_ops.ag_gemm(arena, buf_off=flat_off, shard_bytes=Sb * 2, chunk_flags=chunk_flags,
+                              chunk_bytes=chunk_kb * 1024, epoch=ep3[0], gather_a=False, operand_off=pad * 2,
+                              other=xa, M=tok, N=3 * dg, K=dg, out=outq, src_flags_off=bflags,
+                              n_copy_ctas=ncopy)
+        res.append((f"fsdp unit gather+qkv fused chunk={chunk_kb}K copy_ctas={ncopy}", timed(fused3), flops3))
+
+    def nccl3():
+        dist.all_gather_into_tensor(flat_full, shard)
+        native.gemm(xa, flat_full[pad:pad + dg * 3 * dg].view(dg, 3 * dg), out=outq)
+    res.append((f"fsdp unit all_gather ({flat_n * 2 >> 20} MB) + qkv gemm (nccl)", timed(nccl3), flops3))
+    res.append(("qkv gemm alone", timed(lambda: native.gemm(xa, flat_full[pad:pad + dg * 3 * dg].view(dg, 3 * dg),
+                                                            out=outq)), flops3))
     if rank == 0:
         print(f"tokens {M}, d {d}, ffn/rank {ffn}, world {world}, status {native.read_status()}")
         for k, t, fl in res:
-            print(f"  {k:44s} {t * 1e3:9.1f} us  {fl / t / 1e9:7.0f} TFLOP/s")
+            print(f"  {k:60s} {t * 1e3:9.1f} us  {fl / t / 1e9:7.0f} TFLOP/s")
     dist.barrier()
     dist.destroy_process_group()
 

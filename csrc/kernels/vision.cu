@@ -296,9 +296,10 @@ __global__ void __launch_bounds__(256)
     mu[j] = BWD ? mean[c0 + j] : 0.f;
     rs[j] = BWD ? rstd[c0 + j] : 1.f;
   }
-  for (long long r = r0 + ty; r < r1; r += lanes) {
+  // four rows in flight per thread: the loads of a batch are issued before any of them is used
+  auto fold = [&](const uint4& xq, const uint4& dq, const uint4& yq) {
     float xv[8];
-    unpack8f<T>(*reinterpret_cast<const uint4*>(x + r * C + c0), xv);
+    unpack8f<T>(xq, xv);
     if (!BWD) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -307,10 +308,10 @@ __global__ void __launch_bounds__(256)
       }
     } else {
       float d[8];
-      unpack8f<T>(*reinterpret_cast<const uint4*>(dy + r * C + c0), d);
+      unpack8f<T>(dq, d);
       if (relu) {
         float yv[8];
-        unpack8f<T>(*reinterpret_cast<const uint4*>(y + r * C + c0), yv);
+        unpack8f<T>(yq, yv);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           if (yv[j] <= 0.f) d[j] = 0.f;
@@ -321,6 +322,27 @@ __global__ void __launch_bounds__(256)
         b[j] += d[j] * (xv[j] - mu[j]) * rs[j];
       }
     }
+  };
+  long long r = r0 + ty;
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  for (; r + 3ll * lanes < r1; r += 4ll * lanes) {
+    uint4 xq[4], dq[4], yq[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long o = (r + (long long)u * lanes) * C + c0;
+      xq[u] = *reinterpret_cast<const uint4*>(x + o);
+      dq[u] = BWD ? *reinterpret_cast<const uint4*>(dy + o) : zero4;
+      yq[u] = (BWD && relu) ? *reinterpret_cast<const uint4*>(y + o) : zero4;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) fold(xq[u], dq[u], yq[u]);
+  }
+  for (; r < r1; r += lanes) {
+    const long long o = r * C + c0;
+    const uint4 xq = *reinterpret_cast<const uint4*>(x + o);
+    const uint4 dq = BWD ? *reinterpret_cast<const uint4*>(dy + o) : zero4;
+    const uint4 yq = (BWD && relu) ? *reinterpret_cast<const uint4*>(y + o) : zero4;
+    fold(xq, dq, yq);
   }
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
@@ -405,35 +427,49 @@ __global__ void __launch_bounds__(256)
   dgamma[c] = from_f32<T>(q);
 }
 
-// Per-channel coefficients live in shared memory (computed once per CTA): reading mean / rstd /
-// gamma / beta per element from global memory cost 16 scattered 4-byte loads per 8 channels and
-// made these kernels L1-bound at ~1.8 TB/s.
+// Per-channel coefficients live in registers: the grid stride is a multiple of the number of
+// 8-channel groups (a power of two, at most 512; the launcher keeps gridDim.x even), so a thread
+// meets the same 8 channels on every iteration and computes their coefficients once.  Reading
+// mean / rstd / gamma / beta per element cost 16 scattered 4-byte loads per 8 channels and made
+// these kernels L1-bound at ~1.8 TB/s; the 64-bit `i % groups` per element and a single 16-byte
+// load in flight per thread held the second version near half of the copy bandwidth.
 //   forward:  y = relu(x * a + b + res),  a = rstd * gamma,  b = beta - mean * a
+__device__ __forceinline__ void load8f(const float* p, float* f) {
+  const float4 v0 = *reinterpret_cast<const float4*>(p), v1 = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = v0.x; f[1] = v0.y; f[2] = v0.z; f[3] = v0.w;
+  f[4] = v1.x; f[5] = v1.y; f[6] = v1.z; f[7] = v1.w;
+}
+
 template <typename T>
-__global__ void bn_apply_vec8_kernel(const T* __restrict__ x, const T* __restrict__ res,
-                                     const T* __restrict__ gamma, const T* __restrict__ beta,
-                                     const float* __restrict__ mean, const float* __restrict__ rstd,
-                                     T* __restrict__ y, long long n8, int C, int relu) {
-  extern __shared__ float s_coef[];   // [2][C]
-  float* sa = s_coef;
-  float* sb = s_coef + C;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    const float a = rstd[c] * to_f32<T>(gamma[c]);
-    sa[c] = a;
-    sb[c] = to_f32<T>(beta[c]) - mean[c] * a;
-  }
-  __syncthreads();
+__global__ void __launch_bounds__(256, 4)
+    bn_apply_vec8_kernel(const T* __restrict__ x, const T* __restrict__ res,
+                         const T* __restrict__ gamma, const T* __restrict__ beta,
+                         const float* __restrict__ mean, const float* __restrict__ rstd,
+                         T* __restrict__ y, long long n8, int C, int relu) {
   const int CG = C >> 3;
   const long long gs = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += gs) {
-    const int c0 = (int)(i % CG) * 8;
+  const long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int c0 = (int)(i0 & (CG - 1)) * 8;
+  float av[8], bv[8];
+  {
+    float mu[8], g[8], be[8];
+    load8f(rstd + c0, av);
+    load8f(mean + c0, mu);
+    unpack8f<T>(*reinterpret_cast<const uint4*>(gamma + c0), g);
+    unpack8f<T>(*reinterpret_cast<const uint4*>(beta + c0), be);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      av[j] *= g[j];
+      bv[j] = be[j] - mu[j] * av[j];
+    }
+  }
+  const uint4* x4 = reinterpret_cast<const uint4*>(x);
+  const uint4* r4 = reinterpret_cast<const uint4*>(res);
+  uint4* y4 = reinterpret_cast<uint4*>(y);
+  auto one = [&](const uint4& xq, const uint4& rq) {
     float xv[8], rv[8];
-    unpack8f<T>(reinterpret_cast<const uint4*>(x)[i], xv);
-    if (res) unpack8f<T>(reinterpret_cast<const uint4*>(res)[i], rv);
-    const float4 a0 = *reinterpret_cast<const float4*>(sa + c0), a1 = *reinterpret_cast<const float4*>(sa + c0 + 4);
-    const float4 b0 = *reinterpret_cast<const float4*>(sb + c0), b1 = *reinterpret_cast<const float4*>(sb + c0 + 4);
-    const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-    const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    unpack8f<T>(xq, xv);
+    if (res) unpack8f<T>(rq, rv);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float v = fmaf(xv[j], av[j], bv[j]);
@@ -441,68 +477,105 @@ __global__ void bn_apply_vec8_kernel(const T* __restrict__ x, const T* __restric
       if (relu) v = fmaxf(v, 0.f);
       xv[j] = v;
     }
-    reinterpret_cast<uint4*>(y)[i] = pack8f<T>(xv);
+    return pack8f<T>(xv);
+  };
+  long long i = i0;
+  for (; i + 3 * gs < n8; i += 4 * gs) {
+    uint4 xq[4], rq[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      xq[u] = x4[i + u * gs];
+      rq[u] = res ? r4[i + u * gs] : xq[u];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) y4[i + u * gs] = one(xq[u], rq[u]);
+  }
+  for (; i < n8; i += gs) {
+    const uint4 xq = x4[i];
+    const uint4 rq = res ? r4[i] : xq;
+    y4[i] = one(xq, rq);
   }
 }
 
 //   backward: dx = A * d + Bc * x + Cc with d = dy masked by the ReLU, and (training)
 //   A = gamma*rstd, Bc = -A*rstd*S2/M, Cc = -A*S1/M - Bc*mean;  (eval) Bc = Cc = 0
 template <typename T>
-__global__ void bn_bwd_apply_vec8_kernel(const T* __restrict__ x, const T* __restrict__ dy,
-                                         const T* __restrict__ y, const T* __restrict__ gamma,
-                                         const float* __restrict__ mean,
-                                         const float* __restrict__ rstd,
-                                         const float* __restrict__ sums, T* __restrict__ dx,
-                                         T* __restrict__ dres, long long n8, int C, long long M,
-                                         int relu, int training) {
-  extern __shared__ float s_coef[];   // [3][C]
-  float* sA = s_coef;
-  float* sB = s_coef + C;
-  float* sC = s_coef + 2 * C;
-  const float invM = 1.f / (float)M;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    const float rs = rstd[c];
-    const float A = to_f32<T>(gamma[c]) * rs;
-    float Bc = 0.f, Cc = 0.f;
-    if (training) {
-      Bc = -A * rs * sums[C + c] * invM;
-      Cc = -A * sums[c] * invM - Bc * mean[c];
-    }
-    sA[c] = A;
-    sB[c] = Bc;
-    sC[c] = Cc;
-  }
-  __syncthreads();
+__global__ void __launch_bounds__(256, 4)
+    bn_bwd_apply_vec8_kernel(const T* __restrict__ x, const T* __restrict__ dy,
+                             const T* __restrict__ y, const T* __restrict__ gamma,
+                             const float* __restrict__ mean, const float* __restrict__ rstd,
+                             const float* __restrict__ sums, T* __restrict__ dx,
+                             T* __restrict__ dres, long long n8, int C, long long M, int relu,
+                             int training) {
   const int CG = C >> 3;
   const long long gs = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += gs) {
-    const int c0 = (int)(i % CG) * 8;
+  const long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int c0 = (int)(i0 & (CG - 1)) * 8;
+  float Av[8], Bv[8], Cv[8];
+  {
+    const float invM = 1.f / (float)M;
+    float rs[8], mu[8], g[8], s1[8], s2[8];
+    load8f(rstd + c0, rs);
+    load8f(mean + c0, mu);
+    unpack8f<T>(*reinterpret_cast<const uint4*>(gamma + c0), g);
+    if (training) {
+      load8f(sums + c0, s1);
+      load8f(sums + C + c0, s2);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      Av[j] = g[j] * rs[j];
+      Bv[j] = Cv[j] = 0.f;
+      if (training) {
+        Bv[j] = -Av[j] * rs[j] * s2[j] * invM;
+        Cv[j] = -Av[j] * s1[j] * invM - Bv[j] * mu[j];
+      }
+    }
+  }
+  const uint4* x4 = reinterpret_cast<const uint4*>(x);
+  const uint4* d4 = reinterpret_cast<const uint4*>(dy);
+  const uint4* y4 = reinterpret_cast<const uint4*>(y);
+  uint4* o4 = reinterpret_cast<uint4*>(dx);
+  uint4* dr4 = reinterpret_cast<uint4*>(dres);
+  auto one = [&](long long at, const uint4& dq, const uint4& yq, const uint4& xq) {
     float d[8], o[8];
-    unpack8f<T>(reinterpret_cast<const uint4*>(dy)[i], d);
+    unpack8f<T>(dq, d);
     if (relu) {
       float yv[8];
-      unpack8f<T>(reinterpret_cast<const uint4*>(y)[i], yv);
+      unpack8f<T>(yq, yv);
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         if (yv[j] <= 0.f) d[j] = 0.f;
     }
-    if (dres) reinterpret_cast<uint4*>(dres)[i] = pack8f<T>(d);
-    const float4 A0 = *reinterpret_cast<const float4*>(sA + c0), A1 = *reinterpret_cast<const float4*>(sA + c0 + 4);
-    const float Av[8] = {A0.x, A0.y, A0.z, A0.w, A1.x, A1.y, A1.z, A1.w};
+    if (dres) dr4[at] = pack8f<T>(d);
     if (training) {
       float xv[8];
-      unpack8f<T>(reinterpret_cast<const uint4*>(x)[i], xv);
-      const float4 B0 = *reinterpret_cast<const float4*>(sB + c0), B1 = *reinterpret_cast<const float4*>(sB + c0 + 4);
-      const float4 C0 = *reinterpret_cast<const float4*>(sC + c0), C1 = *reinterpret_cast<const float4*>(sC + c0 + 4);
-      const float Bv[8] = {B0.x, B0.y, B0.z, B0.w, B1.x, B1.y, B1.z, B1.w};
-      const float Cv[8] = {C0.x, C0.y, C0.z, C0.w, C1.x, C1.y, C1.z, C1.w};
+      unpack8f<T>(xq, xv);
 #pragma unroll
       for (int j = 0; j < 8; ++j) o[j] = fmaf(Av[j], d[j], fmaf(Bv[j], xv[j], Cv[j]));
     } else {
 #pragma unroll
       for (int j = 0; j < 8; ++j) o[j] = Av[j] * d[j];
     }
-    reinterpret_cast<uint4*>(dx)[i] = pack8f<T>(o);
+    o4[at] = pack8f<T>(o);
+  };
+  long long i = i0;
+  for (; i + gs < n8; i += 2 * gs) {
+    uint4 dq[2], yq[2], xq[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      dq[u] = d4[i + u * gs];
+      yq[u] = relu ? y4[i + u * gs] : dq[u];
+      xq[u] = training ? x4[i + u * gs] : dq[u];
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) one(i + u * gs, dq[u], yq[u], xq[u]);
+  }
+  for (; i < n8; i += gs) {
+    const uint4 dq = d4[i];
+    const uint4 yq = relu ? y4[i] : dq;
+    const uint4 xq = training ? x4[i] : dq;
+    one(i, dq, yq, xq);
   }
 }
 
@@ -717,6 +790,15 @@ int rb_col2im_nhwc(int dtype, const void* dcols, void* dx, int B, int H, int W, 
   RB_DISPATCH_T(dtype, (col2im_nhwc_kernel<T><<<vgrid(n), 256, 0, st>>>((const T*)dcols, (T*)dx, B, H, W, C, KH, KW, Ho, Wo, stride, pad, dil, Kpad)));
   RB_RET_LAST();
 }
+// Grid of the 16-byte batch-norm apply kernels: an even number of 256-thread CTAs (so the grid
+// stride is a multiple of 512 channel groups), at most the four per SM that are resident.
+static unsigned bn_grid(long long n8) {
+  long long b = (n8 + 255) / 256;
+  const long long cap = (long long)rbh::sm_count() * 4;
+  if (b > cap) b = cap;
+  b = (b + 1) & ~1ll;
+  return (unsigned)b;
+}
 int rb_bn_slabs(long long M) {
   long long s = (M + 255) / 256;
   if (s > 2048) s = 2048;
@@ -733,7 +815,7 @@ int rb_bn_fwd(int dtype, const void* x, const void* res, const void* gamma, cons
   const int cg = C / 8;
   auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   const bool vec8 = dtype != rbh::DT_F32 && C % 8 == 0 && C <= 4096 && (cg & (cg - 1)) == 0 && al16(x) &&
-                    al16(res) && al16(gamma) && al16(beta) && al16(y);
+                    al16(res) && al16(gamma) && al16(beta) && al16(y) && al16(mean) && al16(rstd);
   const int cgb = cg < 32 ? cg : 32;
   if (training) {
     const int slabs = rb_bn_slabs(M);
@@ -749,7 +831,7 @@ int rb_bn_fwd(int dtype, const void* x, const void* res, const void* gamma, cons
     }
   }
   if (vec8) {
-    RB_DISPATCH_16(dtype, (bn_apply_vec8_kernel<T><<<vgrid(M * cg), 256, 2 * C * sizeof(float), st>>>((const T*)x, (const T*)res, (const T*)gamma, (const T*)beta, mean, rstd, (T*)y, M * cg, C, relu)));
+    RB_DISPATCH_16(dtype, (bn_apply_vec8_kernel<T><<<bn_grid(M * cg), 256, 0, st>>>((const T*)x, (const T*)res, (const T*)gamma, (const T*)beta, mean, rstd, (T*)y, M * cg, C, relu)));
   } else {
     RB_DISPATCH_T(dtype, (bn_apply_kernel<T><<<vgrid(M * C), 256, 0, st>>>((const T*)x, (const T*)res, (const T*)gamma, (const T*)beta, mean, rstd, (T*)y, M * C, C, relu)));
   }
@@ -767,13 +849,14 @@ int rb_bn_bwd(int dtype, const void* x, const void* dy, const void* y, const voi
   const int cg = C / 8;
   auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   const bool vec8 = dtype != rbh::DT_F32 && C % 8 == 0 && C <= 4096 && (cg & (cg - 1)) == 0 && al16(x) &&
-                    al16(dy) && al16(y) && al16(gamma) && al16(dx) && al16(dres);
+                    al16(dy) && al16(y) && al16(gamma) && al16(dx) && al16(dres) && al16(mean) && al16(rstd) &&
+                    al16(sums);
   if (vec8) {
     const int cgb = cg < 32 ? cg : 32;
     dim3 grid(cg / cgb, slabs);
     RB_DISPATCH_16(dtype, (bn_partial_vec8_kernel<T, true><<<grid, 256, 0, st>>>((const T*)x, (const T*)dy, (const T*)y, mean, rstd, scratch, M, C, rps, relu, cgb)));
     RB_DISPATCH_16(dtype, (bn_finalize_bwd_par_kernel<T><<<(C + 31) / 32, 256, 0, st>>>(scratch, slabs, C, sums, (T*)dgamma, (T*)dbeta)));
-    RB_DISPATCH_16(dtype, (bn_bwd_apply_vec8_kernel<T><<<vgrid(M * cg), 256, 3 * C * sizeof(float), st>>>((const T*)x, (const T*)dy, (const T*)y, (const T*)gamma, mean, rstd, sums, (T*)dx, (T*)dres, M * cg, C, M, relu, training)));
+    RB_DISPATCH_16(dtype, (bn_bwd_apply_vec8_kernel<T><<<bn_grid(M * cg), 256, 0, st>>>((const T*)x, (const T*)dy, (const T*)y, (const T*)gamma, mean, rstd, sums, (T*)dx, (T*)dres, M * cg, C, M, relu, training)));
     RB_RET_LAST();
   }
   dim3 grid((C + 63) / 64, slabs);

@@ -18,6 +18,8 @@ native.register_signature("rb_im2col_nhwc", [I, P, P] + [I] * 12 + [P])
 native.register_signature("rb_col2im_nhwc", [I, P, P] + [I] * 12 + [P])
 native.register_signature("rb_conv_igemm", [I, I, P, P, P, P, I] + [I] * 15 + [P])
 native.register_signature("rb_conv_igemm_wgrad", [I, P, P, P] + [I] * 12 + [P])
+native.register_signature("rb_conv_stem_fwd", [I, P, P, P, P, I, I, I, P])
+native.register_signature("rb_conv_stem_wgrad", [I, P, P, P, I, I, I, P])
 native.register_signature("rb_bn_slabs", [LL])
 native.register_signature("rb_bn_fwd", [I, P, P, P, P, P, P, P, P, P, P, LL, I, F, F, I, I, P])
 native.register_signature("rb_bn_bwd", [I, P, P, P, P, P, P, P, P, P, P, P, P, LL, I, I, I, P])
@@ -78,6 +80,46 @@ def _igemm_ok(x: torch.Tensor, cin: int, cout: int) -> bool:
             and os.environ.get("RB_CONV_IGEMM", "1") == "1")
 
 
+def _stem_ok(x: torch.Tensor, weight: torch.Tensor, stride: int, padding: int, dilation: int) -> bool:
+    """The direct stem kernels (``csrc/kernels/conv_stem.cu``) cover one layer shape: 3 input channels,
+    7x7 taps, stride 2, padding 3, 64 output channels, 16-bit, image width a multiple of 8."""
+    import os
+    return (x.dtype in (torch.bfloat16, torch.float16) and tuple(weight.shape) == (64, 3, 7, 7)
+            and stride == 2 and padding == 3 and dilation == 1 and x.shape[3] % 8 == 0
+            and os.environ.get("RB_CONV_STEM", "1") == "1")
+
+
+STEM_K = 192      # K of the stem's weight matrix: kh*24 + 1 + kw*3 + ci, zero elsewhere
+
+
+def _stem_weight_matrix(weight: torch.Tensor) -> torch.Tensor:
+    """[64, 3, 7, 7] -> [64, 192]: per tap row 24 slots = one zero, the 7 taps x 3 channels, two zeros."""
+    w = weight.permute(0, 2, 3, 1).reshape(64, 7, 21)
+    w = torch.nn.functional.pad(w, (1, 2)).reshape(64, 168)
+    return torch.nn.functional.pad(w, (0, STEM_K - 168)).contiguous()
+
+
+def conv_stem(xh: torch.Tensor, wk: torch.Tensor, bias=None) -> torch.Tensor:
+    """x NHWC ``[B, H, W, 3]`` -> NHWC ``[B, H/2, W/2, 64]`` (7x7, stride 2, padding 3)."""
+    B, H, W, _ = xh.shape
+    Ho, Wo = _out(H, 7, 2, 3), _out(W, 7, 2, 3)
+    y = torch.empty((B, Ho, Wo, 64), dtype=xh.dtype, device=xh.device)
+    check(native.lib().rb_conv_stem_fwd(native.dtype_code(xh.dtype), ptr(xh), ptr(wk), ptr(bias), ptr(y), B, H, W,
+                                        stream_ptr()), "rb_conv_stem_fwd")
+    count_launch()
+    return y
+
+
+def conv_stem_wgrad(xh: torch.Tensor, dyh: torch.Tensor) -> torch.Tensor:
+    """x NHWC ``[B, H, W, 3]``, dY NHWC ``[B, Ho, Wo, 64]`` -> weight gradient ``[64, 3, 7, 7]`` in fp32."""
+    B, H, W, _ = xh.shape
+    dwk = torch.zeros((STEM_K, 64), dtype=torch.float32, device=xh.device)
+    check(native.lib().rb_conv_stem_wgrad(native.dtype_code(xh.dtype), ptr(xh), ptr(dyh), ptr(dwk), B, H, W,
+                                          stream_ptr()), "rb_conv_stem_wgrad")
+    count_launch()
+    return dwk[:168].view(7, 24, 64)[:, 1:22].reshape(7, 7, 3, 64).permute(3, 2, 0, 1)
+
+
 def _pixel_tile(B: int, Ho: int, Wo: int):
     """(tw, th, tn): the patch of 128 output pixels (tw x th pixels of tn images, powers of two) that
     wastes the fewest rows on the edges of the ``B x Ho x Wo`` grid; ties go to the larger patch."""
@@ -127,6 +169,18 @@ class Conv2dFn(torch.autograd.Function):
         xh = _nhwc(x)
         esz = x.element_size()
         pointwise = KH == 1 and KW == 1 and stride == 1 and padding == 0 and Cin % (16 // esz) == 0
+        if not ctx.needs_input_grad[0] and _stem_ok(x, weight, stride, padding, dilation):
+            # the image needs no gradient: direct kernels, no patch matrix
+            wk = _stem_weight_matrix(weight)
+            b = bias.to(x.dtype).contiguous() if bias is not None else None
+            y = conv_stem(xh, wk, b)
+            ctx.stem = True
+            ctx.geom = (B, H, W, Cin, Cout, KH, KW, Ho, Wo, stride, padding, dilation, 0, False)
+            ctx.save_for_backward(xh, wk)
+            ctx.has_bias = bias is not None
+            ctx.w_dtype = weight.dtype
+            return _as_nchw(y)
+        ctx.stem = False
         igemm = not pointwise and _igemm_ok(x, Cin, Cout)
         Kpad = Cin if pointwise else (KH * KW * Cin if igemm else _pad8(KH * KW * Cin, esz))
         wm = _weight_matrix(weight, Kpad)
@@ -150,6 +204,12 @@ class Conv2dFn(torch.autograd.Function):
         B, H, W, Cin, Cout, KH, KW, Ho, Wo, stride, padding, dilation, Kpad, pointwise = ctx.geom
         dyh = _nhwc(dy).view(B * Ho * Wo, Cout)
         dx = dw = db = None
+        if ctx.stem:
+            if ctx.needs_input_grad[1]:
+                dw = conv_stem_wgrad(xh, dyh.view(B, Ho, Wo, Cout)).to(ctx.w_dtype).contiguous()
+            if ctx.has_bias and ctx.needs_input_grad[2]:
+                db = native.colsum(dyh)
+            return dx, dw, db, None, None, None
         if ctx.igemm:
             dy4 = dyh.view(B, Ho, Wo, Cout)
             if ctx.needs_input_grad[1]:

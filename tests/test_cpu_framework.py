@@ -309,3 +309,32 @@ def test_reference_op_names_are_all_present():
     assert (F.dequantize(F.quantize(w)) - w).abs().max() < 0.05
     F.to_dtype(F.tanh_act(x), torch.float64).sum().backward()
     assert x.grad is not None and x.grad.shape == x.shape
+
+
+def test_stem_weight_matrix_order_matches_the_patch_rows():
+    """The direct stem kernels order K as kh*24 + 1 + kw*3 + ci: a patch matrix built that way times the
+    permuted weight is the convolution, and the inverse map turns a [192, 64] gradient back into
+    [64, 3, 7, 7]."""
+    import torch.nn.functional as TF
+    from rumus_b200.ops.vision_cuda import STEM_K, _stem_weight_matrix
+    torch.manual_seed(0)
+    B, H, W = 2, 12, 16
+    x = torch.randn(B, 3, H, W, dtype=torch.float64)
+    w = torch.randn(64, 3, 7, 7, dtype=torch.float64, requires_grad=True)
+    y = TF.conv2d(x, w, None, 2, 3, 1)
+    Ho, Wo = y.shape[2], y.shape[3]
+    xp = TF.pad(x.permute(0, 2, 3, 1), (0, 0, 3, 3 + 8, 3, 3))                  # NHWC, zero border
+    cols = torch.zeros(B, Ho, Wo, STEM_K, dtype=torch.float64)
+    for kh in range(7):
+        for oh in range(Ho):
+            for ow in range(Wo):
+                run = xp[:, 2 * oh + kh, 2 * ow:2 * ow + 7].reshape(B, 21)        # 7 taps x 3 channels
+                cols[:, oh, ow, kh * 24 + 1:kh * 24 + 22] = run
+    wk = _stem_weight_matrix(w.detach())
+    assert wk.shape == (64, STEM_K)
+    torch.testing.assert_close((cols.view(-1, STEM_K) @ wk.t()).view(B, Ho, Wo, 64).permute(0, 3, 1, 2), y.detach())
+    g = torch.randn_like(y)
+    y.backward(g)
+    dwk = cols.view(-1, STEM_K).t() @ g.permute(0, 2, 3, 1).reshape(-1, 64)      # [192, 64]
+    dw = dwk[:168].view(7, 24, 64)[:, 1:22].reshape(7, 7, 3, 64).permute(3, 2, 0, 1)
+    torch.testing.assert_close(dw, w.grad)

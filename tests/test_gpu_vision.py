@@ -80,12 +80,16 @@ def test_batch_norm2d(relu, use_res):
     assert _rel(ye.cpu(), yer) < 1e-4
 
 
-@pytest.mark.parametrize("C,relu,use_res", [(64, True, True), (256, False, False), (16, True, False)])
-def test_batch_norm2d_half_vector_path(C, relu, use_res):
+@pytest.mark.parametrize("C,relu,use_res,shape", [
+    (64, True, True, (6, 9, 11)), (256, False, False, (6, 9, 11)), (16, True, False, (6, 9, 11)),
+    (64, True, True, (8, 100, 100)),      # long enough for the unrolled main loops of all three kernels
+    (512, True, False, (4, 41, 40)),      # 32 channel groups per CTA, ragged row count
+])
+def test_batch_norm2d_half_vector_path(C, relu, use_res, shape):
     """fp16 channels-last batch norm with C % 8 == 0 (16-byte kernels) against the fp32 CPU form."""
     from rumus_b200.ops import vision as V
     torch.manual_seed(5)
-    B, H, W = 6, 9, 11
+    B, H, W = shape
     x32 = torch.randn(B, C, H, W)
     r32 = torch.randn(B, C, H, W) if use_res else None
     w32, b32 = 1 + 0.1 * torch.randn(C), 0.1 * torch.randn(C)
@@ -183,6 +187,40 @@ def test_conv2d_implicit_gemm(dtype, cfg):
     assert _rel(x.grad, xr.grad) < 1e-2
     assert _rel(w.grad, wr.grad) < 1e-2
     assert _rel(b.grad, br.grad) < 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H,W,bias", [(2, 64, 64, False), (3, 40, 56, True), (1, 224, 224, False), (5, 18, 8, True)])
+def test_conv2d_direct_stem(dtype, B, H, W, bias):
+    """The 3-channel 7x7 stride-2 stem takes the direct kernels (window in shared memory, tcgen05 product,
+    weight gradient accumulated in TMEM): forward and weight / bias gradients against fp32."""
+    from rumus_b200.ops import native
+    from rumus_b200.ops import vision as V
+    from rumus_b200.ops import vision_cuda as VC
+    torch.manual_seed(2)
+    x = torch.randn(B, 3, H, W, device="cuda").to(dtype)
+    w = (torch.randn(64, 3, 7, 7, device="cuda") * 0.1).to(dtype).requires_grad_(True)
+    b = torch.randn(64, device="cuda").to(dtype).requires_grad_(True) if bias else None
+    assert VC._stem_ok(x, w, 2, 3, 1)
+    y = V.conv2d(x, w, b, 2, 3, 1)
+    g = torch.randn_like(y)
+    y.backward(g)
+    wr = w.detach().float().requires_grad_(True)
+    br = b.detach().float().requires_grad_(True) if bias else None
+    yr = TF.conv2d(x.float(), wr, br, 2, 3, 1)
+    yr.backward(g.float())
+    assert native.read_status() == 0
+    assert y.shape == yr.shape
+    assert _rel(y, yr) < 1e-2
+    assert _rel(w.grad, wr.grad) < 1e-2
+    if bias:
+        assert _rel(b.grad, br.grad) < 1e-2
+    # an image that needs a gradient keeps the general path
+    xg = x.clone().requires_grad_(True)
+    V.conv2d(xg, w, b, 2, 3, 1).backward(g)
+    xr = x.float().requires_grad_(True)
+    TF.conv2d(xr, wr.detach(), br.detach() if bias else None, 2, 3, 1).backward(g.float())
+    assert _rel(xg.grad, xr.grad) < 1e-2
 
 
 def test_pixel_tile_choice_covers_the_grid_with_128_pixels():
