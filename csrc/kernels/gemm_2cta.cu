@@ -10,13 +10,13 @@
 
 namespace rb {
 
-template <typename T, int MT, bool LEAN, bool A_MN, bool B_MN>
+template <typename T, int MT, int EPI, bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
     gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                      const __grid_constant__ CUtensorMap tma_c, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   NoHooks hooks;
-  gemm_pair_body<T, MT, LEAN, A_MN, B_MN, NoHooks>(&tma_a, &tma_b, &tma_c, p, hooks, smem_raw, blockIdx.x / 2,
+  gemm_pair_body<T, MT, EPI, A_MN, B_MN, NoHooks>(&tma_a, &tma_b, &tma_c, p, hooks, smem_raw, blockIdx.x / 2,
                                              gridDim.x / 2);
 }
 
@@ -74,7 +74,7 @@ int max_resident_clusters(K kern, int smem_bytes) {
   return n;
 }
 
-template <typename T, int MT, bool LEAN, bool A_MN, bool B_MN>
+template <typename T, int MT, int EPI, bool A_MN, bool B_MN>
 int launch_gemm_2cta(GemmArgs& a) {
   using C = PairCfg<MT>;
   CUtensorMap ta, tb, tc;
@@ -86,7 +86,7 @@ int launch_gemm_2cta(GemmArgs& a) {
   } else {
     tc = ta;
   }
-  auto kern = gemm_2cta_kernel<T, MT, LEAN, A_MN, B_MN>;
+  auto kern = gemm_2cta_kernel<T, MT, EPI, A_MN, B_MN>;
   static int resident = 0;
   if (resident == 0) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
@@ -103,26 +103,38 @@ int launch_gemm_2cta(GemmArgs& a) {
   return e == cudaSuccess ? 0 : 3000 + (int)e;
 }
 
-template <typename T, int MT, bool LEAN>
+template <typename T, int MT, int EPI>
 int launch_gemm_2cta_major(GemmArgs& a) {
-  if (!a.a_mn && !a.b_mn) return launch_gemm_2cta<T, MT, LEAN, false, false>(a);
-  if (!a.a_mn && a.b_mn) return launch_gemm_2cta<T, MT, LEAN, false, true>(a);
-  if (a.a_mn && !a.b_mn) return launch_gemm_2cta<T, MT, LEAN, true, false>(a);
-  return launch_gemm_2cta<T, MT, LEAN, true, true>(a);
+  if (!a.a_mn && !a.b_mn) return launch_gemm_2cta<T, MT, EPI, false, false>(a);
+  if (!a.a_mn && a.b_mn) return launch_gemm_2cta<T, MT, EPI, false, true>(a);
+  if constexpr (EPI == EPI_FULL || EPI == EPI_LEAN) {
+    if (a.a_mn && !a.b_mn) return launch_gemm_2cta<T, MT, EPI, true, false>(a);
+    return launch_gemm_2cta<T, MT, EPI, true, true>(a);
+  }
+  return -1;       // the activation flavours are built for a K-major A (activations, output gradients) only
 }
 
-// Two flavours of the kernel.  LEAN: 16-bit output through the TMA-store epilogue with only the
+// Flavours of the kernel.  LEAN: 16-bit output through the TMA-store epilogue with only the
 // common epilogue terms (alpha, bias, residual) compiled in; its epilogue code is a few KB, which is
 // what keeps the drain of 512-row tiles short (the epilogue of the full flavour — every activation,
 // derivative, side output, fp32 output, per-row stores — is so much code that fetching it costs more
-// than executing it).  FULL: everything, 256-row tiles only, where the epilogue of one tile runs
-// under the main loop of the next.
+// than executing it).  GELU_AUX / DGELU: the two activation epilogues of a transformer MLP (first
+// layer forward: bias, pre-activation side output, tanh-GELU; second layer's data gradient: times
+// the GELU derivative of the stored pre-activation), specialised for the same reason.  FULL:
+// everything, decided at run time.  All but LEAN use 256-row tiles, where the epilogue of one tile
+// runs under the main loop of the next.
 template <typename T>
 int launch_gemm_2cta_flavour(GemmArgs& a, int mt) {
   const GemmParams& p = a.p;
-  const bool lean = p.tma_store && !p.out_f32 && !p.aux_out && !p.aux_in && p.act == ACT_NONE;
-  if (!lean) return launch_gemm_2cta_major<T, 1, false>(a);
-  return mt == 2 ? launch_gemm_2cta_major<T, 2, true>(a) : launch_gemm_2cta_major<T, 1, true>(a);
+  const bool staged16 = p.tma_store && !p.out_f32;
+  const bool lean = staged16 && !p.aux_out && !p.aux_in && p.act == ACT_NONE;
+  if (lean) return mt == 2 ? launch_gemm_2cta_major<T, 2, EPI_LEAN>(a) : launch_gemm_2cta_major<T, 1, EPI_LEAN>(a);
+  const char* sp = getenv("RB_G2_SPECIAL");        // "0": always take the full flavour for activation epilogues
+  if (staged16 && !a.a_mn && !(sp && sp[0] == '0')) {
+    if (p.aux_out && !p.aux_in && p.act == ACT_GELU) return launch_gemm_2cta_major<T, 1, EPI_GELU_AUX>(a);
+    if (p.aux_in && !p.aux_out && p.act == ACT_NONE && p.dact == ACT_GELU) return launch_gemm_2cta_major<T, 1, EPI_DGELU>(a);
+  }
+  return launch_gemm_2cta_major<T, 1, EPI_FULL>(a);
 }
 
 // Rows of A per CTA and tile.  512 x 256 tiles move a quarter less operand data per FLOP than

@@ -172,7 +172,14 @@ __device__ __forceinline__ bool bar_vote_and(int id, int threads, bool pred) {
 
 // Everything of the fused epilogue except the final store: v = dact(aux_in) * act(alpha*acc + bias) + residual
 // for 32 consecutive columns of one row; the pre-activation side output is stored here.
-template <typename T, typename OT, bool LEAN = false>
+// EPI selects what is compiled in: EPI_FULL everything (decided at run time), EPI_LEAN none of the
+// activation terms, EPI_GELU_AUX = store the pre-activation, then tanh-GELU (an MLP's first layer in
+// forward), EPI_DGELU = multiply by the tanh-GELU derivative of a stored pre-activation (the data
+// gradient of its second layer).  The specialised bodies are a few hundred instructions; the full one is
+// large enough for its instruction fetch to show in the tile time.
+enum { EPI_FULL = 0, EPI_LEAN = 1, EPI_GELU_AUX = 2, EPI_DGELU = 3 };
+
+template <typename T, typename OT, int EPI = EPI_FULL>
 __device__ __forceinline__ void epilogue_math32(const GemmParams& p, const uint32_t* acc_bits, long long row,
                                                 int col, int ncols_valid, bool row_ok, float* v) {
 #pragma unroll
@@ -196,10 +203,22 @@ __device__ __forceinline__ void epilogue_math32(const GemmParams& p, const uint3
   }
   const bool vec = p.vec_ok != 0;
   if (!row_ok || ncols_valid <= 0) return;
-  if constexpr (!LEAN) {     // LEAN: the caller has checked that there is no side output / derivative input
+  // the specialised flavours: the caller has checked which terms the call has
+  if constexpr (EPI == EPI_GELU_AUX) {
+    store_row32<OT>(reinterpret_cast<OT*>(p.aux_out), p.ldaux_out, row, col, ncols_valid, vec, v);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_fast(v[i]);
+  }
+  if constexpr (EPI == EPI_DGELU) {
+    float a[32];
+    load_row32<OT>(reinterpret_cast<const OT*>(p.aux_in), p.ldaux_in, row, col, ncols_valid, vec, a);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] *= gelu_tanh_grad_fast(a[i]);
+  }
+  if constexpr (EPI == EPI_FULL) {
     if (p.aux_out) store_row32<OT>(reinterpret_cast<OT*>(p.aux_out), p.ldaux_out, row, col, ncols_valid, vec, v);
   }
-  if constexpr (!LEAN) {
+  if constexpr (EPI == EPI_FULL) {
     // one loop per activation kind (a switch inside the unrolled loop would lay down every kind 32 times)
     if (p.act == ACT_RELU) {
 #pragma unroll
@@ -313,12 +332,15 @@ __device__ __forceinline__ void stage_packed32(uint8_t* staging, int r, int piec
   }
 }
 
-template <typename T, int MT, bool LEAN, bool A_MN, bool B_MN, typename Hooks>
+template <typename T, int MT, int EPI, bool A_MN, bool B_MN, typename Hooks>
 __device__ __forceinline__ void gemm_pair_body(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
                                                const CUtensorMap* tma_c, const GemmParams& p, const Hooks& hooks,
                                                uint8_t* smem_raw, int cluster_id, int num_clusters) {
   using C = PairCfg<MT>;
   constexpr int STAGES = C::STAGES;
+  // every flavour but the full one writes 16-bit output through the staged TMA store
+  constexpr bool LEAN = EPI != EPI_FULL;
+  static_assert(EPI == EPI_LEAN || MT == 1, "512-row tiles exist for the lean flavour only");
   // both CTAs of a pair must use the same shared-memory offsets (the MMA addresses the peer's
   // operands by offset, remote arrivals address barriers by offset); the dynamic segment starts at
   // the same offset in every CTA of a kernel, so aligning the same way gives the same layout
@@ -696,7 +718,7 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap* tma_a, const C
                   const int col = col0 + pc * 32;
                   const int ncols_valid = min(32, p.N - col);
                   if constexpr (LEAN)
-                    epilogue_math32<T, T, true>(p, r[pc], row, col, ncols_valid, row_ok, v[pc]);
+                    epilogue_math32<T, T, EPI>(p, r[pc], row, col, ncols_valid, row_ok, v[pc]);
                   else if (p.out_f32)
                     epilogue_math32<T, float>(p, r[pc], row, col, ncols_valid, row_ok, v[pc]);
                   else

@@ -366,6 +366,199 @@ __global__ void __launch_bounds__(kColGroups* kColGroupThreads)
   for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) out[i] = s_fold[i];
 }
 
+// Ring variant of the column-owner kernel: the rows a group will visit next are already on their way
+// into shared memory (untiled bulk copies completing on an mbarrier: x, dy and the residual-stream
+// gradient of `stages` rows per group), so the bytes in flight are bounded by shared memory (~190 KB per
+// SM), not by the registers a thread can spare for prefetched rows (the register-prefetch form above
+// keeps 8 KB per group in flight and loads the residual gradient late, which held it at 2.6-2.8 TB/s).
+// One persistent CTA per SM; thread / chunk ownership, the two row reductions and the register-resident
+// d_gamma / d_beta accumulators are the same as in norm_bwd_cols_kernel.
+template <typename T, bool RMS, int NCHUNK, int kColGroups>
+__global__ void __launch_bounds__(kColGroups* kColGroupThreads)
+    norm_bwd_ring_kernel(const T* __restrict__ x, const T* __restrict__ dy,
+                         const T* __restrict__ gamma, const float* __restrict__ stats,
+                         const T* __restrict__ dres, T* __restrict__ dx,
+                         float* __restrict__ partials /* [grid,2,D] */, long long rows, int D,
+                         int stages, int* status) {
+  constexpr int VEC = Vec16<T>::N;
+  extern __shared__ uint8_t ring_raw[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ring_raw) + 127) & ~static_cast<uintptr_t>(127));
+  const int row_bytes = D * (int)sizeof(T);
+  const int stage_bytes = 3 * row_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)kColGroups * stages * stage_bytes);   // [group][stage]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kColGroups * stages);
+  __shared__ float s_red[2][kColGroups][4][2];            // [buffer][group][warp][c1,c2]
+  __shared__ int s_stop[2][kColGroups];                   // the abort flag as one thread of the group saw it
+  const int grp = threadIdx.x / kColGroupThreads;
+  const int tg = threadIdx.x % kColGroupThreads;
+  const int wg = tg >> 5, lane = tg & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kColGroups * stages; ++i) mbar_init(smem_u32(&bars[i]), 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  uint8_t* my_ring = ring + (size_t)grp * stages * stage_bytes;
+  uint64_t* my_bars = bars + grp * stages;
+  const long long row_step = (long long)gridDim.x * kColGroups;
+  const long long first = (long long)blockIdx.x * kColGroups + grp;
+  // every group runs the same number of trips so that the named barrier below stays matched
+  const long long trips = (rows + row_step - 1) / row_step;
+  auto request = [&](long long row, int stage) {       // one thread per group
+    const uint32_t bar = smem_u32(&my_bars[stage]);
+    uint8_t* dst = my_ring + (size_t)stage * stage_bytes;
+    mbar_arrive_expect_tx(bar, (dres ? 3 : 2) * row_bytes);
+    bulk_load_1d(smem_u32(dst), x + row * D, row_bytes, bar);
+    bulk_load_1d(smem_u32(dst + row_bytes), dy + row * D, row_bytes, bar);
+    if (dres) bulk_load_1d(smem_u32(dst + 2 * row_bytes), dres + row * D, row_bytes, bar);
+  };
+  long long requested = 0;                              // trips whose copies were issued (thread tg == 0)
+  if (tg == 0) {
+    for (int s0 = 0; s0 < stages; ++s0) {
+      const long long row = first + s0 * row_step;
+      if (row < rows) {
+        request(row, s0);
+        requested = s0 + 1;
+      }
+    }
+  }
+  float acc_g[NCHUNK][VEC], acc_b[NCHUNK][VEC];
+  Vec16<T> gv[NCHUNK];
+#pragma unroll
+  for (int i = 0; i < NCHUNK; ++i) {
+    const int c = (i * kColGroupThreads + tg) * VEC;
+    gv[i].raw = c < D ? *reinterpret_cast<const uint4*>(gamma + c) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc_g[i][j] = acc_b[i][j] = 0.f;
+  }
+  const float inv_d = 1.f / (float)D;
+  int buf = 0, stage = 0;
+  uint32_t phase = 0;
+  long long trip = 0;
+  for (; trip < trips; ++trip) {
+    const long long row = trip * row_step + first;
+    const bool live = row < rows;
+    Vec16<T> xv[NCHUNK], dv[NCHUNK], rv[NCHUNK];
+    float mean = 0.f, rstd = 0.f;
+    if (live) {
+      mean = RMS ? 0.f : stats[row * 2];
+      rstd = stats[row * 2 + 1];
+      mbar_wait(smem_u32(&my_bars[stage]), phase, abort_flag, status, RB_ERR_TIMEOUT_FULL);
+      const uint8_t* src = my_ring + (size_t)stage * stage_bytes;
+#pragma unroll
+      for (int i = 0; i < NCHUNK; ++i) {
+        const int c = (i * kColGroupThreads + tg) * VEC;
+        if (c < D) {
+          xv[i].raw = *reinterpret_cast<const uint4*>(src + (size_t)c * sizeof(T));
+          dv[i].raw = *reinterpret_cast<const uint4*>(src + row_bytes + (size_t)c * sizeof(T));
+          rv[i].raw = dres ? *reinterpret_cast<const uint4*>(src + 2 * row_bytes + (size_t)c * sizeof(T))
+                           : make_uint4(0, 0, 0, 0);
+        } else {
+          xv[i].raw = dv[i].raw = rv[i].raw = make_uint4(0, 0, 0, 0);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < NCHUNK; ++i) xv[i].raw = dv[i].raw = rv[i].raw = make_uint4(0, 0, 0, 0);
+    }
+    float c1 = 0.f, c2 = 0.f;  // sum(dy*g), sum(dy*g*xhat)
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i)
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const float xh = (xv[i].get(j) - mean) * rstd;
+        const float dg = dv[i].get(j) * gv[i].get(j);
+        c1 += dg;
+        c2 += dg * xh;
+      }
+    c1 = warp_sum(c1);
+    c2 = warp_sum(c2);
+    if (lane == 0) {
+      s_red[buf][grp][wg][0] = c1;
+      s_red[buf][grp][wg][1] = c2;
+    }
+    if (tg == 0) s_stop[buf][grp] = *abort_flag;
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(kColGroupThreads) : "memory");
+    // after a wait that ran out the group leaves together: every thread acts on the one reading of the
+    // flag taken before the barrier (a thread that reads the flag for itself could leave alone and
+    // strand the others at the next barrier); a flag raised later is seen one row later
+    if (s_stop[buf][grp]) break;
+    // every thread of the group has taken its part of this stage: it can receive a later row
+    if (tg == 0 && live) {
+      const long long next = row + (long long)stages * row_step;
+      if (next < rows) {
+        request(next, stage);
+        requested = trip + stages + 1;
+      }
+    }
+    if (++stage == stages) {
+      stage = 0;
+      phase ^= 1;
+    }
+    c1 = (s_red[buf][grp][0][0] + s_red[buf][grp][1][0] + s_red[buf][grp][2][0] +
+          s_red[buf][grp][3][0]) * inv_d;
+    c2 = (s_red[buf][grp][0][1] + s_red[buf][grp][1][1] + s_red[buf][grp][2][1] +
+          s_red[buf][grp][3][1]) * inv_d;
+    buf ^= 1;
+    if (RMS) c1 = 0.f;
+    if (live) {
+#pragma unroll
+      for (int i = 0; i < NCHUNK; ++i) {
+        const int c = (i * kColGroupThreads + tg) * VEC;
+        if (c < D) {
+          Vec16<T> ov;
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) {
+            const float xh = (xv[i].get(j) - mean) * rstd;
+            const float d = dv[i].get(j);
+            float o = rstd * (d * gv[i].get(j) - c1 - xh * c2);
+            if (dres) o += rv[i].get(j);
+            ov.set(j, o);
+            acc_g[i][j] += d * xh;
+            acc_b[i][j] += d;
+          }
+          *reinterpret_cast<uint4*>(dx + row * D + c) = ov.raw;
+        }
+      }
+    }
+  }
+  // after a failed wait: give the copies still in flight their time before the ring is reused below
+  if (tg == 0 && trip < trips) {
+    for (long long t2 = trip; t2 < requested; ++t2) {
+      const uint64_t t0 = globaltimer_ns();
+      while (!mbar_try_wait(smem_u32(&my_bars[t2 % stages]), (uint32_t)((t2 / stages) & 1))) {
+        if (globaltimer_ns() - t0 > RB_WAIT_BUDGET_NS) break;
+      }
+    }
+  }
+  __syncthreads();
+  // fold the groups through the (now idle) ring: group 0 stores, the others add in turn
+  float* s_fold = reinterpret_cast<float*>(ring);
+  for (int gsel = 0; gsel < kColGroups; ++gsel) {
+    if (grp == gsel) {
+#pragma unroll
+      for (int i = 0; i < NCHUNK; ++i) {
+        const int c = (i * kColGroupThreads + tg) * VEC;
+        if (c < D) {
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) {
+            if (gsel == 0) {
+              s_fold[c + j] = acc_g[i][j];
+              s_fold[D + c + j] = acc_b[i][j];
+            } else {
+              s_fold[c + j] += acc_g[i][j];
+              s_fold[D + c + j] += acc_b[i][j];
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  float* out = partials + (long long)blockIdx.x * 2 * D;
+  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) out[i] = s_fold[i];
+}
+
 // partials [n,2,D] -> dgamma[D], dbeta[D] (dbeta may be null)
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -441,6 +634,39 @@ int launch_norm_bwd(const void* x, const void* dy, const void* gamma, const floa
   const int vec = (D % VEC == 0) && al(x) && al(dy) && al(gamma) && al(dres) && al(dx);
   const int chunks = (D + kColGroupThreads * VEC - 1) / (kColGroupThreads * VEC);
   if (vec && chunks <= 4) {
+    // ring kernel: one persistent CTA per SM, `stages` rows per group in flight in shared memory
+    const int groups = chunks <= 2 ? 4 : 2;
+    const int row_bytes = D * (int)sizeof(T);
+    int stages = (200 * 1024) / (groups * 3 * row_bytes);
+    if (stages > 8) stages = 8;
+    static const bool ring_on = [] {
+      const char* e = getenv("RB_NORM_RING");
+      return !(e && e[0] == '0');
+    }();
+    if (ring_on && stages >= 2) {
+      if (grid > rbh::sm_count()) grid = rbh::sm_count();
+      const size_t smem = (size_t)groups * stages * 3 * row_bytes + (size_t)groups * stages * 8 + 16 + 128;
+      cudaError_t e1 = cudaSuccess;
+#define RB_RING(N, G)                                                                                      \
+  do {                                                                                                     \
+    auto k = norm_bwd_ring_kernel<T, RMS, N, G>;                                                           \
+    e1 = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                  \
+    if (e1 == cudaSuccess)                                                                                 \
+      k<<<grid, G * kColGroupThreads, smem, st>>>((const T*)x, (const T*)dy, (const T*)gamma, stats,       \
+                                                  (const T*)dres, (T*)dx, partials, rows, D, stages,       \
+                                                  rbh::device_status_word());                              \
+  } while (0)
+      if (chunks == 1) RB_RING(1, 4);
+      else if (chunks == 2) RB_RING(2, 4);
+      else if (chunks == 3) RB_RING(3, 2);
+      else RB_RING(4, 2);
+#undef RB_RING
+      if (e1 != cudaSuccess) return 2000 + (int)e1;
+      norm_bwd_reduce_kernel<T><<<(D + 31) / 32, 256, 0, st>>>(partials, grid, D, (T*)dgamma,
+                                                               RMS ? nullptr : (T*)dbeta);
+      cudaError_t e2 = cudaGetLastError();
+      return e2 == cudaSuccess ? 0 : 3000 + (int)e2;
+    }
     const size_t fold = (size_t)2 * D * sizeof(float);
 #define RB_COLS(N, G)                                                                            \
   norm_bwd_cols_kernel<T, RMS, N, G><<<grid, G * kColGroupThreads, fold, st>>>(                  \
