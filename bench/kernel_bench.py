@@ -49,17 +49,14 @@ print("== GEMM bf16 (TFLOP/s): mine vs torch.matmul")
 for (M,N,K,bt) in [(16384,2048,2048,False),(16384,6144,2048,False),(16384,8192,2048,False),(16384,2048,8192,False),(16384,50304,2048,False),(8192,8192,8192,False),(16384,2048,8192,True)]:
     a=torch.randn(M,K,device='cuda').bfloat16(); 
     bs=torch.randn((N,K) if bt else (K,N),device='cuda').bfloat16(); b=bs.t() if bt else bs
-    for bn in (128,256):
-        t=timeit(lambda: native.gemm(a,b,path=1,bn=bn)); 
-        print(f"M{M} N{N} K{K} bt={bt} bn={bn}: {t:.3f} ms {2*M*N*K/t/1e9:.0f} TF", flush=True)
-    if os.environ.get("RB_GEMM_2CTA", "0") == "1":   # the two-CTA kernel, once it is switched on
-        t=timeit(lambda: native.gemm(a,b,path=3)); print(f"   two-CTA 256x256: {t:.3f} ms {2*M*N*K/t/1e9:.0f} TF", flush=True)
+    t=timeit(lambda: native.gemm(a,b)); print(f"M{M} N{N} K{K} bt={bt} default (CTA pairs): {t:.3f} ms {2*M*N*K/t/1e9:.0f} TF", flush=True)
+    t=timeit(lambda: native.gemm(a,b,path=1,bn=256)); print(f"   one-CTA 128x256: {t:.3f} ms {2*M*N*K/t/1e9:.0f} TF", flush=True)
     t=timeit(lambda: torch.matmul(a,b)); print(f"   torch: {t:.3f} ms {2*M*N*K/t/1e9:.0f} TF", flush=True)
     st=native.read_status(); assert st==0, st
 # wgrad-like: A^T B
 M,N,K=2048,8192,16384
 x=torch.randn(K,M,device='cuda').bfloat16(); dy=torch.randn(K,N,device='cuda').bfloat16()
-t=timeit(lambda: native.gemm(x.t(),dy,path=1)); print(f"wgrad M{M} N{N} K{K}: {t:.3f} ms {2*M*N*K/t/1e9:.0f} TF")
+t=timeit(lambda: native.gemm(x.t(),dy)); print(f"wgrad M{M} N{N} K{K} default (CTA pairs): {t:.3f} ms {2*M*N*K/t/1e9:.0f} TF")
 t=timeit(lambda: torch.matmul(x.t(),dy)); print(f"   torch: {t:.3f} ms {2*M*N*K/t/1e9:.0f} TF")
 print("== FlashAttention fwd/bwd B8 H16 S2048 D128 causal")
 B,S,H,D=8,2048,16,128

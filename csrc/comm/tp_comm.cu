@@ -76,22 +76,29 @@ struct GatherHooks {
   int total_rows;       // M or K
   int first_local_step; // tile / K block where this rank's own shard starts (rotation origin)
   mutable unsigned long long ready[4];  // chunks already seen ready (<= 256 chunks)
+  mutable int remaining;                // remote chunks not yet seen ready by this thread
 
+  // Byte offsets inside the gathered buffer fit 32 bits (the launcher checks world * shard_bytes < 4 GB):
+  // the producer lane runs this before every K block of a gathered weight, so it has to cost tens of
+  // cycles, not the hundreds that 64-bit divisions take, and nothing once every chunk has been seen.
   __device__ __forceinline__ bool range_ready(long long lo, long long hi, volatile int* abort_flag,
                                               int* status) const {
+    if (remaining <= 0) return true;
+    const uint32_t shard = (uint32_t)shard_bytes, chunk = (uint32_t)chunk_bytes;
     bool waited = false;
-    for (long long b = lo; b < hi;) {
-      const int src = (int)(b / shard_bytes);
-      const long long in_shard = b - (long long)src * shard_bytes;
-      const int c = (int)(in_shard / chunk_bytes);
-      const long long chunk_end = (long long)src * shard_bytes + min(shard_bytes, (long long)(c + 1) * chunk_bytes);
-      if (src != rank && src < world) {
-        const int idx = src * chunks_per_shard + c;
+    for (uint32_t b = (uint32_t)lo; b < (uint32_t)hi;) {
+      const uint32_t src = b / shard;
+      const uint32_t in_shard = b - src * shard;
+      const uint32_t c = in_shard / chunk;
+      const uint32_t chunk_end = src * shard + min(shard, (c + 1) * chunk);
+      if ((int)src != rank && (int)src < world) {
+        const int idx = (int)src * chunks_per_shard + (int)c;
         const unsigned long long bit = 1ull << (idx & 63);
         if (!(ready[(idx >> 6) & 3] & bit)) {
           if (!wait_flag_gpu(chunk_flags + idx, epoch, status, RB_ERR_TIMEOUT_FLAG, abort_flag))
             return false;
           ready[(idx >> 6) & 3] |= bit;
+          --remaining;
           waited = true;
         }
       }
@@ -158,6 +165,7 @@ __global__ void __launch_bounds__(512, 1)
   }
   if (threadIdx.x >= kGemmThreads) return;  // GEMM CTAs use 10 warps; the block is sized for the copy role
   hooks.ready[0] = hooks.ready[1] = hooks.ready[2] = hooks.ready[3] = 0ull;
+  hooks.remaining = (hooks.world - 1) * hooks.chunks_per_shard;
   if (gp.sched != nullptr)
     gemm_cta_body<T, BN, false, B_MN, GatherHooks>(&tma_a, &tma_b, gp, hooks, smem_raw, blockIdx.x,
                                                    gridDim.x);
@@ -379,11 +387,21 @@ int rb_ag_gemm(int dtype, void* const* bases, int world, int rank, long long buf
                void* aux_out, int n_copy_ctas, void* stream) {
   using namespace rb;
   if (world > kMaxRanks || shard_bytes % 16 != 0) return 30;
+  if ((long long)world * shard_bytes >= (1ll << 32)) return 31;   // the readiness check works on 32-bit offsets
   const int esz = 2;
   AgParamsTp ap;
   ap.peers = make_table_tp(bases, world, rank);
   ap.buf_off = buf_off; ap.shard_bytes = shard_bytes; ap.src_flags_off = src_flags_off;
   ap.chunk_flags = chunk_flags;
+  {
+    // the ready bitmap of a GEMM warp has 256 bits: a shard too large for the requested chunk size is
+    // cut into larger chunks instead of being refused
+    const long long max_cps = 256 / world;
+    if (chunk_bytes < 16 || (shard_bytes + chunk_bytes - 1) / chunk_bytes > max_cps) {
+      chunk_bytes = (shard_bytes + max_cps - 1) / max_cps;
+      chunk_bytes = (chunk_bytes + 1023) / 1024 * 1024;
+    }
+  }
   ap.chunk_bytes = chunk_bytes;
   ap.chunks_per_shard = (int)((shard_bytes + chunk_bytes - 1) / chunk_bytes);
   if (ap.chunks_per_shard * world > 256) return 32;

@@ -9,8 +9,10 @@
 //                X[patch of 128 output pixels shifted by the tap, 64 channels] . W[(kh,kw,c), Cout]
 //                A tile = one box {64 channels, TW, TH, TN} (TW*TH*TN = 128 output pixels of TN images),
 //                B tile = rows of the [Cout, KH*KW*Cin] weight matrix (plain 2-D copy)
-//   data grad    (stride 1) the same kernel on dY with the taps mirrored and the weight matrix
-//                rearranged to [Cin, (kh,kw,co)]
+//   data grad    the same kernel on dY with the taps mirrored and the weight matrix rearranged to
+//                [Cin, (kh,kw,co)].  Stride s > 1: one launch per phase (ih + pad) mod s, (iw + pad) mod s
+//                of the input pixels; a phase sees only the taps kh = phase + s*a, is a stride-1
+//                gather over dY, and writes every s-th input pixel
 //   weight grad  dW[Cout, (kh,kw,ci)] = sum over pixels dY[pixel, co] . X[pixel shifted by tap, ci]:
 //                K runs over 8 x 8 patches of output pixels; A = boxes of dY (M-major operand),
 //                B = boxes of X shifted by the tap (N-major operand); K is split across CTAs and the
@@ -32,6 +34,8 @@ struct ConvGeom {
   int tiles_w, tiles_h;
   int cblocks;            // 64-channel blocks of the gathered tensor
   int patches_w, patches_h;   // weight grad: 8 x 8 pixel patches per image
+  int os, oe_h, oe_w;     // rows are written to pixel (h*os + oe_h, w*os + oe_w) of an OH x OW image
+  int OH, OW;             //   (os = 1, oe = 0, OH x OW = Ho x Wo except for the phases of a strided data gradient)
 };
 
 struct ConvHooksBase {
@@ -70,7 +74,7 @@ struct ConvRowHooks : ConvHooksBase {
     const int h = th * g.TH + q % g.TH;
     const int n = tn * g.TN + q / g.TH;
     if (w >= g.Wo || h >= g.Ho || n >= g.B) return -1;
-    return (static_cast<long long>(n) * g.Ho + h) * g.Wo + w;
+    return (static_cast<long long>(n) * g.OH + (h * g.os + g.oe_h)) * g.OW + (w * g.os + g.oe_w);
   }
 };
 
@@ -167,6 +171,7 @@ int rb_conv_igemm(int mode, int dtype, const void* act, const void* wmat, void* 
   g.TW = tw; g.TH = th; g.TN = tn;
   g.tiles_w = (Wo + tw - 1) / tw; g.tiles_h = (Ho + th - 1) / th;
   g.cblocks = C / 64; g.patches_w = g.patches_h = 0;
+  g.os = 1; g.oe_h = g.oe_w = 0; g.OH = Ho; g.OW = Wo;
   const int tiles_n = (B + tn - 1) / tn;
   const int num_m = g.tiles_w * g.tiles_h * tiles_n;
   const long long K = (long long)KH * KW * C;
@@ -183,6 +188,56 @@ int rb_conv_igemm(int mode, int dtype, const void* act, const void* wmat, void* 
   GemmParams p{};
   p.M = num_m * 128; p.N = N; p.K = (int)K;
   p.out = out; p.ldc = N; p.bias = bias; p.act = relu ? ACT_RELU : ACT_NONE; p.alpha = 1.f;
+  p.vec_ok = 1; p.group_m = 8; p.split_k = 1;
+  p.status = rbh::device_status_word();
+  p.sched = rbh::dynamic_tiles() ? rbh::next_sched_slot() : nullptr;
+  const int items = num_m * ((N + BN - 1) / BN);
+  cudaStream_t st = (cudaStream_t)stream;
+#define RB_CONV_ROW(T_) \
+  (BN == 128 ? launch_conv<T_, 128, false, false, ConvRowHooks>(ta, tb, p, h, items, st) \
+             : launch_conv<T_, 256, false, false, ConvRowHooks>(ta, tb, p, h, items, st))
+  return dtype == rbh::DT_BF16 ? RB_CONV_ROW(__nv_bfloat16) : RB_CONV_ROW(__half);
+#undef RB_CONV_ROW
+}
+
+// One phase of the data gradient of a convolution with stride s > 1 (dilation 1): the input pixels
+// (s*u + e_h, s*v + e_w) of dx [B, H, W, N] receive sum over the phase's taps (a, b) of
+// dY[u + c_h - a, v + c_w - b, :] . wphase[n, (a, b, co)], dY [B, Hy, Wy, C], C % 64 == 0.
+// wphase [N, KHp*KWp*C] holds the taps kh = rh + s*a, kw = rw + s*b of the phase (the caller derives
+// e, c and the tap counts from rh, rw, s and the padding).  Other pixels of dx are not touched.
+int rb_conv_igemm_dgrad_phase(int dtype, const void* dy, const void* wphase, void* dx, int B, int Hy, int Wy, int C,
+                              int H, int W, int N, int KHp, int KWp, int s, int c_h, int c_w, int e_h, int e_w,
+                              int tw, int th, int tn, void* stream) {
+  using namespace rb;
+  if (dtype != rbh::DT_BF16 && dtype != rbh::DT_F16) return 60;
+  if (C % 64 || N % 8 || tw * th * tn != 128 || s < 1 || KHp < 1 || KWp < 1) return 60;
+  if ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(wphase) | reinterpret_cast<uintptr_t>(dx)) & 15) return 60;
+  if (e_h >= H || e_w >= W) return 0;
+  ConvRowHooks h;
+  ConvGeom& g = h.g;
+  g.B = B; g.Ho = (H - e_h + s - 1) / s; g.Wo = (W - e_w + s - 1) / s;
+  g.KH = KHp; g.KW = KWp; g.stride = 1; g.dil = 1;
+  g.off_h = c_h; g.off_w = c_w; g.tap_sign = -1;
+  g.TW = tw; g.TH = th; g.TN = tn;
+  g.tiles_w = (g.Wo + tw - 1) / tw; g.tiles_h = (g.Ho + th - 1) / th;
+  g.cblocks = C / 64; g.patches_w = g.patches_h = 0;
+  g.os = s; g.oe_h = e_h; g.oe_w = e_w; g.OH = H; g.OW = W;
+  const int tiles_n = (B + tn - 1) / tn;
+  const int num_m = g.tiles_w * g.tiles_h * tiles_n;
+  const long long K = (long long)KHp * KWp * C;
+  CUtensorMap ta, tb;
+  int rc = make_act_map(&ta, dtype, dy, B, Hy, Wy, C, tw, th, tn, 1);
+  if (rc) return 1000 + rc;
+  const int BN = N <= 128 ? 128 : 256;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)N}, strides[2] = {2, (uint64_t)K * 2};
+    uint32_t box[2] = {64, (uint32_t)BN};
+    rc = rbh::encode_tensor_map(&tb, dtype, 2, const_cast<void*>(wphase), dims, strides, box, 1);
+    if (rc) return 1000 + rc;
+  }
+  GemmParams p{};
+  p.M = num_m * 128; p.N = N; p.K = (int)K;
+  p.out = dx; p.ldc = N; p.act = ACT_NONE; p.alpha = 1.f;
   p.vec_ok = 1; p.group_m = 8; p.split_k = 1;
   p.status = rbh::device_status_word();
   p.sched = rbh::dynamic_tiles() ? rbh::next_sched_slot() : nullptr;

@@ -82,14 +82,6 @@ __device__ __forceinline__ void stem_build_row(const uint8_t* patch, uint8_t* sA
   }
 }
 
-// bounded wait that ignores the CTA's abort flag: used on the way out for copies still in flight
-__device__ __forceinline__ void stem_drain(uint32_t bar, uint32_t parity) {
-  const uint64_t t0 = globaltimer_ns();
-  while (!mbar_try_wait(bar, parity)) {
-    if (globaltimer_ns() - t0 > RB_WAIT_BUDGET_NS) break;
-  }
-}
-
 // ------------------------------------------------------------------------------------ forward
 template <typename T>
 __global__ void __launch_bounds__(128, 2)
@@ -204,7 +196,7 @@ __global__ void __launch_bounds__(128, 2)
   }
   // leave: copies still in flight (only after a failed wait) are given their time, then TMEM goes back
   if (tid == 0 && !ok) {
-    for (int i = max(0, issued - 2); i < issued; ++i) stem_drain(smem_u32(&win_full[i & 1]), (i >> 1) & 1);
+    for (int i = max(0, issued - 2); i < issued; ++i) mbar_drain(smem_u32(&win_full[i & 1]), (i >> 1) & 1, p.status);
   }
   tc_fence_before();
   __syncthreads();
@@ -334,7 +326,7 @@ __global__ void __launch_bounds__(128, 2)
     }
   }
   if (tid == 0 && !ok) {
-    for (int i = max(0, issued - 2); i < issued; ++i) stem_drain(smem_u32(&full[i & 1]), (i >> 1) & 1);
+    for (int i = max(0, issued - 2); i < issued; ++i) mbar_drain(smem_u32(&full[i & 1]), (i >> 1) & 1, p.status);
   }
   tc_fence_before();
   __syncthreads();

@@ -524,12 +524,8 @@ __global__ void __launch_bounds__(kColGroups* kColGroupThreads)
   }
   // after a failed wait: give the copies still in flight their time before the ring is reused below
   if (tg == 0 && trip < trips) {
-    for (long long t2 = trip; t2 < requested; ++t2) {
-      const uint64_t t0 = globaltimer_ns();
-      while (!mbar_try_wait(smem_u32(&my_bars[t2 % stages]), (uint32_t)((t2 / stages) & 1))) {
-        if (globaltimer_ns() - t0 > RB_WAIT_BUDGET_NS) break;
-      }
-    }
+    for (long long t2 = trip; t2 < requested; ++t2)
+      mbar_drain(smem_u32(&my_bars[t2 % stages]), (uint32_t)((t2 / stages) & 1), status);
   }
   __syncthreads();
   // fold the groups through the (now idle) ring: group 0 stores, the others add in turn

@@ -113,6 +113,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Bounded wait that ignores the CTA's abort flag: a role that is leaving after a failed wait gives
+// its own copies still in flight their time before the shared memory they land in is reused or freed.
+__device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity, int* status) {
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return;
+    if (globaltimer_ns() - t0 > RB_WAIT_BUDGET_NS) {
+      record_error(status, RB_ERR_TIMEOUT_FULL);
+      return;
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------
 // TMA (cp.async.bulk.tensor), loads complete on an mbarrier, no multicast
 // ----------------------------------------------------------------------------

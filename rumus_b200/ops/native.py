@@ -101,9 +101,23 @@ def lib():
     return _L()
 
 
+_BAD_STATUS_HOOKS = []
+
+
+def on_bad_status(fn) -> None:
+    """Registers ``fn()`` to run whenever a non-zero device status word is read: a kernel that gave up
+    on a bounded wait may have left shared scratch state (split-K workspaces, tile counters) half
+    written, and whoever caches such state drops it here."""
+    _BAD_STATUS_HOOKS.append(fn)
+
+
 def read_status() -> int:
     """Synchronises and returns the device status word (0 = clean), clearing it."""
-    return int(_L().rb_read_status())
+    s = int(_L().rb_read_status())
+    if s != 0:
+        for fn in _BAD_STATUS_HOOKS:
+            fn()
+    return s
 
 
 class DeviceWaitTimeout(RuntimeError):

@@ -83,10 +83,12 @@ _W4_WS = {}
 
 
 def _w4_workspace(device, numel: int, tiles: int):
-    """Per-device fp32 accumulation buffer and per-tile counters for split-K launches.  Both are zero
-    between launches (the kernel that finishes a tile puts them back), so consecutive launches on one
-    stream share them; they only grow."""
-    key = (device.type, device.index)
+    """Per-device, per-stream fp32 accumulation buffer and per-tile counters for split-K launches.
+    Both are zero between launches (the kernel that finishes a tile puts them back), so consecutive
+    launches on one stream share them; they only grow.  Launches on different streams may overlap, so
+    each stream has its own pair; a kernel that gave up on a wait leaves them dirty, so they are
+    dropped when a non-zero status word is read (``native.on_bad_status``)."""
+    key = (device.type, device.index, stream_ptr())
     ws, cnt = _W4_WS.get(key, (None, None))
     if ws is None or ws.numel() < numel:
         ws = torch.zeros(max(numel, 1 << 22), dtype=torch.float32, device=device)
@@ -95,6 +97,8 @@ def _w4_workspace(device, numel: int, tiles: int):
     _W4_WS[key] = (ws, cnt)
     return ws, cnt
 
+
+native.on_bad_status(_W4_WS.clear)
 
 _GEMV_SCRATCH = {}
 

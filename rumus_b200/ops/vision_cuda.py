@@ -18,6 +18,7 @@ native.register_signature("rb_im2col_nhwc", [I, P, P] + [I] * 12 + [P])
 native.register_signature("rb_col2im_nhwc", [I, P, P] + [I] * 12 + [P])
 native.register_signature("rb_conv_igemm", [I, I, P, P, P, P, I] + [I] * 15 + [P])
 native.register_signature("rb_conv_igemm_wgrad", [I, P, P, P] + [I] * 12 + [P])
+native.register_signature("rb_conv_igemm_dgrad_phase", [I, P, P, P] + [I] * 17 + [P])
 native.register_signature("rb_conv_stem_fwd", [I, P, P, P, P, I, I, I, P])
 native.register_signature("rb_conv_stem_wgrad", [I, P, P, P, I, I, I, P])
 native.register_signature("rb_bn_slabs", [LL])
@@ -149,6 +150,37 @@ def conv_igemm(mode: int, act: torch.Tensor, wmat: torch.Tensor, Ho: int, Wo: in
     return out
 
 
+def conv_igemm_dgrad_strided(dy4: torch.Tensor, wm: torch.Tensor, H: int, W: int, Cin: int, KH: int, KW: int,
+                             stride: int, pad: int) -> torch.Tensor:
+    """Data gradient of a convolution with stride > 1 (dilation 1) without a patch matrix: the input
+    pixels split into stride x stride phases by ``(ih + pad) % stride, (iw + pad) % stride``; a phase
+    only ever meets the taps ``kh = phase + stride * a``, so it is a stride-1 gather over dY with those
+    taps, written to every stride-th input pixel.  dY NHWC ``[B, Ho, Wo, Cout]``, ``wm [Cout, KH*KW*Cin]``
+    (K ordered kh, kw, ci) -> dx NHWC ``[B, H, W, Cin]``."""
+    B, Ho, Wo, Cout = dy4.shape
+    s = stride
+    w4 = wm.view(Cout, KH, KW, Cin)
+    every_phase_has_taps = KH >= s and KW >= s
+    dx = (torch.empty if every_phase_has_taps else torch.zeros)((B, H, W, Cin), dtype=dy4.dtype, device=dy4.device)
+    L = native.lib()
+    for rh in range(min(s, KH)):
+        for rw in range(min(s, KW)):
+            e_h, e_w = (rh - pad) % s, (rw - pad) % s
+            if e_h >= H or e_w >= W:
+                continue
+            c_h, c_w = (e_h + pad - rh) // s, (e_w + pad - rw) // s
+            taps = w4[:, rh::s, rw::s, :]                                   # [Cout, KHp, KWp, Cin]
+            KHp, KWp = taps.shape[1], taps.shape[2]
+            wphase = taps.permute(3, 1, 2, 0).reshape(Cin, KHp * KWp * Cout).contiguous()
+            Hu, Wu = -(-(H - e_h) // s), -(-(W - e_w) // s)
+            tw, th, tn = _pixel_tile(B, Hu, Wu)
+            check(L.rb_conv_igemm_dgrad_phase(native.dtype_code(dy4.dtype), ptr(dy4), ptr(wphase), ptr(dx), B, Ho, Wo,
+                                              Cout, H, W, Cin, KHp, KWp, s, c_h, c_w, e_h, e_w, tw, th, tn,
+                                              stream_ptr()), "rb_conv_igemm_dgrad_phase")
+            count_launch()
+    return dx
+
+
 def conv_igemm_wgrad(dyh: torch.Tensor, xh: torch.Tensor, KH: int, KW: int, stride: int, pad: int, dil: int) -> torch.Tensor:
     """dY NHWC ``[B, Ho, Wo, Cout]``, x NHWC ``[B, H, W, C]`` -> fp32 ``[Cout, KH*KW*C]`` (K ordered kh, kw, c)."""
     B, Ho, Wo, Cout = dyh.shape
@@ -220,6 +252,8 @@ class Conv2dFn(torch.autograd.Function):
                     # data gradient = the same gather on dY with mirrored taps; weight as [Cin, (kh, kw, co)]
                     wd = wm.view(Cout, KH, KW, Cin).permute(3, 1, 2, 0).reshape(Cin, KH * KW * Cout).contiguous()
                     dx = _as_nchw(conv_igemm(1, dy4, wd, H, W, KH, KW, 1, padding, dilation))
+                elif stride > 1 and dilation == 1 and Cout % 64 == 0:
+                    dx = _as_nchw(conv_igemm_dgrad_strided(dy4, wm, H, W, Cin, KH, KW, stride, padding))
                 else:
                     dcols = native.gemm(dyh, wm)           # [M, K]: strided data gradients scatter through col2im
                     dx = _as_nchw(_col2im(dcols, B, H, W, Cin, KH, KW, Ho, Wo, stride, padding, dilation, Kpad))

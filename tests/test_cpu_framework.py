@@ -338,3 +338,40 @@ def test_stem_weight_matrix_order_matches_the_patch_rows():
     dwk = cols.view(-1, STEM_K).t() @ g.permute(0, 2, 3, 1).reshape(-1, 64)      # [192, 64]
     dw = dwk[:168].view(7, 24, 64)[:, 1:22].reshape(7, 7, 3, 64).permute(3, 2, 0, 1)
     torch.testing.assert_close(dw, w.grad)
+
+
+def test_strided_conv_data_gradient_decomposes_into_stride1_phases():
+    """The strided data gradient of the implicit-GEMM convolution runs one stride-1 gather per phase
+    ((ih + pad) % s, (iw + pad) % s) with the taps kh = phase + s*a.  The same index arithmetic in plain
+    PyTorch reproduces autograd's data gradient, including 1x1 kernels (phases without taps stay zero)
+    and ragged sizes."""
+    import torch.nn.functional as TF
+    torch.manual_seed(0)
+    for (H, W, K, s, pad) in ((15, 13, 3, 2, 1), (14, 14, 1, 2, 0), (9, 12, 5, 3, 2), (8, 8, 3, 2, 0)):
+        B, Cin, Cout = 2, 3, 4
+        x = torch.randn(B, Cin, H, W, dtype=torch.float64, requires_grad=True)
+        w = torch.randn(Cout, Cin, K, K, dtype=torch.float64)
+        y = TF.conv2d(x, w, None, s, pad, 1)
+        g = torch.randn_like(y)
+        y.backward(g)
+        Ho, Wo = y.shape[2], y.shape[3]
+        dy = g.permute(0, 2, 3, 1)                                          # NHWC
+        dx = torch.zeros(B, H, W, Cin, dtype=torch.float64)
+        for rh in range(min(s, K)):
+            for rw in range(min(s, K)):
+                e_h, e_w = (rh - pad) % s, (rw - pad) % s
+                if e_h >= H or e_w >= W:
+                    continue
+                c_h, c_w = (e_h + pad - rh) // s, (e_w + pad - rw) // s
+                taps = w[:, :, rh::s, rw::s]                                # [Cout, Cin, KHp, KWp]
+                Hu, Wu = -(-(H - e_h) // s), -(-(W - e_w) // s)
+                for u in range(Hu):
+                    for v in range(Wu):
+                        acc = torch.zeros(B, Cin, dtype=torch.float64)
+                        for a in range(taps.shape[2]):
+                            for b in range(taps.shape[3]):
+                                oh, ow = u + c_h - a, v + c_w - b
+                                if 0 <= oh < Ho and 0 <= ow < Wo:
+                                    acc += dy[:, oh, ow, :] @ taps[:, :, a, b]
+                        dx[:, s * u + e_h, s * v + e_w, :] = acc
+        torch.testing.assert_close(dx.permute(0, 3, 1, 2), x.grad)

@@ -300,3 +300,16 @@ def test_canary_guard_detects_out_of_bounds_writes():
         with canary_guard(devices=("cpu",)):
             a = torch.empty((8,), dtype=torch.float32, device="cpu")
             torch.as_strided(a, (1,), (1,), storage_offset=a.storage_offset() - 1).fill_(3.0)
+
+
+def test_split_k_workspaces_are_dropped_after_a_bad_device_status():
+    """A kernel that gave up on a bounded wait may leave the shared split-K workspace and tile counters
+    non-zero; reading a non-zero status word runs the registered hooks, which drop the cached buffers so
+    that the next call starts from fresh zeros."""
+    import torch
+    from rumus_b200.ops import native, quant_cuda
+    assert quant_cuda._W4_WS.clear in native._BAD_STATUS_HOOKS
+    quant_cuda._W4_WS[("cpu", None, 0)] = (torch.ones(4), torch.ones(4, dtype=torch.int32))
+    for fn in native._BAD_STATUS_HOOKS:
+        fn()
+    assert not quant_cuda._W4_WS

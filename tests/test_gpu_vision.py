@@ -159,14 +159,16 @@ def test_resnet_bottleneck_stack_trains_fp16():
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("cfg", [
     dict(B=4, Cin=64, Cout=64, H=28, W=28, k=3, s=1, p=1, d=1),      # 3x3, tiles of 4 x 4 pixels x 8 images
-    dict(B=3, Cin=128, Cout=256, H=15, W=13, k=3, s=2, p=1, d=1),    # strided gather, ragged image, col2im data grad
+    dict(B=3, Cin=128, Cout=256, H=15, W=13, k=3, s=2, p=1, d=1),    # strided gather, ragged image, data grad in 4 phases
+    dict(B=2, Cin=64, Cout=64, H=13, W=11, k=5, s=3, p=2, d=1),      # stride 3: 9 phases with 1..4 taps
     dict(B=2, Cin=256, Cout=128, H=14, W=14, k=1, s=2, p=0, d=1),    # strided 1x1 shortcut
     dict(B=5, Cin=64, Cout=192, H=9, W=20, k=3, s=1, p=2, d=2),      # dilation, Cout not a multiple of 128
     dict(B=2, Cin=192, Cout=64, H=7, W=7, k=5, s=1, p=2, d=1),       # 5x5 taps, three channel blocks
 ])
 def test_conv2d_implicit_gemm(dtype, cfg):
     """Convolutions with 64-channel blocks take the implicit-GEMM kernels (no patch matrix): forward,
-    data gradient (stride 1: mirrored gather; strided: GEMM + col2im) and weight gradient against fp32."""
+    data gradient (stride 1: mirrored gather; strided: one stride-1 gather per phase) and weight gradient
+    against fp32."""
     from rumus_b200.ops import native
     from rumus_b200.ops import vision as V
     from rumus_b200.ops import vision_cuda as VC
