@@ -42,6 +42,12 @@ if "--small" in sys.argv:
     q, k, v = [(torch.randn(B, S, H, D, device='cuda') * 0.5).bfloat16().requires_grad_(True) for _ in range(3)]
     o = F.flash_attention(q, k, v, True)
     o.backward(torch.randn_like(o))
+    # LayerNorm forward (with the residual add) and backward (with the residual-stream gradient), 16384 x 2048
+    x = torch.randn(16384, 2048, device='cuda').bfloat16(); r = torch.randn_like(x)
+    g = torch.ones(2048, device='cuda').bfloat16(); bb = torch.zeros(2048, device='cuda').bfloat16()
+    for _ in range(2):
+        y, h, stats = native.norm_fwd(x, g, bb, 1e-5, False, residual=r)
+        native.norm_bwd(h, y, g, stats, False, dres=r)
     torch.cuda.synchronize()
     print("small case done, status", native.read_status())
     sys.exit(0)

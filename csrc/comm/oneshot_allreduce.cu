@@ -23,6 +23,8 @@ struct OneShotParams {
   long long buf_off;     // bytes: this epoch's partial buffer (same offset on every rank)
   long long flags_off;   // bytes: int[world] epoch flags in the arena
   int epoch;
+  const int* epoch_base; // device int added to `epoch` (null: 0).  A captured launch is replayed with the
+                         // arguments it was captured with; the caller advances this word between replays
   long long numel;       // multiple of 16 bytes worth of elements
   const void* residual;  // local [numel] or null
   void* out;             // local [numel]
@@ -35,14 +37,15 @@ __global__ void __launch_bounds__(256) oneshot_allreduce_kernel(const OneShotPar
   __shared__ int s_ok;
   const PeerTable& pt = p.peers;
   if (threadIdx.x == 0) {
+    const int epoch = p.epoch + (p.epoch_base ? *p.epoch_base : 0);
     if (blockIdx.x == 0) {
       __threadfence_system();
       for (int r = 0; r < pt.world; ++r)
-        st_release_sys(peer_ptr<int>(pt, r, p.flags_off) + pt.rank, p.epoch);
+        st_release_sys(peer_ptr<int>(pt, r, p.flags_off) + pt.rank, epoch);
     }
     bool ok = true;
     for (int r = 0; r < pt.world && ok; ++r)
-      ok = wait_flag_sys(peer_ptr<int>(pt, pt.rank, p.flags_off) + r, p.epoch, p.status, RB_ERR_TIMEOUT_FLAG);
+      ok = wait_flag_sys(peer_ptr<int>(pt, pt.rank, p.flags_off) + r, epoch, p.status, RB_ERR_TIMEOUT_FLAG);
     s_ok = ok ? 1 : 0;
   }
   __syncthreads();
@@ -92,10 +95,11 @@ __global__ void __launch_bounds__(256) oneshot_allreduce_kernel(const OneShotPar
 extern "C" {
 
 // out[numel] = residual[numel] + sum over ranks of (arena buffer at buf_off)[numel]; see the file
-// comment for the protocol.  numel * element size must be a multiple of 16 bytes.
+// comment for the protocol.  numel * element size must be a multiple of 16 bytes.  The epoch the ranks
+// agree on is `epoch` + *epoch_base (epoch_base: a device int, or null for 0).
 int rb_oneshot_allreduce(int dtype, void* const* bases, void* mc_base, int world, int rank, long long buf_off,
                          long long flags_off, int epoch, long long numel, const void* residual, void* out,
-                         int use_multimem, int ctas, void* stream) {
+                         int use_multimem, int ctas, const int* epoch_base, void* stream) {
   using namespace rb;
   if (world > kMaxRanks) return 30;
   const int esz = dtype == rbh::DT_F32 ? 4 : 2;
@@ -103,7 +107,7 @@ int rb_oneshot_allreduce(int dtype, void* const* bases, void* mc_base, int world
   OneShotParams p;
   for (int i = 0; i < kMaxRanks; ++i) p.peers.base[i] = i < world ? bases[i] : nullptr;
   p.peers.mc_base = mc_base; p.peers.world = world; p.peers.rank = rank;
-  p.buf_off = buf_off; p.flags_off = flags_off; p.epoch = epoch; p.numel = numel;
+  p.buf_off = buf_off; p.flags_off = flags_off; p.epoch = epoch; p.epoch_base = epoch_base; p.numel = numel;
   p.residual = residual; p.out = out;
   p.use_multimem = use_multimem && mc_base != nullptr;
   p.status = rbh::device_status_word();

@@ -19,7 +19,7 @@ native.register_signature("rb_all_gather", [P, I, I, LL, LL, LL, P, LL, I, I, P]
 native.register_signature("rb_shard_gather", [P, I, I, LL, P, LL, LL, I, I, P])
 native.register_signature("rb_allreduce_unscale", [I, P, P, I, I, LL, LL, LL, LL, LL, I, P, F, P, P,
                                                    I, I, P])
-native.register_signature("rb_oneshot_allreduce", [I, P, P, I, I, LL, LL, I, LL, P, P, I, I, P])
+native.register_signature("rb_oneshot_allreduce", [I, P, P, I, I, LL, LL, I, LL, P, P, I, I, P, P])
 native.register_signature("rb_ag_gemm", [I, P, I, I, LL, LL, LL, P, LL, I, I, LL, P, LL, I, I, I, I,
                                          P, LL, P, P, LL, I, P, I, P])
 native.register_signature("rb_gemm_rs", [I, P, I, I, P, LL, P, LL, I, I, I, I, LL, LL, P, I, P, P, P,
@@ -138,17 +138,20 @@ def gemm_rs(arena: SymmArena, a: torch.Tensor, b: torch.Tensor, *, partial_off: 
 
 
 def oneshot_allreduce(arena: SymmArena, partial: torch.Tensor, out: torch.Tensor, *, flags_off: int, epoch: int,
-                      residual: Optional[torch.Tensor] = None, ctas: int = 32):
+                      residual: Optional[torch.Tensor] = None, ctas: int = 32,
+                      epoch_base: Optional[torch.Tensor] = None):
     """``out = residual + sum over ranks of partial`` for a small arena-resident ``partial`` (decode
     activations): one flag round and one pass of peer loads (``csrc/comm/oneshot_allreduce.cu``).  The
-    caller alternates ``partial`` between two arena buffers from one call to the next."""
+    caller alternates ``partial`` between two arena buffers from one call to the next.  ``epoch_base``
+    (an int32 device tensor) is added to ``epoch`` on the device: a launch captured in a CUDA graph keeps
+    its arguments, so the caller moves the epochs forward through that word between replays."""
     assert partial.is_contiguous() and out.is_contiguous() and out.numel() == partial.numel()
     if residual is not None:
         assert residual.is_contiguous() and residual.numel() == partial.numel() and residual.dtype == partial.dtype
     rc = native.lib().rb_oneshot_allreduce(native.dtype_code(partial.dtype), arena.bases(), c_void_p(arena.mc_ptr),
                                            arena.world, arena.rank, arena.offset_of(partial), flags_off, epoch,
                                            partial.numel(), ptr(residual), ptr(out), 1 if arena.mc_ptr else 0,
-                                           ctas, stream_ptr())
+                                           ctas, ptr(epoch_base), stream_ptr())
     check(rc, "rb_oneshot_allreduce")
     count_launch()
     return out

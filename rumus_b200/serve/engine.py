@@ -147,6 +147,9 @@ class ServeConfig:
     # [blocks, Hkv, block_size, D] (a head's tokens together: long contiguous reads in decode
     # attention).  Opt-in until measured on hardware.
     kv_head_major: bool = field(default_factory=lambda: os.environ.get("RB_KV_HEAD_MAJOR", "0") == "1")
+    # Decode batches run as captured CUDA graphs (one per padded batch size and context bucket): a decode
+    # step is ~450 small launches whose host cost exceeds their device time.  RB_SERVE_GRAPHS=0 disables.
+    cuda_graphs: bool = field(default_factory=lambda: os.environ.get("RB_SERVE_GRAPHS", "1") == "1")
 
 
 class _Layer:
@@ -164,9 +167,14 @@ class Int4LlamaShard:
         hd = m.d_model // m.num_heads
         self.hd = hd
         self.h_local, self.hkv_local = m.num_heads // world, m.num_kv_heads // world
-        ffn_local = m.ffn_dim // world
-        # row-parallel K splits must fall on quantisation-group boundaries
-        assert (self.h_local * hd) % cfg.group_size == 0 and ffn_local % cfg.group_size == 0 or world == 1
+        # row-parallel K splits must fall on quantisation-group boundaries: the FFN width is padded with
+        # zero columns (gate, up) / zero rows (down) to a multiple of world x group size, which leaves the
+        # function unchanged (silu(0) * 0 = 0 meets zero rows).  Llama-7B: 11008 -> 11264 at 4 and 8 ranks.
+        step = world * cfg.group_size
+        ffn_pad = (m.ffn_dim + step - 1) // step * step if world > 1 else m.ffn_dim
+        ffn_local = ffn_pad // world
+        self.ffn_padded = ffn_pad
+        assert (self.h_local * hd) % cfg.group_size == 0 or world == 1
         # full matrices are drawn (same seed on every rank, so the slices fit together) and
         # quantised on the device the shard lives on
         gdev = device if torch.device(device).type == "cuda" else "cpu"
@@ -192,9 +200,14 @@ class Int4LlamaShard:
             wo = rnd(m.num_heads * hd, m.d_model)
             L.out = q(wo[r * ql:(r + 1) * ql])
             wg, wu = rnd(m.d_model, m.ffn_dim), rnd(m.d_model, m.ffn_dim)
+            if ffn_pad != m.ffn_dim:
+                wg = torch.nn.functional.pad(wg, (0, ffn_pad - m.ffn_dim))
+                wu = torch.nn.functional.pad(wu, (0, ffn_pad - m.ffn_dim))
             L.gate_up = q(torch.cat([wg[:, r * ffn_local:(r + 1) * ffn_local],
                                      wu[:, r * ffn_local:(r + 1) * ffn_local]], dim=1))
             wd = rnd(m.ffn_dim, m.d_model)
+            if ffn_pad != m.ffn_dim:
+                wd = torch.nn.functional.pad(wd, (0, 0, 0, ffn_pad - m.ffn_dim))
             L.down = q(wd[r * ffn_local:(r + 1) * ffn_local])
             L.ln1 = torch.ones(m.d_model, dtype=cfg.dtype, device=device)
             L.ln2 = torch.ones(m.d_model, dtype=cfg.dtype, device=device)
@@ -329,6 +342,8 @@ class Engine:
     # one flag round, latency bound); larger ones (long prompt chunks) are bandwidth bound and go
     # through NCCL's reduce-scatter / all-gather schedule
     ONESHOT_MAX_BYTES = 2 << 20
+    # decode batches are padded to one of these sizes before they are captured / replayed
+    GRAPH_BATCHES = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
     def __init__(self, cfg: ServeConfig, device=None, group: Optional[dist.ProcessGroup] = None, seed: int = 0):
         self.cfg = cfg
@@ -344,6 +359,11 @@ class Engine:
         self.steps = 0
         self.tokens_out = 0
         self._ar = None
+        self._graphs: Dict[tuple, object] = {}
+        self._graph_pool = None
+        self._capturing = False
+        self._cap_k = 0
+        self.graph_replays = 0
         if self.world > 1 and cfg.comm_mode == "fused" and self.device.type == "cuda":
             from ..parallel.symm import SymmArena
             n = cfg.token_budget * cfg.model.d_model
@@ -353,6 +373,8 @@ class Engine:
             self._ar_bufs = [self.arena.alloc(n, cfg.dtype)[0] for _ in range(2)]
             self._ar_flags = self.arena.alloc_flags(self.world)
             self._ar_epoch = 0
+            # added on the device to the epochs of captured all-reduce launches (see _decode_graph)
+            self._ar_gen = torch.zeros(1, dtype=torch.int32, device=self.device)
             self.arena.barrier()
             self._ar = True
 
@@ -377,13 +399,20 @@ class Engine:
             from ..ops.quant_cuda import int4_matmul
             from ..parallel import fused_ops
             T = h.shape[0]
-            self._ar_epoch += 1
-            part = self._ar_bufs[self._ar_epoch & 1][: T * qw.n].view(T, qw.n)
+            if self._capturing:
+                # a captured launch keeps its arguments: its epoch is (device word) + k, k = its position in
+                # the graph; the word is even at every replay, so buffer k & 1 matches the eager convention
+                self._cap_k += 1
+                epoch, base = self._cap_k, self._ar_gen
+            else:
+                self._ar_epoch += 1
+                epoch, base = self._ar_epoch, None
+            part = self._ar_bufs[epoch & 1][: T * qw.n].view(T, qw.n)
             int4_matmul(h, qw, out=part)
             out = torch.empty_like(residual)
             with trace_range("serve.oneshot_allreduce"):
                 fused_ops.oneshot_allreduce(self.arena, part, out, flags_off=self._ar_flags,
-                                            epoch=self._ar_epoch, residual=residual.contiguous())
+                                            epoch=epoch, residual=residual.contiguous(), epoch_base=base)
             return out
         part = qmatmul_int4(h, qw)
         dist.all_reduce(part, group=self.group)
@@ -434,6 +463,92 @@ class Engine:
         blk = torch.tensor(table, dtype=torch.int64)[pos // bs]
         return (blk * bs + pos % bs).to(self.device)
 
+    # ------------------------------------------------------------------ decode step as a CUDA graph
+    def _capture_decode(self, Bp: int, ctx_bucket: int, scale: float):
+        """Captures the decoder stack for a padded batch of ``Bp`` sequences whose contexts fit
+        ``ctx_bucket`` tokens.  Inputs live in static device tensors; padded rows carry cache slot -1
+        (the append kernel skips them), context length 1 and block table 0, and their outputs are ignored."""
+        from types import SimpleNamespace
+        dev = self.device
+        st = SimpleNamespace(
+            toks=torch.zeros(Bp, dtype=torch.int64, device=dev), pos=torch.zeros(Bp, dtype=torch.int64, device=dev),
+            slots=torch.full((Bp,), -1, dtype=torch.int64, device=dev),
+            tables=torch.zeros((Bp, self.max_blocks), dtype=torch.int32, device=dev),
+            ctx=torch.ones(Bp, dtype=torch.int32, device=dev))
+
+        def attend(li, q, k, v):
+            return paged_decode_attention(q.contiguous(), self.cache.k[li], self.cache.v[li], st.tables, st.ctx,
+                                          scale, ctx_bucket, head_major=self.cache.head_major)
+
+        # one eager pass first, on a side stream: whatever the kernels set up lazily (function attributes,
+        # workspaces, communicator channels) exists before the capture begins
+        cur = torch.cuda.current_stream(dev)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            self._forward(st.toks, st.pos, st.slots, attend)
+        cur.wait_stream(side)
+        torch.cuda.synchronize(dev)
+        g = torch.cuda.CUDAGraph()
+        self._capturing, self._cap_k = True, 0
+        try:
+            with torch.cuda.graph(g, pool=self._graph_pool, capture_error_mode="thread_local"):
+                st.hidden = self._forward(st.toks, st.pos, st.slots, attend)
+        finally:
+            self._capturing = False
+        if self._graph_pool is None:
+            self._graph_pool = g.pool()
+        st.graph, st.n_allreduce = g, self._cap_k
+        return st
+
+    def warmup_graphs(self, max_ctx: Optional[int] = None) -> int:
+        """Captures the decode graphs a run can meet (every padded batch size up to ``max_batch``, every
+        context bucket up to ``max_ctx``) before traffic arrives, so that no request waits for a capture.
+        Every tensor-parallel rank has to call it (the captures run collectives).  Returns how many."""
+        if not (self.cfg.cuda_graphs and self.device.type == "cuda"):
+            return 0
+        scale = 1.0 / math.sqrt(self.model.hd)
+        top = max_ctx or (self.cfg.model.seq_len + 512)
+        n, cb = 0, 256
+        while True:
+            for Bp in self.GRAPH_BATCHES:
+                if (Bp, cb) not in self._graphs:
+                    self._graphs[(Bp, cb)] = self._capture_decode(Bp, cb, scale)
+                    n += 1
+                if Bp >= self.cfg.max_batch:
+                    break
+            if cb >= top:
+                break
+            cb *= 2
+        return n
+
+    def _decode_graph(self, B: int, last, ctx, slots_h: torch.Tensor, tables_h: torch.Tensor, scale: float):
+        """Runs the decoder stack for this step's decode batch by replaying a captured graph; returns the
+        hidden states ``[B, d]``, or None when the batch is larger than the largest captured size."""
+        Bp = next((b for b in self.GRAPH_BATCHES if b >= B), None)
+        if Bp is None:
+            return None
+        ctx_bucket = max(256, 1 << (max(ctx) - 1).bit_length())
+        st = self._graphs.get((Bp, ctx_bucket))
+        if st is None:
+            st = self._graphs[(Bp, ctx_bucket)] = self._capture_decode(Bp, ctx_bucket, scale)
+        pad = Bp - B
+        st.toks.copy_(torch.tensor(list(last) + [0] * pad, dtype=torch.int64))
+        st.pos.copy_(torch.tensor([c - 1 for c in ctx] + [0] * pad, dtype=torch.int64))
+        st.ctx.copy_(torch.tensor(list(ctx) + [1] * pad, dtype=torch.int32))
+        st.slots.copy_(torch.cat([slots_h.to(torch.int64), torch.full((pad,), -1, dtype=torch.int64)]))
+        tp = torch.zeros((Bp, self.max_blocks), dtype=torch.int32)
+        tp[:B] = tables_h.to(torch.int32)
+        st.tables.copy_(tp)
+        if self._ar and st.n_allreduce:
+            if self._ar_epoch & 1:
+                self._ar_epoch += 1          # every rank skips the same epoch number; flags only ever grow
+            self._ar_gen.fill_(self._ar_epoch)
+            self._ar_epoch += st.n_allreduce
+        st.graph.replay()
+        self.graph_replays += 1
+        return st.hidden[:B]
+
     # ------------------------------------------------------------------ one engine step
     def step(self) -> List[int]:
         """Runs one scheduling step; returns the ids of requests that finished."""
@@ -471,8 +586,6 @@ class Engine:
             last = [self.requests[r].output[-1] if self.requests[r].output else self.requests[r].prompt[-1]
                     for r in decode_ids]
             ctx = [len(self.requests[r].prompt) + len(self.requests[r].output) for r in decode_ids]
-            toks = torch.tensor(last, dtype=torch.int64, device=dev)
-            pos = torch.tensor([c - 1 for c in ctx], dtype=torch.int64, device=dev)
             bs = self.cfg.block_size
             pin = dev.type == "cuda"
             tables_h = self.sched.block_tables(decode_ids, self.max_blocks, pin=pin)
@@ -480,17 +593,23 @@ class Engine:
             # cache slot of each sequence's newest token: its block's id * block size + offset
             slots_h = (tables_h.gather(1, (last_pos // bs)[:, None]).squeeze(1).to(torch.int64) * bs
                        + last_pos % bs)
-            tables = tables_h.to(dev, non_blocking=pin)
-            slots_t = slots_h.to(dev)
-            ctx_t = torch.tensor(ctx, dtype=torch.int32, device=dev)
-            max_ctx = max(ctx)
-
-            def attend_dec(li, q, k, v):
-                return paged_decode_attention(q.contiguous(), self.cache.k[li], self.cache.v[li], tables,
-                                              ctx_t, scale, max_ctx, head_major=self.cache.head_major)
-
             with trace_range("serve.decode_batch"):
-                hidden = self._forward(toks, pos, slots_t, attend_dec)
+                hidden = None
+                if self.cfg.cuda_graphs and dev.type == "cuda":
+                    hidden = self._decode_graph(B, last, ctx, slots_h, tables_h, scale)
+                if hidden is None:
+                    toks = torch.tensor(last, dtype=torch.int64, device=dev)
+                    pos = torch.tensor([c - 1 for c in ctx], dtype=torch.int64, device=dev)
+                    tables = tables_h.to(dev, non_blocking=pin)
+                    slots_t = slots_h.to(dev)
+                    ctx_t = torch.tensor(ctx, dtype=torch.int32, device=dev)
+                    max_ctx = max(ctx)
+
+                    def attend_dec(li, q, k, v):
+                        return paged_decode_attention(q.contiguous(), self.cache.k[li], self.cache.v[li], tables,
+                                                      ctx_t, scale, max_ctx, head_major=self.cache.head_major)
+
+                    hidden = self._forward(toks, pos, slots_t, attend_dec)
             ids = self._logits_argmax(hidden)
             for r, t in zip(decode_ids, ids.tolist()):
                 now_tokens[r] = int(t)

@@ -104,6 +104,8 @@ def main(argv=None):
                     help="tensor-parallel reductions: one-shot arena kernel, or NCCL all-reduce")
     ap.add_argument("--tp", type=int, default=0,
                     help="tensor-parallel degree; must equal the number of ranks started by torch.distributed.run")
+    ap.add_argument("--no-graphs", action="store_true",
+                    help="launch every decode kernel from the host instead of replaying captured CUDA graphs")
     ap.add_argument("--num-blocks", type=int, default=0,
                     help="KV-cache blocks per rank (0: sized to at most 35%% of device memory)")
     a = ap.parse_args(argv)
@@ -134,11 +136,16 @@ def main(argv=None):
                       token_budget=8192, comm_mode=a.comm,
                       dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32,
                       scale_dtype=torch.float16 if dev.type == "cuda" else torch.float32)
+    if a.no_graphs:
+        cfg.cuda_graphs = False
     eng = Engine(cfg, dev)
+    eng.warmup_graphs(max_ctx=2048 + 512)       # prompts U[128,2048] + outputs U[128,512]
     res = run(eng, a.requests, a.rate, vocab=mc.vocab_size)
     if int(os.environ.get("RANK", "0")) == 0:
         res.update({"model": a.model, "tp": world, "rate_req_s": a.rate, "weights": "INT4 g128 fp16 scales",
                     "kv_blocks": num_blocks, "comm_mode": a.comm if world > 1 else "local",
+                    "decode_graphs": bool(cfg.cuda_graphs and dev.type == "cuda"),
+                    "graph_replays": eng.graph_replays, "graphs_captured": len(eng._graphs), "engine_steps": eng.steps,
                     "device_status": native_status()})
         print(json.dumps(res))
     if world > 1:

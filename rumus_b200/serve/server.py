@@ -197,6 +197,7 @@ def main(argv=None):
                       dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32,
                       scale_dtype=torch.float16 if dev.type == "cuda" else torch.float32)
     engine = Engine(cfg, dev)
+    engine.warmup_graphs()          # every rank: the decode graphs are captured before traffic arrives
     if world > 1 and dist.get_rank() != 0:
         follower_loop(engine, cpu_group)
         dist.destroy_process_group()

@@ -229,3 +229,23 @@ def test_tensor_parallel_load_generator_keeps_ranks_in_step():
     from dist_utils import run_ranks
     a, b = run_ranks(_tp_loadgen_worker, 2)
     assert a == b and a["tokens"] > 0
+
+
+def test_ffn_width_is_padded_to_the_row_parallel_group_grid():
+    """A feed-forward width that does not split into whole quantisation groups per rank (Llama-7B:
+    11008 over 4 or 8 ranks at group size 128) is padded with zero columns / rows; the ranks' partial
+    products still add up to the unsplit layer's output."""
+    from rumus_b200.nn.quant import qmatmul_int4
+    from rumus_b200.ops import functional as F
+    from rumus_b200.serve.engine import Int4LlamaShard
+    mc = LlamaConfig(vocab_size=64, seq_len=64, d_model=128, num_heads=2, num_kv_heads=2, num_layers=1, ffn_dim=320)
+    cfg = ServeConfig(model=mc, group_size=64, num_blocks=4, block_size=8, max_batch=2, token_budget=16,
+                      dtype=torch.float32, scale_dtype=torch.float32)
+    whole = Int4LlamaShard(cfg, torch.device("cpu"), 0, 1, seed=7)
+    parts = [Int4LlamaShard(cfg, torch.device("cpu"), r, 2, seed=7) for r in range(2)]
+    assert whole.ffn_padded == 320 and parts[0].ffn_padded == 384
+    assert parts[0].layers[0].down.k == 192 and parts[0].layers[0].gate_up.n == 384
+    x = torch.randn(5, 128, generator=torch.Generator().manual_seed(0))
+    ref = qmatmul_int4(F.swiglu(qmatmul_int4(x, whole.layers[0].gate_up)), whole.layers[0].down)
+    got = sum(qmatmul_int4(F.swiglu(qmatmul_int4(x, p.layers[0].gate_up)), p.layers[0].down) for p in parts)
+    torch.testing.assert_close(got, ref, rtol=1e-4, atol=1e-5)

@@ -99,3 +99,34 @@ def test_engine_gpu_generates_and_frees_blocks():
     assert e.sched.free_blocks() == 128
     from rumus_b200.ops import native
     assert native.read_status() == 0
+
+
+def test_engine_decode_graphs_match_eager_decode():
+    """Decode steps replayed from captured CUDA graphs (padded batch, static inputs) produce the same
+    tokens as launching every kernel eagerly (split-K sums are not ordered, so a near-tie between two
+    logits may fall the other way: most sequences, not all, have to agree token for token)."""
+    import dataclasses
+    from rumus_b200.models.llama import LlamaConfig
+    from rumus_b200.ops import native
+    from rumus_b200.serve import Engine, ServeConfig
+    mc = LlamaConfig(vocab_size=512, seq_len=512, d_model=256, num_heads=2, num_kv_heads=2, num_layers=2,
+                     ffn_dim=512)
+    base = ServeConfig(model=mc, num_blocks=128, block_size=16, max_batch=8, token_budget=256)
+    results = []
+    for graphs in (False, True):
+        e = Engine(dataclasses.replace(base, cuda_graphs=graphs), torch.device("cuda"), seed=3)
+        r = random.Random(1)
+        for i in range(7):
+            e.add_request(i + 1, [r.randrange(512) for _ in range(r.randint(5, 200))], r.randint(3, 20))
+        outs = {}
+        while e.has_work():
+            for rid in e.step():
+                outs[rid] = e.requests.pop(rid).output
+        results.append(outs)
+        assert (e.graph_replays > 0) == graphs
+        assert e.sched.free_blocks() == 128
+    assert native.read_status() == 0
+    assert results[0].keys() == results[1].keys()
+    assert all(len(results[0][k]) == len(results[1][k]) for k in results[0])
+    same = sum(results[0][k] == results[1][k] for k in results[0])
+    assert same >= 5, (same, results)
