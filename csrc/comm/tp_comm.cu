@@ -22,6 +22,7 @@
 // replicates the input (tensor_parallel.rs:30-36).
 #include "../kernels/gemm_launch.cuh"
 #include "comm_common.cuh"
+#include "../kernels/gemm_pair_launch.cuh"
 
 namespace rb {
 
@@ -74,7 +75,9 @@ struct GatherHooks {
   long long base_off;   // bytes: first row of the operand inside the gathered buffer
   int rows_per_step;    // 128 (A tile rows) or BK (B rows per K block)
   int total_rows;       // M or K
-  int first_local_step; // tile / K block where this rank's own shard starts (rotation origin)
+  int first_local_step; // K block where this rank's own shard starts (rotation origin of a gathered B)
+  int raster_first;     // row tile (in the kernel's tile height) where this rank's own rows start (gathered A)
+  int raster_group;     // row tiles walked together per column panel
   mutable unsigned long long ready[4];  // chunks already seen ready (<= 256 chunks)
   mutable int remaining;                // remote chunks not yet seen ready by this thread
 
@@ -134,7 +137,7 @@ struct GatherHooks {
   __device__ __forceinline__ void raster(int tile, int num_m, int num_n, int& m_idx,
                                          int& n_idx) const {
     // grouped raster (8 row tiles per group), rotated so this rank's own rows come first
-    const int group_m = 8;
+    const int group_m = raster_group;
     const int group_size = group_m * num_n;
     const int g = tile / group_size;
     const int first_m = g * group_m;
@@ -143,7 +146,7 @@ struct GatherHooks {
     int m = first_m + r % gm;
     n_idx = r / gm;
     if (gather_a) {
-      m += first_local_step;
+      m += raster_first;
       if (m >= num_m) m -= num_m;
     }
     m_idx = m;
@@ -174,16 +177,43 @@ __global__ void __launch_bounds__(512, 1)
                                                    blockIdx.x - n_copy_ctas, gridDim.x - n_copy_ctas);
 }
 
+// The same on the CTA-pair GEMM body (clusters of two CTAs, 256-row tiles, TMA-store epilogue): copy
+// CTAs come in whole clusters, and with the dynamic tile scheduler a copy cluster joins the GEMM once
+// its share is gathered.  Every load of the gathered operand is a plain TMA copy of this GPU's own
+// staging buffer.
+template <typename T, int EPI, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
+    ag_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                        const __grid_constant__ CUtensorMap tma_c, const GemmParams gp, const AgParamsTp ap,
+                        GatherHooks hooks, int n_copy_ctas) {
+  extern __shared__ uint8_t smem_raw[];
+  if ((int)blockIdx.x < n_copy_ctas) {
+    ag_copy_role_tp(ap, blockIdx.x, n_copy_ctas);
+    if (gp.sched == nullptr) return;
+    __syncthreads();
+  }
+  hooks.ready[0] = hooks.ready[1] = hooks.ready[2] = hooks.ready[3] = 0ull;
+  hooks.remaining = (hooks.world - 1) * hooks.chunks_per_shard;
+  if (gp.sched != nullptr)
+    gemm_pair_body<T, 1, EPI, false, B_MN, GatherHooks>(&tma_a, &tma_b, &tma_c, gp, hooks, smem_raw, blockIdx.x / 2,
+                                                         gridDim.x / 2);
+  else
+    gemm_pair_body<T, 1, EPI, false, B_MN, GatherHooks>(&tma_a, &tma_b, &tma_c, gp, hooks, smem_raw,
+                                                         (blockIdx.x - n_copy_ctas) / 2, (gridDim.x - n_copy_ctas) / 2);
+}
+
 // ---------------------------------------------------------------------------------------------
 struct RsHooks {
   PeerTable peers;
   long long tile_flags_off;  // bytes: int[tiles_per_owner][world] on every rank
   int* tile_counters;        // local int[num_m * num_n], monotonically increasing
-  int epoch, num_n, m_tiles_per_rank;
+  int epoch, num_n, m_tiles_per_rank;   // m_tiles_per_rank: 128-row blocks of the output per owner
+  int raster_m_per_rank;                // row tiles of the kernel's tile height per owner
 
   __device__ __forceinline__ bool before_tile_load(int, int, volatile int*, int*) const { return true; }
   __device__ __forceinline__ bool before_k_load(int, int, int, volatile int*, int*) const { return true; }
   __device__ __forceinline__ int map_kb(int kb, int) const { return kb; }
+  // m_idx: 128-row block of the output (both kernels store and count per 128 x 256 block)
   __device__ __forceinline__ void after_tile_store(int m_idx, int n_idx, int quarter) const {
     __threadfence_system();
     const int prev = atomicAdd(tile_counters + m_idx * num_n + n_idx, 1);
@@ -200,12 +230,12 @@ struct RsHooks {
   static constexpr bool kCustomRaster = true;
   __device__ __forceinline__ void raster(int tile, int num_m, int num_n_, int& m_idx,
                                          int& n_idx) const {
-    const int per_owner = m_tiles_per_rank * num_n_;
+    const int per_owner = raster_m_per_rank * num_n_;
     const int k = tile / per_owner;
     const int owner = (peers.rank + 1 + k) % peers.world;  // own tiles last
     const int local = tile - k * per_owner;
     n_idx = local % num_n_;
-    m_idx = owner * m_tiles_per_rank + local / num_n_;
+    m_idx = owner * raster_m_per_rank + local / num_n_;
   }
 };
 
@@ -220,21 +250,24 @@ struct RsReduceParams {
   int* status;
 };
 
+// Run by `nthr` threads of the CTA (tid = 0 .. nthr-1) that meet at named barrier `bar_id`.
 template <typename T>
-__device__ __forceinline__ void rs_reduce_role(const RsReduceParams& p, int cta, int n_ctas) {
+__device__ __forceinline__ void rs_reduce_role(const RsReduceParams& p, int cta, int n_ctas, int tid, int nthr,
+                                               int bar_id) {
   __shared__ int s_ok;
   const PeerTable& pt = p.peers;
   const int tiles = p.m_tiles_per_rank * p.num_n;
   const int rows_per_rank = p.M / pt.world;
+  auto group_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthr) : "memory"); };
   for (int t = cta; t < tiles; t += n_ctas) {
-    if (threadIdx.x == 0) {
+    if (tid == 0) {
       bool ok = true;
       const int* f = peer_ptr<int>(pt, pt.rank, p.tile_flags_off) + t * pt.world;
       for (int r = 0; r < pt.world && ok; ++r)
         ok = wait_flag_sys(f + r, p.epoch, p.status, RB_ERR_TIMEOUT_FLAG);
       s_ok = ok ? 1 : 0;
     }
-    __syncthreads();
+    group_sync();
     if (!s_ok) return;
     const int m_local = (t / p.num_n) * 128;
     const int n0 = (t % p.num_n) * p.BN;
@@ -245,13 +278,13 @@ __device__ __forceinline__ void rs_reduce_role(const RsReduceParams& p, int cta,
     // load takes microseconds, so the bytes in flight per thread set the reducer's bandwidth
     constexpr int kU = 4;
     const int nvec = nrows * vec_per_row;
-    for (int i0 = threadIdx.x; i0 < nvec; i0 += blockDim.x * kU) {
+    for (int i0 = tid; i0 < nvec; i0 += nthr * kU) {
       float acc[kU][8];
       long long goff[kU];
       int cc[kU], rr[kU];
 #pragma unroll
       for (int u = 0; u < kU; ++u) {
-        const int i = i0 + u * blockDim.x;
+        const int i = i0 + u * nthr;
         const int r = i < nvec ? i / vec_per_row : 0;
         rr[u] = r;
         cc[u] = n0 + ((i < nvec ? i : 0) - r * vec_per_row) * 8;
@@ -265,7 +298,7 @@ __device__ __forceinline__ void rs_reduce_role(const RsReduceParams& p, int cta,
         uint4 raw[kU];
 #pragma unroll
         for (int u = 0; u < kU; ++u)
-          raw[u] = (i0 + u * (int)blockDim.x) < nvec ? ld_nc_v4(base + goff[u]) : make_uint4(0, 0, 0, 0);
+          raw[u] = (i0 + u * nthr) < nvec ? ld_nc_v4(base + goff[u]) : make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
           const T* e = reinterpret_cast<const T*>(&raw[u]);
@@ -275,7 +308,7 @@ __device__ __forceinline__ void rs_reduce_role(const RsReduceParams& p, int cta,
       }
 #pragma unroll
       for (int u = 0; u < kU; ++u) {
-        if (i0 + u * (int)blockDim.x >= nvec) break;
+        if (i0 + u * nthr >= nvec) break;
         const int c = cc[u];
         if (p.bias) {
 #pragma unroll
@@ -295,7 +328,7 @@ __device__ __forceinline__ void rs_reduce_role(const RsReduceParams& p, int cta,
         *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.out) + orow * p.N + c) = o;
       }
     }
-    __syncthreads();
+    group_sync();
   }
 }
 
@@ -313,16 +346,32 @@ __global__ void __launch_bounds__(512, 1)
       gemm_cta_body<T, BN, false, B_MN, RsHooks>(&tma_a, &tma_b, gp, hooks, smem_raw, blockIdx.x,
                                                  gridDim.x);
     asm volatile("bar.sync 2, 512;" ::: "memory");
-    rs_reduce_role<T>(rp, blockIdx.x, gridDim.x);
+    rs_reduce_role<T>(rp, blockIdx.x, gridDim.x, threadIdx.x, 512, 0);
     return;
   }
   if ((int)blockIdx.x < n_reduce_ctas) {
-    rs_reduce_role<T>(rp, blockIdx.x, n_reduce_ctas);
+    rs_reduce_role<T>(rp, blockIdx.x, n_reduce_ctas, threadIdx.x, 512, 0);
     return;
   }
   if (threadIdx.x >= kGemmThreads) return;
   gemm_cta_body<T, BN, false, B_MN, RsHooks>(&tma_a, &tma_b, gp, hooks, smem_raw,
                                              blockIdx.x - n_reduce_ctas, gridDim.x - n_reduce_ctas);
+}
+
+// GEMM -> reduce-scatter on the CTA-pair body (unified mode only): every cluster computes 256-row tiles
+// until the scheduler runs dry, tiles owned by the other ranks first; then the two epilogue warpgroups
+// of every CTA (they hold the registers at that point) reduce a share of this rank's own blocks.
+template <typename T, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
+    gemm_rs_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                        const __grid_constant__ CUtensorMap tma_c, const GemmParams gp, const RsHooks hooks,
+                        const RsReduceParams rp) {
+  extern __shared__ uint8_t smem_raw[];
+  gemm_pair_body<T, 1, EPI_LEAN, false, B_MN, RsHooks>(&tma_a, &tma_b, &tma_c, gp, hooks, smem_raw, blockIdx.x / 2,
+                                                        gridDim.x / 2);
+  const int tid = (int)threadIdx.x - G2_EPI_WARP0 * 32;
+  if (tid < 0) return;
+  rs_reduce_role<T>(rp, blockIdx.x, gridDim.x, tid, G2_EPI_WARPS * 32, 5);
 }
 
 static PeerTable make_table_tp(void* const* bases, int world, int rank) {
@@ -367,6 +416,71 @@ int launch_gemm_rs(const GemmArgs& a, const RsHooks& h, const RsReduceParams& rp
   if (gemm_ctas > tiles) gemm_ctas = tiles;
   kern<<<n_red + gemm_ctas, 512, C::SMEM_BYTES, a.stream>>>(ta, tb, a.p, h, rp, n_red);
   e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
+}
+
+// Launch of the pair kernels: clusters of two CTAs, one cluster per SM pair.
+static bool tp_pair_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("RB_TP_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+template <typename T, int EPI, bool B_MN>
+int launch_ag_gemm_pair(GemmArgs& a, const AgParamsTp& ap, const GatherHooks& h, int n_copy) {
+  using C = PairCfg<1>;
+  CUtensorMap ta, tb, tc;
+  int rc = make_pair_operand_maps<T, false, B_MN>(a, &ta, &tb);
+  if (rc) return 1000 + rc;
+  if (a.p.tma_store) {
+    rc = make_pair_output_map(a.p, a.dtype, &tc);
+    if (rc) return 1000 + rc;
+  } else {
+    tc = ta;
+  }
+  auto kern = ag_gemm_pair_kernel<T, EPI, B_MN>;
+  static int resident = 0;
+  if (resident == 0) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return 2000 + (int)e;
+    resident = max_resident_clusters(kern, C::SMEM_BYTES);
+  }
+  n_copy = (n_copy + 1) & ~1;                      // whole clusters
+  int clusters = resident;
+  if (a.p.sched == nullptr) {
+    // static schedule: copy clusters never join, the rest split the tiles
+    const int tiles = ((a.p.M + C::BM - 1) / C::BM) * ((a.p.N + G2_BN - 1) / G2_BN);
+    int gemm_clusters = clusters - n_copy / 2;
+    if (gemm_clusters < 1) gemm_clusters = 1;
+    if (gemm_clusters > tiles) gemm_clusters = tiles;
+    clusters = gemm_clusters + n_copy / 2;
+  }
+  if (clusters * 2 <= n_copy) clusters = n_copy / 2 + 1;
+  kern<<<2 * clusters, G2_THREADS, C::SMEM_BYTES, a.stream>>>(ta, tb, tc, a.p, ap, h, n_copy);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
+}
+
+template <typename T, bool B_MN>
+int launch_gemm_rs_pair(GemmArgs& a, const RsHooks& h, const RsReduceParams& rp) {
+  using C = PairCfg<1>;
+  CUtensorMap ta, tb, tc;
+  int rc = make_pair_operand_maps<T, false, B_MN>(a, &ta, &tb);
+  if (rc) return 1000 + rc;
+  rc = make_pair_output_map(a.p, a.dtype, &tc);
+  if (rc) return 1000 + rc;
+  auto kern = gemm_rs_pair_kernel<T, B_MN>;
+  static int resident = 0;
+  if (resident == 0) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return 2000 + (int)e;
+    resident = max_resident_clusters(kern, C::SMEM_BYTES);
+  }
+  // every resident cluster is launched even when there are fewer tiles: all CTAs take part in the reduction
+  kern<<<2 * resident, G2_THREADS, C::SMEM_BYTES, a.stream>>>(ta, tb, tc, a.p, h, rp);
+  cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 3000 + (int)e;
 }
 
@@ -449,8 +563,30 @@ int rb_ag_gemm(int dtype, void* const* bases, int world, int rank, long long buf
     h.first_local_step = (int)(s >= nsteps ? 0 : s);
   }
   h.ready[0] = h.ready[1] = h.ready[2] = h.ready[3] = 0;
+  h.remaining = 0;
+  h.raster_first = gather_a ? h.first_local_step : 0;
+  h.raster_group = 8;
   int ncopy = n_copy_ctas > 0 ? n_copy_ctas : 16;
   if (world == 1) ncopy = 0;
+  // CTA-pair body: 16-bit operands, at least one 256 x 256 tile, output rows the TMA store can address
+  p.tma_store = al(out) && (ldc * esz) % 16 == 0;
+  if (tp_pair_enabled() && M >= 256 && N >= 256 && (p.tma_store || act != ACT_NONE || aux_out)) {
+    p.group_m = 4;
+    h.raster_group = 4;
+    // rotation origin in 256-row tiles: the first tile that lies completely inside this rank's shard
+    h.raster_first = gather_a ? (h.first_local_step + 1) / 2 : 0;
+    if (h.raster_first >= (M + 255) / 256) h.raster_first = 0;
+    const bool lean = p.tma_store && act == ACT_NONE && !aux_out;
+#define RB_AG_PAIR(T_)                                                                                     \
+  (lean ? (b_mn ? launch_ag_gemm_pair<T_, EPI_LEAN, true>(a, ap, h, ncopy)                                 \
+                : launch_ag_gemm_pair<T_, EPI_LEAN, false>(a, ap, h, ncopy))                               \
+        : (b_mn ? launch_ag_gemm_pair<T_, EPI_FULL, true>(a, ap, h, ncopy)                                 \
+                : launch_ag_gemm_pair<T_, EPI_FULL, false>(a, ap, h, ncopy)))
+    if (dtype == rbh::DT_BF16) return RB_AG_PAIR(__nv_bfloat16);
+    if (dtype == rbh::DT_F16) return RB_AG_PAIR(__half);
+#undef RB_AG_PAIR
+    return 31;
+  }
   const int gemm_ctas = rbh::sm_count() - ncopy;
   if (dtype == rbh::DT_BF16)
     return b_mn ? launch_ag_gemm<__nv_bfloat16, true>(a, ap, h, ncopy, gemm_ctas)
@@ -490,12 +626,23 @@ int rb_gemm_rs(int dtype, void* const* bases, int world, int rank, const void* A
   h.tile_flags_off = tile_flags_off; h.tile_counters = tile_counters; h.epoch = epoch;
   h.num_n = (N + 255) / 256;
   h.m_tiles_per_rank = M / world / 128;
+  h.raster_m_per_rank = h.m_tiles_per_rank;
   RsReduceParams rp;
   rp.peers = h.peers; rp.partial_off = partial_off; rp.tile_flags_off = tile_flags_off;
   rp.out = out; rp.bias = bias; rp.residual = residual; rp.M = M; rp.N = N; rp.BN = 256;
   rp.epoch = epoch; rp.num_n = h.num_n; rp.m_tiles_per_rank = h.m_tiles_per_rank;
   rp.status = p.status;
   int nred = n_reduce_ctas > 0 ? n_reduce_ctas : 0;   // 0: unified mode (see gemm_rs_kernel)
+  if (tp_pair_enabled() && nred == 0 && M % (256 * world) == 0 && N >= 256 && (N * esz) % 16 == 0) {
+    p.tma_store = 1;
+    p.group_m = 4;
+    h.raster_m_per_rank = M / world / 256;
+    if (dtype == rbh::DT_BF16)
+      return b_mn ? launch_gemm_rs_pair<__nv_bfloat16, true>(a, h, rp) : launch_gemm_rs_pair<__nv_bfloat16, false>(a, h, rp);
+    if (dtype == rbh::DT_F16)
+      return b_mn ? launch_gemm_rs_pair<__half, true>(a, h, rp) : launch_gemm_rs_pair<__half, false>(a, h, rp);
+    return 31;
+  }
   const int gemm_ctas = rbh::sm_count() - nred;
   if (dtype == rbh::DT_BF16)
     return b_mn ? launch_gemm_rs<__nv_bfloat16, true>(a, h, rp, nred, gemm_ctas)

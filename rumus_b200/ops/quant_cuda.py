@@ -88,7 +88,7 @@ def _w4_workspace(device, numel: int, tiles: int):
     launches on one stream share them; they only grow.  Launches on different streams may overlap, so
     each stream has its own pair; a kernel that gave up on a wait leaves them dirty, so they are
     dropped when a non-zero status word is read (``native.on_bad_status``)."""
-    key = (device.type, device.index, stream_ptr())
+    key = (device.type, device.index, int(torch.cuda.current_stream(device).cuda_stream))
     ws, cnt = _W4_WS.get(key, (None, None))
     if ws is None or ws.numel() < numel:
         ws = torch.zeros(max(numel, 1 << 22), dtype=torch.float32, device=device)

@@ -21,9 +21,11 @@ def _run(script, nproc, extra_env=None, timeout=600):
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2,
                     reason="needs >= 2 GPUs")
-def test_fused_collective_kernels_match_nccl():
+@pytest.mark.parametrize("tp_pair", ["1", "0"])
+def test_fused_collective_kernels_match_nccl(tp_pair):
+    """``tp_pair``: the tensor-parallel kernels on the CTA-pair GEMM body (default) or on the one-CTA body."""
     n = min(torch.cuda.device_count(), 4)
-    r = _run(os.path.join(ROOT, "tests", "multi_gpu", "fused_checks.py"), n)
+    r = _run(os.path.join(ROOT, "tests", "multi_gpu", "fused_checks.py"), n, {"RB_TP_PAIR": tp_pair})
     assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-4000:]
     assert "ALL FUSED CHECKS PASSED" in r.stdout
 
