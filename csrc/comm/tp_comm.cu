@@ -250,8 +250,9 @@ struct RsReduceParams {
   int* status;
 };
 
-// Run by `nthr` threads of the CTA (tid = 0 .. nthr-1) that meet at named barrier `bar_id`.
-template <typename T>
+// Run by `nthr` threads of the CTA (tid = 0 .. nthr-1) that meet at named barrier `bar_id`; kU 16-byte
+// vectors per thread and source are in flight at a time.
+template <typename T, int kU = 4>
 __device__ __forceinline__ void rs_reduce_role(const RsReduceParams& p, int cta, int n_ctas, int tid, int nthr,
                                                int bar_id) {
   __shared__ int s_ok;
@@ -276,7 +277,6 @@ __device__ __forceinline__ void rs_reduce_role(const RsReduceParams& p, int cta,
     const int nrows = min(128, rows_per_rank - m_local);
     // kU vectors per thread and trip, the kU loads of one source issued back to back: a peer
     // load takes microseconds, so the bytes in flight per thread set the reducer's bandwidth
-    constexpr int kU = 4;
     const int nvec = nrows * vec_per_row;
     for (int i0 = tid; i0 < nvec; i0 += nthr * kU) {
       float acc[kU][8];
@@ -371,7 +371,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
                                                         gridDim.x / 2);
   const int tid = (int)threadIdx.x - G2_EPI_WARP0 * 32;
   if (tid < 0) return;
-  rs_reduce_role<T>(rp, blockIdx.x, gridDim.x, tid, G2_EPI_WARPS * 32, 5);
+  rs_reduce_role<T, 8>(rp, blockIdx.x, gridDim.x, tid, G2_EPI_WARPS * 32, 5);   // 256 threads: twice the vectors each
 }
 
 static PeerTable make_table_tp(void* const* bases, int world, int rank) {
@@ -633,7 +633,14 @@ int rb_gemm_rs(int dtype, void* const* bases, int world, int rank, const void* A
   rp.epoch = epoch; rp.num_n = h.num_n; rp.m_tiles_per_rank = h.m_tiles_per_rank;
   rp.status = p.status;
   int nred = n_reduce_ctas > 0 ? n_reduce_ctas : 0;   // 0: unified mode (see gemm_rs_kernel)
-  if (tp_pair_enabled() && nred == 0 && M % (256 * world) == 0 && N >= 256 && (N * esz) % 16 == 0) {
+  // Measured at 2 ranks on 8192 x 4096 x 5504: 400 us on the pair body against 342 us on the one-CTA body
+  // (long K: the one-CTA main loop is already at rate, and the pair kernel reduces with 256 threads per
+  // CTA instead of 512), so the pair form is opt-in (RB_TP_PAIR_RS=1) until it wins.
+  static const bool rs_pair = [] {
+    const char* e = getenv("RB_TP_PAIR_RS");
+    return e && e[0] == '1';
+  }();
+  if (rs_pair && tp_pair_enabled() && nred == 0 && M % (256 * world) == 0 && N >= 256 && (N * esz) % 16 == 0) {
     p.tma_store = 1;
     p.group_m = 4;
     h.raster_m_per_rank = M / world / 256;
