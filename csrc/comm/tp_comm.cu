@@ -570,7 +570,15 @@ int rb_ag_gemm(int dtype, void* const* bases, int world, int rank, long long buf
   if (world == 1) ncopy = 0;
   // CTA-pair body: 16-bit operands, at least one 256 x 256 tile, output rows the TMA store can address
   p.tma_store = al(out) && (ldc * esz) % 16 == 0;
-  if (tp_pair_enabled() && M >= 256 && N >= 256 && (p.tma_store || act != ACT_NONE || aux_out)) {
+  // Measured on the Llama-7B shapes: at 2 ranks the pair body wins (323 vs 346 us); at 4 ranks its copy
+  // CTAs (384 threads instead of 512) gather more slowly and the GEMM waits for them (261 vs 227 us with 32
+  // copy CTAs), so larger groups stay on the one-CTA body.  RB_TP_PAIR_MAX_WORLD overrides.
+  static const int pair_max_world = [] {
+    const char* e = getenv("RB_TP_PAIR_MAX_WORLD");
+    return e ? atoi(e) : 2;
+  }();
+  if (tp_pair_enabled() && world <= pair_max_world && M >= 256 && N >= 256 &&
+      (p.tma_store || act != ACT_NONE || aux_out)) {
     p.group_m = 4;
     h.raster_group = 4;
     // rotation origin in 256-row tiles: the first tile that lies completely inside this rank's shard

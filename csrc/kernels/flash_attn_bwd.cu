@@ -474,7 +474,8 @@ template <typename T>
 __global__ void fa_bwd_delta_kernel(const T* __restrict__ o, const T* __restrict__ dout,
                                     long long do_sb, long long do_ss, long long do_sh,
                                     const float* __restrict__ lse, float* __restrict__ delta,
-                                    float* __restrict__ lse2, int B, int H, int Sq, int sq_pad) {
+                                    float* __restrict__ lse2, float* __restrict__ dq_zero, int B, int H, int Sq,
+                                    int sq_pad) {
   const long long hw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
   const int l16 = threadIdx.x & 15;
   const long long total = static_cast<long long>(B) * Sq * H;
@@ -486,6 +487,11 @@ __global__ void fa_bwd_delta_kernel(const T* __restrict__ o, const T* __restrict
   const int b = bq / Sq;
   float acc = 0.f;
   if (live) {
+    // this row of the fp32 dQ accumulator starts at zero (the main kernel adds into it with reds)
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4* dz = reinterpret_cast<float4*>(dq_zero + r * 128 + l16 * 8);
+    dz[0] = z;
+    dz[1] = z;
     const uint4 ov = *reinterpret_cast<const uint4*>(o + r * 128 + l16 * 8);
     const uint4 dv = *reinterpret_cast<const uint4*>(dout + b * do_sb + q * do_ss + h * do_sh + l16 * 8);
     const T* oe = reinterpret_cast<const T*>(&ov);
@@ -535,7 +541,7 @@ int launch_fa_bwd(int dtype, const void* q, const void* k, const void* v, const 
     const long long blocks = (rows * 16 + threads - 1) / threads;
     fa_bwd_delta_kernel<T><<<(unsigned)blocks, threads, 0, st>>>(
         (const T*)o, (const T*)dout, dos[0], dos[1], dos[2], lse, stats,
-        stats + static_cast<long long>(p.B) * p.H * p.sq_pad, p.B, p.H, p.Sq, p.sq_pad);
+        stats + static_cast<long long>(p.B) * p.H * p.sq_pad, p.dq_accum, p.B, p.H, p.Sq, p.sq_pad);
   }
   CUtensorMap tq, tk, tv, tdo;
   auto mk = [&](CUtensorMap* m, const void* base, const long long* s, int S, int heads, int rows) {
@@ -562,7 +568,7 @@ int launch_fa_bwd(int dtype, const void* q, const void* k, const void* v, const 
 
 extern "C" {
 // head_dim must be 128.  Strides are {batch, seq, head} in elements.
-// o is [B,Sq,H,128] contiguous; dq_accum is fp32 [B,Sq,H,128] and must be zero on entry;
+// o is [B,Sq,H,128] contiguous; dq_accum is fp32 [B,Sq,H,128] scratch (zeroed by the first kernel);
 // stats is fp32 scratch of 2*B*H*sq_pad elements, sq_pad = Sq rounded up to a multiple of 64,
 // zero on entry (the kernel fills delta and the base-2 log-sum-exp; the padding must stay finite);
 // dk/dv are [B,Sk,Hkv,128] views with element strides dkv_strides = {batch, seq, head}

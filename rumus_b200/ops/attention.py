@@ -55,7 +55,7 @@ def fa_backward(q, k, v, o, lse, dout, causal: bool, scale: float, out=None):
     _, Sk, Hkv, _ = k.shape
     if not _tma_ok(dout):
         dout = dout.contiguous()
-    dq32 = torch.zeros((B, Sq, H, D), dtype=torch.float32, device=q.device)
+    dq32 = torch.empty((B, Sq, H, D), dtype=torch.float32, device=q.device)   # zeroed by the delta kernel
     if out is None:
         dq = torch.empty((B, Sq, H, D), dtype=q.dtype, device=q.device)
         dk = torch.empty((B, Sk, Hkv, D), dtype=q.dtype, device=q.device)

@@ -141,7 +141,9 @@ def _fused_ag_gemm_impl(ctx: TPContext, x_local, w, bias=None, act=None):
     out = torch.empty((M, N), dtype=x_local.dtype, device=x_local.device)
     fused_ops.ag_gemm(a, buf_off=ctx.gather_off, shard_bytes=shard_bytes, chunk_flags=ctx.chunk_flags,
                       chunk_bytes=chunk, epoch=epoch, gather_a=True, operand_off=0, other=w, M=M,
-                      N=N, K=K, out=out, src_flags_off=ctx.enter_flags, bias=bias, act=act)
+                      N=N, K=K, out=out, src_flags_off=ctx.enter_flags, bias=bias, act=act,
+                      # with more ranks the gather is a larger share of the kernel (227 vs 238 us at 4 ranks)
+                      n_copy_ctas=32 if ctx.world >= 4 else 16)
     return out, stage
 
 
@@ -193,7 +195,7 @@ class _ColumnParallelFn(torch.autograd.Function):
         x_full, w = ctx.saved_tensors
         tp = ctx.tp
         dy = dy.contiguous()
-        if tp.mode == "fused" and dy.is_cuda and _fusable(tp, dy.shape[0]):
+        if tp.mode == "fused" and dy.is_cuda and _fusable_rs(tp, dy.shape[0]):
             dx_local = _fused_gemm_rs(tp, dy, w.t())
         else:
             dx_local = tp.reduce_scatter_rows(_mm(dy, w.t()))
@@ -207,7 +209,7 @@ class _ColumnParallelFn(torch.autograd.Function):
 class _RowParallelFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias, tp: TPContext, residual=None):
-        if tp.mode == "fused" and x.is_cuda and _fusable(tp, x.shape[0]):
+        if tp.mode == "fused" and x.is_cuda and _fusable_rs(tp, x.shape[0]):
             y_local = _fused_gemm_rs(tp, x, w, bias, residual.contiguous() if residual is not None else None)
         else:
             y_local = tp.reduce_scatter_rows(_mm(x, w))
@@ -240,6 +242,18 @@ class _RowParallelFn(torch.autograd.Function):
 
 
 _fallback_logged = set()
+
+
+# GEMM -> reduce-scatter cannot overlap its reduction pass with the GEMM (a row block is complete only
+# when every rank has computed its partial, and each rank computes its own blocks last): measured on the
+# Llama-7B layer shapes the fused kernel wins at 2 ranks (342 vs 359 us) and loses at 4 (271 vs 259 us),
+# so above this group size the row-parallel side runs the plain GEMM + NCCL reduce-scatter.
+# RB_TP_FUSE_RS_MAX overrides.
+FUSED_RS_MAX_WORLD = int(__import__("os").environ.get("RB_TP_FUSE_RS_MAX", "2"))
+
+
+def _fusable_rs(tp: TPContext, M: int) -> bool:
+    return tp.world <= FUSED_RS_MAX_WORLD and _fusable(tp, M)
 
 
 def _fusable(tp: TPContext, M: int) -> bool:

@@ -26,7 +26,7 @@ def test_fused_collective_kernels_match_nccl(tp_pair):
     """``tp_pair``: the tensor-parallel kernels on the CTA-pair GEMM body (default) or on the one-CTA body."""
     n = min(torch.cuda.device_count(), 4)
     r = _run(os.path.join(ROOT, "tests", "multi_gpu", "fused_checks.py"), n,
-             {"RB_TP_PAIR": tp_pair, "RB_TP_PAIR_RS": tp_pair})
+             {"RB_TP_PAIR": tp_pair, "RB_TP_PAIR_RS": tp_pair, "RB_TP_PAIR_MAX_WORLD": "8"})
     assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-4000:]
     assert "ALL FUSED CHECKS PASSED" in r.stdout
 
