@@ -24,6 +24,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--mode", default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "torch"])
+    ap.add_argument("--host-scaler", action="store_true",
+                    help="keep the loss scale on the host (one device-to-host read of the overflow flag per step)")
     ap.add_argument("--kernel-profile", action="store_true",
                     help="print a per-kernel breakdown of two extra steps to stderr")
     a = ap.parse_args()
@@ -47,7 +49,8 @@ def main():
     model = ResNet50(device=dev, dtype=torch.float16)
     dp = DataParallel(model, mode=a.mode)
     opt = SGD(model.parameters(), lr=0.1, momentum=0.9)
-    scaler = GradScaler(init_scale=1024.0)
+    # the scale lives on the device: no host read of the overflow flag between steps
+    scaler = GradScaler(init_scale=1024.0, device_side=not a.host_scaler)
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     x = torch.randn(a.batch, 3, 224, 224, device=dev, generator=g).half().contiguous(memory_format=torch.channels_last)
     y = torch.randint(0, 1000, (a.batch,), device=dev, generator=g)

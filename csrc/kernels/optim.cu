@@ -239,9 +239,38 @@ __global__ void scale_check_kernel(T* __restrict__ x, long long n, const float* 
   if (bad && found_inf) *found_inf = 1;
 }
 
+// Loss-scale bookkeeping on the device (no host read of the overflow flag, so the host can keep
+// launching the next step): after an overflow the scale is multiplied by `backoff` and the run of clean
+// steps starts again; every `interval` clean steps it is multiplied by `growth`.
+__global__ void scaler_update_kernel(float* scale, float* inv_scale, int* good_steps, const int* found_inf,
+                                     float growth, float backoff, int interval) {
+  if (blockIdx.x != 0 || threadIdx.x != 0) return;
+  float s = *scale;
+  int g = *good_steps;
+  if (*found_inf != 0) {
+    s *= backoff;
+    g = 0;
+  } else {
+    g += 1;
+    if (interval > 0 && g % interval == 0) s *= growth;
+  }
+  *scale = s;
+  *inv_scale = 1.f / s;
+  *good_steps = g;
+}
+
 }  // namespace rb
 
 extern "C" {
+
+int rb_scaler_update(float* scale, float* inv_scale, int* good_steps, const int* found_inf, float growth,
+                     float backoff, int interval, void* stream) {
+  rb::scaler_update_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(scale, inv_scale, good_steps, found_inf, growth, backoff,
+                                                              interval);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
+}
+
 
 struct RbTensorList {
   int count;

@@ -74,6 +74,7 @@ def _declare(lib) -> None:
     lib.rb_colsum_slabs.argtypes = [LL]
     lib.rb_colsum.argtypes = [I, P, P, P, LL, I, LL, P]
     lib.rb_adam_flat.argtypes = [I, P, P, P, P, P, LL, F, F, F, F, F, F, F, I, P, P, P, P]
+    lib.rb_scaler_update.argtypes = [P, P, P, P, F, F, I, P]
     lib.rb_sumsq_partials.argtypes = [I, P, LL, P, I, P, P]
     lib.rb_norm_finalize.argtypes = [P, I, F, F, P, P, P]
     lib.rb_scale_check.argtypes = [I, P, LL, P, F, P, P]

@@ -14,6 +14,7 @@ from typing import Iterable, List, Optional
 import torch
 
 from ..ops import native
+from ..ops._lib import check, ptr, stream_ptr
 
 
 class Optimizer:
@@ -316,23 +317,46 @@ class GradScaler:
     """
 
     def __init__(self, init_scale: float = 2.0 ** 16, growth_factor: float = 2.0,
-                 backoff_factor: float = 0.5, growth_interval: int = 2000, device=None):
-        self.scale_value = float(init_scale)
+                 backoff_factor: float = 0.5, growth_interval: int = 2000, device=None,
+                 device_side: bool = False):
+        """``device_side``: the scale, its reciprocal and the count of clean steps live on the device and
+        ``update()`` is one tiny kernel that reads the overflow flag there — the host never waits for a
+        step to finish before it launches the next one.  ``update()`` then returns None, and reading
+        ``scale_value`` synchronises."""
+        self._scale_host = float(init_scale)
         self.growth_factor, self.backoff_factor = growth_factor, backoff_factor
         self.growth_interval = growth_interval
         self._good_steps = 0
         self.device = device
+        self.device_side = device_side
         self.inv_scale: Optional[torch.Tensor] = None
         self.found_inf: Optional[torch.Tensor] = None
+        self._scale_dev: Optional[torch.Tensor] = None
+        self._good_dev: Optional[torch.Tensor] = None
+
+    @property
+    def scale_value(self) -> float:
+        if self.device_side and self._scale_dev is not None:
+            return float(self._scale_dev.item())
+        return self._scale_host
+
+    @scale_value.setter
+    def scale_value(self, v: float) -> None:
+        self._scale_host = float(v)
+        if self._scale_dev is not None:
+            self._scale_dev.fill_(float(v))
 
     def _ensure(self, device):
         if self.inv_scale is None:
-            self.inv_scale = torch.full((), 1.0 / self.scale_value, dtype=torch.float32, device=device)
+            self.inv_scale = torch.full((), 1.0 / self._scale_host, dtype=torch.float32, device=device)
             self.found_inf = torch.zeros(1, dtype=torch.int32, device=device)
+            if self.device_side:
+                self._scale_dev = torch.full((), self._scale_host, dtype=torch.float32, device=device)
+                self._good_dev = torch.full((), self._good_steps, dtype=torch.int32, device=device)
 
     def scale(self, loss: torch.Tensor) -> torch.Tensor:
         self._ensure(loss.device)
-        return loss * self.scale_value
+        return loss * (self._scale_dev if self.device_side else self._scale_host)
 
     def unscale_and_check(self, optimizer: Optimizer) -> None:
         params = optimizer._active()
@@ -351,30 +375,55 @@ class GradScaler:
         self._optimizer = optimizer
 
     def update(self) -> bool:
-        """Returns True when the last step overflowed (and was skipped)."""
-        overflow = bool(int(self.found_inf.item())) if self.found_inf is not None else False
+        """Returns True when the last step overflowed (and was skipped); None in device-side mode."""
         opt = getattr(self, "_optimizer", None)
+        if self.device_side and self._scale_dev is not None and not getattr(opt, "_device_skip_pending", False):
+            if self._scale_dev.is_cuda:
+                check(native.lib().rb_scaler_update(ptr(self._scale_dev), ptr(self.inv_scale), ptr(self._good_dev),
+                                                    ptr(self.found_inf), float(self.growth_factor),
+                                                    float(self.backoff_factor), int(self.growth_interval),
+                                                    stream_ptr()), "rb_scaler_update")
+            else:
+                bad = self.found_inf.reshape(()) != 0
+                good = torch.where(bad, torch.zeros_like(self._good_dev), self._good_dev + 1)
+                grow = (~bad) & (good % max(1, self.growth_interval) == 0)
+                s2 = torch.where(bad, self._scale_dev * self.backoff_factor,
+                                 torch.where(grow, self._scale_dev * self.growth_factor, self._scale_dev))
+                self._scale_dev.copy_(s2)
+                self._good_dev.copy_(good)
+                self.inv_scale.copy_(1.0 / s2)
+            return None
+        overflow = bool(int(self.found_inf.item())) if self.found_inf is not None else False
         if opt is not None and getattr(opt, "_device_skip_pending", False):
             # the device-side step counted itself before the flag was known: a skipped step must not
             # advance the bias-correction exponent (the CPU path never counts it)
             if overflow:
                 opt.step_count -= 1
             opt._device_skip_pending = False
+        if self.device_side and self._scale_dev is not None:      # an optimizer that needs the flag on the host
+            self._scale_host = float(self._scale_dev.item())
+            self._good_steps = int(self._good_dev.item())
         if overflow:
-            self.scale_value *= self.backoff_factor
+            self._scale_host *= self.backoff_factor
             self._good_steps = 0
         else:
             self._good_steps += 1
             if self._good_steps % self.growth_interval == 0:
-                self.scale_value *= self.growth_factor
+                self._scale_host *= self.growth_factor
+        if self._scale_dev is not None:
+            self._scale_dev.fill_(self._scale_host)
+            self._good_dev.fill_(self._good_steps)
         if self.inv_scale is not None:
-            self.inv_scale.fill_(1.0 / self.scale_value)
+            self.inv_scale.fill_(1.0 / self._scale_host)
         return overflow
 
     def state_dict(self):
-        return {"scale": self.scale_value, "good_steps": self._good_steps}
+        good = int(self._good_dev.item()) if (self.device_side and self._good_dev is not None) else self._good_steps
+        return {"scale": self.scale_value, "good_steps": good}
 
     def load_state_dict(self, sd):
         self.scale_value, self._good_steps = sd["scale"], sd["good_steps"]
+        if self._good_dev is not None:
+            self._good_dev.fill_(self._good_steps)
         if self.inv_scale is not None:
-            self.inv_scale.fill_(1.0 / self.scale_value)
+            self.inv_scale.fill_(1.0 / self._scale_host)

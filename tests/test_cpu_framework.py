@@ -251,6 +251,20 @@ def test_clip_and_schedulers_and_scaler():
         q.grad = torch.full((3,), 4.0)      # scaled by 4 -> true grad 1
         sc.unscale_and_check(opt); opt.step(); assert sc.update() is False
     assert sc.scale_value == 8.0 and torch.allclose(q.data, torch.full((3,), -1.0))
+    # the same sequence with the scale kept next to the gradients (no host read of the flag in update())
+    q2 = nn.Parameter(torch.ones(3))
+    opt2 = SGD([q2], lr=1.0)
+    sd = GradScaler(init_scale=8.0, growth_interval=2, device_side=True)
+    q2.grad = torch.tensor([float("inf"), 1., 1.])
+    sd._ensure(q2.device); sd.unscale_and_check(opt2); opt2.step()
+    assert sd.update() is None and sd.scale_value == 4.0 and torch.equal(q2.data, torch.ones(3))
+    assert float(sd.inv_scale) == 0.25
+    for _ in range(2):
+        q2.grad = torch.full((3,), 4.0)
+        sd.unscale_and_check(opt2); opt2.step(); sd.update()
+    assert sd.scale_value == 8.0 and torch.allclose(q2.data, torch.full((3,), -1.0))
+    assert sd.state_dict() == {"scale": 8.0, "good_steps": 2}
+    assert float((torch.ones(()) * 1.0 * sd._scale_dev)) == float(sd.scale(torch.ones(())))
 
 
 def test_int4_and_q8_formats():

@@ -87,3 +87,21 @@ def test_bounded_wait_times_out_and_context_survives():
     assert torch.allclose(native.gemm(torch.ones(128, 64, device="cuda").bfloat16(),
                                       torch.ones(64, 128, device="cuda").bfloat16(), path=1).float(),
                           torch.full((128, 128), 64.0, device="cuda"))
+
+
+def test_grad_scaler_device_side_update_kernel():
+    """The loss-scale update kernel: halve after an overflow, double after `growth_interval` clean steps,
+    reciprocal kept in step — all without a host read of the flag."""
+    import torch
+    from rumus_b200.optim import GradScaler
+    sc = GradScaler(init_scale=64.0, growth_interval=3, device_side=True)
+    sc._ensure(torch.device("cuda"))
+    seen = []
+    for bad in (1, 0, 0, 0, 0, 1, 0):
+        sc.found_inf.fill_(bad)
+        assert sc.update() is None
+        seen.append((sc.scale_value, float(sc.inv_scale), int(sc._good_dev)))
+    assert [s for s, _, _ in seen] == [32.0, 32.0, 32.0, 64.0, 64.0, 32.0, 32.0]
+    assert all(abs(i * s - 1.0) < 1e-6 for s, i, _ in seen)
+    assert [g for _, _, g in seen] == [0, 1, 2, 3, 4, 0, 1]
+    assert float(sc.scale(torch.ones((), device="cuda"))) == 32.0
