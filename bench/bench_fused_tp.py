@@ -102,6 +102,20 @@ def main():
                               tile_counters=tcount, epoch=ep2[0], out=out2, n_reduce_ctas=nred)
         res.append((f"gemm_rs fused reduce_ctas={nred}", timed(fused2), flops2))
 
+    # push form: the epilogue stores every tile into the owner's slot for this rank, a local pass sums the slots
+    slot_sets = [part_off, arena.alloc_bytes(M * d * 2)[1]]
+    pflags = arena.alloc_flags(world)
+    pcount = arena.alloc_local_ints(world)
+    torch.cuda.synchronize()
+    arena.barrier()
+    ep4 = [0]
+
+    def fused_push():
+        ep4[0] += 1
+        fused_ops.gemm_rs_push(arena, a2, w2, slots_off=slot_sets[ep4[0] & 1], done_flags_off=pflags,
+                               owner_counters=pcount, epoch=ep4[0], out=out2)
+    res.append(("gemm_rs fused, pushed from the epilogue", timed(fused_push), flops2))
+
     def nccl2():
         native.gemm(a2, w2, out=full2)
         dist.reduce_scatter_tensor(out2, full2)

@@ -374,6 +374,127 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
   rs_reduce_role<T, 8>(rp, blockIdx.x, gridDim.x, tid, G2_EPI_WARPS * 32, 5);   // 256 threads: twice the vectors each
 }
 
+// ---------------------------------------------------------------------------------------------
+// GEMM -> reduce-scatter, push form.  The epilogue of a tile stores it, rounded to T, straight into the
+// OWNER's memory: every rank has one slot [M/W, N] per source rank, so the stores of different ranks never
+// meet and need no atomics (adding into one shared sum with reds — fp32 or packed 16-bit — made the kernel
+// atomic-bound: 585-618 us against 342 us for the pull form at 2 ranks, remote reds ran at ~100 GB/s).
+// The transfers ride under the main loop as posted writes; what is left at the end is a LOCAL pass
+//   out[M/W, N] = T(sum over sources of slot[src] + bias + residual).
+// Two slot sets alternate from call to call: a rank can reach its next-but-one call only after every
+// peer signalled the call in between, which a peer does after the pass that read this call's slots.
+struct RsPushHooks {
+  PeerTable peers;
+  long long slots_off;       // bytes: this call's slot set [W][M/W, N] of T (same offset on every rank)
+  long long done_flags_off;  // bytes: int[world] on every rank: flag[r] = epoch once rank r stored all it has
+  int* owner_counters;       // local int[world], zero between calls
+  int epoch, num_n, m_tiles_per_rank, N;
+  uint8_t* stage;            // shared memory: 4 KB per epilogue warp (set by the kernel)
+
+  __device__ __forceinline__ bool before_tile_load(int, int, volatile int*, int*) const { return true; }
+  __device__ __forceinline__ bool before_k_load(int, int, int, volatile int*, int*) const { return true; }
+  __device__ __forceinline__ int map_kb(int kb, int) const { return kb; }
+  __device__ __forceinline__ uint8_t* push_stage(int epi_warp) const { return stage + epi_warp * 4096; }
+  __device__ __forceinline__ void* push_base(int m_idx) const {
+    const int owner = m_idx / m_tiles_per_rank;
+    const int blk = m_idx - owner * m_tiles_per_rank;
+    const long long row0 = static_cast<long long>(peers.rank) * m_tiles_per_rank * 128 + static_cast<long long>(blk) * 128;
+    return peer_ptr<char>(peers, owner, slots_off) + row0 * N * 2;
+  }
+  // one lane per epilogue warp, after the warp's stores of this tile: the last arrival of all tiles this
+  // rank computes for `owner` tells the owner that this rank's slot is complete
+  __device__ __forceinline__ void after_tile_store(int m_idx, int, int) const {
+    __threadfence_system();
+    const int owner = m_idx / m_tiles_per_rank;
+    const int total = m_tiles_per_rank * num_n * kGemmEpiWarps;
+    const int prev = atomicAdd(owner_counters + owner, 1);
+    if (prev == total - 1) {
+      owner_counters[owner] = 0;     // last arrival of this call: the next call (any shape) starts from zero
+      __threadfence_system();
+      st_release_sys(peer_ptr<int>(peers, owner, done_flags_off) + peers.rank, epoch);
+    }
+  }
+  static constexpr bool kCustomLoadA = false, kCustomLoadB = false, kCustomRows = false;
+  static constexpr bool kNeedsStoreComplete = false;
+  static constexpr bool kCustomRaster = true;
+  static constexpr bool kPushOut = true;
+  __device__ __forceinline__ void raster(int tile, int num_m, int num_n_, int& m_idx, int& n_idx) const {
+    const int per_owner = m_tiles_per_rank * num_n_;
+    const int k = tile / per_owner;
+    const int owner = (peers.rank + 1 + k) % peers.world;  // other ranks' tiles first: their stores travel
+    const int local = tile - k * per_owner;                // while this rank still computes its own
+    n_idx = local % num_n_;
+    m_idx = owner * m_tiles_per_rank + local / num_n_;
+  }
+};
+
+struct RsPushFinalParams {
+  PeerTable peers;
+  long long slots_off, done_flags_off;
+  void* out;              // [M/W, N] of T
+  const void* bias;       // [N] or null
+  const void* residual;   // [M/W, N] or null
+  long long numel;        // M/W * N
+  int N, epoch;
+  int* status;
+};
+
+template <typename T>
+__device__ __forceinline__ void rs_push_final_role(const RsPushFinalParams& p, int cta, int n_ctas) {
+  __shared__ int s_ok;
+  const PeerTable& pt = p.peers;
+  if (threadIdx.x == 0) {
+    bool ok = true;
+    const int* f = peer_ptr<int>(pt, pt.rank, p.done_flags_off);
+    for (int r = 0; r < pt.world && ok; ++r) ok = wait_flag_sys(f + r, p.epoch, p.status, RB_ERR_TIMEOUT_FLAG);
+    s_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const uint4* slots = peer_ptr<uint4>(pt, pt.rank, p.slots_off);
+  const T* bias = reinterpret_cast<const T*>(p.bias);
+  const uint4* res = reinterpret_cast<const uint4*>(p.residual);
+  uint4* out = reinterpret_cast<uint4*>(p.out);
+  const long long nvec = p.numel / 8;
+  const long long stride = static_cast<long long>(n_ctas) * blockDim.x;
+  auto add8 = [](float* v, const uint4& q) {
+    const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] += to_f32<T>(e[j]);
+  };
+  for (long long i = static_cast<long long>(cta) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    // the peers' stores arrived in this GPU's L2 over NVLink: read the slots there
+    uint4 q[kMaxRanks];
+#pragma unroll
+    for (int k = 0; k < kMaxRanks; ++k)
+      if (k < pt.world) q[k] = __ldcg(slots + static_cast<long long>(k) * nvec + i);
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int k = 0; k < kMaxRanks; ++k)
+      if (k < pt.world) add8(v, q[k]);
+    if (bias) add8(v, *reinterpret_cast<const uint4*>(bias + static_cast<int>((i * 8) % p.N)));
+    if (res) add8(v, res[i]);
+    uint4 o;
+    T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) oe[j] = from_f32<T>(v[j]);
+    out[i] = o;
+  }
+}
+
+template <typename T, int BN, bool B_MN>
+__global__ void __launch_bounds__(512, 1)
+    gemm_rs_push_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                        const GemmParams gp, const RsPushHooks hooks_in, const RsPushFinalParams fp) {
+  extern __shared__ uint8_t smem_raw[];
+  RsPushHooks hooks = hooks_in;
+  hooks.stage = smem_raw + GemmCfg<T, BN>::SMEM_BYTES;       // behind the GEMM body's own shared memory
+  if (threadIdx.x < kGemmThreads)
+    gemm_cta_body<T, BN, false, B_MN, RsPushHooks>(&tma_a, &tma_b, gp, hooks, smem_raw, blockIdx.x, gridDim.x);
+  asm volatile("bar.sync 2, 512;" ::: "memory");
+  rs_push_final_role<T>(fp, blockIdx.x, gridDim.x);
+}
+
 static PeerTable make_table_tp(void* const* bases, int world, int rank) {
   PeerTable t;
   for (int i = 0; i < kMaxRanks; ++i) t.base[i] = i < world ? bases[i] : nullptr;
@@ -415,6 +536,23 @@ int launch_gemm_rs(const GemmArgs& a, const RsHooks& h, const RsReduceParams& rp
   const int tiles = ((a.p.M + 127) / 128) * ((a.p.N + BN - 1) / BN);
   if (gemm_ctas > tiles) gemm_ctas = tiles;
   kern<<<n_red + gemm_ctas, 512, C::SMEM_BYTES, a.stream>>>(ta, tb, a.p, h, rp, n_red);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 3000 + (int)e;
+}
+
+template <typename T, bool B_MN>
+int launch_gemm_rs_push(const GemmArgs& a, const RsPushHooks& h, const RsPushFinalParams& fp) {
+  constexpr int BN = 256;
+  using C = GemmCfg<T, BN>;
+  CUtensorMap ta, tb;
+  int rc = make_gemm_tensor_maps<T, BN>(a, &ta, &tb);
+  if (rc) return 1000 + rc;
+  auto kern = gemm_rs_push_kernel<T, BN, B_MN>;
+  constexpr int smem = C::SMEM_BYTES + kGemmEpiWarps * 4096;   // + the epilogue warps' staging blocks
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return 2000 + (int)e;
+  // every SM takes part in the final pass, whatever the number of tiles
+  kern<<<rbh::sm_count(), 512, smem, a.stream>>>(ta, tb, a.p, h, fp);
   e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 3000 + (int)e;
 }
@@ -665,6 +803,42 @@ int rb_gemm_rs(int dtype, void* const* bases, int world, int rank, const void* A
   if (dtype == rbh::DT_F16)
     return b_mn ? launch_gemm_rs<__half, true>(a, h, rp, nred, gemm_ctas)
                 : launch_gemm_rs<__half, false>(a, h, rp, nred, gemm_ctas);
+  return 31;
+}
+
+// Row-parallel linear, push form: out[M/W, N] = T(sum_r A_r[M, K_r] . B_r[K_r, N] + bias + residual).
+// slots_off: [W][M/W, N] slot set of the compute dtype in the arena (the caller alternates between two
+// sets); done_flags_off: int[W] in the arena; owner_counters: local int[W], zero between calls.
+int rb_gemm_rs_push(int dtype, void* const* bases, int world, int rank, const void* A, long long lda,
+                    const void* B, long long ldb, int b_mn, int M, int N, int K, long long slots_off,
+                    long long done_flags_off, int* owner_counters, int epoch, void* out, const void* bias,
+                    const void* residual, void* stream) {
+  using namespace rb;
+  if (world > kMaxRanks) return 30;
+  if (M % (128 * world) != 0 || N % 8 != 0 || slots_off % 16 != 0) return 34;
+  const int esz = 2;
+  GemmArgs a{};
+  a.dtype = dtype; a.a_mn = 0; a.b_mn = b_mn; a.A = A; a.lda = lda; a.B = B; a.ldb = ldb;
+  a.max_ctas = 0;
+  a.stream = (cudaStream_t)stream;
+  GemmParams& p = a.p;
+  p = GemmParams{};
+  p.M = M; p.N = N; p.K = K; p.out = nullptr; p.ldc = N; p.alpha = 1.f; p.vec_ok = 1; p.group_m = 8;
+  p.status = rbh::device_status_word();
+  p.sched = rbh::dynamic_tiles() ? rbh::next_sched_slot() : nullptr;
+  auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (!al(A) || !al(B) || !al(out) || !al(bias) || !al(residual) || (lda * esz) % 16 || (ldb * esz) % 16) return 10;
+  RsPushHooks h;
+  h.peers = make_table_tp(bases, world, rank);
+  h.slots_off = slots_off; h.done_flags_off = done_flags_off; h.owner_counters = owner_counters; h.epoch = epoch;
+  h.num_n = (N + 255) / 256; h.m_tiles_per_rank = M / world / 128; h.N = N; h.stage = nullptr;
+  RsPushFinalParams fp;
+  fp.peers = h.peers; fp.slots_off = slots_off; fp.done_flags_off = done_flags_off; fp.out = out; fp.bias = bias;
+  fp.residual = residual; fp.numel = (long long)(M / world) * N; fp.N = N; fp.epoch = epoch; fp.status = p.status;
+  if (dtype == rbh::DT_BF16)
+    return b_mn ? launch_gemm_rs_push<__nv_bfloat16, true>(a, h, fp) : launch_gemm_rs_push<__nv_bfloat16, false>(a, h, fp);
+  if (dtype == rbh::DT_F16)
+    return b_mn ? launch_gemm_rs_push<__half, true>(a, h, fp) : launch_gemm_rs_push<__half, false>(a, h, fp);
   return 31;
 }
 }

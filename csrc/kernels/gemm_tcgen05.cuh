@@ -86,6 +86,19 @@ struct NoHooks {
                                          int& n_idx) const {}
 };
 
+// A hook type that defines `static constexpr bool kPushOut = true`, `void* push_base(int m_idx)` and
+// `uint8_t* push_stage(int epilogue_warp)` (4 KB of shared memory per epilogue warp) makes the epilogue
+// store each tile, rounded to T, at push_base(m_idx)[row_in_tile * N + col] instead of into `out`; the
+// destination may be another GPU's memory, so the rows are written as whole 128-byte segments.
+template <typename H, typename = void>
+struct hook_push_out {
+  static constexpr bool value = false;
+};
+template <typename H>
+struct hook_push_out<H, decltype((void)H::kPushOut)> {
+  static constexpr bool value = H::kPushOut;
+};
+
 template <typename T, int BN>
 struct GemmCfg {
   static constexpr int BM = 128;
@@ -504,6 +517,46 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
         row_ok = row >= 0;
       }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      if constexpr (hook_push_out<Hooks>::value && sizeof(T) == 2) {
+        // Push mode: the tile goes to push_base(m_idx), which may be another GPU's memory, where 16-byte
+        // pieces scattered over 32 rows travel badly.  Two 32-column chunks at a time are rounded to T,
+        // laid down in this warp's 32 x 128-byte staging block (16-byte pieces XOR-swizzled by row) and
+        // written out as whole 128-byte row segments: 8 lanes per row, 4 rows per instruction.
+        uint8_t* stg = hooks.push_stage((warp_idx - 2));
+        T* base = reinterpret_cast<T*>(hooks.push_base(m_idx)) + static_cast<long long>(quarter * 32) * p.N;
+        const int rows_ok = static_cast<int>(min(32ll, static_cast<long long>(p.M) - (static_cast<long long>(m_idx) * BM + quarter * 32)));
+#pragma unroll 1
+        for (int ci = 0; ci < CHUNKS_PER_HALF; ci += 2) {
+          const int c = half * CHUNKS_PER_HALF + ci;
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, r0);
+          tmem_ld_32x32b_x32(taddr + c * 32 + 32, r1);
+          tmem_ld_wait();
+          const int col0 = n_idx * BN + c * 32;
+          const int valid = min(64, p.N - col0);          // columns of this 64-wide piece that exist
+          uint8_t* myrow = stg + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t* src = j < 4 ? r0 + j * 8 : r1 + (j - 4) * 8;
+            uint4 q;
+            q.x = pack2<T>(__uint_as_float(src[0]) * p.alpha, __uint_as_float(src[1]) * p.alpha);
+            q.y = pack2<T>(__uint_as_float(src[2]) * p.alpha, __uint_as_float(src[3]) * p.alpha);
+            q.z = pack2<T>(__uint_as_float(src[4]) * p.alpha, __uint_as_float(src[5]) * p.alpha);
+            q.w = pack2<T>(__uint_as_float(src[6]) * p.alpha, __uint_as_float(src[7]) * p.alpha);
+            *reinterpret_cast<uint4*>(myrow + ((j ^ (lane & 7)) << 4)) = q;
+          }
+          __syncwarp();
+          const int jj = lane & 7;
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + (lane >> 3);
+            const uint4 q = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((jj ^ (rr & 7)) << 4));
+            if (rr < rows_ok && jj * 8 < valid)
+              *reinterpret_cast<uint4*>(base + static_cast<long long>(rr) * p.N + col0 + jj * 8) = q;
+          }
+          __syncwarp();
+        }
+      } else {
 #pragma unroll 1
       for (int ci = 0; ci < CHUNKS_PER_HALF; ++ci) {
         const int c = half * CHUNKS_PER_HALF + ci;
@@ -520,6 +573,7 @@ __device__ __forceinline__ void gemm_cta_body(const CUtensorMap* tma_a, const CU
           else
             epilogue_chunk<T, T>(p, r, row, col, ncols_valid);
         }
+      }
       }
       tc_fence_before();
       __syncwarp();

@@ -19,6 +19,7 @@ native.register_signature("rb_all_gather", [P, I, I, LL, LL, LL, P, LL, I, I, P]
 native.register_signature("rb_shard_gather", [P, I, I, LL, P, LL, LL, I, I, P])
 native.register_signature("rb_allreduce_unscale", [I, P, P, I, I, LL, LL, LL, LL, LL, I, P, F, P, P,
                                                    I, I, P])
+native.register_signature("rb_gemm_rs_push", [I, P, I, I, P, LL, P, LL, I, I, I, I, LL, LL, P, I, P, P, P, P])
 native.register_signature("rb_oneshot_allreduce", [I, P, P, I, I, LL, LL, I, LL, P, P, I, I, P, P])
 native.register_signature("rb_ag_gemm", [I, P, I, I, LL, LL, LL, P, LL, I, I, LL, P, LL, I, I, I, I,
                                          P, LL, P, P, LL, I, P, I, P])
@@ -133,6 +134,30 @@ def gemm_rs(arena: SymmArena, a: torch.Tensor, b: torch.Tensor, *, partial_off: 
                       tile_flags_off, ptr(tile_counters), epoch, ptr(out), ptr(bias), ptr(residual),
                       n_reduce_ctas, stream_ptr())
     check(rc, "rb_gemm_rs")
+    count_launch()
+    return out
+
+
+def gemm_rs_push(arena: SymmArena, a: torch.Tensor, b: torch.Tensor, *, slots_off: int, done_flags_off: int,
+                 owner_counters: torch.Tensor, epoch: int, out: torch.Tensor, bias=None, residual=None):
+    """GEMM -> reduce-scatter with the transfer pushed from the GEMM's epilogue: every tile is stored,
+    in the compute dtype, into the OWNER rank's slot for this source rank (plain stores over NVLink, no
+    atomics: slots of different sources are disjoint), and each rank ends with a local pass
+    ``out = sum of its slots + bias + residual``.  ``out [M/W, N]``; ``slots_off`` is the arena offset of a
+    ``[W][M/W, N]`` slot set and the caller alternates between two sets (``csrc/comm/tp_comm.cu``)."""
+    L = native.lib()
+    M, K = a.shape
+    _, N = b.shape
+    assert a.stride(1) == 1 and out.is_contiguous()
+    bt, ldb = native._mat_major(b)
+    assert bt is not None
+    if residual is not None:
+        assert residual.is_contiguous() and residual.shape == out.shape
+    rc = L.rb_gemm_rs_push(native.dtype_code(a.dtype), arena.bases(), arena.world, arena.rank, ptr(a),
+                           a.stride(0) if M > 1 else K, ptr(b), ldb, 0 if bt else 1, M, N, K, slots_off,
+                           done_flags_off, ptr(owner_counters), epoch, ptr(out), ptr(bias), ptr(residual),
+                           stream_ptr())
+    check(rc, "rb_gemm_rs_push")
     count_launch()
     return out
 

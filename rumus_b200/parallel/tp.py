@@ -52,8 +52,10 @@ class TPContext:
             from .symm import SymmArena
             esz = torch.empty((), dtype=dtype).element_size()
             stage_bytes = max_tokens * max_features * esz
+            # slot sets of the push-form reduce-scatter: two of [world][max_tokens / world, max_features]
+            push_bytes = stage_bytes
             if self.arena is None:
-                self.arena = SymmArena(2 * stage_bytes + (64 << 20), group)
+                self.arena = SymmArena(2 * stage_bytes + push_bytes + (64 << 20), group)
             a = self.arena
             self.gather_buf, self.gather_off = a.alloc_bytes(stage_bytes)
             self.partial_buf, self.partial_off = a.alloc_bytes(stage_bytes)
@@ -65,6 +67,18 @@ class TPContext:
             self.bar_flags = a.alloc_flags(self.world)
             self.bar_epoch = 0
             self.stage_bytes = stage_bytes
+            self.push_acc = None
+            if os.environ.get("RB_TP_PUSH", "1") == "1" and push_bytes > 0:
+                try:
+                    # the pull form's partial-sum buffer doubles as the first slot set
+                    self.push_acc = [self.partial_off, a.alloc_bytes(push_bytes)[1]]
+                    self.push_bytes = push_bytes
+                    self.push_flags = a.alloc_flags(self.world)
+                    self.push_counters = a.alloc_local_ints(self.world)
+                    self.push_epoch = 0
+                except Exception:       # an arena handed in from outside may have no room: keep the pull form
+                    self.push_acc = None
+            torch.cuda.synchronize()
             a.barrier()
         self._last_fused = None
 
@@ -166,6 +180,14 @@ def _fused_gemm_rs_impl(ctx: TPContext, a_mat, w, bias=None, residual=None):
     N = w.shape[1]
     out = torch.empty((M // ctx.world, N), dtype=a_mat.dtype, device=a_mat.device)
     ctx.order_fused("R")
+    if ctx.push_acc is not None and M * N * a_mat.element_size() <= ctx.push_bytes and N % 8 == 0:
+        # tiles stored from the GEMM's epilogue into the owners' per-source slots
+        ctx.push_epoch += 1
+        fused_ops.gemm_rs_push(ctx.arena, a_mat, w, slots_off=ctx.push_acc[ctx.push_epoch & 1],
+                               done_flags_off=ctx.push_flags, owner_counters=ctx.push_counters,
+                               epoch=ctx.push_epoch, out=out, bias=bias,
+                               residual=residual.contiguous() if residual is not None else None)
+        return out
     epoch = ctx.next_epoch()
     fused_ops.gemm_rs(ctx.arena, a_mat, w, partial_off=ctx.partial_off,
                       tile_flags_off=ctx.tile_flags_off, tile_counters=ctx.tile_counters, epoch=epoch,
@@ -253,6 +275,9 @@ FUSED_RS_MAX_WORLD = int(__import__("os").environ.get("RB_TP_FUSE_RS_MAX", "2"))
 
 
 def _fusable_rs(tp: TPContext, M: int) -> bool:
+    # the push form has no second pass over the partial sums, so it is not limited to small groups
+    if getattr(tp, "push_acc", None) is not None:
+        return _fusable(tp, M)
     return tp.world <= FUSED_RS_MAX_WORLD and _fusable(tp, M)
 
 

@@ -183,6 +183,31 @@ def fsdp_reshard_programs(world: int, steps: int, wait_param_flags: bool = True,
     return progs
 
 
+def rs_push_programs(world: int, steps: int, alternate: bool = True) -> List[List[Action]]:
+    """GEMM -> reduce-scatter in its push form (``gemm_rs_push_kernel``): per call every rank adds its
+    tiles into each owner's sum buffer (modelled as one sub-buffer per contributing rank), tells the
+    owner it is done, and the owner — once everybody said so — reads the sums and puts the buffer back
+    to zero.  No barrier follows.  With two buffers used in turn a peer can only reach the next use of a
+    buffer after the owner's pass over it (it needs the owner's flag of the call in between, which the
+    owner sends after that pass, in program order); with a single buffer (``alternate=False``) a fast
+    peer adds the next call's tiles into sums the owner is still reading."""
+    progs: List[List[Action]] = []
+    for r in range(world):
+        p: List[Action] = []
+        for t in range(1, steps + 1):
+            b = (t & 1) if alternate else 0
+            for o in range(world):                                   # epilogue: add my tiles of owner o
+                p.append(("write", f"sum{o}.{b}.from{r}", t))
+                p.append(("set", f"done[{o}][{r}]", t))
+            for q in range(world):                                   # final pass of my own sums
+                p.append(("wait", f"done[{r}][{q}]", t))
+            for q in range(world):
+                p.append(("begin_read", f"sum{r}.{b}.from{q}", t))
+                p.append(("end_read", f"sum{r}.{b}.from{q}"))
+        progs.append(p)
+    return progs
+
+
 def tp_sequence_programs(world: int, ops: str) -> List[List[Action]]:
     """A sequence of fused tensor-parallel operations on one ``TPContext`` (``parallel/tp.py``,
     ``csrc/comm/tp_comm.cu``).  ``ops`` is a string over

@@ -191,6 +191,26 @@ def main():
     check("gemm_rs + residual", rel(outr, ref_local + resr.float()), 1.5e-2)
     arena.barrier()
 
+    # ---------------- gemm_rs, push form: four calls in a row over the two alternating slot sets, no barrier
+    # between them (no rank may run ahead into slots a peer is still reading)
+    slot_sets = [arena.alloc_bytes(Mr * Nr * 2)[1] for _ in range(2)]
+    pflags = arena.alloc_flags(world)
+    pcount = arena.alloc_local_ints(world)
+    torch.cuda.synchronize()
+    arena.barrier()
+    outs_p = []
+    for epoch in range(1, 5):
+        outp = torch.empty(Mr // world, Nr, device=dev, dtype=torch.bfloat16)
+        fused_ops.gemm_rs_push(arena, ar, br, slots_off=slot_sets[epoch & 1], done_flags_off=pflags,
+                               owner_counters=pcount, epoch=epoch, out=outp, bias=biasr,
+                               residual=resr if epoch % 2 == 0 else None)
+        outs_p.append(outp)
+    torch.cuda.synchronize()
+    for epoch, outp in enumerate(outs_p, start=1):
+        want_p = ref_local + (resr.float() if epoch % 2 == 0 else 0)
+        check(f"gemm_rs_push call {epoch}", rel(outp, want_p), 1.5e-2)
+    arena.barrier()
+
     # ---------------- one-shot all-reduce of decode-sized partial sums (+ residual), two buffers in turn
     T, d = 48, 4096
     bufs = [arena.alloc(128 * d, torch.bfloat16)[0] for _ in range(2)]

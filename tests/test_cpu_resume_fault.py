@@ -166,6 +166,12 @@ def test_flag_protocols_hold_on_every_interleaving():
         explore(fsdp_reshard_programs(2, 2, wait_grad_flags=False))
     # fused tensor-parallel operations on one context: gather (A) and reduce (R) operations may follow
     # each other without a barrier only when they alternate; the context inserts one (b) otherwise
+    # push-form reduce-scatter: two sum buffers in turn are enough, one is not
+    from rumus_b200.utils.protocol_check import rs_push_programs
+    assert explore(rs_push_programs(2, 4)) > 100
+    assert explore(rs_push_programs(3, 3)) > 1000
+    with pytest.raises(ProtocolViolation):
+        explore(rs_push_programs(2, 3, alternate=False))
     assert explore(tp_sequence_programs(2, "ARARAR")) > 100
     assert explore(tp_sequence_programs(3, "RARA")) > 1000
     assert explore(tp_sequence_programs(3, "AbARbR")) > 1000
