@@ -150,7 +150,9 @@ def _fused_ag_gemm_impl(ctx: TPContext, x_local, w, bias=None, act=None):
     stage[ctx.rank * Ml:(ctx.rank + 1) * Ml].copy_(x_local)
     epoch = ctx.next_epoch()
     _announce(ctx, epoch)
-    chunk = max(1 << 20, (shard_bytes * ctx.world + 255) // 256)
+    # chunk = the unit in which GEMM tiles learn that gathered rows have arrived: 256 KB measured best at 4
+    # ranks (227 us against 287 us with 1 MB chunks), no difference at 2
+    chunk = max(256 << 10, (shard_bytes * ctx.world + 255) // 256)
     chunk = (chunk + 15) // 16 * 16
     out = torch.empty((M, N), dtype=x_local.dtype, device=x_local.device)
     fused_ops.ag_gemm(a, buf_off=ctx.gather_off, shard_bytes=shard_bytes, chunk_flags=ctx.chunk_flags,
@@ -266,11 +268,11 @@ class _RowParallelFn(torch.autograd.Function):
 _fallback_logged = set()
 
 
-# GEMM -> reduce-scatter cannot overlap its reduction pass with the GEMM (a row block is complete only
-# when every rank has computed its partial, and each rank computes its own blocks last): measured on the
-# Llama-7B layer shapes the fused kernel wins at 2 ranks (342 vs 359 us) and loses at 4 (271 vs 259 us),
-# so above this group size the row-parallel side runs the plain GEMM + NCCL reduce-scatter.
-# RB_TP_FUSE_RS_MAX overrides.
+# The PULL form of GEMM -> reduce-scatter cannot overlap its reduction pass with the GEMM (a row block is
+# complete only when every rank has computed its partial, and each rank computes its own blocks last):
+# measured on the Llama-7B layer shapes it wins at 2 ranks (342 vs 359 us) and loses at 4 (271 vs 259 us),
+# so without the push form (the default, see _fused_gemm_rs_impl) the row-parallel side above this group
+# size runs the plain GEMM + NCCL reduce-scatter.  RB_TP_FUSE_RS_MAX overrides.
 FUSED_RS_MAX_WORLD = int(__import__("os").environ.get("RB_TP_FUSE_RS_MAX", "2"))
 
 
