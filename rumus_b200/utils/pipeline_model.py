@@ -15,7 +15,8 @@ when the phase of parity ``p`` has completed, i.e. when the current phase's pari
 "the stage is free the first time round").  A phase completes when ``count`` arrivals have been
 made (a TMA transaction or a ``tcgen05.commit`` counts as one arrival here).
 
-Used for ``csrc/kernels/w4a16_gemm.cu`` (``w4a16_roles``).
+Used for ``csrc/kernels/w4a16_gemm.cu`` (``w4a16_roles``), the CTA-pair GEMM (``gemm_2cta_roles``) and the
+bulk-copy ring of the LayerNorm backward kernel (``norm_ring_roles``).
 """
 from __future__ import annotations
 
@@ -283,4 +284,67 @@ def gemm_2cta_roles(num_tiles: int, num_kb: int, stages: int = 6, epi_warps: int
     for cta in range(2):
         for w in range(epi_warps):
             roles[f"epi{cta}.{w}"] = epilogue(cta, w)
+    return roles
+
+
+def norm_ring_roles(rows: int, stages: int = 4, threads: int = 3, bug: str = "") -> Dict[str, Role]:
+    """One row group of ``norm_bwd_ring_kernel`` (``csrc/kernels/norm.cu``): ``stages`` shared-memory
+    slots, each filled by bulk copies that complete on the slot's mbarrier; the group's threads wait for
+    a slot, take their part of the row into registers, meet at the group's named barrier, and only then
+    does one of them request the row ``stages`` ahead into the slot just emptied.  ``threads`` model
+    threads stand for the group's 128.  ``bug``: ``"refill_early"`` requests the next row before the
+    barrier (a slot may be overwritten while a slower thread still reads it), ``"parity"`` flips the
+    phase one trip late."""
+    full = [Mbar(1) for _ in range(stages)]
+    tag: List = [None] * stages
+    reading = [0] * stages
+    requests: List = []                     # (slot, row) issued and not yet landed
+    state = {"landed": 0, "done_threads": 0, "arrived": 0, "generation": 0}
+
+    def request(slot, row):
+        requests.append((slot, row))
+
+    def engine():
+        total = rows
+        while state["landed"] < total:
+            yield (lambda: bool(requests))
+            slot, row = requests.pop(0)
+            if reading[slot]:
+                raise PipelineError(f"row {row} lands in slot {slot} while {reading[slot]} thread(s) still read it")
+            tag[slot] = row
+            full[slot].arrive()
+            state["landed"] += 1
+
+    def thread(t: int):
+        if t == 0:
+            for s0 in range(min(stages, rows)):
+                request(s0, s0)
+        slot, phase = 0, 0
+        for i in range(rows):
+            yield (lambda slot=slot, phase=phase: full[slot].passed(phase))
+            if tag[slot] != i:
+                raise PipelineError(f"thread {t}: slot {slot} holds row {tag[slot]}, expected {i}")
+            reading[slot] += 1
+            yield (lambda: True)            # shared-memory loads into registers
+            reading[slot] -= 1
+            if bug == "refill_early" and t == 0 and i + stages < rows:
+                request(slot, i + stages)
+            gen = state["generation"]       # the group's named barrier
+            state["arrived"] += 1
+            if state["arrived"] == threads:
+                state["arrived"] = 0
+                state["generation"] += 1
+            yield (lambda gen=gen: state["generation"] != gen)
+            if bug != "refill_early" and t == 0 and i + stages < rows:
+                request(slot, i + stages)
+            slot += 1
+            if slot == stages:
+                slot = 0
+                if bug != "parity" or i >= stages:
+                    phase ^= 1
+        state["done_threads"] += 1
+
+    roles: Dict[str, Role] = {"engine": engine()}
+    for t in range(threads):
+        roles[f"thread{t}"] = thread(t)
     return roles

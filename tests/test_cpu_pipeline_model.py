@@ -63,3 +63,24 @@ def test_two_cta_gemm_planted_defects_are_caught(bug):
         except PipelineError:
             caught += 1
     assert caught == 12
+
+
+@pytest.mark.parametrize("rows,stages", [(1, 4), (3, 4), (4, 4), (9, 4), (23, 2), (40, 8)])
+def test_norm_ring_protocol(rows, stages):
+    """The bulk-copy ring of the LayerNorm backward kernel: no slot is refilled while a thread still reads
+    it and every thread meets the rows in order, under random schedules."""
+    from rumus_b200.utils.pipeline_model import norm_ring_roles, run
+    for seed in range(20):
+        assert run(norm_ring_roles(rows, stages), seed=seed) > 0
+
+
+@pytest.mark.parametrize("bug", ["refill_early", "parity"])
+def test_norm_ring_planted_defects_are_caught(bug):
+    from rumus_b200.utils.pipeline_model import PipelineError, norm_ring_roles, run
+    caught = 0
+    for seed in range(40):
+        try:
+            run(norm_ring_roles(17, 4, bug=bug), seed=seed)
+        except PipelineError:
+            caught += 1
+    assert caught > 0
