@@ -16,7 +16,8 @@ when the phase of parity ``p`` has completed, i.e. when the current phase's pari
 made (a TMA transaction or a ``tcgen05.commit`` counts as one arrival here).
 
 Used for ``csrc/kernels/w4a16_gemm.cu`` (``w4a16_roles``), the CTA-pair GEMM (``gemm_2cta_roles``) and the
-bulk-copy ring of the LayerNorm backward kernel (``norm_ring_roles``).
+bulk-copy ring of the LayerNorm backward kernel (``norm_ring_roles``) and the window / accumulator
+hand-offs of the direct stem convolution's weight-gradient kernel (``conv_stem_wgrad_roles``).
 """
 from __future__ import annotations
 
@@ -345,6 +346,76 @@ def norm_ring_roles(rows: int, stages: int = 4, threads: int = 3, bug: str = "")
         state["done_threads"] += 1
 
     roles: Dict[str, Role] = {"engine": engine()}
+    for t in range(threads):
+        roles[f"thread{t}"] = thread(t)
+    return roles
+
+
+def conv_stem_wgrad_roles(tiles: int, threads: int = 3, bug: str = "") -> Dict[str, Role]:
+    """One CTA of ``conv_stem_wgrad_kernel`` (``csrc/kernels/conv_stem.cu``) walking ``tiles`` tiles: two
+    input buffers (image window + dY tile, filled by TMA on ``full[buf]``), one operand tile that the
+    threads rebuild for every tile, MMAs that read the operand tile and the dY buffer and commit to
+    ``mma_done``.  Per iteration: wait for the previous tile's MMAs, request the next tile into the other
+    buffer, wait for this tile's buffer, build, barrier, issue.  ``bug``: ``"no_mma_wait"`` skips the wait
+    for the previous MMAs (the operand tile is rebuilt, and the other dY buffer refilled, under them)."""
+    full = [Mbar(1), Mbar(1)]
+    mma_done = Mbar(1)
+    buf_tag: List = [None, None]
+    operand = {"tile": None, "writers": 0}
+    state = {"mma_reading": None, "landed": 0, "issued_mma": 0, "arrived": 0, "generation": 0}
+    requests: List = []
+
+    def barrier():
+        gen = state["generation"]
+        state["arrived"] += 1
+        if state["arrived"] == threads:
+            state["arrived"] = 0
+            state["generation"] += 1
+        return lambda gen=gen: state["generation"] != gen
+
+    def engine():
+        while state["landed"] < tiles:
+            yield (lambda: bool(requests))
+            buf, tile = requests.pop(0)
+            if state["mma_reading"] is not None and state["mma_reading"][1] == buf:
+                raise PipelineError(f"tile {tile} lands in buffer {buf} while MMAs still read its dY tile")
+            buf_tag[buf] = tile
+            full[buf].arrive()
+            state["landed"] += 1
+
+    def tensor_core():
+        for i in range(tiles):
+            yield (lambda i=i: state["issued_mma"] > i)
+            yield (lambda: True)            # the MMAs execute asynchronously
+            state["mma_reading"] = None
+            mma_done.arrive()
+
+    def thread(t: int):
+        if t == 0 and tiles > 0:
+            requests.append((0, 0))
+        for it in range(tiles):
+            buf = it & 1
+            if it > 0 and bug != "no_mma_wait":
+                yield (lambda it=it: mma_done.passed((it - 1) & 1))
+            yield barrier()
+            if t == 0 and it + 1 < tiles:
+                requests.append((buf ^ 1, it + 1))
+            yield (lambda buf=buf, it=it: full[buf].passed((it >> 1) & 1))
+            if buf_tag[buf] != it:
+                raise PipelineError(f"thread {t}: buffer {buf} holds tile {buf_tag[buf]}, expected {it}")
+            if state["mma_reading"] is not None:
+                raise PipelineError(f"thread {t} rebuilds the operand tile while the MMAs of tile "
+                                    f"{state['mma_reading'][0]} read it")
+            yield (lambda: True)            # build this thread's operand row
+            operand["tile"] = it
+            yield barrier()
+            if t == 0:
+                state["mma_reading"] = (it, buf)
+                state["issued_mma"] += 1
+        if tiles > 0:
+            yield (lambda: mma_done.passed((tiles - 1) & 1))
+
+    roles: Dict[str, Role] = {"engine": engine(), "tensor_core": tensor_core()}
     for t in range(threads):
         roles[f"thread{t}"] = thread(t)
     return roles

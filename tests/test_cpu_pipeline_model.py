@@ -84,3 +84,22 @@ def test_norm_ring_planted_defects_are_caught(bug):
         except PipelineError:
             caught += 1
     assert caught > 0
+
+
+@pytest.mark.parametrize("tiles", [0, 1, 2, 3, 8, 21])
+def test_conv_stem_wgrad_protocol(tiles):
+    """Window / dY double buffering and operand-tile reuse of the stem weight-gradient kernel."""
+    from rumus_b200.utils.pipeline_model import conv_stem_wgrad_roles, run
+    for seed in range(20):
+        run(conv_stem_wgrad_roles(tiles), seed=seed)
+
+
+def test_conv_stem_wgrad_needs_the_wait_for_the_previous_mmas():
+    from rumus_b200.utils.pipeline_model import PipelineError, conv_stem_wgrad_roles, run
+    caught = 0
+    for seed in range(40):
+        try:
+            run(conv_stem_wgrad_roles(9, bug="no_mma_wait"), seed=seed)
+        except PipelineError:
+            caught += 1
+    assert caught > 0
