@@ -3,6 +3,7 @@ entropy and Adam bandwidth.  CUDA-event timing, 3 warm-ups, L2 flushed between i
 
     python bench/kernel_bench.py            # full sweep
     python bench/kernel_bench.py --small    # one small GEMM + attention call (sized for an ncu capture)
+    python bench/kernel_bench.py --attn-llama   # attention at the Llama-7B tensor-parallel shapes vs SDPA
 """
 import torch, sys, time
 import os
@@ -18,6 +19,27 @@ def timeit(fn, n=10, warm=3):
         s=torch.cuda.Event(enable_timing=True); e=torch.cuda.Event(enable_timing=True)
         s.record(); fn(); e.record(); torch.cuda.synchronize(); ts.append(s.elapsed_time(e))
     ts.sort(); return ts[len(ts)//2]
+if "--attn-llama" in sys.argv:
+    # FlashAttention forward / backward against torch SDPA at B 2, S 4096, D 128 with 16 and 8 local heads
+    # (Llama-7B under 2- and 4-way tensor parallelism)
+    import torch.nn.functional as TF
+    for (B, S, H) in ((2, 4096, 16), (2, 4096, 8)):
+        D = 128
+        q, k, v = [(torch.randn(B, S, H, D, device='cuda') * 0.5).bfloat16().requires_grad_(True) for _ in range(3)]
+        fl = 4 * B * H * S * S * D / 2
+        t = timeit(lambda: F.flash_attention(q, k, v, True)); print(f"B{B} S{S} H{H} fwd ours {t:.3f} ms {fl/t/1e9:.0f} TF")
+        o = F.flash_attention(q, k, v, True); do = torch.randn_like(o)
+        def bw():
+            q.grad = k.grad = v.grad = None; o.backward(do, retain_graph=True)
+        t = timeit(bw); print(f"   bwd ours {t:.3f} ms {2.5*fl/t/1e9:.0f} TF")
+        qt, kt, vt = [x.detach().transpose(1, 2).requires_grad_(True) for x in (q, k, v)]
+        t = timeit(lambda: TF.scaled_dot_product_attention(qt, kt, vt, is_causal=True)); print(f"   fwd sdpa {t:.3f} ms {fl/t/1e9:.0f} TF")
+        ot = TF.scaled_dot_product_attention(qt, kt, vt, is_causal=True); dot = torch.randn_like(ot)
+        def bw2():
+            qt.grad = kt.grad = vt.grad = None; ot.backward(dot, retain_graph=True)
+        t = timeit(bw2); print(f"   bwd sdpa {t:.3f} ms {2.5*fl/t/1e9:.0f} TF")
+    print("status", native.read_status())
+    sys.exit(0)
 if "--gemm-compare" in sys.argv:
     # one GEMM shape through the one-CTA kernel, the two-CTA kernel and torch.matmul, a few launches
     # each (sized for a counter capture: python bench/kernel_bench.py --gemm-compare M N K)
